@@ -1,0 +1,244 @@
+// extern "C" surface of libmoe_b200 (declared in include/moe_b200.h): argument
+// checks on the host, workspace layout, plan construction, and the launch
+// sequence of the whole block (reference MOE.forward, model.py:200-276).
+#include <cuda.h>
+#include <stdio.h>
+#include <string.h>
+#include "common.cuh"
+
+namespace moe {
+
+static thread_local char g_err[256] = "ok";
+
+int set_error(int code, const char* msg) {
+  snprintf(g_err, sizeof(g_err), "%s", msg);
+  return code;
+}
+int cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_err, sizeof(g_err), "CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), where);
+  return 1000 + (int)e;
+}
+
+int64_t dispatch_scratch_ints(int64_t N, int E, int k);
+
+static int check_shape(int64_t N, int d, int f, int E, int k, int dtype) {
+  if (dtype != MOE_B200_F32 && dtype != MOE_B200_BF16)
+    return set_error(MOE_B200_ERR_DTYPE, "dtype must be MOE_B200_F32 or MOE_B200_BF16");
+  if (N < 0 || N > (int64_t)1 << 28) return set_error(MOE_B200_ERR_SHAPE, "N out of range");
+  if (d < 8 || (d & 7)) return set_error(MOE_B200_ERR_SHAPE, "d must be a positive multiple of 8");
+  if (f < 8 || (f & 7)) return set_error(MOE_B200_ERR_SHAPE, "f must be a positive multiple of 8");
+  if (E < 1 || E > kMaxExperts) return set_error(MOE_B200_ERR_SHAPE, "E must be in [1,256]");
+  if (k < 1 || k > kMaxTopK || k > E) return set_error(MOE_B200_ERR_SHAPE, "k must be in [1,min(8,E)]");
+  if (N * (int64_t)k >= (int64_t)1 << 31) return set_error(MOE_B200_ERR_SHAPE, "N*k exceeds int32 rows");
+  return 0;
+}
+
+static size_t align_up(size_t v) { return (v + 1023) & ~(size_t)1023; }
+
+static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off, size_t* total) {
+  const size_t es = dtype == MOE_B200_BF16 ? 2 : 4;
+  const size_t M = (size_t)N * k;
+  const size_t rb = (size_t)((N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock);
+  size_t sizes[MOE_B200_WS_NUM];
+  sizes[MOE_B200_WS_STATUS] = 16 * sizeof(int32_t);
+  sizes[MOE_B200_WS_LOGITS] = (size_t)N * E * sizeof(float);
+  sizes[MOE_B200_WS_IDX] = M * sizeof(int32_t);
+  sizes[MOE_B200_WS_W] = M * sizeof(float);
+  sizes[MOE_B200_WS_PSUM_PART] = rb * E * sizeof(float);
+  sizes[MOE_B200_WS_PSUM] = (size_t)E * sizeof(float);
+  sizes[MOE_B200_WS_AUX] = sizeof(float);
+  sizes[MOE_B200_WS_SCRATCH] = (size_t)dispatch_scratch_ints(N, E, k) * sizeof(int32_t);
+  sizes[MOE_B200_WS_CNT_SLOT] = (size_t)k * E * sizeof(int32_t);
+  sizes[MOE_B200_WS_OFFSETS] = (size_t)(E + 1) * sizeof(int32_t);
+  sizes[MOE_B200_WS_ROW_OF] = M * sizeof(int32_t);
+  sizes[MOE_B200_WS_PERM] = M * d * es;
+  sizes[MOE_B200_WS_H] = M * f * es;
+  sizes[MOE_B200_WS_Y] = M * d * es;
+  size_t pos = 0;
+  for (int i = 0; i < MOE_B200_WS_NUM; ++i) {
+    off[i] = pos;
+    pos += align_up(sizes[i] ? sizes[i] : 1);
+  }
+  *total = pos;
+}
+
+}  // namespace moe
+
+using namespace moe;
+
+extern "C" {
+
+int moe_b200_version(void) { return MOE_B200_ABI_VERSION; }
+
+const char* moe_b200_last_error_string(void) { return g_err; }
+
+size_t moe_b200_workspace_bytes(int64_t N, int d, int f, int E, int k, int dtype) {
+  if (check_shape(N, d, f, E, k, dtype)) return 0;
+  size_t off[MOE_B200_WS_NUM], total;
+  layout(N, d, f, E, k, dtype, off, &total);
+  return total;
+}
+
+int moe_b200_workspace_layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* h_offsets) {
+  if (h_offsets == nullptr) return set_error(MOE_B200_ERR_NULL, "h_offsets is NULL");
+  int rc = check_shape(N, d, f, E, k, dtype);
+  if (rc) return rc;
+  size_t total;
+  layout(N, d, f, E, k, dtype, h_offsets, &total);
+  return 0;
+}
+
+size_t moe_b200_plan_bytes(int E) {
+  if (E < 1 || E > kMaxExperts) return 0;
+  return plan_ptr_bytes(E) + (size_t)2 * E * 128;
+}
+
+int moe_b200_plan_build(const void* const* h_W1, const void* const* h_b1, const void* const* h_W2,
+                        const void* const* h_b2, int E, int d, int f, int dtype, void* plan,
+                        size_t plan_bytes, void* stream) {
+  if (!h_W1 || !h_b1 || !h_W2 || !h_b2 || !plan) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  int rc = check_shape(0, d, f, E, 1, dtype);
+  if (rc) return rc;
+  if (plan_bytes < moe_b200_plan_bytes(E)) return set_error(MOE_B200_ERR_WORKSPACE, "plan buffer too small");
+  if (!aligned16(plan) || ((uintptr_t)plan & 127)) return set_error(MOE_B200_ERR_ALIGN, "plan must be 128-byte aligned");
+  for (int e = 0; e < E; ++e) {
+    if (!h_W1[e] || !h_b1[e] || !h_W2[e] || !h_b2[e]) return set_error(MOE_B200_ERR_NULL, "NULL expert parameter");
+    if (!aligned16(h_W1[e]) || !aligned16(h_W2[e]) || !aligned16(h_b1[e]) || !aligned16(h_b2[e]))
+      return set_error(MOE_B200_ERR_ALIGN, "expert parameters must be 16-byte aligned");
+  }
+  const size_t bytes = moe_b200_plan_bytes(E);
+  // staged on the host stack/heap; cudaMemcpyAsync from pageable memory copies
+  // the source before it returns
+  static thread_local unsigned char* stage = nullptr;
+  static thread_local size_t stage_cap = 0;
+  if (stage_cap < bytes) {
+    free(stage);
+    stage = static_cast<unsigned char*>(aligned_alloc(128, (bytes + 127) & ~(size_t)127));
+    stage_cap = bytes;
+  }
+  memset(stage, 0, bytes);
+  const void** ptrs = reinterpret_cast<const void**>(stage);
+  for (int e = 0; e < E; ++e) {
+    ptrs[e] = h_W1[e];
+    ptrs[E + e] = h_b1[e];
+    ptrs[2 * E + e] = h_W2[e];
+    ptrs[3 * E + e] = h_b2[e];
+  }
+  if (dtype == MOE_B200_BF16) {
+    rc = build_weight_tensor_maps(h_W1, h_W2, E, d, f, stage + plan_ptr_bytes(E));
+    if (rc) return rc;
+  }
+  MOE_CUDA_CHECK(cudaMemcpyAsync(plan, stage, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  // the staging buffer is reused by the next call on this thread
+  MOE_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream));
+  return 0;
+}
+
+int64_t moe_b200_router_blocks(int64_t N) {
+  return (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
+}
+
+size_t moe_b200_dispatch_scratch_bytes(int64_t N, int E, int k) {
+  if (N < 0 || E < 1 || E > kMaxExperts || k < 1 || k > kMaxTopK) return 0;
+  return (size_t)dispatch_scratch_ints(N, E, k) * sizeof(int32_t);
+}
+
+int moe_b200_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+                    int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+                    int32_t* status, void* stream) {
+  int rc = check_shape(N, d, 8, E, k, dtype);
+  if (rc) return rc;
+  if (N == 0) return 0;
+  if (!x || !Wg || !bg || !out_idx || !out_w || !psum_part) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(x) || !aligned16(Wg)) return set_error(MOE_B200_ERR_ALIGN, "x and Wg must be 16-byte aligned");
+  return launch_router(x, Wg, bg, N, d, E, k, dtype, out_logits, out_idx, out_w, psum_part, status,
+                       (cudaStream_t)stream);
+}
+
+int moe_b200_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
+                      int32_t* scratch, int32_t* cnt_slot, int32_t* offsets, int32_t* row_of,
+                      void* perm, const float* psum_part, float* psum, float* aux, int32_t* status,
+                      void* stream) {
+  int rc = check_shape(N, d, 8, E, k, dtype);
+  if (rc) return rc;
+  if (!scratch || !cnt_slot || !offsets || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (N > 0 && (!x || !idx || !row_of || !perm)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (psum_part && (!psum || !aux)) return set_error(MOE_B200_ERR_NULL, "psum and aux are required with psum_part");
+  if (!aligned16(x) || !aligned16(perm)) return set_error(MOE_B200_ERR_ALIGN, "x and perm must be 16-byte aligned");
+  return launch_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
+                         psum_part, psum, aux, status, (cudaStream_t)stream);
+}
+
+int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
+                     int f, int E, int dtype, int flags, void* h, void* y, int32_t* status,
+                     void* stream) {
+  int rc = check_shape(0, d, f, E, 1, dtype);
+  if (rc) return rc;
+  if (M < 0 || M >= (int64_t)1 << 31) return set_error(MOE_B200_ERR_SHAPE, "M out of range");
+  if (M == 0) return 0;
+  if (!perm || !offsets || !plan || !h || !y || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(perm) || !aligned16(h) || !aligned16(y)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  if (dtype == MOE_B200_BF16 && !(flags & MOE_B200_FLAG_SIMT_EXPERTS))
+    return launch_experts_tc(perm, offsets, plan, M, d, f, E, h, y, status, (cudaStream_t)stream);
+  return launch_experts_simt(perm, offsets, plan, M, d, f, E, dtype, h, y, (cudaStream_t)stream);
+}
+
+int moe_b200_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
+                     int64_t N, int d, int k, int dtype, void* out, void* stream) {
+  int rc = check_shape(N, d, 8, k, k, dtype);
+  if (rc) return rc;
+  if (N == 0) return 0;
+  if (!y || !row_of || !w || !out) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(y) || !aligned16(out) || !aligned16(residual))
+    return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  return launch_combine(y, row_of, w, residual, N, d, k, dtype, out, (cudaStream_t)stream);
+}
+
+int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* plan,
+                     const void* residual, int64_t N, int d, int f, int E, int k, int dtype,
+                     int flags, void* workspace, size_t workspace_bytes, void* out, void* stream) {
+  int rc = check_shape(N, d, f, E, k, dtype);
+  if (rc) return rc;
+  if (!workspace) return set_error(MOE_B200_ERR_NULL, "workspace is NULL");
+  size_t off[MOE_B200_WS_NUM], total;
+  layout(N, d, f, E, k, dtype, off, &total);
+  if (workspace_bytes < total) return set_error(MOE_B200_ERR_WORKSPACE, "workspace too small");
+  if (((uintptr_t)workspace & 1023)) return set_error(MOE_B200_ERR_ALIGN, "workspace must be 1024-byte aligned");
+  if (N > 0 && (!x || !Wg || !bg || !plan || !out)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  char* ws = static_cast<char*>(workspace);
+  int32_t* status = reinterpret_cast<int32_t*>(ws + off[MOE_B200_WS_STATUS]);
+  float* logits = reinterpret_cast<float*>(ws + off[MOE_B200_WS_LOGITS]);
+  int32_t* idx = reinterpret_cast<int32_t*>(ws + off[MOE_B200_WS_IDX]);
+  float* w = reinterpret_cast<float*>(ws + off[MOE_B200_WS_W]);
+  float* psum_part = reinterpret_cast<float*>(ws + off[MOE_B200_WS_PSUM_PART]);
+  float* psum = reinterpret_cast<float*>(ws + off[MOE_B200_WS_PSUM]);
+  float* aux = reinterpret_cast<float*>(ws + off[MOE_B200_WS_AUX]);
+  int32_t* scratch = reinterpret_cast<int32_t*>(ws + off[MOE_B200_WS_SCRATCH]);
+  int32_t* cnt_slot = reinterpret_cast<int32_t*>(ws + off[MOE_B200_WS_CNT_SLOT]);
+  int32_t* offsets = reinterpret_cast<int32_t*>(ws + off[MOE_B200_WS_OFFSETS]);
+  int32_t* row_of = reinterpret_cast<int32_t*>(ws + off[MOE_B200_WS_ROW_OF]);
+  void* perm = ws + off[MOE_B200_WS_PERM];
+  void* h = ws + off[MOE_B200_WS_H];
+  void* y = ws + off[MOE_B200_WS_Y];
+  cudaStream_t s = (cudaStream_t)stream;
+
+  MOE_CUDA_CHECK(cudaMemsetAsync(status, 0, 16 * sizeof(int32_t), s));
+  rc = moe_b200_router(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, psum_part, status, stream);
+  if (rc) return rc;
+  rc = moe_b200_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
+                         N > 0 ? psum_part : nullptr, psum, aux, status, stream);
+  if (rc) return rc;
+  rc = moe_b200_experts(perm, offsets, plan, N * k, d, f, E, dtype, flags, h, y, status, stream);
+  if (rc) return rc;
+  return moe_b200_combine(y, row_of, w, residual, N, d, k, dtype, out, stream);
+}
+
+int moe_b200_read_status(const int32_t* status, int32_t* h_status, void* stream) {
+  if (!status || !h_status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  MOE_CUDA_CHECK(cudaMemcpyAsync(h_status, status, 16 * sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                 (cudaStream_t)stream));
+  MOE_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream));
+  return h_status[0];
+}
+
+}  // extern "C"

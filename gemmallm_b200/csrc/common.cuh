@@ -1,0 +1,153 @@
+// Shared helpers of libmoe_b200: error plumbing, vector load/store of bf16/fp32
+// rows as fp32, and the internal launch prototypes each .cu file exports.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include "../../include/moe_b200.h"
+
+namespace moe {
+
+constexpr int kMaxExperts = 256;
+constexpr int kMaxTopK = 8;
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+// Tokens per router block and per dispatch chunk. Both kernels partition the
+// token range the same way, in token order.
+constexpr int kRouterTokensPerBlock = 32;
+constexpr int kDispatchChunk = 128;
+
+int set_error(int code, const char* msg);
+int cuda_error(cudaError_t e, const char* where);
+
+#define MOE_CUDA_CHECK(expr)                                  \
+  do {                                                        \
+    cudaError_t e__ = (expr);                                 \
+    if (e__ != cudaSuccess) return moe::cuda_error(e__, #expr); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- device helpers -------------------------------------------------------
+
+template <typename T> struct Vec8;  // 8 consecutive elements of a row, as fp32
+
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Load 8 consecutive elements starting at p (16-byte aligned for bf16,
+// 32-byte aligned pairs of float4 for fp32) into fp32 registers.
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  uint4 r = *reinterpret_cast<const uint4*>(p);
+  v[0] = bf16_lo(r.x); v[1] = bf16_hi(r.x);
+  v[2] = bf16_lo(r.y); v[3] = bf16_hi(r.y);
+  v[4] = bf16_lo(r.z); v[5] = bf16_hi(r.z);
+  v[6] = bf16_lo(r.w); v[7] = bf16_hi(r.w);
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8_ldg(const __nv_bfloat16* p, float (&v)[8]) {
+  uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  v[0] = bf16_lo(r.x); v[1] = bf16_hi(r.x);
+  v[2] = bf16_lo(r.y); v[3] = bf16_hi(r.y);
+  v[4] = bf16_lo(r.z); v[5] = bf16_hi(r.z);
+  v[6] = bf16_lo(r.w); v[7] = bf16_hi(r.w);
+}
+__device__ __forceinline__ void load8_ldg(const float* p, float (&v)[8]) {
+  float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 r;
+  r.x = pack_bf16x2(v[0], v[1]);
+  r.y = pack_bf16x2(v[2], v[3]);
+  r.z = pack_bf16x2(v[4], v[5]);
+  r.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = r;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void from_f32(float& o, float v) { o = v; }
+__device__ __forceinline__ void from_f32(__nv_bfloat16& o, float v) { o = __float2bfloat16_rn(v); }
+
+// GELU, tanh form, exactly the expression of F.gelu(approximate="tanh")
+// (used at model.py:181): 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+__device__ __forceinline__ float gelu_tanh_precise(float g) {
+  const float kBeta = 0.7978845608028654f;  // sqrt(2/pi)
+  float inner = kBeta * (g + 0.044715f * g * g * g);
+  return 0.5f * g * (1.0f + tanhf(inner));
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_tanh_fast(float g) {
+  const float kBeta = 0.7978845608028654f;
+  float g2 = g * g;
+  float inner = g * fmaf(0.044715f * kBeta, g2, kBeta);
+  float hg = 0.5f * g;
+  return fmaf(hg, tanh_approx(inner), hg);
+}
+
+// Plan buffer layout (device memory owned by the caller).
+//   [0, 4*E*8)            : W1[E], b1[E], W2[E], b2[E] device pointers
+//   then, 128-byte aligned: tensor maps W1[E], W2[E] (128 bytes each)
+struct PlanView {
+  const void* const* W1;
+  const void* const* b1;
+  const void* const* W2;
+  const void* const* b2;
+  const void* tmap_W1;  // CUtensorMap[E]
+  const void* tmap_W2;  // CUtensorMap[E]
+};
+__host__ __device__ inline size_t plan_ptr_bytes(int E) {
+  return ((size_t)4 * E * sizeof(void*) + 127) & ~(size_t)127;
+}
+__host__ __device__ inline PlanView plan_view(const void* plan, int E) {
+  const char* p = static_cast<const char*>(plan);
+  PlanView v;
+  v.W1 = reinterpret_cast<const void* const*>(p);
+  v.b1 = v.W1 + E;
+  v.W2 = v.b1 + E;
+  v.b2 = v.W2 + E;
+  v.tmap_W1 = p + plan_ptr_bytes(E);
+  v.tmap_W2 = p + plan_ptr_bytes(E) + (size_t)128 * E;
+  return v;
+}
+
+// ---- launchers implemented in the other translation units -----------------
+int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+                  int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+                  int32_t* status, cudaStream_t s);
+int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
+                    int32_t* chunk_cnt, int32_t* cnt_slot, int32_t* offsets, int32_t* row_of,
+                    void* perm, const float* psum_part, float* psum, float* aux, int32_t* status,
+                    cudaStream_t s);
+int launch_experts_simt(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
+                        int d, int f, int E, int dtype, void* h, void* y, cudaStream_t s);
+int launch_experts_tc(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
+                      int f, int E, void* h, void* y, int32_t* status, cudaStream_t s);
+int launch_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
+                   int64_t N, int d, int k, int dtype, void* out, cudaStream_t s);
+int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, int E, int d, int f,
+                             void* h_tmaps /* 2*E*128 bytes */);
+
+}  // namespace moe

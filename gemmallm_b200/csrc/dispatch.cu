@@ -1,0 +1,255 @@
+// Dispatch kernel: histogram of the routing indices, exclusive scan, and the
+// permutation of token rows into one expert-contiguous buffer, in a single
+// cooperative launch. Replaces the reference's per-slot argsort, the Python
+// count loop with its device->host reads, the gather and the split
+// (model.py:226-253), and finishes the load-balancing loss (model.py:213-216).
+//
+// HBM-bound: x [N,d] is read once and written k times with 16-byte accesses.
+// Tokens are cut into chunks of 64; chunk c belongs to block c mod gridDim in
+// both phases. Phase 1 counts experts per chunk into scratch. After a grid
+// barrier every block sums the chunk counts (all of them for the expert
+// offsets, those before its own chunk for its base), ranks its chunk's
+// (token, slot) pairs in token order, and copies the rows. Rows of one expert
+// therefore stay in token order whatever the grid size.
+#include <cooperative_groups.h>
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace moe {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kChunk = kDispatchChunk;
+constexpr int kScratchHeader = 32;  // ints: [0] = blocks finished
+
+__host__ __device__ inline int64_t num_chunks(int64_t N) { return (N + kChunk - 1) / kChunk; }
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_t N, int d, int E,
+                int k, int32_t* __restrict__ scratch, int32_t* __restrict__ cnt_slot,
+                int32_t* __restrict__ offsets, int32_t* __restrict__ row_of, T* __restrict__ perm,
+                const float* __restrict__ psum_part, int64_t router_blocks,
+                float* __restrict__ psum, float* __restrict__ aux, int32_t* __restrict__ status) {
+  cg::grid_group grid = cg::this_grid();
+  extern __shared__ int s_int[];
+  int* s_hist = s_int;             // [E]  chunk histogram, later totals
+  int* s_base = s_hist + E;        // [E]  rows of earlier chunks per expert
+  int* s_off = s_base + E;         // [E+1]
+  int* s_run = s_off + E + 1;      // [E]  running rank inside the chunk
+  int* s_slot = s_run + E;         // [k*E]
+  int* s_row = s_slot + k * E;     // [kChunk*k]
+  float* s_red = reinterpret_cast<float*>(s_row + kChunk * k);  // [kThreads]
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x;
+  const int G = gridDim.x;
+  const int64_t nchunk = num_chunks(N);
+  int32_t* done = scratch;
+  int32_t* chunk_cnt = scratch + kScratchHeader;     // [nchunk][E]
+  int32_t* blk_slot = chunk_cnt + nchunk * E;        // [G][k][E]
+
+  // ---- phase 1: histograms -----------------------------------------------
+  for (int i = tid; i < k * E; i += kThreads) s_slot[i] = 0;
+  if (blockIdx.x == 0 && tid == 0) *done = 0;
+  for (int64_t c = blockIdx.x; c < nchunk; c += G) {
+    for (int e = tid; e < E; e += kThreads) s_hist[e] = 0;
+    __syncthreads();
+    const int64_t t0 = c * kChunk;
+    const int ntok = (int)((N - t0) < kChunk ? (N - t0) : kChunk);
+    for (int p = tid; p < ntok * k; p += kThreads) {
+      int e = idx[t0 * k + p];
+      if ((unsigned)e >= (unsigned)E) {
+        atomicMax(&status[0], MOE_B200_DEV_BAD_INDEX);
+        continue;
+      }
+      atomicAdd(&s_hist[e], 1);
+      atomicAdd(&s_slot[(p % k) * E + e], 1);
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += kThreads) chunk_cnt[c * E + e] = s_hist[e];
+    __syncthreads();
+  }
+  for (int i = tid; i < k * E; i += kThreads) blk_slot[(size_t)blockIdx.x * k * E + i] = s_slot[i];
+
+  grid.sync();
+
+  // ---- phase 2: scan ------------------------------------------------------
+  for (int e = tid; e < E; e += kThreads) { s_hist[e] = 0; s_base[e] = 0; }
+  __syncthreads();
+  const int64_t c0 = blockIdx.x;
+  for (int64_t i = tid; i < nchunk * E; i += kThreads) {
+    int v = __ldcg(&chunk_cnt[i]);
+    int64_t cc = i / E;
+    int e = (int)(i - cc * E);
+    if (v != 0) {
+      atomicAdd(&s_hist[e], v);
+      if (cc < c0) atomicAdd(&s_base[e], v);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) { s_off[e] = acc; acc += s_hist[e]; }
+    s_off[E] = acc;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int e = tid; e <= E; e += kThreads) offsets[e] = s_off[e];
+
+  // ---- phase 2: rank and copy ---------------------------------------------
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int64_t c = c0; c < nchunk; c += G) {
+    const int64_t t0 = c * kChunk;
+    const int ntok = (int)((N - t0) < kChunk ? (N - t0) : kChunk);
+    const int npair = ntok * k;
+    if (warp == 0) {
+      for (int e = lane; e < E; e += 32) s_run[e] = 0;
+      __syncwarp();
+      for (int p0 = 0; p0 < npair; p0 += 32) {
+        int p = p0 + lane;
+        int e = p < npair ? idx[t0 * k + p] : -1;
+        bool ok = (unsigned)e < (unsigned)E;
+        // lanes with the same expert form a group; rank = earlier lanes of it
+        unsigned grp = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+        int row = -1;
+        if (ok) {
+          int before = __popc(grp & ((1u << lane) - 1u));
+          row = s_off[e] + s_base[e] + s_run[e] + before;
+        }
+        __syncwarp();
+        if (ok && (grp >> lane) == 1u) s_run[e] += __popc(grp);  // highest lane of the group
+        __syncwarp();
+        if (p < npair) {
+          s_row[p] = row;
+          row_of[t0 * k + p] = row;
+        }
+      }
+    }
+    __syncthreads();
+    // copy rows: one warp per token, 16-byte pieces, 4 loads in flight per lane
+    constexpr int kVec = 16 / (int)sizeof(T);
+    const int pieces = d / kVec;
+    for (int tl = warp; tl < ntok; tl += kThreads / 32) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + (t0 + tl) * d);
+      for (int i0 = lane; i0 < pieces; i0 += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          int i = i0 + 32 * u;
+          if (i < pieces) v[u] = __ldg(src + i);
+        }
+        for (int j = 0; j < k; ++j) {
+          int row = s_row[tl * k + j];
+          if (row < 0) continue;
+          uint4* dst = reinterpret_cast<uint4*>(perm + (int64_t)row * d);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            int i = i0 + 32 * u;
+            if (i < pieces) __stcs(dst + i, v[u]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    // rows of chunks [c, c+G) precede this block's next chunk
+    for (int64_t i = tid; i < (int64_t)G * E; i += kThreads) {
+      int64_t cc = c + i / E;
+      int e = (int)(i % E);
+      if (cc < nchunk) {
+        int v = __ldcg(&chunk_cnt[cc * E + e]);
+        if (v != 0) atomicAdd(&s_base[e], v);
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- tail: per-slot counts, probability sums, loss ----------------------
+  if (blockIdx.x == 0) {
+    for (int i = tid; i < k * E; i += kThreads) {
+      int acc = 0;
+      for (int b = 0; b < G; ++b) acc += __ldcg(&blk_slot[(size_t)b * k * E + i]);
+      cnt_slot[i] = acc;
+    }
+  }
+  if (psum_part == nullptr) return;
+  for (int e = blockIdx.x; e < E; e += G) {
+    float acc = 0.f;
+    for (int64_t b = tid; b < router_blocks; b += kThreads) acc += psum_part[b * E + e];
+    s_red[tid] = acc;
+    __syncthreads();
+    for (int o = kThreads / 2; o > 0; o >>= 1) {
+      if (tid < o) s_red[tid] += s_red[tid + o];
+      __syncthreads();
+    }
+    if (tid == 0) psum[e] = s_red[0];
+    __syncthreads();
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = (atomicAdd(done, 1) == G - 1);
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    // E^2 * mean_e( psum[e]/N * cnt0[e]/N ), model.py:213-216 (slot 0 only)
+    float acc = 0.f;
+    for (int e = tid; e < E; e += kThreads) {
+      float prob = __ldcg(&psum[e]) / (float)N;
+      float freq = (float)__ldcg(&cnt_slot[e]) / (float)N;
+      acc += prob * freq;
+    }
+    s_red[tid] = acc;
+    __syncthreads();
+    for (int o = kThreads / 2; o > 0; o >>= 1) {
+      if (tid < o) s_red[tid] += s_red[tid + o];
+      __syncthreads();
+    }
+    if (tid == 0) aux[0] = s_red[0] / (float)E * (float)(E * E);
+  }
+}
+
+int g_sm_count = 0;
+int g_blocks_per_sm[2] = {0, 0};
+
+}  // namespace
+
+int64_t dispatch_scratch_ints(int64_t N, int E, int k) {
+  return kScratchHeader + num_chunks(N) * E + (int64_t)kNumSMs * 2 * k * E;
+}
+
+int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
+                    int32_t* scratch, int32_t* cnt_slot, int32_t* offsets, int32_t* row_of,
+                    void* perm, const float* psum_part, float* psum, float* aux, int32_t* status,
+                    cudaStream_t s) {
+  const size_t smem =
+      sizeof(int) * (size_t)(4 * E + 1 + k * E + kChunk * k) + sizeof(float) * kThreads;
+  const int ti = dtype == MOE_B200_BF16 ? 1 : 0;
+  const void* fn = ti ? (const void*)dispatch_kernel<__nv_bfloat16> : (const void*)dispatch_kernel<float>;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    MOE_CUDA_CHECK(cudaGetDevice(&dev));
+    MOE_CUDA_CHECK(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if (g_blocks_per_sm[ti] == 0) {
+    int per_sm = 0;
+    MOE_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
+    g_blocks_per_sm[ti] = per_sm < 1 ? 1 : per_sm;
+  }
+  int per_sm = g_blocks_per_sm[ti] > 2 ? 2 : g_blocks_per_sm[ti];
+  int64_t grid = (int64_t)g_sm_count * per_sm;
+  if (grid > (int64_t)kNumSMs * 2) grid = (int64_t)kNumSMs * 2;
+  int64_t nchunk = num_chunks(N);
+  if (nchunk < 1) nchunk = 1;
+  if (grid > nchunk) grid = nchunk;
+  int64_t router_blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
+  void* args[] = {(void*)&x,        (void*)&idx,     (void*)&N,       (void*)&d,
+                  (void*)&E,        (void*)&k,       (void*)&scratch, (void*)&cnt_slot,
+                  (void*)&offsets,  (void*)&row_of,  (void*)&perm,    (void*)&psum_part,
+                  (void*)&router_blocks, (void*)&psum, (void*)&aux,   (void*)&status};
+  MOE_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem, s));
+  return 0;
+}
+
+}  // namespace moe

@@ -1,0 +1,219 @@
+"""Drop-in modules for GemmaLLM's Mixture-of-Experts block.
+
+``MOE`` and ``FeedForward`` keep the constructor, attribute names, parameter
+names/shapes and ``state_dict`` layout of the reference classes
+(model.py:192-198 and model.py:154-171), so
+``new.load_state_dict(ref.state_dict(), strict=True)`` works in both
+directions. ``forward`` runs the hand-written sm_100a kernels of
+libmoe_b200.so through its C ABI: this module only hands over device pointers,
+sizes and the current CUDA stream. There is no CPU or eager-PyTorch path.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import _cabi
+from ._cabi import lib, check
+
+_DTYPES = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"libmoe_b200 computes in float32 or bfloat16, got {t.dtype}") from None
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class _Plan:
+    """Device copy of the experts' parameter pointers and TMA tensor maps.
+
+    Rebuilt whenever a parameter's storage, dtype or device changes (``.to()``,
+    ``load_state_dict`` keep storage; ``.to(dtype)`` replaces it)."""
+
+    def __init__(self):
+        self.key = None
+        self.buf = None
+
+    def get(self, experts, d: int, f: int, dtype: int, device: torch.device) -> int:
+        params = []
+        for ex in experts:
+            params += [ex.gate_and_up.weight, ex.gate_and_up.bias, ex.down.weight, ex.down.bias]
+        key = (dtype, str(device), tuple(p.data_ptr() for p in params))
+        if key != self.key:
+            for p in params:
+                if p.device != device or _dtype_code(p) != dtype or not p.is_contiguous():
+                    raise ValueError("expert parameters must be contiguous and share the input's "
+                                     "device and dtype")
+            E = len(experts)
+            nbytes = lib.moe_b200_plan_bytes(E)
+            buf = torch.empty(nbytes + 128, dtype=torch.uint8, device=device)
+            base = (buf.data_ptr() + 127) & ~127
+            w1 = _cabi.ptr_array([ex.gate_and_up.weight.data_ptr() for ex in experts])
+            b1 = _cabi.ptr_array([ex.gate_and_up.bias.data_ptr() for ex in experts])
+            w2 = _cabi.ptr_array([ex.down.weight.data_ptr() for ex in experts])
+            b2 = _cabi.ptr_array([ex.down.bias.data_ptr() for ex in experts])
+            check(lib.moe_b200_plan_build(w1, b1, w2, b2, E, d, f, dtype, base, nbytes,
+                                          _stream(device)), "plan_build")
+            self.key, self.buf, self.base = key, buf, base
+        return self.base
+
+
+class FeedForward(nn.Module):
+    """GeGLU feed-forward expert; mirrors reference model.py:154-190.
+
+    ``gate_and_up`` maps d -> 2f (rows [0,f) gate, rows [f,2f) up), ``down`` maps
+    f -> d. The LoRA tensors exist so that checkpoints load strictly; the
+    ``fine_tuning=True`` branch (model.py:175-179,185-189) is not implemented
+    and raises.
+
+    ``d_ff`` (keyword-only) sets f directly for widths that are not an integer
+    multiple of ``hidden_size``."""
+
+    def __init__(self, hidden_size: int, expansion_factor: int = 4, dropout_ratio: float = 0.1,
+                 lora_rank: int = 16, lora_alpha: int = 32, *, d_ff: int | None = None):
+        super().__init__()
+        f = hidden_size * expansion_factor if d_ff is None else d_ff
+        self.hidden_size, self.d_ff = hidden_size, f
+        self.gate_and_up = nn.Linear(hidden_size, f * 2)
+        self.down = nn.Linear(f, hidden_size)
+        self.dropout = nn.Dropout(p=dropout_ratio)
+        self.lora_scale = lora_alpha / lora_rank
+        self.lora_gate_and_up_a = nn.Linear(hidden_size, lora_rank)
+        self.lora_gate_and_up_b = nn.Linear(lora_rank, f * 2)
+        self.lora_down_a = nn.Linear(f, lora_rank)
+        self.lora_down_b = nn.Linear(lora_rank, hidden_size)
+        self._plan = _Plan()
+
+    def forward(self, tensor: torch.Tensor, fine_tuning: bool = False) -> torch.Tensor:
+        """y = down(gelu_tanh(gate) * up) for every row, through the grouped
+        expert kernels with a single group."""
+        if fine_tuning:
+            raise NotImplementedError("the LoRA branch (fine_tuning=True) is not implemented")
+        if self.training and self.dropout.p > 0:
+            raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
+        if not tensor.is_cuda:
+            raise RuntimeError("libmoe_b200 runs on CUDA tensors only; there is no CPU path")
+        dtype = _dtype_code(tensor)
+        shape = tensor.shape
+        x = tensor.reshape(-1, shape[-1]).contiguous()
+        M, d, f = x.shape[0], self.hidden_size, self.d_ff
+        dev = x.device
+        with torch.cuda.device(dev):
+            plan = self._plan.get([self], d, f, dtype, dev)
+            offsets = torch.tensor([0, M], dtype=torch.int32, device=dev)
+            status = torch.zeros(16, dtype=torch.int32, device=dev)
+            h = torch.empty(M, f, dtype=x.dtype, device=dev)
+            y = torch.empty(M, d, dtype=x.dtype, device=dev)
+            check(lib.moe_b200_experts(x.data_ptr(), offsets.data_ptr(), plan, M, d, f, 1, dtype, 0,
+                                       h.data_ptr(), y.data_ptr(), status.data_ptr(), _stream(dev)),
+                  "experts")
+        return y.reshape(shape)
+
+
+class MOE(nn.Module):
+    """Mixture-of-experts feed-forward block; mirrors reference model.py:192-276.
+
+    Same positional/keyword arguments as the reference constructor
+    (model.py:193); ``device`` is accepted and stored but not used, the kernels
+    run where the input lives. Keyword-only extensions: ``top_k`` (the reference
+    fixes 2, model.py:210) and ``d_ff`` (free per-branch width)."""
+
+    def __init__(self, hidden_size: int, num_experts: int = 8, expansion_factor: int = 4,
+                 dropout_ratio: float = 0.1, lora_rank: int = 16, lora_alpha: int = 32,
+                 device: str = "mps", *, top_k: int = 2, d_ff: int | None = None):
+        super().__init__()
+        self.gate = nn.Linear(hidden_size, num_experts)
+        self.num_experts = num_experts
+        self.experts = nn.ModuleList([
+            FeedForward(hidden_size, expansion_factor=expansion_factor, dropout_ratio=dropout_ratio,
+                        lora_rank=lora_rank, lora_alpha=lora_alpha, d_ff=d_ff)
+            for _ in range(num_experts)])
+        self.device = device
+        self.hidden_size = hidden_size
+        self.d_ff = self.experts[0].d_ff
+        self.top_k = top_k
+        self.flags = _cabi.FLAG_DEFAULT
+        self._plan = _Plan()
+        self._ws = None
+        self._ws_key = None
+        self.last = None  # views into the workspace of the most recent call
+
+    # -- workspace ---------------------------------------------------------
+    def _workspace(self, N: int, dtype: int, device: torch.device):
+        key = (N, dtype, str(device))
+        if key != self._ws_key:
+            d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
+            nbytes = _cabi.workspace_bytes(N, d, f, E, k, dtype)
+            buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+            base = (buf.data_ptr() + 1023) & ~1023
+            self._ws = (buf, base, nbytes, _cabi.workspace_layout(N, d, f, E, k, dtype))
+            self._ws_key = key
+        return self._ws
+
+    def _view(self, name: str, dtype: torch.dtype, shape) -> torch.Tensor:
+        buf, base, _, layout = self._ws
+        start = base - buf.data_ptr() + layout[name]
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        return buf[start:start + nbytes].view(dtype).view(*shape)
+
+    def forward(self, tensor: torch.Tensor, fine_tuning: bool = False, *,
+                residual: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """``tensor`` [B,S,d] -> ([B,S,d] in the input dtype, load-balancing loss).
+
+        With ``residual`` (same shape and dtype) the caller's skip connection
+        (model.py:319) is added inside the combine kernel."""
+        if fine_tuning:
+            raise NotImplementedError("the LoRA branch (fine_tuning=True) is not implemented")
+        if self.training and self.experts[0].dropout.p > 0:
+            raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
+        if not tensor.is_cuda:
+            raise RuntimeError("libmoe_b200 runs on CUDA tensors only; there is no CPU path")
+        dtype = _dtype_code(tensor)
+        shape = tensor.shape
+        d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
+        if shape[-1] != d:
+            raise ValueError(f"last dimension {shape[-1]} != hidden_size {d}")
+        x = tensor.reshape(-1, d).contiguous()
+        N = x.shape[0]
+        dev = x.device
+        res_ptr = None
+        if residual is not None:
+            if residual.shape != shape or residual.dtype != tensor.dtype or residual.device != dev:
+                raise ValueError("residual must match the input's shape, dtype and device")
+            residual = residual.reshape(-1, d).contiguous()
+            res_ptr = residual.data_ptr()
+        gw, gb = self.gate.weight, self.gate.bias
+        if gw.device != dev or _dtype_code(gw) != dtype:
+            raise ValueError("gate parameters must share the input's device and dtype")
+        out = torch.empty_like(x)
+        with torch.cuda.device(dev):
+            plan = self._plan.get(self.experts, d, f, dtype, dev)
+            _, base, nbytes, _ = self._workspace(N, dtype, dev)
+            check(lib.moe_b200_forward(x.data_ptr(), gw.data_ptr(), gb.data_ptr(), plan, res_ptr,
+                                       N, d, f, E, k, dtype, self.flags, base, nbytes,
+                                       out.data_ptr(), _stream(dev)), "forward")
+        self.last = {
+            "logits": self._view("logits", torch.float32, (N, E)),
+            "idx": self._view("idx", torch.int32, (N, k)),
+            "w": self._view("w", torch.float32, (N, k)),
+            "cnt_slot": self._view("cnt_slot", torch.int32, (k, E)),
+            "offsets": self._view("offsets", torch.int32, (E + 1,)),
+            "psum": self._view("psum", torch.float32, (E,)),
+            "row_of": self._view("row_of", torch.int32, (N, k)),
+            "status": self._view("status", torch.int32, (16,)),
+        }
+        aux = self._view("aux", torch.float32, (1,))[0].clone()
+        return out.reshape(shape), aux
+
+    def device_status(self) -> int:
+        """Status word of the most recent call (0 = ok); synchronises."""
+        return int(self.last["status"][0].item()) if self.last else 0

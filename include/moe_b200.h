@@ -1,0 +1,190 @@
+/*
+ * moe_b200.h — C ABI of libmoe_b200.so: the Mixture-of-Experts feed-forward
+ * block of GemmaLLM (reference model.py:192-276, expert model.py:154-190)
+ * as hand-written CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name starts with h_.
+ *   - Every call is asynchronous on the given stream (a cudaStream_t passed as
+ *     void*; NULL = the legacy default stream) unless stated otherwise.
+ *   - Return value: 0 = ok; negative = argument error found on the host before
+ *     any launch (nothing ran); positive = CUDA runtime error code + 1000.
+ *     Errors detected on the device (a wait that ran out, a bad index) are
+ *     written to the workspace status word; read it with moe_b200_read_status.
+ *   - The library owns no device memory and never allocates: the caller
+ *     passes inputs, outputs, a workspace and a "plan" buffer.
+ *   - Matrices are row-major and contiguous. Tokens are rows: x is [N, d].
+ *   - dtype: MOE_B200_F32 or MOE_B200_BF16 applies to x, the parameters and
+ *     the output alike. The router always computes in fp32.
+ *
+ * Symbols: N tokens, d = hidden size, f = per-branch expert width
+ * (gate_and_up.weight is [2f, d]: rows [0,f) gate, rows [f,2f) up,
+ * model.py:180), E experts, k = experts per token (the reference fixes k = 2,
+ * model.py:210).
+ */
+#ifndef MOE_B200_H
+#define MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_B200_ABI_VERSION 1
+
+enum { MOE_B200_F32 = 0, MOE_B200_BF16 = 1 };
+
+/* host-side argument errors */
+enum {
+  MOE_B200_OK = 0,
+  MOE_B200_ERR_NULL = -1,      /* a required pointer is NULL */
+  MOE_B200_ERR_SHAPE = -2,     /* N, d, f, E or k out of the supported range */
+  MOE_B200_ERR_ALIGN = -3,     /* a pointer or row pitch is not 16-byte aligned */
+  MOE_B200_ERR_DTYPE = -4,     /* unknown dtype */
+  MOE_B200_ERR_WORKSPACE = -5, /* workspace or plan buffer too small */
+  MOE_B200_ERR_DRIVER = -6,    /* tensor-map encoding entry point unavailable */
+  MOE_B200_ERR_UNSUPPORTED = -7
+};
+
+/* device-side status codes (workspace status word 0) */
+enum {
+  MOE_B200_DEV_OK = 0,
+  MOE_B200_DEV_TIMEOUT = 1,   /* a bounded wait inside a kernel ran out */
+  MOE_B200_DEV_BAD_INDEX = 2  /* an expert index outside [0,E) was seen */
+};
+
+/* flags for moe_b200_experts / moe_b200_forward */
+enum {
+  MOE_B200_FLAG_DEFAULT = 0,
+  /* run the expert products on the plain CUDA-core kernel even for bf16 (the
+   * fp32 dtype always uses it). For tests: a second implementation of the same
+   * arithmetic to check the tensor-core kernel against. */
+  MOE_B200_FLAG_SIMT_EXPERTS = 1,
+  /* never take the small-N weight-streaming path */
+  MOE_B200_FLAG_NO_DECODE_PATH = 2
+};
+
+/* Indices into the array filled by moe_b200_workspace_layout. */
+enum {
+  MOE_B200_WS_STATUS = 0, /* int32[16]; word 0 = device status code */
+  MOE_B200_WS_LOGITS,     /* float [N,E]   router logits (model.py:206) */
+  MOE_B200_WS_IDX,        /* int32 [N,k]   chosen experts, slot 0 = best (model.py:210) */
+  MOE_B200_WS_W,          /* float [N,k]   renormalised scores (model.py:219-223) */
+  MOE_B200_WS_PSUM_PART,  /* float [router blocks, E] partial sums of softmax */
+  MOE_B200_WS_PSUM,       /* float [E]     sum over tokens of softmax (model.py:215) */
+  MOE_B200_WS_AUX,        /* float [1]     load-balancing loss (model.py:216) */
+  MOE_B200_WS_SCRATCH,    /* int32 [moe_b200_dispatch_scratch_bytes/4] dispatch scratch */
+  MOE_B200_WS_CNT_SLOT,   /* int32 [k,E]   per-slot expert counts (model.py:237-245) */
+  MOE_B200_WS_OFFSETS,    /* int32 [E+1]   start row of each expert in the sorted buffers */
+  MOE_B200_WS_ROW_OF,     /* int32 [N,k]   sorted-buffer row of (token, slot) */
+  MOE_B200_WS_PERM,       /* T [N*k, d]    tokens sorted by expert (model.py:248-253) */
+  MOE_B200_WS_H,          /* T [N*k, f]    gelu_tanh(gate)*up (model.py:180-182) */
+  MOE_B200_WS_Y,          /* T [N*k, d]    expert outputs, sorted order (model.py:184) */
+  MOE_B200_WS_NUM
+};
+
+/* ABI version of the loaded library (no reference counterpart: the reference
+ * is a Python class, model.py:192). Synchronous. */
+int moe_b200_version(void);
+
+/* Text for the last non-zero return value on this thread. Synchronous. */
+const char* moe_b200_last_error_string(void);
+
+/* Bytes of workspace moe_b200_forward needs; 0 on bad arguments. Replaces the
+ * temporaries the reference allocates per call (model.py:226-268).
+ * Synchronous, touches no GPU. */
+size_t moe_b200_workspace_bytes(int64_t N, int d, int f, int E, int k, int dtype);
+
+/* Byte offset of each workspace region (h_offsets[MOE_B200_WS_NUM]). */
+int moe_b200_workspace_layout(int64_t N, int d, int f, int E, int k, int dtype,
+                              size_t* h_offsets);
+
+/* Bytes of the plan buffer for E experts. */
+size_t moe_b200_plan_bytes(int E);
+
+/* Record the E experts' parameter pointers (and, for bf16, their TMA tensor
+ * maps) in the caller's plan buffer. Stands for the reference's
+ * nn.ModuleList of FeedForward (model.py:197): h_W1[e] = gate_and_up.weight
+ * [2f,d], h_b1[e] = gate_and_up.bias [2f], h_W2[e] = down.weight [d,f],
+ * h_b2[e] = down.bias [d] (model.py:162-163). Call again whenever a
+ * parameter's storage moves. The host arrays may be freed on return. */
+int moe_b200_plan_build(const void* const* h_W1, const void* const* h_b1,
+                        const void* const* h_W2, const void* const* h_b2,
+                        int E, int d, int f, int dtype,
+                        void* plan, size_t plan_bytes, void* stream);
+
+/* Part 1 — router: logits = x Wg^T + bg (model.py:206), fp32 softmax
+ * (model.py:207), top-k (model.py:210), renormalise (model.py:219-223), and
+ * the sums the load-balancing loss needs (model.py:213-216).
+ *   out_logits  float [N,E]  or NULL
+ *   out_idx     int32 [N,k]  slot 0 = highest probability
+ *   out_w       float [N,k]
+ *   psum_part   float [moe_b200_router_blocks(N), E] scratch
+ */
+int moe_b200_router(const void* x, const void* Wg, const void* bg,
+                    int64_t N, int d, int E, int k, int dtype,
+                    float* out_logits, int32_t* out_idx, float* out_w,
+                    float* psum_part, int32_t* status, void* stream);
+
+int64_t moe_b200_router_blocks(int64_t N);
+
+/* Part 2 — dispatch: histogram of idx, exclusive scan, and permutation of the
+ * token rows into one expert-contiguous buffer; replaces the per-slot argsort,
+ * count loop, gather and split of model.py:226-253. Rows of one expert keep
+ * token order (stable).
+ *   scratch    moe_b200_dispatch_scratch_bytes(N,E,k) bytes: per-chunk expert
+ *              counts and per-block per-slot counts; contents need no
+ *              initialisation and are overwritten by every call
+ *   cnt_slot   int32 [k,E]   (top_expert_counts, second_expert_counts, ...)
+ *   offsets    int32 [E+1]
+ *   row_of     int32 [N,k]
+ *   perm       T [N*k, d]
+ *   psum_part/psum/aux: when psum_part is non-NULL the router's partial sums
+ *   are reduced in a fixed order into psum[E] and the load-balancing loss
+ *   aux[0] (model.py:213-216); otherwise these three may be NULL.
+ */
+int moe_b200_dispatch(const void* x, const int32_t* idx,
+                      int64_t N, int d, int E, int k, int dtype,
+                      int32_t* scratch, int32_t* cnt_slot, int32_t* offsets,
+                      int32_t* row_of, void* perm,
+                      const float* psum_part, float* psum, float* aux,
+                      int32_t* status, void* stream);
+
+size_t moe_b200_dispatch_scratch_bytes(int64_t N, int E, int k);
+
+/* Part 3 — experts: for every expert e and its rows [offsets[e], offsets[e+1])
+ * of perm: h = gelu_tanh(x W1g^T + b1g) * (x W1u^T + b1u), y = h W2^T + b2
+ * (FeedForward.forward, model.py:173-190 with fine_tuning=False, dropout in
+ * eval mode). M = N*k rows. bf16 runs on tcgen05 tensor cores with fp32
+ * accumulation; fp32 runs on CUDA cores. h [M,f] and y [M,d] are outputs. */
+int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
+                     int64_t M, int d, int f, int E, int dtype, int flags,
+                     void* h, void* y, int32_t* status, void* stream);
+
+/* Parts 4+5 — combine: out[t] = sum_j w[t,j] * y[row_of[t,j]] in slot order
+ * in fp32 (model.py:264-271), plus residual[t] when residual is non-NULL (the
+ * caller's `tensor += skip_connection`, model.py:319), rounded once to T. */
+int moe_b200_combine(const void* y, const int32_t* row_of, const float* w,
+                     const void* residual, int64_t N, int d, int k, int dtype,
+                     void* out, void* stream);
+
+/* The whole block: MOE.forward (model.py:200-276) for x [N,d] -> out [N,d],
+ * with the optional fused residual. Wg [E,d], bg [E] are gate.weight/bias
+ * (model.py:195). After it the workspace holds logits, idx, w, counts,
+ * offsets, psum and the loss (see moe_b200_workspace_layout). */
+int moe_b200_forward(const void* x, const void* Wg, const void* bg,
+                     const void* plan, const void* residual,
+                     int64_t N, int d, int f, int E, int k, int dtype, int flags,
+                     void* workspace, size_t workspace_bytes,
+                     void* out, void* stream);
+
+/* Copy the 16 status words to the host after synchronising the stream.
+ * Returns h_status[0]. Synchronous. */
+int moe_b200_read_status(const int32_t* status, int32_t* h_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H */

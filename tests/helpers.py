@@ -1,0 +1,97 @@
+"""Thin test-side wrappers: call each C-ABI entry point with torch tensors."""
+from __future__ import annotations
+
+import torch
+
+from gemmallm_b200 import _cabi, synthetic
+from gemmallm_b200._cabi import lib, check
+
+CODE = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16}
+
+
+def stream(dev):
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def router(x, gate_w, gate_b, k):
+    N, d = x.shape
+    E = gate_w.shape[0]
+    dev = x.device
+    logits = torch.empty(N, E, dtype=torch.float32, device=dev)
+    idx = torch.empty(N, k, dtype=torch.int32, device=dev)
+    w = torch.empty(N, k, dtype=torch.float32, device=dev)
+    psum_part = torch.empty(max(1, lib.moe_b200_router_blocks(N)), E, dtype=torch.float32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_router(x.data_ptr(), gate_w.data_ptr(), gate_b.data_ptr(), N, d, E, k,
+                              CODE[x.dtype], logits.data_ptr(), idx.data_ptr(), w.data_ptr(),
+                              psum_part.data_ptr(), status.data_ptr(), stream(dev)), "router")
+    return logits, idx, w, psum_part
+
+
+def dispatch(x, idx, E, psum_part=None):
+    N, d = x.shape
+    k = idx.shape[1]
+    dev = x.device
+    nbytes = lib.moe_b200_dispatch_scratch_bytes(N, E, k)
+    # poison the scratch: the kernel must not depend on its previous contents
+    scratch = torch.full((nbytes // 4,), 0x5A5A5A5A, dtype=torch.int32, device=dev)
+    cnt_slot = torch.empty(k, E, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    row_of = torch.empty(N, k, dtype=torch.int32, device=dev)
+    perm = torch.empty(N * k, d, dtype=x.dtype, device=dev)
+    psum = torch.empty(E, dtype=torch.float32, device=dev)
+    aux = torch.zeros(1, dtype=torch.float32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_dispatch(x.data_ptr(), idx.data_ptr(), N, d, E, k, CODE[x.dtype],
+                                scratch.data_ptr(), cnt_slot.data_ptr(), offsets.data_ptr(),
+                                row_of.data_ptr(), perm.data_ptr(),
+                                None if psum_part is None else psum_part.data_ptr(),
+                                psum.data_ptr(), aux.data_ptr(), status.data_ptr(), stream(dev)),
+          "dispatch")
+    return {"cnt_slot": cnt_slot, "offsets": offsets, "row_of": row_of, "perm": perm,
+            "psum": psum, "aux": aux, "status": status}
+
+
+class Plan:
+    def __init__(self, w1, b1, w2, b2):
+        """w1 [E,2f,d], b1 [E,2f], w2 [E,d,f], b2 [E,d] on the device."""
+        E, f2, d = w1.shape
+        self.E, self.d, self.f = E, d, f2 // 2
+        dev = w1.device
+        nbytes = lib.moe_b200_plan_bytes(E)
+        self.buf = torch.empty(nbytes + 128, dtype=torch.uint8, device=dev)
+        self.ptr = (self.buf.data_ptr() + 127) & ~127
+        self.keep = (w1, b1, w2, b2)
+        arr = lambda t: _cabi.ptr_array([t[e].data_ptr() for e in range(E)])
+        check(lib.moe_b200_plan_build(arr(w1), arr(b1), arr(w2), arr(b2), E, d, self.f,
+                                      CODE[w1.dtype], self.ptr, nbytes, stream(dev)), "plan_build")
+
+
+def experts(perm, offsets, plan: Plan, flags=0):
+    M, d = perm.shape
+    dev = perm.device
+    h = torch.empty(M, plan.f, dtype=perm.dtype, device=dev)
+    y = torch.empty(M, d, dtype=perm.dtype, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_experts(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d, plan.f, plan.E,
+                               CODE[perm.dtype], flags, h.data_ptr(), y.data_ptr(),
+                               status.data_ptr(), stream(dev)), "experts")
+    return h, y, status
+
+
+def combine(y, row_of, w, residual=None):
+    N, k = row_of.shape
+    d = y.shape[1]
+    out = torch.empty(N, d, dtype=y.dtype, device=y.device)
+    check(lib.moe_b200_combine(y.data_ptr(), row_of.data_ptr(), w.data_ptr(),
+                               None if residual is None else residual.data_ptr(), N, d, k,
+                               CODE[y.dtype], out.data_ptr(), stream(y.device)), "combine")
+    return out
+
+
+def device_params(params: dict, dtype, dev) -> dict:
+    return {n: t.to(dtype).to(dev).contiguous() for n, t in params.items()}
+
+
+def rounded_params(params: dict, dtype) -> dict:
+    return {n: synthetic.round_to(t, dtype) for n, t in params.items()}
