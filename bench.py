@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the Mixture-of-Experts block: tokens/s and grouped-GEMM
+fraction of the measured bf16 tensor peak.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One step = one forward of the block over the workload's token batch. At N=1 the
+workload is the bf16 prefill block (16384 tokens, d_model 1024, 8 experts,
+d_ff 4096, top-2, uniform routing). Under torchrun every rank runs the same
+block on its own token batch (tokens sharded, no data-path collective; weak
+scaling). Rank 0 prints one JSON line.
+
+``--impl reference`` times the CPU restatement of the reference block
+(oracle/moe_oracle.py, bit-identical to the reference class at k=2) on this
+host's cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+CPU_SAMPLE_TOKENS = 4096
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            if "hbm_gbs" in d and "bf16_tflops" in d:
+                return d, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed
+    region runs (read-only queries)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def workload_config(wl, extra):
+    cfg = {"workload": wl.name, "tokens": wl.tokens, "d_model": wl.d_model,
+           "n_experts": wl.n_experts, "d_ff": wl.d_ff, "top_k": wl.top_k, "routing": wl.gate_bias}
+    cfg.update(extra)
+    return cfg
+
+
+def cpu_baseline(wl, tokens, repeats, warmup):
+    """Oracle (port of the reference block) on the host cores, fp32 on
+    bf16-rounded values: the reference cannot run in bf16."""
+    from gemmallm_b200 import synthetic
+    from oracle import moe_oracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    dt = synthetic.torch_dtype(wl.dtype)
+    params = {n: synthetic.round_to(t, dt) for n, t in synthetic.make_params(
+        wl.d_model, wl.n_experts, wl.d_ff, seed=0, gate_bias_kind=wl.gate_bias).items()}
+    x = synthetic.round_to(synthetic.make_input(tokens, wl.d_model, seed=1), dt)
+    with torch.no_grad():
+        for _ in range(warmup):
+            moe_oracle.moe_forward(x, params, wl.top_k)
+        times = []
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            moe_oracle.moe_forward(x, params, wl.top_k)
+            times.append(time.perf_counter() - t0)
+    return times, cores
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tokens = min(wl.tokens, CPU_SAMPLE_TOKENS)
+    times, cores = cpu_baseline(wl, tokens, args.steps, args.warmup)
+    total = sum(times)
+    value = tokens * args.steps / total
+    sample = f"first {tokens} of {wl.tokens} tokens per step, fp32 on bf16-rounded values"
+    line = {
+        "impl": "reference", "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(wl, {"parallelism": "cpu"}),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, wl):
+    import torch.distributed as dist
+    from gemmallm_b200 import MOE, _cabi, synthetic
+    from gemmallm_b200._cabi import lib, check
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU path")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dt = synthetic.torch_dtype(wl.dtype)
+    es = 2 if wl.dtype == "bf16" else 4
+    N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+    params = synthetic.make_params(d, E, f, seed=0, gate_bias_kind=wl.gate_bias)
+    m = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda").eval()
+    synthetic.load_into(m, params, dt, dev)
+    del params
+    # each rank owns its own token batch (seed differs per rank)
+    x_host = synthetic.make_input(N, d, seed=1 + rank).to(dt).pin_memory()
+    x = x_host.to(dev).view(1, N, d)
+    out_host = torch.empty(N, d, dtype=dt).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+        return ms
+
+    # ---- device-resident throughput -------------------------------------
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            m(x)
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            ev0.record()
+            for _ in range(args.steps):
+                m(x)
+            ev1.record()
+            barrier()
+        ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    status = m.device_status()
+    if status != 0:
+        raise RuntimeError(f"device status {status} after the timed region")
+    ms_step = ms_total / args.steps
+    value = N * world * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end: host buffers in, host buffers out --------------------
+    with torch.no_grad():
+        for _ in range(2):
+            xd = x_host.to(dev, non_blocking=True).view(1, N, d)
+            o, aux = m(xd)
+            out_host.copy_(o.view(N, d), non_blocking=True)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            xd = x_host.to(dev, non_blocking=True).view(1, N, d)
+            o, aux = m(xd)
+            out_host.copy_(o.view(N, d), non_blocking=True)
+            aux_host = float(aux)  # the loss is read on the host every step
+        e1.record()
+        barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    e2e_value = N * world * args.steps / (e2e_ms * 1e-3)
+
+    # ---- per-stage times through the stage entry points --------------------
+    stage_ms, launches_per_step = {}, 5
+    if rank == 0:
+        stage_ms = time_stages(m, x.view(N, d), wl, dev)
+    peaks, peak_kind = load_peaks()
+    line = None
+    if rank == 0:
+        flops = 6.0 * k * d * f * N
+        t_gemm = stage_ms["experts"] * 1e-3
+        achieved = flops / t_gemm / 1e12
+        peak = float(peaks["bf16_tflops"])
+        hbm = float(peaks["hbm_gbs"])
+        stage_bytes = {
+            "router": N * d * es + E * d * es + N * k * 8,
+            "dispatch": N * d * es + N * k * d * es + N * k * 8,
+            "combine": N * k * d * es + N * d * es + N * k * 8,
+        }
+        line = {
+            "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic",
+            "config": workload_config(wl, {
+                "parallelism": "single" if world == 1 else f"tokens sharded over {world} ranks, experts replicated",
+                "l2": "working set per step (weights 201 MB + activations) exceeds the 126 MB L2"}),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": N * d * es,
+                    "d2h_bytes_per_step": N * d * es + 4, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+            "roofline": {"kernel": "grouped_gemm_tc_kernel (GEGLU pass + down pass)",
+                         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{peak_kind} bf16 burst", "flops_per_step": flops,
+                         "ms": stage_ms["experts"]},
+            "stages_ms": stage_ms,
+            "stages_hbm": {n: {"bytes": b, "gbs": b / (stage_ms[n] * 1e-3) / 1e9,
+                               "frac": b / (stage_ms[n] * 1e-3) / 1e9 / hbm}
+                           for n, b in stage_bytes.items()},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            tokens = min(N, CPU_SAMPLE_TOKENS)
+            times, cores = cpu_baseline(wl, tokens, 3, 1)
+            times.sort()
+            line["cpu_baseline"] = {
+                "value": tokens / times[len(times) // 2], "unit": "tokens/s", "cores": cores,
+                "kind": "port",
+                "sample": f"first {tokens} of {N} tokens, median of 3, fp32 on bf16-rounded values"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def time_stages(m, x2d, wl, dev, reps: int = 20):
+    """CUDA-event time of each stage, called through its own C-ABI entry point
+    on the buffers of the module's workspace, on the current stream."""
+    from gemmallm_b200 import _cabi
+    from gemmallm_b200._cabi import lib, check
+    N, d = x2d.shape
+    f, E, k = wl.d_ff, wl.n_experts, wl.top_k
+    code = _cabi.BF16 if wl.dtype == "bf16" else _cabi.F32
+    buf, base, nbytes, lay = m._ws
+    p = {n: base + off for n, off in lay.items()}
+    plan = m._plan.base
+    s = torch.cuda.current_stream(dev).cuda_stream
+    out = torch.empty_like(x2d)
+    gw, gb = m.gate.weight, m.gate.bias
+    calls = {
+        "router": lambda: lib.moe_b200_router(x2d.data_ptr(), gw.data_ptr(), gb.data_ptr(), N, d, E,
+                                              k, code, p["logits"], p["idx"], p["w"],
+                                              p["psum_part"], p["status"], s),
+        "dispatch": lambda: lib.moe_b200_dispatch(x2d.data_ptr(), p["idx"], N, d, E, k, code,
+                                                  p["scratch"], p["cnt_slot"], p["offsets"],
+                                                  p["row_of"], p["perm"], p["psum_part"], p["psum"],
+                                                  p["aux"], p["status"], s),
+        "experts": lambda: lib.moe_b200_experts(p["perm"], p["offsets"], plan, N * k, d, f, E, code,
+                                                m.flags, p["h"], p["y"], p["status"], s),
+        "combine": lambda: lib.moe_b200_combine(p["y"], p["row_of"], p["w"], None, N, d, k, code,
+                                                out.data_ptr(), s),
+    }
+    res = {}
+    for name, fn in calls.items():
+        for _ in range(3):
+            check(fn(), name)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        res[name] = e0.elapsed_time(e1) / reps
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c1_uniform")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    from gemmallm_b200 import synthetic
+    wl = synthetic.WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

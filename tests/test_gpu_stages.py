@@ -1,0 +1,183 @@
+"""Parity of each C-ABI stage with the CPU oracle on the same seeded inputs:
+routing indices and counts bit-exact, floating point within stated tolerances."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import helpers
+from gemmallm_b200 import _cabi, synthetic
+from oracle import moe_oracle
+
+pytestmark = pytest.mark.gpu
+
+ROUTER_CASES = [
+    # N, d, E, k, dtype
+    (1, 64, 8, 2, torch.float32), (2, 64, 8, 2, torch.float32), (3, 64, 8, 2, torch.float32),
+    (31, 64, 8, 2, torch.float32), (32, 64, 8, 2, torch.float32), (33, 64, 8, 2, torch.float32),
+    (127, 64, 8, 2, torch.bfloat16), (128, 64, 8, 2, torch.bfloat16), (129, 64, 8, 2, torch.bfloat16),
+    (512, 512, 8, 2, torch.float32), (1000, 256, 64, 4, torch.bfloat16),
+    (300, 128, 256, 8, torch.bfloat16), (77, 72, 5, 3, torch.float32), (50, 40, 1, 1, torch.float32),
+    (4096, 2048, 64, 4, torch.bfloat16),
+]
+
+
+def make_gate(N, d, E, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    gate_w = synthetic.round_to(torch.randn(E, d, generator=g) * 0.05, dtype)
+    gate_b = synthetic.round_to(torch.randn(E, generator=g) * 0.3, dtype)
+    x = synthetic.round_to(torch.randn(N, d, generator=g), dtype)
+    return x, gate_w, gate_b
+
+
+@pytest.mark.parametrize("N,d,E,k,dtype", ROUTER_CASES)
+def test_router_matches_oracle(cuda_device, N, d, E, k, dtype):
+    x, gw, gb = make_gate(N, d, E, dtype, seed=N + d + E)
+    logits, idx, w, psum_part = helpers.router(x.to(dtype).to(cuda_device), gw.to(dtype).to(cuda_device),
+                                               gb.to(dtype).to(cuda_device), k)
+    torch.cuda.synchronize()
+    logits, idx, w, psum_part = logits.cpu(), idx.cpu(), w.cpu(), psum_part.cpu()
+    ref_logits = F.linear(x, gw, gb)
+    assert (logits - ref_logits).abs().max() <= 2e-5 * max(1.0, float(ref_logits.abs().max()))
+    # bit-exact routing given the kernel's own fp32 logits
+    r = moe_oracle.route_from_logits(logits, k)
+    ties = moe_oracle.tie_rows(r["probs"], k)
+    ok = ~ties
+    assert torch.equal(idx[ok].long(), r["idx"][ok]), "routing indices differ from topk(softmax(logits))"
+    assert torch.allclose(w[ok], r["w"][ok], atol=2e-6, rtol=0)
+    assert torch.allclose(psum_part.sum(0), r["probs"].sum(0), rtol=1e-5, atol=1e-5)
+    assert ((idx >= 0) & (idx < E)).all()
+    # no expert twice for one token
+    assert (idx.sort(dim=1).values.diff(dim=1) > 0).all() if k > 1 else True
+
+
+DISPATCH_CASES = [(1, 64, 8, 2), (2, 64, 8, 2), (63, 64, 8, 2), (64, 64, 8, 2), (65, 64, 8, 2),
+                  (129, 128, 8, 2), (1000, 256, 64, 4), (5000, 512, 8, 2), (333, 72, 5, 3),
+                  (4097, 64, 256, 8), (40000, 64, 8, 2)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N,d,E,k", DISPATCH_CASES)
+def test_dispatch_is_a_stable_counting_sort(cuda_device, N, d, E, k, dtype):
+    g = torch.Generator().manual_seed(N * 7 + E)
+    x = torch.randn(N, d, generator=g).to(dtype)
+    # k distinct experts per token, skewed popularity
+    score = torch.rand(N, E, generator=g) + torch.linspace(0.5, 0, E)
+    idx = score.topk(k, dim=1).indices.to(torch.int32)
+    psum_part = torch.rand(max(1, _cabi.lib.moe_b200_router_blocks(N)), E, generator=g)
+    out = helpers.dispatch(x.to(cuda_device), idx.to(cuda_device), E, psum_part.to(cuda_device))
+    torch.cuda.synchronize()
+    cnt_slot, offsets, row_of, perm = (out[n].cpu() for n in ("cnt_slot", "offsets", "row_of", "perm"))
+    assert int(out["status"][0]) == 0
+    ref_cnt = torch.stack([torch.bincount(idx[:, j].long(), minlength=E) for j in range(k)])
+    assert torch.equal(cnt_slot.long(), ref_cnt)
+    total = ref_cnt.sum(0)
+    assert torch.equal(offsets.long(), torch.cat([torch.zeros(1, dtype=torch.long), total.cumsum(0)]))
+    flat = row_of.long().flatten()
+    assert torch.equal(flat.sort().values, torch.arange(N * k))          # a permutation
+    e_of_row = torch.bucketize(flat, offsets.long()[1:], right=True)
+    assert torch.equal(e_of_row, idx.long().flatten())                  # rows land in their expert
+    assert torch.equal(perm[flat].view(N, k, d), x[:, None, :].expand(N, k, d))  # rows are copies
+    # stable: inside one expert, rows follow token order
+    tok_of_row = torch.empty(N * k, dtype=torch.long)
+    tok_of_row[flat] = torch.arange(N).repeat_interleave(k)
+    for e in range(E):
+        seg = tok_of_row[offsets[e]:offsets[e + 1]]
+        assert (seg.diff() > 0).all()
+    # load-balancing loss from the partial sums, fixed-order reduction
+    psum = psum_part.sum(0)
+    aux = (psum / N * (ref_cnt[0].float() / N)).mean() * float(E * E)
+    assert torch.allclose(out["psum"].cpu(), psum, rtol=1e-5)
+    assert abs(float(out["aux"][0]) - float(aux)) <= 1e-5 * abs(float(aux)) + 1e-7
+
+
+def test_dispatch_reports_bad_index(cuda_device):
+    x = torch.randn(10, 64, device=cuda_device)
+    idx = torch.zeros(10, 2, dtype=torch.int32, device=cuda_device)
+    idx[:, 1] = 1
+    idx[4, 1] = 99
+    out = helpers.dispatch(x, idx, 8)
+    torch.cuda.synchronize()
+    assert int(out["status"][0]) == _cabi.DEV_BAD_INDEX
+    assert int(out["row_of"][4, 1]) == -1
+    assert int(out["offsets"][-1]) == 19
+
+
+EXPERT_CASES = [
+    # rows per expert, d, f
+    ([5, 0, 130, 1], 64, 128), ([128, 128], 128, 256), ([127, 129, 0, 0, 300], 256, 384),
+    ([1], 64, 64), ([0, 0, 7], 72, 88), ([700, 3, 0, 513, 64, 1, 255, 256], 512, 1024),
+]
+
+
+def expert_inputs(rows, d, f, dtype, seed):
+    E = len(rows)
+    params = synthetic.make_params(d, E, f, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    params["b1"] = torch.randn(E, 2 * f, generator=g) * 0.05
+    params["b2"] = torch.randn(E, d, generator=g) * 0.05
+    params["w1"] *= 3.0
+    params["w2"] *= 3.0
+    params = helpers.rounded_params(params, dtype)
+    M = sum(rows)
+    x = synthetic.round_to(torch.randn(M, d, generator=g), dtype)
+    offsets = torch.tensor([0] + rows).cumsum(0).to(torch.int32)
+    return params, x, offsets
+
+
+def oracle_experts(params, x, offsets):
+    hs, ys = [], []
+    for e in range(len(offsets) - 1):
+        seg = x[offsets[e]:offsets[e + 1]]
+        gu = F.linear(seg, params["w1"][e], params["b1"][e])
+        gate, up = gu.chunk(2, dim=-1)
+        hs.append(F.gelu(gate, approximate="tanh") * up)
+        ys.append(moe_oracle.expert_ffn(seg, params["w1"][e], params["b1"][e], params["w2"][e],
+                                        params["b2"][e]))
+    return torch.cat(hs), torch.cat(ys)
+
+
+@pytest.mark.parametrize("rows,d,f", EXPERT_CASES)
+def test_experts_fp32(cuda_device, rows, d, f):
+    params, x, offsets = expert_inputs(rows, d, f, torch.float32, seed=len(rows) + d)
+    dp = helpers.device_params(params, torch.float32, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    h, y, status = helpers.experts(x.to(cuda_device), offsets.to(cuda_device), plan)
+    torch.cuda.synchronize()
+    h_ref, y_ref = oracle_experts(params, x, offsets)
+    assert (h.cpu() - h_ref).abs().max() <= 1e-4     # fp32 tolerance of the block: max-abs 1e-4
+    assert (y.cpu() - y_ref).abs().max() <= 1e-4
+
+
+@pytest.mark.parametrize("flags", [_cabi.FLAG_DEFAULT, _cabi.FLAG_SIMT_EXPERTS])
+@pytest.mark.parametrize("rows,d,f", EXPERT_CASES)
+def test_experts_bf16(cuda_device, rows, d, f, flags):
+    params, x, offsets = expert_inputs(rows, d, f, torch.bfloat16, seed=len(rows) + d)
+    dp = helpers.device_params(params, torch.bfloat16, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    h, y, status = helpers.experts(x.to(torch.bfloat16).to(cuda_device), offsets.to(cuda_device),
+                                   plan, flags)
+    torch.cuda.synchronize()
+    assert status.cpu().tolist()[0] == 0, f"device status {status.cpu().tolist()[:4]}"
+    h_ref, y_ref = oracle_experts(params, x, offsets)
+    # bf16 tolerance of the block: relative error 2e-2 (max-abs over the largest reference value)
+    assert (h.float().cpu() - h_ref).abs().max() <= 2e-2 * h_ref.abs().max()
+    assert (y.float().cpu() - y_ref).abs().max() <= 2e-2 * y_ref.abs().max()
+    assert (y.float().cpu() - y_ref).norm() <= 2e-2 * y_ref.norm()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N,d,k", [(1, 64, 2), (130, 128, 2), (1000, 512, 4), (33, 72, 1)])
+def test_combine_is_exact(cuda_device, N, d, k, dtype):
+    g = torch.Generator().manual_seed(N + d)
+    y = torch.randn(N * k, d, generator=g).to(dtype)
+    row_of = torch.randperm(N * k, generator=g).view(N, k).to(torch.int32)
+    w = torch.rand(N, k, generator=g)
+    res = torch.randn(N, d, generator=g).to(dtype)
+    acc = torch.zeros(N, d)
+    for j in range(k):
+        acc = acc + w[:, j:j + 1] * y[row_of[:, j].long()].float()
+    for residual, expect in ((None, acc), (res, acc + res.float())):
+        out = helpers.combine(y.to(cuda_device), row_of.to(cuda_device), w.to(cuda_device),
+                              None if residual is None else residual.to(cuda_device))
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), expect.to(dtype))
