@@ -210,6 +210,16 @@ def run_ours(args, wl):
     ms_step = ms_total / args.steps
     value = N * world * args.steps / (ms_total * 1e-3)
 
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s",
+                              "n_gpus": world, "steps": args.steps, "ms_per_step": ms_step,
+                              "quick": True, "config": workload_config(wl, {})}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
     # ---- end to end: host buffers in, host buffers out --------------------
     with torch.no_grad():
         for _ in range(2):
@@ -332,6 +342,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1_uniform")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true",
+                    help="device-resident loop only (for profiler captures): no end-to-end leg, "
+                         "no per-stage timing, no CPU baseline; prints a reduced line")
     args = ap.parse_args()
     from gemmallm_b200 import synthetic
     wl = synthetic.WORKLOADS[args.workload]
