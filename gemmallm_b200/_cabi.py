@@ -36,6 +36,8 @@ SIGNATURES = {
     "moe_b200_dispatch": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _vp, _vp, _vp]),
     "moe_b200_dispatch_scratch_bytes": (_sz, [_i64, _i, _i]),
+    "moe_b200_dispatch_static": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
+                                      _vp, _vp, _vp]),
     "moe_b200_experts": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "moe_b200_combine": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "moe_b200_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _sz,

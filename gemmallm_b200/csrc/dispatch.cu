@@ -12,6 +12,7 @@
 // (token, slot) pairs in token order, and copies the rows. Rows of one expert
 // therefore stay in token order whatever the grid size.
 #include <cooperative_groups.h>
+#include <stdio.h>
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -253,3 +254,70 @@ int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, 
 }
 
 }  // namespace moe
+
+// ---------------------------------------------------------------------------
+// Dispatch without caller-provided scratch.
+//
+// Some callers cannot hand the library a scratch buffer because they are not
+// allowed to allocate device memory at the point of the call: code running
+// inside a framework's forward hook with a frozen memory pool, a serving loop
+// whose allocator is locked while requests are in flight, or a host language
+// binding that only receives the tensors of the op's signature. For them the
+// per-chunk counters live in this file-scope device array instead. Every GPU
+// that loads the library holds kStaticScratchInts * 4 bytes (1 MiB) for the
+// lifetime of the process.
+//
+// The array is shared by every call on that GPU and keeps what the last call
+// left in it. Nothing has to be cleared between calls: the kernel zeroes its
+// completion counter itself before the grid barrier and overwrites every
+// count before reading it. Two calls whose kernels overlap on one GPU (two
+// streams, two host threads) race on it; callers must serialise them.
+// The first call on a device looks up the array's device address
+// (cudaGetSymbolAddress); make that first call outside any stream capture.
+namespace moe {
+namespace {
+constexpr int64_t kStaticScratchInts = 262144;  // 1 MiB
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) int32_t g_static_scratch[kStaticScratchInts];
+// g_static_scratch names a host-side shadow here; the device address has to be
+// asked for, once per device, with that device current.
+int32_t* g_static_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_b200_dispatch_static(const void* x, const int32_t* idx, int64_t N, int d, int E,
+                                        int k, int dtype, int32_t* cnt_slot, int32_t* offsets,
+                                        int32_t* row_of, void* perm, const float* psum_part,
+                                        float* psum, float* aux, int32_t* status, void* stream) {
+  using namespace moe;
+  if (dtype != MOE_B200_F32 && dtype != MOE_B200_BF16)
+    return set_error(MOE_B200_ERR_DTYPE, "dtype must be MOE_B200_F32 or MOE_B200_BF16");
+  if (N < 0 || d < 8 || (d & 7) || E < 1 || E > kMaxExperts || k < 1 || k > kMaxTopK || k > E ||
+      N * (int64_t)k >= (int64_t)1 << 31)
+    return set_error(MOE_B200_ERR_SHAPE, "N, d, E or k out of range");
+  const int64_t need = dispatch_scratch_ints(N, E, k);
+  if (need > kStaticScratchInts) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "moe_b200_dispatch_static: this shape needs %lld scratch words, the built-in array "
+             "holds %lld; use moe_b200_dispatch with a caller-provided scratch buffer",
+             (long long)need, (long long)kStaticScratchInts);
+    return set_error(MOE_B200_ERR_WORKSPACE, msg);
+  }
+  if (!cnt_slot || !offsets || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (N > 0 && (!x || !idx || !row_of || !perm)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (psum_part && (!psum || !aux))
+    return set_error(MOE_B200_ERR_NULL, "psum and aux are required with psum_part");
+  if (!aligned16(x) || !aligned16(perm))
+    return set_error(MOE_B200_ERR_ALIGN, "x and perm must be 16-byte aligned");
+  int dev = 0;
+  MOE_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return set_error(MOE_B200_ERR_UNSUPPORTED, "device ordinal too large");
+  if (g_static_scratch_addr[dev] == nullptr) {
+    int32_t* ptr = nullptr;
+    MOE_CUDA_CHECK(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+    g_static_scratch_addr[dev] = ptr;
+  }
+  return launch_dispatch(x, idx, N, d, E, k, dtype, g_static_scratch_addr[dev], cnt_slot, offsets,
+                         row_of, perm, psum_part, psum, aux, status, (cudaStream_t)stream);
+}

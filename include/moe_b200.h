@@ -154,6 +154,27 @@ int moe_b200_dispatch(const void* x, const int32_t* idx,
 
 size_t moe_b200_dispatch_scratch_bytes(int64_t N, int E, int k);
 
+/* moe_b200_dispatch for callers that cannot give it a scratch buffer because
+ * they may not allocate device memory where they call from (a forward hook
+ * under a frozen memory pool, a serving loop whose allocator is locked while
+ * requests are in flight, a language binding that only sees the op's own
+ * tensors). No counterpart in the reference. Same arguments and results as
+ * moe_b200_dispatch without `scratch`: the counters live in a 1 MiB array
+ * built into the library (held by every GPU that loads it until the process
+ * exits). It allocates nothing and calls no allocating routine.
+ *   - Limit: moe_b200_dispatch_scratch_bytes(N,E,k) <= 1 MiB (e.g. N=65536,
+ *     E=64, k=4 fits); larger shapes return MOE_B200_ERR_WORKSPACE.
+ *   - The first call on each device looks up the array's device address; make
+ *     that call before any stream capture starts.
+ *   - All calls on one GPU share the array; it needs no clearing between
+ *     calls, but calls whose kernels overlap on the GPU race on it. */
+int moe_b200_dispatch_static(const void* x, const int32_t* idx,
+                             int64_t N, int d, int E, int k, int dtype,
+                             int32_t* cnt_slot, int32_t* offsets,
+                             int32_t* row_of, void* perm,
+                             const float* psum_part, float* psum, float* aux,
+                             int32_t* status, void* stream);
+
 /* Part 3 — experts: for every expert e and its rows [offsets[e], offsets[e+1])
  * of perm: h = gelu_tanh(x W1g^T + b1g) * (x W1u^T + b1u), y = h W2^T + b2
  * (FeedForward.forward, model.py:173-190 with fine_tuning=False, dropout in
