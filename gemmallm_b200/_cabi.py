@@ -7,9 +7,11 @@ fallback and importing this module raises. Build it with
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libmoe_b200.so"
+# MOE_B200_LIB selects another build of the same library (e.g. an instrumented one)
+LIB_PATH = Path(os.environ.get("MOE_B200_LIB") or Path(__file__).resolve().parent / "libmoe_b200.so")
 
 F32, BF16 = 0, 1
 FLAG_DEFAULT, FLAG_SIMT_EXPERTS, FLAG_NO_DECODE_PATH = 0, 1, 2
@@ -17,7 +19,7 @@ DEV_OK, DEV_TIMEOUT, DEV_BAD_INDEX = 0, 1, 2
 
 WS_NAMES = (
     "status", "logits", "idx", "w", "psum_part", "psum", "aux", "scratch",
-    "cnt_slot", "offsets", "row_of", "perm", "h", "y",
+    "cnt_slot", "offsets", "row_of", "perm", "h", "y", "part",
 )
 WS_NUM = len(WS_NAMES)
 
@@ -39,6 +41,11 @@ SIGNATURES = {
     "moe_b200_dispatch_static": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                                       _vp, _vp, _vp]),
     "moe_b200_experts": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "moe_b200_experts_decode": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "moe_b200_decode_splits": (_i, [_i]),
+    "moe_b200_decode_max_rows": (_i64, []),
+    "moe_b200_combine_decode": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _vp, _i64, _i, _i, _vp,
+                                     _vp]),
     "moe_b200_combine": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "moe_b200_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _sz,
                               _vp, _vp]),

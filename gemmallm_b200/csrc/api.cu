@@ -54,6 +54,8 @@ static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off
   sizes[MOE_B200_WS_PERM] = M * d * es;
   sizes[MOE_B200_WS_H] = M * f * es;
   sizes[MOE_B200_WS_Y] = M * d * es;
+  sizes[MOE_B200_WS_PART] =
+      (dtype == MOE_B200_BF16 && M <= kDecodeMaxRows) ? (size_t)decode_splits(f) * M * d * sizeof(float) : 0;
   size_t pos = 0;
   for (int i = 0; i < MOE_B200_WS_NUM; ++i) {
     off[i] = pos;
@@ -90,7 +92,7 @@ int moe_b200_workspace_layout(int64_t N, int d, int f, int E, int k, int dtype, 
 
 size_t moe_b200_plan_bytes(int E) {
   if (E < 1 || E > kMaxExperts) return 0;
-  return plan_ptr_bytes(E) + (size_t)2 * E * 128;
+  return plan_ptr_bytes(E) + (size_t)kPlanMapsPerExpert * E * 128;
 }
 
 int moe_b200_plan_build(const void* const* h_W1, const void* const* h_b1, const void* const* h_W2,
@@ -183,6 +185,34 @@ int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
   return launch_experts_simt(perm, offsets, plan, M, d, f, E, dtype, h, y, (cudaStream_t)stream);
 }
 
+int moe_b200_decode_splits(int f) { return f >= 8 ? decode_splits(f) : 0; }
+
+int64_t moe_b200_decode_max_rows(void) { return kDecodeMaxRows; }
+
+int moe_b200_experts_decode(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
+                            int d, int f, int E, void* h, float* part, int32_t* status,
+                            void* stream) {
+  int rc = check_shape(0, d, f, E, 1, MOE_B200_BF16);
+  if (rc) return rc;
+  if (M < 0 || M > kDecodeMaxRows) return set_error(MOE_B200_ERR_SHAPE, "M exceeds the small-N path's row limit");
+  if (M == 0) return 0;
+  if (!perm || !offsets || !plan || !h || !part || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(perm) || !aligned16(h) || !aligned16(part)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  return launch_experts_tc_decode(perm, offsets, plan, M, d, f, E, h, part, status, (cudaStream_t)stream);
+}
+
+int moe_b200_combine_decode(const float* part, int ksplit, int64_t M, const int32_t* row_of,
+                            const int32_t* idx, const float* w, const void* plan, int E,
+                            const void* residual, int64_t N, int d, int k, void* out, void* stream) {
+  int rc = check_shape(N, d, 8, E, k, MOE_B200_BF16);
+  if (rc) return rc;
+  if (N == 0) return 0;
+  if (!part || !row_of || !idx || !w || !plan || !out) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (ksplit < 1 || ksplit > 8 || M < 0) return set_error(MOE_B200_ERR_SHAPE, "ksplit or M out of range");
+  if (!aligned16(part) || !aligned16(out) || !aligned16(residual)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  return launch_combine_decode(part, ksplit, M, row_of, idx, w, plan, E, residual, N, d, k, out, (cudaStream_t)stream);
+}
+
 int moe_b200_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
                      int64_t N, int d, int k, int dtype, void* out, void* stream) {
   int rc = check_shape(N, d, 8, k, k, dtype);
@@ -220,7 +250,10 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   void* perm = ws + off[MOE_B200_WS_PERM];
   void* h = ws + off[MOE_B200_WS_H];
   void* y = ws + off[MOE_B200_WS_Y];
+  float* part = reinterpret_cast<float*>(ws + off[MOE_B200_WS_PART]);
   cudaStream_t s = (cudaStream_t)stream;
+  const bool small_n = dtype == MOE_B200_BF16 && N * k <= kDecodeMaxRows &&
+                       !(flags & (MOE_B200_FLAG_SIMT_EXPERTS | MOE_B200_FLAG_NO_DECODE_PATH));
 
   MOE_CUDA_CHECK(cudaMemsetAsync(status, 0, 16 * sizeof(int32_t), s));
   rc = moe_b200_router(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, psum_part, status, stream);
@@ -228,6 +261,13 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   rc = moe_b200_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
                          N > 0 ? psum_part : nullptr, psum, aux, status, stream);
   if (rc) return rc;
+  if (small_n) {
+    // few tokens per expert: weight streaming with narrow tiles and split-K
+    rc = moe_b200_experts_decode(perm, offsets, plan, N * k, d, f, E, h, part, status, stream);
+    if (rc) return rc;
+    return moe_b200_combine_decode(part, decode_splits(f), N * k, row_of, idx, w, plan, E, residual,
+                                   N, d, k, out, stream);
+  }
   rc = moe_b200_experts(perm, offsets, plan, N * k, d, f, E, dtype, flags, h, y, status, stream);
   if (rc) return rc;
   return moe_b200_combine(y, row_of, w, residual, N, d, k, dtype, out, stream);

@@ -45,7 +45,70 @@ combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ row_of,
   store8(out + t * d + c, acc);
 }
 
+// Small-N variant: the down product arrives as `ksplit` fp32 partial buffers
+// part[s][M][d] without bias; sum them in order s = 0..ksplit-1, add the
+// expert's down.bias, then weight and add as above.
+__global__ void __launch_bounds__(256)
+combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_stride,
+                      const int32_t* __restrict__ row_of, const int32_t* __restrict__ idx,
+                      const float* __restrict__ w, const void* const* __restrict__ b2,
+                      const __nv_bfloat16* __restrict__ residual, int64_t N, int d, int k,
+                      __nv_bfloat16* __restrict__ out) {
+  const int pieces = d >> 3;
+  const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= N * pieces) return;
+  const int64_t t = item / pieces;
+  const int c = (int)(item - t * pieces) << 3;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int j = 0; j < k; ++j) {
+    const int row = __ldg(&row_of[t * k + j]);
+    if (row < 0) continue;
+    const int e = __ldg(&idx[t * k + j]);
+    const float wj = __ldg(&w[t * k + j]);
+    float v[8];
+    load8_ldg(static_cast<const __nv_bfloat16*>(b2[e]) + c, v);
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = 0.f;
+    for (int sp = 0; sp < ksplit; ++sp) {
+      float pv[8];
+      load8(part + (int64_t)sp * part_stride + (int64_t)row * d + c, pv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s[i] += pv[i];
+    }
+    // the expert's output is rounded to bf16 before weighting, as on the large-N path
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float yv = __bfloat162float(__float2bfloat16_rn(s[i] + v[i]));
+      acc[i] = __fadd_rn(acc[i], __fmul_rn(wj, yv));
+    }
+  }
+  if (residual != nullptr) {
+    float r[8];
+    load8(residual + t * d + c, r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
+  }
+  store8(out + t * d + c, acc);
+}
+
 }  // namespace
+
+int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_t* row_of,
+                          const int32_t* idx, const float* w, const void* plan, int E,
+                          const void* residual, int64_t N, int d, int k, void* out, cudaStream_t s) {
+  if (N == 0) return 0;
+  PlanView pv = plan_view(plan, E);
+  const int64_t items = N * (d >> 3);
+  const int64_t blocks = (items + 255) / 256;
+  combine_decode_kernel<<<(unsigned)blocks, 256, 0, s>>>(
+      part, ksplit, M * (int64_t)d, row_of, idx, w, pv.b2,
+      static_cast<const __nv_bfloat16*>(residual), N, d, k, static_cast<__nv_bfloat16*>(out));
+  MOE_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 int launch_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
                    int64_t N, int d, int k, int dtype, void* out, cudaStream_t s) {

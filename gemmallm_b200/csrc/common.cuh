@@ -15,8 +15,11 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
 
 // Tokens per router block and per dispatch chunk. Both kernels partition the
 // token range the same way, in token order.
-constexpr int kRouterTokensPerBlock = 32;
-constexpr int kDispatchChunk = 128;
+constexpr int kRouterTokensPerBlock = 64;
+constexpr int kDispatchChunk = 64;
+
+// The small-N (weight-streaming) expert path is taken up to this many sorted rows (N*k).
+constexpr int64_t kDecodeMaxRows = 256;
 
 int set_error(int code, const char* msg);
 int cuda_error(cudaError_t e, const char* where);
@@ -109,7 +112,8 @@ __device__ __forceinline__ float gelu_tanh_fast(float g) {
 
 // Plan buffer layout (device memory owned by the caller).
 //   [0, 4*E*8)            : W1[E], b1[E], W2[E], b2[E] device pointers
-//   then, 128-byte aligned: tensor maps W1[E], W2[E] (128 bytes each)
+//   then, 128-byte aligned: tensor maps (128 bytes each) W1[E], W2[E] with
+//   128-row boxes, then W1[E], W2[E] with 64-row boxes for the small-N path
 struct PlanView {
   const void* const* W1;
   const void* const* b1;
@@ -117,7 +121,10 @@ struct PlanView {
   const void* const* b2;
   const void* tmap_W1;  // CUtensorMap[E]
   const void* tmap_W2;  // CUtensorMap[E]
+  const void* tmap_W1_dec;
+  const void* tmap_W2_dec;
 };
+constexpr int kPlanMapsPerExpert = 4;
 __host__ __device__ inline size_t plan_ptr_bytes(int E) {
   return ((size_t)4 * E * sizeof(void*) + 127) & ~(size_t)127;
 }
@@ -130,6 +137,8 @@ __host__ __device__ inline PlanView plan_view(const void* plan, int E) {
   v.b2 = v.W2 + E;
   v.tmap_W1 = p + plan_ptr_bytes(E);
   v.tmap_W2 = p + plan_ptr_bytes(E) + (size_t)128 * E;
+  v.tmap_W1_dec = p + plan_ptr_bytes(E) + (size_t)128 * 2 * E;
+  v.tmap_W2_dec = p + plan_ptr_bytes(E) + (size_t)128 * 3 * E;
   return v;
 }
 
@@ -148,6 +157,15 @@ int launch_experts_tc(const void* perm, const int32_t* offsets, const void* plan
 int launch_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
                    int64_t N, int d, int k, int dtype, void* out, cudaStream_t s);
 int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, int E, int d, int f,
-                             void* h_tmaps /* 2*E*128 bytes */);
+                             void* h_tmaps /* kPlanMapsPerExpert*E*128 bytes */);
+int encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+int sm_count(int* sms);
+int decode_splits(int f);
+int launch_experts_tc_decode(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
+                             int d, int f, int E, void* h, float* part, int32_t* status,
+                             cudaStream_t s);
+int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_t* row_of,
+                          const int32_t* idx, const float* w, const void* plan, int E,
+                          const void* residual, int64_t N, int d, int k, void* out, cudaStream_t s);
 
 }  // namespace moe

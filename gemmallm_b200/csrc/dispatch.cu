@@ -91,10 +91,29 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
     }
   }
   __syncthreads();
-  if (tid == 0) {
-    int acc = 0;
-    for (int e = 0; e < E; ++e) { s_off[e] = acc; acc += s_hist[e]; }
-    s_off[E] = acc;
+  if (tid < 32) {
+    // exclusive scan over E <= 256 experts by one warp: 8 consecutive experts per lane
+    int loc[kMaxExperts / 32];
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) {
+      int e = tid * (kMaxExperts / 32) + i;
+      loc[i] = sum;
+      sum += e < E ? s_hist[e] : 0;
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (tid >= o) incl += v;
+    }
+    const int excl = incl - sum;
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) {
+      int e = tid * (kMaxExperts / 32) + i;
+      if (e < E) s_off[e] = excl + loc[i];
+    }
+    if (tid == 31) s_off[E] = incl;
   }
   __syncthreads();
   if (blockIdx.x == 0)
@@ -130,31 +149,34 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
       }
     }
     __syncthreads();
-    // copy rows: one warp per token, 16-byte pieces, 4 loads in flight per lane
+    // copy rows: the chunk's 16-byte pieces are spread over the block, 8 loads
+    // in flight per thread; each piece is stored once per slot
     constexpr int kVec = 16 / (int)sizeof(T);
+    constexpr int kInFlight = 8;
     const int pieces = d / kVec;
-    for (int tl = warp; tl < ntok; tl += kThreads / 32) {
-      const uint4* src = reinterpret_cast<const uint4*>(x + (t0 + tl) * d);
-      for (int i0 = lane; i0 < pieces; i0 += 128) {
-        uint4 v[4];
+    const int items = ntok * pieces;
+    const uint4* src = reinterpret_cast<const uint4*>(x + t0 * d);
+    for (int i0 = tid; i0 < items; i0 += kThreads * kInFlight) {
+      uint4 v[kInFlight];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          int i = i0 + 32 * u;
-          if (i < pieces) v[u] = __ldg(src + i);
-        }
-        for (int j = 0; j < k; ++j) {
-          int row = s_row[tl * k + j];
-          if (row < 0) continue;
-          uint4* dst = reinterpret_cast<uint4*>(perm + (int64_t)row * d);
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < items) v[u] = __ldg(src + i);
+      }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            int i = i0 + 32 * u;
-            if (i < pieces) __stcs(dst + i, v[u]);
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < items) {
+          const int tl = i / pieces, pc = i - tl * pieces;
+          for (int j = 0; j < k; ++j) {
+            const int row = s_row[tl * k + j];
+            if (row >= 0) __stcs(reinterpret_cast<uint4*>(perm + (int64_t)row * d) + pc, v[u]);
           }
         }
       }
     }
     __syncthreads();
+    if (c + G >= nchunk) break;
     // rows of chunks [c, c+G) precede this block's next chunk
     for (int64_t i = tid; i < (int64_t)G * E; i += kThreads) {
       int64_t cc = c + i / E;
@@ -168,12 +190,13 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
   }
 
   // ---- tail: per-slot counts, probability sums, loss ----------------------
-  if (blockIdx.x == 0) {
-    for (int i = tid; i < k * E; i += kThreads) {
-      int acc = 0;
-      for (int b = 0; b < G; ++b) acc += __ldcg(&blk_slot[(size_t)b * k * E + i]);
-      cnt_slot[i] = acc;
-    }
+  // per-slot counts: entry i = (slot, expert) is summed over the blocks by one warp
+  for (int i = blockIdx.x * (kThreads / 32) + warp; i < k * E; i += G * (kThreads / 32)) {
+    int acc = 0;
+    for (int b = lane; b < G; b += 32) acc += __ldcg(&blk_slot[(size_t)b * k * E + i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) cnt_slot[i] = acc;
   }
   if (psum_part == nullptr) return;
   for (int e = blockIdx.x; e < E; e += G) {

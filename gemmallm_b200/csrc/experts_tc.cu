@@ -12,27 +12,34 @@
 //   warp 1   : MMA issuer    (tcgen05.mma cta_group::1 kind::f16, M=128 N=256 K=16)
 //   warps 2-5: epilogue      (tcgen05.ld 32 lanes x 32 columns, bias, GeGLU, store)
 // The 512 TMEM columns hold two 128x256 fp32 accumulators, so the epilogue of
-// one tile runs under the main loop of the next. No TMA load uses cluster
-// multicast. Every wait is bounded: when one runs out the CTA records
-// MOE_B200_DEV_TIMEOUT in the status word, stops issuing, frees its TMEM and
-// returns.
+// one tile runs under the main loop of the next.
+//
+// No TMA load uses cluster multicast. Every wait is bounded: when one runs out
+// the CTA records MOE_B200_DEV_TIMEOUT in the status word, stops issuing, frees
+// its TMEM and returns.
+//
+// The small-N ("decode") arrangement of the same products is in
+// experts_decode.cu.
 #include <cuda.h>
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace moe {
 
 namespace {
 
-constexpr int BM = 128;          // rows of the sorted buffer per tile
+using namespace tc;
+
+constexpr int BM = 128;          // rows of the sorted buffer per tile = TMEM lanes
 constexpr int BK = 64;           // bf16 elements = one 128-byte swizzle row
-constexpr int BNB = 256;         // B rows per tile (gate 128 + up 128, or 256 plain)
+constexpr int BN = 256;          // weight rows per tile (gate 128 + up 128, or 256 plain)
 constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2;          // 16 KiB
-constexpr int kBHalfBytes = 128 * BK * 2;     // 16 KiB
+constexpr int kBHalfBytes = (BN / 2) * BK * 2;  // 16 KiB
 constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 512;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr int kTmemCols = 2 * BN;             // two accumulators
+constexpr uint32_t kIdesc = make_idesc(BN);
 
 struct Control {
   uint64_t full[kStages];
@@ -42,122 +49,14 @@ struct Control {
   uint32_t tmem_base;
   int abort;
   int tile_start[kMaxExperts + 1];
+  int offsets[kMaxExperts + 1];  // copy of the row offsets: no global loads in the tile loops
 };
 
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + sizeof(Control);
 
-// ---- PTX wrappers ---------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait. False when the limit passed or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Control* ctl,
-                                          int32_t* status, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = global_ns();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 0) {
-      if (*reinterpret_cast<volatile int*>(&ctl->abort)) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
-        *reinterpret_cast<volatile int*>(&ctl->abort) = 1;
-        atomicMax(&status[0], MOE_B200_DEV_TIMEOUT);
-        status[1] = where;
-        status[2] = (int)blockIdx.x;
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, uint64_t* bar, int c0,
-                                            int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0),
-      "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]^T, one 128 x 256 x 16 step
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                       uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
-      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31},"
-      " [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tc_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128
-// bytes apart, 8-row groups 1024 bytes apart (SBO), version 1.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t desc = 0;
-  desc |= (uint64_t)((saddr & 0x3ffffu) >> 4);   // bits [0,14)  start address / 16
-  desc |= (uint64_t)1 << 16;                     // bits [16,30) leading byte offset / 16 (unused)
-  desc |= (uint64_t)(1024 >> 4) << 32;           // bits [32,46) stride byte offset / 16
-  desc |= (uint64_t)1 << 46;                     // bits [46,48) descriptor version
-  desc |= (uint64_t)2 << 61;                     // bits [61,64) SWIZZLE_128B
-  return desc;
-}
-// Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M=128, N=256.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) |
-                            ((128u >> 4) << 24);
-
+// GEGLU : B = gate rows [n0, n0+128) and up rows [Nout+n0, ...) of W [2*Nout, K];
+//         out[row, n0..n0+128) = gelu_tanh(gate + bg) * (up + bu).
+// plain : B = rows [n0, n0+256) of W [Nout, K]; out[row, n0..n0+256) = acc + bias.
 template <bool GEGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -165,6 +64,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const int32_t* __restrict__ offsets,
                        const void* const* __restrict__ bias_ptrs, int E, int K, int Nout,
                        __nv_bfloat16* __restrict__ out, int32_t* __restrict__ status) {
+#ifdef MOE_TC_PROFILE
+  const long long prof_entry = clock64();
+  constexpr int kProfBase = GEGLU ? 0 : 8;
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -172,7 +75,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr int kTileN = GEGLU ? 128 : 256;  // output columns per tile
+  constexpr int kTileN = GEGLU ? BN / 2 : BN;  // output columns per tile
   const int n_tiles = (Nout + kTileN - 1) / kTileN;
   const int k_blocks = (K + BK - 1) / BK;
 
@@ -181,10 +84,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 128); }
     ctl->abort = 0;
     int acc = 0;
+    int beg = offsets[0];
+    ctl->offsets[0] = beg;
     for (int e = 0; e < E; ++e) {
       ctl->tile_start[e] = acc;
-      int cnt = offsets[e + 1] - offsets[e];
-      acc += ((cnt + BM - 1) / BM) * n_tiles;
+      const int end = offsets[e + 1];
+      ctl->offsets[e + 1] = end;
+      acc += ((end - beg + BM - 1) / BM) * n_tiles;
+      beg = end;
     }
     ctl->tile_start[E] = acc;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -202,7 +109,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
   const int total_tiles = ctl->tile_start[E];
+#ifdef MOE_TC_PROFILE
+  const long long prof_kernel_t0 = clock64();
+  if (blockIdx.x == 0 && threadIdx.x == 0) g_prof[6 + kProfBase] = prof_kernel_t0 - prof_entry;
+#endif
 
+  // tile t of expert e: local = mt * n_tiles + nt
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -214,12 +126,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         while (t >= ctl->tile_start[e + 1]) ++e;
         const int local = t - ctl->tile_start[e];
         const int mt = local / n_tiles, nt = local - mt * n_tiles;
-        const int row0 = offsets[e] + mt * BM;
+        const int row0 = ctl->offsets[e] + mt * BM;
         const int b0 = nt * kTileN;
-        const int b1 = GEGLU ? Nout + nt * kTileN : nt * kTileN + 128;
+        const int b1 = GEGLU ? Nout + nt * kTileN : nt * kTileN + BN / 2;
         const CUtensorMap* tb = tmap_b + e;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, ctl, status, 1)) { ok = false; break; }
+          {
+            PROF_T0();
+            if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort, status, 1)) { ok = false; break; }
+            PROF_ADD(0);
+          }
           uint8_t* sa = smem + (size_t)stage * kStageBytes;
           mbar_expect_tx(&ctl->full[stage], kStageBytes);
           tma_load_2d(sa, &tmap_a, &ctl->full[stage], kb * BK, row0);
@@ -239,11 +155,19 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
         const int a = it & 1;
-        if (!mbar_wait(&ctl->tmem_empty[a], acc_phase ^ 1u, ctl, status, 2)) { ok = false; break; }
+        {
+          PROF_T0();
+          if (!mbar_wait(&ctl->tmem_empty[a], acc_phase ^ 1u, &ctl->abort, status, 2)) { ok = false; break; }
+          PROF_ADD(1);
+        }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)a * 256u;
+        const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&ctl->full[stage], phase, ctl, status, 3)) { ok = false; break; }
+          {
+            PROF_T0();
+            if (!mbar_wait(&ctl->full[stage], phase, &ctl->abort, status, 3)) { ok = false; break; }
+            PROF_ADD(2);
+          }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
           const uint64_t adesc = make_smem_desc(sa);
@@ -274,22 +198,25 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       while (t >= ctl->tile_start[e + 1]) ++e;
       const int local = t - ctl->tile_start[e];
       const int mt = local / n_tiles, nt = local - mt * n_tiles;
-      const int seg_beg = offsets[e], seg_end = offsets[e + 1];
-      const int row = seg_beg + mt * BM + r;
-      const bool row_ok = row < seg_end;
+      const int row = ctl->offsets[e] + mt * BM + r;
+      const bool row_ok = row < ctl->offsets[e + 1];
       const int n0 = nt * kTileN;
       const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(bias_ptrs[e]);
       const int a = it & 1;
-      if (!mbar_wait(&ctl->tmem_full[a], acc_phase, ctl, status, 4)) { ok = false; break; }
+      {
+        PROF_T0();
+        if (!mbar_wait(&ctl->tmem_full[a], acc_phase, &ctl->abort, status, 4)) { ok = false; break; }
+        if (threadIdx.x == 64) PROF_ADD(3);
+      }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)a * 256u;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
       __nv_bfloat16* orow = out + (int64_t)row * Nout + n0;
       if (GEGLU) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kTileN / 32; ++c) {
           uint32_t g[32], u[32];
           tc_ld32(taddr + c * 32, g);
-          tc_ld32(taddr + 128 + c * 32, u);
+          tc_ld32(taddr + BN / 2 + c * 32, u);
           tc_ld_wait();
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -310,7 +237,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < kTileN / 32; ++c) {
           uint32_t v[32];
           tc_ld32(taddr + c * 32, v);
           tc_ld_wait();
@@ -333,6 +260,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
+#ifdef MOE_TC_PROFILE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    g_prof[4 + kProfBase] = clock64() - prof_kernel_t0;
+    g_prof[5 + kProfBase] = total_tiles;
+  }
+#endif
   // ---------------- teardown ----------------
   __syncwarp();
   if (*reinterpret_cast<volatile int*>(&ctl->abort)) {
@@ -350,91 +283,51 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-// ---- host side --------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-            cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-    else
-      (void)cudaGetLastError();
+template <bool GEGLU>
+int launch_one(const CUtensorMap& tm_a, const void* tmap_b, const int32_t* offsets,
+               const void* const* bias, int E, int K, int Nout, void* out, int32_t* status,
+               int sms, cudaStream_t s) {
+  static bool attr_set = false;
+  auto fn = grouped_gemm_tc_kernel<GEGLU>;
+  if (!attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)kSmemBytes));
+    attr_set = true;
   }
-  return fn;
-}
-
-// [rows, cols] row-major bf16, box = 128 rows x 64 columns, 128-byte swizzle.
-int encode_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols) {
-  EncodeTiledFn enc = get_encode();
-  if (enc == nullptr) return set_error(MOE_B200_ERR_DRIVER, "cuTensorMapEncodeTiled unavailable");
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {BK, 128};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
-                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return set_error(MOE_B200_ERR_DRIVER, "cuTensorMapEncodeTiled failed");
+  fn<<<sms, kThreads, kSmemBytes, s>>>(tm_a, static_cast<const CUtensorMap*>(tmap_b), offsets, bias,
+                                       E, K, Nout, static_cast<__nv_bfloat16*>(out), status);
+  MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
-
-bool g_attr_set = false;
 
 }  // namespace
-
-int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, int E, int d, int f,
-                             void* h_tmaps) {
-  static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
-  CUtensorMap* maps = static_cast<CUtensorMap*>(h_tmaps);
-  for (int e = 0; e < E; ++e) {
-    int rc = encode_2d(&maps[e], h_W1[e], (uint64_t)2 * f, (uint64_t)d);
-    if (rc) return rc;
-    rc = encode_2d(&maps[E + e], h_W2[e], (uint64_t)d, (uint64_t)f);
-    if (rc) return rc;
-  }
-  return 0;
-}
 
 int launch_experts_tc(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                       int f, int E, void* h, void* y, int32_t* status, cudaStream_t s) {
   if (M == 0) return 0;
-  if (!g_attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_tc_kernel<true>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)kSmemBytes));
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_tc_kernel<false>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)kSmemBytes));
-    g_attr_set = true;
-  }
   PlanView pv = plan_view(plan, E);
   alignas(64) CUtensorMap tm_x, tm_h;
-  int rc = encode_2d(&tm_x, perm, (uint64_t)M, (uint64_t)d);
+  int rc = encode_tmap_2d(&tm_x, perm, (uint64_t)M, (uint64_t)d, BM);
   if (rc) return rc;
-  rc = encode_2d(&tm_h, h, (uint64_t)M, (uint64_t)f);
+  rc = encode_tmap_2d(&tm_h, h, (uint64_t)M, (uint64_t)f, BM);
   if (rc) return rc;
-  int dev = 0, sms = 0;
-  MOE_CUDA_CHECK(cudaGetDevice(&dev));
-  MOE_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  grouped_gemm_tc_kernel<true><<<sms, kThreads, kSmemBytes, s>>>(
-      tm_x, static_cast<const CUtensorMap*>(pv.tmap_W1), offsets, pv.b1, E, d, f,
-      static_cast<__nv_bfloat16*>(h), status);
-  MOE_CUDA_CHECK(cudaGetLastError());
-  grouped_gemm_tc_kernel<false><<<sms, kThreads, kSmemBytes, s>>>(
-      tm_h, static_cast<const CUtensorMap*>(pv.tmap_W2), offsets, pv.b2, E, f, d,
-      static_cast<__nv_bfloat16*>(y), status);
-  MOE_CUDA_CHECK(cudaGetLastError());
-  return 0;
+  int sms = 0;
+  rc = sm_count(&sms);
+  if (rc) return rc;
+  rc = launch_one<true>(tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, status, sms, s);
+  if (rc) return rc;
+  return launch_one<false>(tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, y, status, sms, s);
 }
+
+#ifdef MOE_TC_PROFILE
+extern "C" void moe_b200_prof_read(long long* out, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, tc::g_prof, sizeof(long long) * 16);
+  if (reset) {
+    long long z[16] = {0};
+    cudaMemcpyToSymbol(tc::g_prof, z, sizeof(z));
+  }
+}
+#endif
 
 }  // namespace moe

@@ -1,12 +1,18 @@
-// Router kernel: logits = x Wg^T + bg in fp32, softmax, top-k, renormalise.
-// Covers reference model.py:206-223 (gate Linear, F.softmax, topk, score
+// Router kernels: logits = x Wg^T + bg in fp32, softmax, top-k, renormalise.
+// Cover reference model.py:206-223 (gate Linear, F.softmax, topk, score
 // renormalisation) and the per-expert probability sums of model.py:215.
 //
 // HBM-bound: x [N,d] is read once; Wg [E,d] stays in L1/L2. A block of four
-// warps owns 32 consecutive tokens. Each warp computes the logits of four
-// tokens at a time (so every Wg register is used four times), eight experts
-// per pass, with 16-byte loads and a warp-shuffle reduction, then does
-// softmax/top-k for its tokens with one expert slice per lane.
+// warps owns 64 consecutive tokens.
+//   bf16: router_mma_kernel. Each warp owns 16 tokens and forms their logits
+//     with mma.sync m16n8k16 (bf16 products are exact in fp32, accumulation in
+//     fp32). Operands go from global memory straight into fragment registers
+//     with 16-byte loads: the contraction index inside each 32-element chunk is
+//     permuted the same way for x and Wg, which a dot product does not notice.
+//     Then one lane per token does softmax / top-k serially over the E logits.
+//   fp32: router_kernel. CUDA-core FMA (TF32 would perturb the logits), four
+//     tokens x eight experts per warp pass, warp-shuffle reductions, softmax and
+//     top-k with one expert slice per lane.
 #include "common.cuh"
 
 namespace moe {
@@ -14,7 +20,7 @@ namespace moe {
 namespace {
 
 constexpr int kWarps = 4;
-constexpr int kTokPerWarp = kRouterTokensPerBlock / kWarps;  // 8
+constexpr int kTokPerWarp = kRouterTokensPerBlock / kWarps;  // 16
 constexpr int kTokGroup = 4;
 constexpr int kExpGroup = 8;
 
@@ -25,7 +31,7 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ Wg, const T* __rest
               int32_t* __restrict__ out_idx, float* __restrict__ out_w,
               float* __restrict__ psum_part) {
   extern __shared__ float smem[];
-  float* s_logits = smem;                                     // [32][E]
+  float* s_logits = smem;                                     // [64][E]
   float* s_psum = smem + (size_t)kRouterTokensPerBlock * E;   // [kWarps][E]
 
   const int warp = threadIdx.x >> 5;
@@ -182,6 +188,173 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ Wg, const T* __rest
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// bf16 path
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kMmaTokPerWarp = 16;
+constexpr int kMmaUnroll = 4;  // 32-element chunks in flight per lane
+
+// NT = n-tiles (of 8 experts) per pass over x; E > 8*NT makes more passes.
+template <int NT>
+__global__ void __launch_bounds__(kWarps * 32)
+router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ Wg,
+                  const __nv_bfloat16* __restrict__ bg, int64_t N, int d, int E, int k,
+                  float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
+                  float* __restrict__ out_w, float* __restrict__ psum_part) {
+  extern __shared__ float smem[];
+  const int ld = E + 1;                                           // row pitch: no bank conflicts
+  float* s_logits = smem;                                          // [64][E+1]
+  float* s_psum = smem + (size_t)kRouterTokensPerBlock * ld;       // [kWarps][E]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t tok0 = (int64_t)blockIdx.x * kRouterTokensPerBlock + warp * kMmaTokPerWarp;
+  const int nvalid = (int)(N - tok0 < kMmaTokPerWarp ? (N - tok0 > 0 ? N - tok0 : 0) : kMmaTokPerWarp);
+  float* my_logits = s_logits + (size_t)warp * kMmaTokPerWarp * ld;
+
+  if (nvalid > 0) {
+    const int row_pieces = d >> 3;  // 16-byte pieces per row
+    const int64_t ra = tok0 + g < N ? tok0 + g : N - 1;
+    const int64_t rb = tok0 + g + 8 < N ? tok0 + g + 8 : N - 1;
+    const uint4* xa = reinterpret_cast<const uint4*>(x + ra * d);
+    const uint4* xb = reinterpret_cast<const uint4*>(x + rb * d);
+    const uint4* w4 = reinterpret_cast<const uint4*>(Wg);
+    const int nchunk = (d + 31) >> 5;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int e_base = 0; e_base < E; e_base += 8 * NT) {
+      float acc[NT][4];
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+      for (int c0 = 0; c0 < nchunk; c0 += kMmaUnroll) {
+        uint4 A[kMmaUnroll], B[kMmaUnroll];
+#pragma unroll
+        for (int u = 0; u < kMmaUnroll; ++u) {
+          const int piece = 4 * (c0 + u) + t;
+          const bool ok = piece < row_pieces;
+          A[u] = ok ? xa[piece] : zero;
+          B[u] = ok ? xb[piece] : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kMmaUnroll; ++u) {
+          const int piece = 4 * (c0 + u) + t;
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            const int row = e_base + 8 * j + g;
+            const uint4 w = (row < E && piece < row_pieces)
+                                ? __ldg(w4 + (size_t)row * row_pieces + piece) : zero;
+            mma_bf16_16816(acc[j], A[u].x, B[u].x, A[u].y, B[u].y, w.x, w.y);
+            mma_bf16_16816(acc[j], A[u].z, B[u].z, A[u].w, B[u].w, w.z, w.w);
+          }
+        }
+      }
+      // accumulator layout: c0,c1 -> token g, experts 2t,2t+1; c2,c3 -> token g+8
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int e = e_base + 8 * j + 2 * t;
+        if (e < E) {
+          const float b = __bfloat162float(bg[e]);
+          my_logits[g * ld + e] = acc[j][0] + b;
+          my_logits[(g + 8) * ld + e] = acc[j][2] + b;
+        }
+        if (e + 1 < E) {
+          const float b = __bfloat162float(bg[e + 1]);
+          my_logits[g * ld + e + 1] = acc[j][1] + b;
+          my_logits[(g + 8) * ld + e + 1] = acc[j][3] + b;
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (out_logits != nullptr) {
+    for (int i = lane; i < nvalid * E; i += 32) {
+      const int tl = i / E, e = i - tl * E;
+      out_logits[tok0 * E + i] = my_logits[tl * ld + e];
+    }
+  }
+  __syncwarp();
+
+  // ---- one lane per token: softmax, top-k by (logit desc, index asc), renormalise ----
+  if (lane < nvalid) {
+    float* lg = my_logits + lane * ld;
+    float m = -INFINITY;
+    for (int e = 0; e < E; ++e) m = fmaxf(m, lg[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) sum += expf(lg[e] - m);
+    int sel[kMaxTopK];
+    float sl[kMaxTopK], vals[kMaxTopK];
+    float total = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; ++j) {
+      if (j < k) {
+        float bl = -INFINITY;
+        int be = 0;
+        for (int e = 0; e < E; ++e) {
+          const float v = lg[e];
+          if (v > bl) { bl = v; be = e; }   // strict: the lowest index wins among equals
+        }
+        sel[j] = be;
+        sl[j] = bl;
+        vals[j] = expf(bl - m) / sum;
+        total += vals[j];                    // left-to-right sum, as model.py:221
+        lg[be] = -INFINITY;                  // taken
+      }
+    }
+    const int64_t tok = tok0 + lane;
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; ++j) {
+      if (j < k) {
+        lg[sel[j]] = sl[j];
+        out_idx[tok * k + j] = sel[j];
+        out_w[tok * k + j] = vals[j] / total;
+      }
+    }
+    for (int e = 0; e < E; ++e) lg[e] = expf(lg[e] - m) / sum;  // probabilities, in place
+  }
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) {
+    float s = 0.f;
+    for (int tl = 0; tl < nvalid; ++tl) s += my_logits[tl * ld + e];
+    s_psum[warp * E + e] = s;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) s += s_psum[w * E + e];
+    psum_part[(size_t)blockIdx.x * E + e] = s;
+  }
+}
+
+template <int NT>
+int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+               float* out_logits, int32_t* out_idx, float* out_w, float* psum_part, cudaStream_t s) {
+  const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
+  const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E);
+  static bool attr_set = false;
+  if (smem > 48 * 1024 && !attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(router_mma_kernel<NT>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    attr_set = true;
+  }
+  router_mma_kernel<NT><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
+      static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part);
+  MOE_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace
 
 int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
@@ -192,9 +365,10 @@ int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int 
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
   const size_t smem = sizeof(float) * (size_t)(kRouterTokensPerBlock + kWarps) * E;
   if (dtype == MOE_B200_BF16) {
-    router_kernel<__nv_bfloat16><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
-        static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part);
+    if (E <= 8) return launch_mma<1>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
+    if (E <= 16) return launch_mma<2>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
+    if (E <= 32) return launch_mma<4>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
+    return launch_mma<8>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
   } else {
     router_kernel<float><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
         static_cast<const float*>(x), static_cast<const float*>(Wg), static_cast<const float*>(bg),

@@ -1,0 +1,140 @@
+// PTX wrappers shared by the tensor-core kernels: mbarrier, TMA tile loads,
+// tcgen05 (MMA, commit, TMEM loads, fences) and the shared-memory matrix
+// descriptor for K-major tiles with the 128-byte swizzle.
+#pragma once
+#include <cuda.h>
+#include "common.cuh"
+
+namespace moe {
+namespace tc {
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+#ifdef MOE_TC_PROFILE
+static __device__ long long g_prof[16];
+#endif
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#ifdef MOE_TC_PROFILE
+#define PROF_T0() long long prof_t0 = clock64()
+#define PROF_ADD(slot) do { if (blockIdx.x == 0) atomicAdd((unsigned long long*)&g_prof[(slot) + kProfBase], (unsigned long long)(clock64() - prof_t0)); } while (0)
+#else
+#define PROF_T0()
+#define PROF_ADD(slot)
+#endif
+
+// Bounded wait. False when the limit passed or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* abort_flag,
+                                          int32_t* status, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*reinterpret_cast<volatile int*>(abort_flag)) return false;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        *reinterpret_cast<volatile int*>(abort_flag) = 1;
+        atomicMax(&status[0], MOE_B200_DEV_TIMEOUT);
+        status[1] = where;
+        status[2] = (int)blockIdx.x;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, uint64_t* bar, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0),
+      "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, one 128 x N x 16 step (N in the instruction descriptor)
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31},"
+      " [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128
+// bytes apart, 8-row groups 1024 bytes apart (SBO), version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((saddr & 0x3ffffu) >> 4);   // bits [0,14)  start address / 16
+  desc |= (uint64_t)1 << 16;                     // bits [16,30) leading byte offset / 16 (unused)
+  desc |= (uint64_t)(1024 >> 4) << 32;           // bits [32,46) stride byte offset / 16
+  desc |= (uint64_t)1 << 46;                     // bits [46,48) descriptor version
+  desc |= (uint64_t)2 << 61;                     // bits [61,64) SWIZZLE_128B
+  return desc;
+}
+
+// Instruction descriptor: fp32 accumulate (bit 4), bf16 x bf16 (bits 7, 10), both
+// operands K-major, N/8 at bit 17, M/16 at bit 24 (M = 128).
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+}  // namespace tc
+}  // namespace moe

@@ -62,7 +62,7 @@ enum {
    * fp32 dtype always uses it). For tests: a second implementation of the same
    * arithmetic to check the tensor-core kernel against. */
   MOE_B200_FLAG_SIMT_EXPERTS = 1,
-  /* never take the small-N weight-streaming path */
+  /* never take the small-N weight-streaming path inside moe_b200_forward */
   MOE_B200_FLAG_NO_DECODE_PATH = 2
 };
 
@@ -82,6 +82,8 @@ enum {
   MOE_B200_WS_PERM,       /* T [N*k, d]    tokens sorted by expert (model.py:248-253) */
   MOE_B200_WS_H,          /* T [N*k, f]    gelu_tanh(gate)*up (model.py:180-182) */
   MOE_B200_WS_Y,          /* T [N*k, d]    expert outputs, sorted order (model.py:184) */
+  MOE_B200_WS_PART,       /* float [splits, N*k, d] split-K partial sums of the small-N path
+                           * (present when N*k <= moe_b200_decode_max_rows(), bf16) */
   MOE_B200_WS_NUM
 };
 
@@ -183,6 +185,27 @@ int moe_b200_dispatch_static(const void* x, const int32_t* idx,
 int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
                      int64_t M, int d, int f, int E, int dtype, int flags,
                      void* h, void* y, int32_t* status, void* stream);
+
+/* Part 3, small-N ("decode") variant, bf16 only, M <= moe_b200_decode_max_rows():
+ * the same products as moe_b200_experts, arranged for weight streaming when
+ * only a few rows reach each expert (the reference runs the same
+ * FeedForward.forward whatever the row count, model.py:256-257). h [M,f] is
+ * written as usual; the down product is split over K into
+ * moe_b200_decode_splits(f) fp32 buffers part[s][M][d] WITHOUT down.bias;
+ * moe_b200_combine_decode sums them. */
+int moe_b200_experts_decode(const void* perm, const int32_t* offsets, const void* plan,
+                            int64_t M, int d, int f, int E, void* h, float* part,
+                            int32_t* status, void* stream);
+int moe_b200_decode_splits(int f);
+int64_t moe_b200_decode_max_rows(void);
+
+/* Parts 4+5 after moe_b200_experts_decode: y = sum_s part[s] + down.bias of
+ * the row's expert (idx), rounded to bf16, then the weighted sum and residual
+ * of moe_b200_combine (model.py:184, 264-271, 319). */
+int moe_b200_combine_decode(const float* part, int ksplit, int64_t M,
+                            const int32_t* row_of, const int32_t* idx, const float* w,
+                            const void* plan, int E, const void* residual,
+                            int64_t N, int d, int k, void* out, void* stream);
 
 /* Parts 4+5 — combine: out[t] = sum_j w[t,j] * y[row_of[t,j]] in slot order
  * in fp32 (model.py:264-271), plus residual[t] when residual is non-NULL (the

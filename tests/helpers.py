@@ -95,3 +95,27 @@ def device_params(params: dict, dtype, dev) -> dict:
 
 def rounded_params(params: dict, dtype) -> dict:
     return {n: synthetic.round_to(t, dtype) for n, t in params.items()}
+
+
+def experts_decode(perm, offsets, plan: Plan):
+    M, d = perm.shape
+    dev = perm.device
+    splits = lib.moe_b200_decode_splits(plan.f)
+    h = torch.empty(M, plan.f, dtype=perm.dtype, device=dev)
+    part = torch.full((splits, M, d), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_experts_decode(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d, plan.f,
+                                      plan.E, h.data_ptr(), part.data_ptr(), status.data_ptr(),
+                                      stream(dev)), "experts_decode")
+    return h, part, status
+
+
+def combine_decode(part, row_of, idx, w, plan: Plan, residual=None):
+    splits, M, d = part.shape
+    N, k = row_of.shape
+    out = torch.empty(N, d, dtype=torch.bfloat16, device=part.device)
+    check(lib.moe_b200_combine_decode(part.data_ptr(), splits, M, row_of.data_ptr(), idx.data_ptr(),
+                                      w.data_ptr(), plan.ptr, plan.E,
+                                      None if residual is None else residual.data_ptr(), N, d, k,
+                                      out.data_ptr(), stream(part.device)), "combine_decode")
+    return out

@@ -35,7 +35,9 @@ def test_version_and_sizes():
     offs = list(lay.values())
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
     assert lib.moe_b200_plan_bytes(8) >= 4 * 8 * 8 + 2 * 8 * 128
-    assert lib.moe_b200_router_blocks(33) == 2
+    assert lib.moe_b200_router_blocks(65) == 2
+    assert lib.moe_b200_decode_splits(4096) == 8 and lib.moe_b200_decode_splits(128) == 1
+    assert lib.moe_b200_decode_max_rows() == 256
     assert lib.moe_b200_dispatch_scratch_bytes(1000, 8, 2) > 0
 
 

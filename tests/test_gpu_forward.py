@@ -20,9 +20,10 @@ def sha(t):
     return hashlib.sha256(t.contiguous().numpy().tobytes()).hexdigest()
 
 
-def build(params, d, E, f, k, dtype, dev):
+def build(params, d, E, f, k, dtype, dev, flags=0):
     m = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda").eval()
     synthetic.load_into(m, params, dtype, dev)
+    m.flags = flags
     return m
 
 
@@ -79,13 +80,16 @@ SMALL = [
 ]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,flags", [(torch.float32, 0), (torch.bfloat16, 0),
+                                         (torch.bfloat16, _cabi.FLAG_NO_DECODE_PATH)])
 @pytest.mark.parametrize("N,d,E,f,k", SMALL)
-def test_small_shapes(cuda_device, N, d, E, f, k, dtype):
+def test_small_shapes(cuda_device, N, d, E, f, k, dtype, flags):
+    """bf16 with N*k <= 256 takes the small-N weight-streaming path unless the
+    flag forbids it; both must meet the same tolerance."""
     params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=N), dtype)
     params["w1"] *= 2.0
     x = synthetic.round_to(synthetic.make_input(N, d, seed=N + 1), dtype)
-    m = build(params, d, E, f, k, dtype, cuda_device)
+    m = build(params, d, E, f, k, dtype, cuda_device, flags)
     check_against_oracle(m, params, x, k, dtype, cuda_device)
     res = synthetic.round_to(synthetic.make_input(N, d, seed=N + 2), dtype)
     check_against_oracle(m, params, x, k, dtype, cuda_device, residual=res)
@@ -131,6 +135,18 @@ def test_c1_full_size_bf16(cuda_device, name):
     if name == "c1_skew":
         share = float(last["cnt_slot"][:, 0].sum()) / (wl.tokens * wl.top_k)
         assert abs(share - pins["expert0_share"]) < 1e-9
+
+
+@pytest.mark.parametrize("name", ["c2_t1", "c2_t8", "c2_t32", "c2_t64"])
+def test_c2_decode_shapes_bf16(cuda_device, name):
+    wl = synthetic.WORKLOADS[name]
+    params = helpers.rounded_params(
+        synthetic.make_params(wl.d_model, wl.n_experts, wl.d_ff, seed=0), torch.bfloat16)
+    x = synthetic.round_to(synthetic.make_input(wl.tokens, wl.d_model, seed=1), torch.bfloat16)
+    m = build(params, wl.d_model, wl.n_experts, wl.d_ff, wl.top_k, torch.bfloat16, cuda_device)
+    res = synthetic.round_to(synthetic.make_input(wl.tokens, wl.d_model, seed=7), torch.bfloat16)
+    check_against_oracle(m, params, x, wl.top_k, torch.bfloat16, cuda_device)
+    check_against_oracle(m, params, x, wl.top_k, torch.bfloat16, cuda_device, residual=res)
 
 
 def test_c4_router_pin(cuda_device):

@@ -165,6 +165,55 @@ def test_experts_bf16(cuda_device, rows, d, f, flags):
     assert (y.float().cpu() - y_ref).norm() <= 2e-2 * y_ref.norm()
 
 
+DECODE_CASES = [
+    ([1, 1], 64, 128), ([0, 2, 0, 5, 1], 72, 264), ([16, 0, 17, 15, 20, 30, 2, 28], 1024, 4096),
+    ([1, 0, 0, 0, 0, 1, 0, 0], 1024, 4096), ([200, 56], 256, 1408), ([130], 128, 512),
+]
+
+
+@pytest.mark.parametrize("rows,d,f", DECODE_CASES)
+def test_experts_decode_path_bf16(cuda_device, rows, d, f):
+    """Small-N path: narrow tiles, split-K partial sums; h and sum(part)+bias
+    against the oracle at the bf16 tolerance, and against the large-N kernels."""
+    params, x, offsets = expert_inputs(rows, d, f, torch.bfloat16, seed=len(rows) + f)
+    dp = helpers.device_params(params, torch.bfloat16, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    xd, od = x.to(torch.bfloat16).to(cuda_device), offsets.to(cuda_device)
+    h, part, status = helpers.experts_decode(xd, od, plan)
+    h2, y2, _ = helpers.experts(xd, od, plan)
+    torch.cuda.synchronize()
+    assert status.cpu().tolist()[0] == 0
+    assert not torch.isnan(part).any()
+    # same products and fp32 accumulation; the MMA operand roles are swapped, so allow an ulp
+    assert (h.float() - h2.float()).abs().max() <= 1e-2 * h2.float().abs().max()
+    M = sum(rows)
+    e_of_row = torch.bucketize(torch.arange(M), offsets.long()[1:], right=True)
+    y = part.sum(0).cpu() + params["b2"][e_of_row]
+    h_ref, y_ref = oracle_experts(params, x, offsets)
+    assert (h.float().cpu() - h_ref).abs().max() <= 2e-2 * h_ref.abs().max()
+    assert (y - y_ref).abs().max() <= 2e-2 * y_ref.abs().max()
+    assert (y - y2.float().cpu()).abs().max() <= 1e-2 * y_ref.abs().max()
+    # combine_decode == fixed-order sum of the partials, bias, bf16 rounding, weights
+    k = 2 if (M % 2 == 0 and len(rows) >= 2) else 1
+    N = M // k
+    g = torch.Generator().manual_seed(M)
+    row_of = torch.randperm(M, generator=g).view(N, k).to(torch.int32)
+    idx = e_of_row[row_of.long()].to(torch.int32)
+    w = torch.rand(N, k, generator=g)
+    res = torch.randn(N, d, generator=g).to(torch.bfloat16)
+    out = helpers.combine_decode(part, row_of.to(cuda_device), idx.to(cuda_device),
+                                 w.to(cuda_device), plan, res.to(cuda_device))
+    torch.cuda.synchronize()
+    acc_s = torch.zeros(M, d)
+    for sp in range(part.shape[0]):
+        acc_s = acc_s + part[sp].cpu()
+    yb = (acc_s + params["b2"][e_of_row]).to(torch.bfloat16).float()
+    acc = torch.zeros(N, d)
+    for j in range(k):
+        acc = acc + w[:, j:j + 1] * yb[row_of[:, j].long()]
+    assert torch.equal(out.cpu(), (acc + res.float()).to(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("N,d,k", [(1, 64, 2), (130, 128, 2), (1000, 512, 4), (33, 72, 1)])
 def test_combine_is_exact(cuda_device, N, d, k, dtype):
