@@ -49,6 +49,12 @@ SIGNATURES = {
     "moe_b200_combine": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "moe_b200_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _sz,
                               _vp, _vp]),
+    "moe_b200_ep_symm_bytes": (_sz, [_i64, _i, _i, _i, _i]),
+    "moe_b200_ep_symm_layout": (_i, [_i64, _i, _i, _i, _i, C.POINTER(_sz)]),
+    "moe_b200_ep_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),
+    "moe_b200_ep_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
+    "moe_b200_ep_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i,
+                                 C.c_uint32, _vp, _vp, _vp, _sz, _vp, _vp]),
     "moe_b200_read_status": (_i, [_vp, C.POINTER(C.c_int32), _vp]),
 }
 
@@ -95,6 +101,23 @@ def workspace_layout(N: int, d: int, f: int, E: int, k: int, dtype: int) -> dict
     arr = (_sz * WS_NUM)()
     check(lib.moe_b200_workspace_layout(N, d, f, E, k, dtype, arr), "workspace_layout")
     return {name: int(arr[i]) for i, name in enumerate(WS_NAMES)}
+
+
+EP_SYMM_NAMES = ("flags", "cnt_all", "recv_meta", "recv_x", "ret_y")
+EP_WS_NAMES = ("status", "logits", "idx", "w", "psum_part", "psum", "aux", "scratch", "cnt_slot0",
+               "offsets_local", "owner", "h")
+
+
+def ep_symm_layout(N_local: int, d: int, E: int, k: int, world: int) -> dict[str, int]:
+    arr = (_sz * len(EP_SYMM_NAMES))()
+    check(lib.moe_b200_ep_symm_layout(N_local, d, E, k, world, arr), "ep_symm_layout")
+    return {name: int(arr[i]) for i, name in enumerate(EP_SYMM_NAMES)}
+
+
+def ep_workspace_layout(N_local: int, d: int, f: int, E: int, k: int, world: int) -> dict[str, int]:
+    arr = (_sz * len(EP_WS_NAMES))()
+    check(lib.moe_b200_ep_workspace_layout(N_local, d, f, E, k, world, arr), "ep_workspace_layout")
+    return {name: int(arr[i]) for i, name in enumerate(EP_WS_NAMES)}
 
 
 def ptr_array(ptrs) -> C.Array:

@@ -27,7 +27,8 @@ combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ row_of,
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   for (int j = 0; j < k; ++j) {
-    const int row = __ldg(&row_of[t * k + j]);
+    // row_of == nullptr: y is already in (token, slot) order (expert-parallel return buffer)
+    const int row = row_of != nullptr ? __ldg(&row_of[t * k + j]) : (int)(t * k + j);
     if (row < 0) continue;
     const float wj = __ldg(&w[t * k + j]);
     float v[8];

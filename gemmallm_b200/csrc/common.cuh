@@ -142,6 +142,24 @@ __host__ __device__ inline PlanView plan_view(const void* plan, int E) {
   return v;
 }
 
+// ---- expert-parallel exchange ------------------------------------------------
+constexpr int kEpMaxRanks = 8;
+enum { kEpFlagCnt = 0, kEpFlagX = 1, kEpFlagY = 2, kEpNumFlags = 3 };
+
+// Pointers into every rank's symmetric buffer (index = rank), valid on this GPU.
+struct EpPeers {
+  uint32_t* flags[kEpMaxRanks];     // [kEpNumFlags][kEpMaxRanks] epoch words, one per (kind, source)
+  int32_t* cnt_all[kEpMaxRanks];    // [world][3E] per source: pair counts, slot-0 counts, psum bits
+  int32_t* recv_meta[kEpMaxRanks];  // [cap] return address of a received row: source << 24 | pair id
+  void* recv_x[kEpMaxRanks];        // [cap][d] received token rows, grouped by owned expert
+  void* ret_y[kEpMaxRanks];         // [N_local*k][d] expert outputs returned to the token owner
+};
+// Destination of the down pass's rows in the expert-parallel configuration.
+struct EpScatter {
+  void* ret_y[kEpMaxRanks];
+  const int32_t* meta;
+};
+
 // ---- launchers implemented in the other translation units -----------------
 int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                   int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
@@ -158,6 +176,19 @@ int launch_combine(const void* y, const int32_t* row_of, const float* w, const v
                    int64_t N, int d, int k, int dtype, void* out, cudaStream_t s);
 int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, int E, int d, int f,
                              void* h_tmaps /* kPlanMapsPerExpert*E*128 bytes */);
+int launch_experts_tc_ep(const void* recv_x, const int32_t* offsets, const void* plan, int64_t cap,
+                         int d, int f, int E_local, void* h, const EpScatter& sc, int32_t* status,
+                         cudaStream_t s);
+int64_t ep_scratch_ints(int64_t N, int E);
+int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
+                       const EpPeers& peers, int rank, int world, uint32_t epoch,
+                       const int32_t* expert_owner, int32_t* scratch, const float* psum_part,
+                       int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
+                       int64_t n_total, int32_t* status, cudaStream_t s);
+int launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, int where,
+                   cudaStream_t s);
+int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint32_t epoch,
+                     cudaStream_t s);
 int encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int sm_count(int* sms);
 int decode_splits(int f);

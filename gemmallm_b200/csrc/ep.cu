@@ -1,0 +1,360 @@
+// Expert-parallel exchange kernels: the dispatch and combine of the block as an
+// all-to-all written with plain NVLink peer stores (no NCCL on the data path, no
+// multicast, no TMA on remote memory).
+//
+// Tokens are sharded over the G ranks (rank r owns N_local tokens), experts are
+// owned by rank expert_owner[e]; the router runs replicated on local tokens.
+// Every rank has one "symmetric" buffer of identical layout that its peers can
+// write (EpSymm below). Per forward, with a caller-supplied increasing epoch:
+//   1. ep_dispatch_kernel (cooperative): per-expert counts of the local
+//      (token, slot) pairs, published to every rank's cnt_all[r] together with
+//      the slot-0 counts and the softmax sums the loss needs; waits for all G
+//      rows; derives the row every pair gets in its destination's receive
+//      buffer (rows of one expert contiguous, ordered by source rank then
+//      token, so the layout is deterministic); pushes the token rows and a
+//      return address (source rank, pair id) with 16-byte peer stores; raises
+//      flag X on every destination.
+//   2. ep_wait_kernel on flag X; the grouped GEMMs run on the receive buffer
+//      (experts_tc.cu). The down pass stores its output rows straight into the
+//      token owners' ret_y through peer pointers (scatter epilogue), so the
+//      return transfer overlaps the math tile by tile.
+//   3. ep_signal_kernel raises flag Y on every rank; ep_wait_kernel on flag Y;
+//      the combine kernel reads ret_y in (token, slot) order.
+// Every wait on a peer's flag is bounded (2 s) and reports
+// MOE_B200_DEV_TIMEOUT through the status word instead of hanging.
+// Replaces, for the sharded configuration, reference model.py:226-268.
+#include <cooperative_groups.h>
+#include <stdio.h>
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace moe {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kChunk = kDispatchChunk;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until *flag >= epoch (epochs only grow). False on timeout.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, int32_t* status,
+                                          int where) {
+  if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    if ((it & 63u) == 0) {
+      if (global_ns() - t0 > kWaitLimitNs) {
+        atomicMax(&status[0], MOE_B200_DEV_TIMEOUT);
+        status[1] = where;
+        return false;
+      }
+      __nanosleep(200);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx, int64_t N, int row_pieces,
+                   int E, int k, EpPeers peers, int rank, int world, uint32_t epoch,
+                   const int32_t* __restrict__ expert_owner, int32_t* __restrict__ scratch,
+                   const float* __restrict__ psum_part, int64_t router_blocks,
+                   int32_t* __restrict__ cnt_slot0, float* __restrict__ psum_global,
+                   int32_t* __restrict__ offsets_local, float* __restrict__ aux, int64_t n_total,
+                   int32_t* __restrict__ status) {
+  cg::grid_group grid = cg::this_grid();
+  extern __shared__ int s_int[];
+  int* s_hist = s_int;                  // [E] local totals
+  int* s_base = s_hist + E;             // [E] local rows of earlier chunks
+  int* s_dest = s_base + E;             // [E] first row of (this rank, expert) at its owner
+  int* s_run = s_dest + E;              // [E]
+  int* s_owner = s_run + E;             // [E]
+  int* s_row = s_owner + E;             // [kChunk*k]
+  int* s_q = s_row + kChunk * k;        // [kChunk*k]
+  int* s_cnt = s_q + kChunk * k;        // [world][E] pair counts of every source rank
+  float* s_red = reinterpret_cast<float*>(s_cnt + world * E);  // [kThreads]
+  __shared__ int s_fail;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = gridDim.x;
+  const int64_t nchunk = (N + kChunk - 1) / kChunk;
+  int32_t* chunk_cnt = scratch;                       // [nchunk][E]
+  int32_t* blk_slot0 = chunk_cnt + nchunk * E;        // [G][E] slot-0 counts per block
+  const int row_ints = 3 * E;                         // published row: counts, slot-0 counts, psum bits
+
+  // ---- phase 1: per-chunk histograms --------------------------------------
+  for (int e = tid; e < E; e += kThreads) { s_run[e] = 0; s_owner[e] = expert_owner[e]; }
+  if (tid == 0) s_fail = 0;
+  __syncthreads();
+  for (int64_t c = blockIdx.x; c < nchunk; c += G) {
+    for (int e = tid; e < E; e += kThreads) s_hist[e] = 0;
+    __syncthreads();
+    const int64_t t0 = c * kChunk;
+    const int ntok = (int)((N - t0) < kChunk ? (N - t0) : kChunk);
+    for (int p = tid; p < ntok * k; p += kThreads) {
+      int e = idx[t0 * k + p];
+      if ((unsigned)e >= (unsigned)E) { atomicMax(&status[0], MOE_B200_DEV_BAD_INDEX); continue; }
+      atomicAdd(&s_hist[e], 1);
+      if (p % k == 0) atomicAdd(&s_run[e], 1);   // s_run doubles as the slot-0 histogram here
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += kThreads) chunk_cnt[c * E + e] = s_hist[e];
+    __syncthreads();
+  }
+  for (int e = tid; e < E; e += kThreads) blk_slot0[(size_t)blockIdx.x * E + e] = s_run[e];
+  grid.sync();
+
+  // ---- phase 2: local totals; block 0 publishes this rank's row ------------
+  for (int e = tid; e < E; e += kThreads) { s_hist[e] = 0; s_base[e] = 0; }
+  __syncthreads();
+  const int64_t c0 = blockIdx.x;
+  for (int64_t i = tid; i < nchunk * E; i += kThreads) {
+    int v = __ldcg(&chunk_cnt[i]);
+    int64_t cc = i / E;
+    int e = (int)(i - cc * E);
+    if (v != 0) {
+      atomicAdd(&s_hist[e], v);
+      if (cc < c0) atomicAdd(&s_base[e], v);
+    }
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    int32_t* my_row = peers.cnt_all[rank] + (size_t)rank * row_ints;
+    for (int e = warp; e < E; e += kThreads / 32) {
+      int c0s = 0;
+      for (int b = lane; b < G; b += 32) c0s += __ldcg(&blk_slot0[(size_t)b * E + e]);
+      float ps = 0.f;
+      for (int64_t b = lane; b < router_blocks; b += 32) ps += psum_part[b * E + e];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        c0s += __shfl_xor_sync(0xffffffffu, c0s, o);
+        ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      }
+      if (lane == 0) {
+        my_row[e] = s_hist[e];
+        my_row[E + e] = c0s;
+        my_row[2 * E + e] = __float_as_int(ps);
+      }
+    }
+    __syncthreads();
+    // copy the row to every peer, then raise the count flag there
+    for (int i = tid; i < row_ints * world; i += kThreads) {
+      int q = i / row_ints, j = i - q * row_ints;
+      if (q != rank) peers.cnt_all[q][(size_t)rank * row_ints + j] = my_row[j];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < world) st_release_sys(peers.flags[tid] + kEpFlagCnt * kEpMaxRanks + rank, epoch);
+  }
+
+  // ---- phase 3: wait for every rank's row, derive destination rows ---------
+  if (tid < world) {
+    if (!wait_flag(peers.flags[rank] + kEpFlagCnt * kEpMaxRanks + tid, epoch, status, 21)) s_fail = 1;
+  }
+  __syncthreads();
+  const bool fail = s_fail != 0;
+  const int32_t* all = peers.cnt_all[rank];
+  for (int i = tid; i < world * E; i += kThreads) {
+    int g = i / E, e = i - g * E;
+    s_cnt[i] = fail ? 0 : (int)__ldcv(&all[(size_t)g * row_ints + e]);
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += kThreads) {
+    const int q = s_owner[e];
+    int base = 0;
+    for (int e2 = 0; e2 < e; ++e2)
+      if (s_owner[e2] == q)
+        for (int g = 0; g < world; ++g) base += s_cnt[g * E + e2];
+    for (int g = 0; g < rank; ++g) base += s_cnt[g * E + e];
+    s_dest[e] = base;
+  }
+  if (blockIdx.x == 0 && !fail) {
+    // rows this rank will receive, per owned expert in increasing expert id
+    if (tid == 0) {
+      int acc = 0, li = 0;
+      for (int e = 0; e < E; ++e) {
+        if (s_owner[e] != rank) continue;
+        offsets_local[li++] = acc;
+        for (int g = 0; g < world; ++g) acc += s_cnt[g * E + e];
+      }
+      offsets_local[li] = acc;
+    }
+    // global slot-0 counts and probability sums, fixed order over ranks; loss
+    // E^2 * mean_e(psum[e]/N_total * cnt0[e]/N_total)  (model.py:213-216)
+    float part = 0.f;
+    for (int e = tid; e < E; e += kThreads) {
+      int c0s = 0;
+      float ps = 0.f;
+      for (int g = 0; g < world; ++g) {
+        c0s += (int)__ldcv(&all[(size_t)g * row_ints + E + e]);
+        ps += __int_as_float((int)__ldcv(&all[(size_t)g * row_ints + 2 * E + e]));
+      }
+      cnt_slot0[e] = c0s;
+      psum_global[e] = ps;
+      part += (ps / (float)n_total) * ((float)c0s / (float)n_total);
+    }
+    s_red[tid] = part;
+    __syncthreads();
+    for (int o = kThreads / 2; o > 0; o >>= 1) {
+      if (tid < o) s_red[tid] += s_red[tid + o];
+      __syncthreads();
+    }
+    if (tid == 0) aux[0] = s_red[0] / (float)E * (float)(E * E);
+  }
+  __syncthreads();
+
+  // ---- phase 4: rank the pairs of each chunk, push rows to their owners ----
+  for (int64_t c = c0; c < nchunk && !fail; c += G) {
+    const int64_t t0 = c * kChunk;
+    const int ntok = (int)((N - t0) < kChunk ? (N - t0) : kChunk);
+    const int npair = ntok * k;
+    if (warp == 0) {
+      for (int e = lane; e < E; e += 32) s_run[e] = 0;
+      __syncwarp();
+      for (int p0 = 0; p0 < npair; p0 += 32) {
+        int p = p0 + lane;
+        int e = p < npair ? idx[t0 * k + p] : -1;
+        bool ok = (unsigned)e < (unsigned)E;
+        unsigned grp = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+        int row = -1, q = 0;
+        if (ok) {
+          row = s_dest[e] + s_base[e] + s_run[e] + __popc(grp & ((1u << lane) - 1u));
+          q = s_owner[e];
+        }
+        __syncwarp();
+        if (ok && (grp >> lane) == 1u) s_run[e] += __popc(grp);
+        __syncwarp();
+        if (p < npair) {
+          s_row[p] = row;
+          s_q[p] = q;
+          if (row >= 0)
+            peers.recv_meta[q][row] = (rank << 24) | (int)((t0 * k + p) & 0xffffff);
+        }
+      }
+    }
+    __syncthreads();
+    constexpr int kInFlight = 8;
+    const int items = ntok * row_pieces;
+    const uint4* src = x + t0 * row_pieces;
+    for (int i0 = tid; i0 < items; i0 += kThreads * kInFlight) {
+      uint4 v[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < items) v[u] = __ldg(src + i);
+      }
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < items) {
+          const int tl = i / row_pieces, pc = i - tl * row_pieces;
+          for (int j = 0; j < k; ++j) {
+            const int row = s_row[tl * k + j];
+            if (row >= 0)
+              reinterpret_cast<uint4*>(peers.recv_x[s_q[tl * k + j]])[(int64_t)row * row_pieces + pc] = v[u];
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (c + G >= nchunk) break;
+    for (int64_t i = tid; i < (int64_t)G * E; i += kThreads) {
+      int64_t cc = c + i / E;
+      int e = (int)(i % E);
+      if (cc < nchunk) {
+        int v = __ldcg(&chunk_cnt[cc * E + e]);
+        if (v != 0) atomicAdd(&s_base[e], v);
+      }
+    }
+    __syncthreads();
+  }
+  __threadfence_system();
+  grid.sync();
+  if (blockIdx.x == 0 && tid < world && !fail)
+    st_release_sys(peers.flags[tid] + kEpFlagX * kEpMaxRanks + rank, epoch);
+}
+
+__global__ void ep_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, int32_t* status,
+                               int where) {
+  if ((int)threadIdx.x < world) wait_flag(flags + threadIdx.x, epoch, status, where);
+}
+
+__global__ void ep_signal_kernel(EpPeers peers, int which, int rank, int world, uint32_t epoch) {
+  __threadfence_system();
+  if ((int)threadIdx.x < world)
+    st_release_sys(peers.flags[threadIdx.x] + which * kEpMaxRanks + rank, epoch);
+}
+
+int g_sm_count = 0;
+int g_blocks_per_sm = 0;
+
+}  // namespace
+
+int64_t ep_scratch_ints(int64_t N, int E) {
+  return ((N + kChunk - 1) / kChunk) * E + (int64_t)kNumSMs * 2 * E;
+}
+
+int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
+                       const EpPeers& peers, int rank, int world, uint32_t epoch,
+                       const int32_t* expert_owner, int32_t* scratch, const float* psum_part,
+                       int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
+                       int64_t n_total, int32_t* status, cudaStream_t s) {
+  const int row_pieces = d * (dtype == MOE_B200_BF16 ? 2 : 4) / 16;
+  const size_t smem = sizeof(int) * (size_t)(5 * E + 2 * kChunk * k + world * E + kThreads);
+  const void* fn = (const void*)ep_dispatch_kernel;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    MOE_CUDA_CHECK(cudaGetDevice(&dev));
+    MOE_CUDA_CHECK(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if (g_blocks_per_sm == 0) {
+    int per_sm = 0;
+    MOE_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
+    g_blocks_per_sm = per_sm < 1 ? 1 : per_sm;
+  }
+  int64_t grid = (int64_t)g_sm_count * (g_blocks_per_sm > 2 ? 2 : g_blocks_per_sm);
+  if (grid > (int64_t)kNumSMs * 2) grid = (int64_t)kNumSMs * 2;
+  int64_t nchunk = (N + kChunk - 1) / kChunk;
+  if (nchunk < 1) nchunk = 1;
+  if (grid > nchunk) grid = nchunk;
+  int64_t router_blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
+  const uint4* x4 = static_cast<const uint4*>(x);
+  EpPeers pv = peers;
+  void* args[] = {(void*)&x4, (void*)&idx, (void*)&N, (void*)&row_pieces, (void*)&E, (void*)&k,
+                  (void*)&pv, (void*)&rank, (void*)&world, (void*)&epoch, (void*)&expert_owner,
+                  (void*)&scratch, (void*)&psum_part, (void*)&router_blocks, (void*)&cnt_slot0,
+                  (void*)&psum_global, (void*)&offsets_local, (void*)&aux, (void*)&n_total,
+                  (void*)&status};
+  MOE_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem, s));
+  return 0;
+}
+
+int launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, int where,
+                   cudaStream_t s) {
+  ep_wait_kernel<<<1, 32, 0, s>>>(flags, world, epoch, status, where);
+  MOE_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint32_t epoch,
+                     cudaStream_t s) {
+  ep_signal_kernel<<<1, 32, 0, s>>>(peers, which, rank, world, epoch);
+  MOE_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace moe

@@ -57,13 +57,17 @@ constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + sizeof(Cont
 // GEGLU : B = gate rows [n0, n0+128) and up rows [Nout+n0, ...) of W [2*Nout, K];
 //         out[row, n0..n0+128) = gelu_tanh(gate + bg) * (up + bu).
 // plain : B = rows [n0, n0+256) of W [Nout, K]; out[row, n0..n0+256) = acc + bias.
-template <bool GEGLU>
+// SCATTER (plain only, expert-parallel): row i goes to the buffer of the rank
+//         that owns its token, sc.ret_y[meta >> 24] + (meta & 0xffffff) * Nout,
+//         with plain stores through the peer mapping.
+template <bool GEGLU, bool SCATTER>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const CUtensorMap* __restrict__ tmap_b,  // [E], global memory
                        const int32_t* __restrict__ offsets,
                        const void* const* __restrict__ bias_ptrs, int E, int K, int Nout,
-                       __nv_bfloat16* __restrict__ out, int32_t* __restrict__ status) {
+                       __nv_bfloat16* __restrict__ out, const EpScatter sc,
+                       int32_t* __restrict__ status) {
 #ifdef MOE_TC_PROFILE
   const long long prof_entry = clock64();
   constexpr int kProfBase = GEGLU ? 0 : 8;
@@ -211,6 +215,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
       __nv_bfloat16* orow = out + (int64_t)row * Nout + n0;
+      if (SCATTER) {
+        const int meta = row_ok ? __ldg(&sc.meta[row]) : 0;
+        orow = static_cast<__nv_bfloat16*>(sc.ret_y[(meta >> 24) & 7]) +
+               (int64_t)(meta & 0xffffff) * Nout + n0;
+      }
       if (GEGLU) {
 #pragma unroll 1
         for (int c = 0; c < kTileN / 32; ++c) {
@@ -258,6 +267,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_arrive(&ctl->tmem_empty[a]);
       if (a == 1) acc_phase ^= 1u;
     }
+    if (SCATTER) __threadfence_system();  // peer stores performed before the kernel ends
   }
 
 #ifdef MOE_TC_PROFILE
@@ -283,19 +293,19 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <bool GEGLU>
+template <bool GEGLU, bool SCATTER>
 int launch_one(const CUtensorMap& tm_a, const void* tmap_b, const int32_t* offsets,
-               const void* const* bias, int E, int K, int Nout, void* out, int32_t* status,
-               int sms, cudaStream_t s) {
+               const void* const* bias, int E, int K, int Nout, void* out, const EpScatter& sc,
+               int32_t* status, int sms, cudaStream_t s) {
   static bool attr_set = false;
-  auto fn = grouped_gemm_tc_kernel<GEGLU>;
+  auto fn = grouped_gemm_tc_kernel<GEGLU, SCATTER>;
   if (!attr_set) {
     MOE_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)kSmemBytes));
     attr_set = true;
   }
   fn<<<sms, kThreads, kSmemBytes, s>>>(tm_a, static_cast<const CUtensorMap*>(tmap_b), offsets, bias,
-                                       E, K, Nout, static_cast<__nv_bfloat16*>(out), status);
+                                       E, K, Nout, static_cast<__nv_bfloat16*>(out), sc, status);
   MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -314,9 +324,34 @@ int launch_experts_tc(const void* perm, const int32_t* offsets, const void* plan
   int sms = 0;
   rc = sm_count(&sms);
   if (rc) return rc;
-  rc = launch_one<true>(tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, status, sms, s);
+  const EpScatter none = {};
+  rc = launch_one<true, false>(tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, none, status, sms, s);
   if (rc) return rc;
-  return launch_one<false>(tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, y, status, sms, s);
+  return launch_one<false, false>(tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, y, none, status, sms, s);
+}
+
+// Expert-parallel: the sorted buffer is this rank's receive buffer (capacity
+// `cap` rows, filled up to offsets[E_local]); the down pass scatters its rows
+// to the token owners.
+int launch_experts_tc_ep(const void* recv_x, const int32_t* offsets, const void* plan, int64_t cap,
+                         int d, int f, int E_local, void* h, const EpScatter& sc, int32_t* status,
+                         cudaStream_t s) {
+  if (cap == 0 || E_local == 0) return 0;
+  PlanView pv = plan_view(plan, E_local);
+  alignas(64) CUtensorMap tm_x, tm_h;
+  int rc = encode_tmap_2d(&tm_x, recv_x, (uint64_t)cap, (uint64_t)d, BM);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tm_h, h, (uint64_t)cap, (uint64_t)f, BM);
+  if (rc) return rc;
+  int sms = 0;
+  rc = sm_count(&sms);
+  if (rc) return rc;
+  const EpScatter none = {};
+  rc = launch_one<true, false>(tm_x, pv.tmap_W1, offsets, pv.b1, E_local, d, f, h, none, status,
+                               sms, s);
+  if (rc) return rc;
+  return launch_one<false, true>(tm_h, pv.tmap_W2, offsets, pv.b2, E_local, f, d, nullptr, sc,
+                                 status, sms, s);
 }
 
 #ifdef MOE_TC_PROFILE

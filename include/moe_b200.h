@@ -224,6 +224,50 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg,
                      void* workspace, size_t workspace_bytes,
                      void* out, void* stream);
 
+/* ---- Expert-parallel configuration ------------------------------------------
+ * Tokens are sharded over `world` ranks (one process per GPU, rank r owns
+ * N_local tokens) and experts are owned by rank h_expert_owner[e]; the
+ * reference has no multi-GPU path, these entry points extend MOE.forward
+ * (model.py:200-276) to that sharding. Dispatch and combine are all-to-all
+ * exchanges written as peer stores inside the kernels; the caller provides, on
+ * every rank, one "symmetric" buffer of moe_b200_ep_symm_bytes bytes that all
+ * ranks can address (h_symm_bases[q] = rank q's buffer as mapped in THIS
+ * process), zero-filled once before the first call. bf16 only. */
+enum {
+  MOE_B200_EP_SYMM_FLAGS = 0, /* uint32 [3][8] epoch words */
+  MOE_B200_EP_SYMM_CNT_ALL,   /* int32 [world][3E] counts published by every rank */
+  MOE_B200_EP_SYMM_RECV_META, /* int32 [cap] return address of each received row */
+  MOE_B200_EP_SYMM_RECV_X,    /* bf16 [cap][d] received rows, cap = N_local*k*world */
+  MOE_B200_EP_SYMM_RET_Y,     /* bf16 [N_local*k][d] expert outputs in (token, slot) order */
+  MOE_B200_EP_SYMM_NUM
+};
+enum {
+  MOE_B200_EP_WS_STATUS = 0, MOE_B200_EP_WS_LOGITS, MOE_B200_EP_WS_IDX, MOE_B200_EP_WS_W,
+  MOE_B200_EP_WS_PSUM_PART, MOE_B200_EP_WS_PSUM, /* float [E], summed over all ranks */
+  MOE_B200_EP_WS_AUX,          /* loss over all N_local*world tokens (model.py:213-216) */
+  MOE_B200_EP_WS_SCRATCH, MOE_B200_EP_WS_CNT_SLOT0, /* int32 [E], all ranks */
+  MOE_B200_EP_WS_OFFSETS_LOCAL, /* int32 [E_local+1] rows received per owned expert */
+  MOE_B200_EP_WS_OWNER, MOE_B200_EP_WS_H, MOE_B200_EP_WS_NUM
+};
+size_t moe_b200_ep_symm_bytes(int64_t N_local, int d, int E, int k, int world);
+int moe_b200_ep_symm_layout(int64_t N_local, int d, int E, int k, int world, size_t* h_offsets);
+size_t moe_b200_ep_workspace_bytes(int64_t N_local, int d, int f, int E, int k, int world);
+int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, int world,
+                                 size_t* h_offsets);
+
+/* One sharded forward on this rank: router on the local tokens, count exchange,
+ * dispatch push to the expert owners, grouped GEMMs on the received rows with
+ * the down pass writing straight to the token owners, combine (+ residual).
+ * plan_local covers the experts this rank owns, in increasing expert id.
+ * `epoch` is 1 on the first call and one more on every later call, the same on
+ * all ranks. All ranks must make the same sequence of calls. A peer that never
+ * arrives makes the bounded waits run out: status word = MOE_B200_DEV_TIMEOUT. */
+int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
+                        const void* residual, int64_t N_local, int d, int f, int E, int k,
+                        int dtype, int rank, int world, uint32_t epoch,
+                        const int32_t* h_expert_owner, void* const* h_symm_bases,
+                        void* workspace, size_t workspace_bytes, void* out, void* stream);
+
 /* Copy the 16 status words to the host after synchronising the stream.
  * Returns h_status[0]. Synchronous. */
 int moe_b200_read_status(const int32_t* status, int32_t* h_status, void* stream);
