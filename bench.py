@@ -170,10 +170,24 @@ def run_ours(args, wl):
     dt = synthetic.torch_dtype(wl.dtype)
     es = 2 if wl.dtype == "bf16" else 4
     N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
-    params = synthetic.make_params(d, E, f, seed=0, gate_bias_kind=wl.gate_bias)
     m = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda").eval()
-    synthetic.load_into(m, params, dt, dev)
-    del params
+    if E > 16:
+        # many experts: draw them one at a time (same rule as the expert-parallel ranks)
+        m.to(device=dev, dtype=dt)
+        gate_w, gate_b = synthetic.make_gate(d, E, 0, wl.gate_bias)
+        with torch.no_grad():
+            m.gate.weight.copy_(gate_w)
+            m.gate.bias.copy_(gate_b)
+            for e, ex in enumerate(m.experts):
+                pe = synthetic.make_expert(d, f, e, 0)
+                ex.gate_and_up.weight.copy_(pe["w1"])
+                ex.down.weight.copy_(pe["w2"])
+                ex.gate_and_up.bias.zero_()
+                ex.down.bias.zero_()
+    else:
+        params = synthetic.make_params(d, E, f, seed=0, gate_bias_kind=wl.gate_bias)
+        synthetic.load_into(m, params, dt, dev)
+        del params
     # each rank owns its own token batch (seed differs per rank)
     x_host = synthetic.make_input(N, d, seed=1 + rank).to(dt).pin_memory()
     x = x_host.to(dev).view(1, N, d)
@@ -337,6 +351,149 @@ def run_ours(args, wl):
         dist.destroy_process_group()
 
 
+def run_ep(args, wl):
+    """Expert-parallel workload under torchrun: tokens and experts sharded over
+    the ranks, strong scaling (the token total is fixed)."""
+    import torch.distributed as dist
+    from gemmallm_b200 import _cabi, synthetic
+    from gemmallm_b200._cabi import lib, check
+    from gemmallm_b200.ep import ExpertParallelMOE
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    dt = synthetic.torch_dtype(wl.dtype)
+    N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+    Nl = N // world
+    placement = None
+    if args.ep_placement == "lpt":
+        # popularity prior from the router bias: softmax mass of the bias alone
+        from gemmallm_b200.ep import lpt_placement
+        prior = torch.softmax(synthetic.gate_bias(wl.gate_bias, E), 0).tolist()
+        placement = lpt_placement(prior, world)
+    m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement).eval()
+    m.flags = args.ep_flags
+    m.to(device=dev, dtype=dt)
+    gate_w, gate_b = synthetic.make_gate(d, E, 0, wl.gate_bias)
+    with torch.no_grad():
+        m.gate.weight.copy_(gate_w)
+        m.gate.bias.copy_(gate_b)
+        for e in m.local_ids:
+            p = synthetic.make_expert(d, f, e, 0)
+            ex = m.experts[str(e)]
+            ex.gate_and_up.weight.copy_(p["w1"])
+            ex.down.weight.copy_(p["w2"])
+            ex.gate_and_up.bias.zero_()
+            ex.down.bias.zero_()
+    x_host = synthetic.make_input(Nl, d, seed=1 + rank).to(dt).pin_memory()
+    x = x_host.to(dev).view(1, Nl, d)
+    out_host = torch.empty(Nl, d, dtype=dt).pin_memory()
+    aux_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        t = torch.tensor([v], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            m(x)
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            ev0.record()
+            for _ in range(args.steps):
+                m(x)
+            ev1.record()
+            barrier()
+        ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+        status = max_over_ranks(float(m.device_status()))
+        if status != 0:
+            raise RuntimeError(f"device status {status} after the timed region")
+        # end to end: pinned host input in, output and loss back, every step
+        x_dev = torch.empty(1, Nl, d, dtype=dt, device=dev)
+        for it in range(2 + args.steps):
+            if it == 2:
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            x_dev.copy_(x_host.view(1, Nl, d), non_blocking=True)
+            o, aux = m(x_dev)
+            out_host.copy_(o.view(Nl, d), non_blocking=True)
+            aux_host.copy_(aux.view(1), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            loss = float(aux_host[0])
+        e1.record()
+        barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+        # grouped GEMMs alone on this rank's received rows
+        rows = int(m.last["offsets_local"][-1])
+        st = m._state
+        recv_x = st["hdl"].buffer_ptrs[rank] + st["symm_layout"]["recv_x"]
+        hbuf = st["ws_base"] + st["ws_layout"]["h"]
+        offs = st["ws_base"] + st["ws_layout"]["offsets_local"]
+        stat = st["ws_base"] + st["ws_layout"]["status"]
+        ybuf = torch.empty(max(rows, 1), d, dtype=dt, device=dev)
+        s_ = torch.cuda.current_stream(dev).cuda_stream
+        call = lambda: lib.moe_b200_experts(recv_x, offs, m._plan.base, rows, d, f, len(m.local_ids),
+                                            _cabi.BF16, 0, hbuf, ybuf.data_ptr(), stat, s_)
+        for _ in range(3):
+            check(call(), "experts")
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(10):
+            call()
+        g1.record()
+        torch.cuda.synchronize()
+        gemm_ms = g0.elapsed_time(g1) / 10
+    info = torch.tensor([float(rows), gemm_ms], device=dev)
+    gathered = [torch.empty_like(info) for _ in range(world)]
+    dist.all_gather(gathered, info)
+    if rank == 0:
+        peaks, peak_kind = load_peaks()
+        peak = float(peaks["bf16_tflops"])
+        es = 2
+        per_rank = [{"rows": int(g[0]), "gemm_ms": float(g[1]),
+                     "tflops": 6.0 * d * f * float(g[0]) / (float(g[1]) * 1e-3) / 1e12} for g in gathered]
+        busiest = max(per_rank, key=lambda r: r["gemm_ms"])
+        share = max(r["rows"] for r in per_rank) / float(N * k)
+        ms_step = ms_total / args.steps
+        line = {
+            "metric": "moe_tokens_per_s", "value": N * args.steps / (ms_total * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": workload_config(wl, {
+                "parallelism": f"ep{world}: tokens and experts sharded over {world} ranks, "
+                               f"{args.ep_placement} expert placement, peer-store all-to-all",
+                "l2": "per-rank working set (received rows, h, owned expert weights) exceeds the 126 MB L2"}),
+            "e2e": {"value": N * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": Nl * d * es * world, "d2h_bytes_per_step": (Nl * d * es + 4) * world,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 9 * args.steps,
+            "clocks": clocks.summary(),
+            "roofline": {"kernel": "grouped_gemm_tc_kernel (GEGLU pass + down pass) on the busiest rank",
+                         "bound": "tensor", "achieved": busiest["tflops"], "peak": peak,
+                         "unit": "TFLOP/s", "frac": busiest["tflops"] / peak, "traffic": None,
+                         "peak_source": f"{peak_kind} bf16 burst", "ms": busiest["gemm_ms"]},
+            "ep": {"per_rank": per_rank, "max_rank_share_of_rows": share,
+                   "balance_limited_speedup": 1.0 / share,
+                   "gemm_ms_over_step_ms": busiest["gemm_ms"] / ms_step},
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20):
     """CUDA-event time of each stage, called through its own C-ABI entry point
     on the buffers of the module's workspace, on the current stream."""
@@ -392,17 +549,25 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1_uniform")
+    ap.add_argument("--workload", default=None,
+                    help="default: c1_uniform on one GPU, c4 (expert-parallel) on several")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-placement", default="strided", choices=["strided", "lpt"])
+    ap.add_argument("--ep-flags", type=int, default=0, help="flags for moe_b200_ep_forward")
     ap.add_argument("--no-graph", action="store_true", help="small-N workloads: time eager calls")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident loop only (for profiler captures): no end-to-end leg, "
                          "no per-stage timing, no CPU baseline; prints a reduced line")
     args = ap.parse_args()
     from gemmallm_b200 import synthetic
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload is None:
+        args.workload = "c1_uniform" if world == 1 else "c4"
     wl = synthetic.WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, wl)
+    elif world > 1 and wl.name == "c4":
+        run_ep(args, wl)
     else:
         run_ours(args, wl)
 

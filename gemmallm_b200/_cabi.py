@@ -14,7 +14,7 @@ from pathlib import Path
 LIB_PATH = Path(os.environ.get("MOE_B200_LIB") or Path(__file__).resolve().parent / "libmoe_b200.so")
 
 F32, BF16 = 0, 1
-FLAG_DEFAULT, FLAG_SIMT_EXPERTS, FLAG_NO_DECODE_PATH = 0, 1, 2
+FLAG_DEFAULT, FLAG_SIMT_EXPERTS, FLAG_NO_DECODE_PATH, FLAG_EP_UNFUSED_RETURN = 0, 1, 2, 4
 DEV_OK, DEV_TIMEOUT, DEV_BAD_INDEX = 0, 1, 2
 
 WS_NAMES = (
@@ -53,7 +53,7 @@ SIGNATURES = {
     "moe_b200_ep_symm_layout": (_i, [_i64, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_ep_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),
     "moe_b200_ep_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
-    "moe_b200_ep_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i,
+    "moe_b200_ep_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
                                  C.c_uint32, _vp, _vp, _vp, _sz, _vp, _vp]),
     "moe_b200_read_status": (_i, [_vp, C.POINTER(C.c_int32), _vp]),
 }
@@ -105,7 +105,7 @@ def workspace_layout(N: int, d: int, f: int, E: int, k: int, dtype: int) -> dict
 
 EP_SYMM_NAMES = ("flags", "cnt_all", "recv_meta", "recv_x", "ret_y")
 EP_WS_NAMES = ("status", "logits", "idx", "w", "psum_part", "psum", "aux", "scratch", "cnt_slot0",
-               "offsets_local", "owner", "h")
+               "offsets_local", "owner", "h", "y")
 
 
 def ep_symm_layout(N_local: int, d: int, E: int, k: int, world: int) -> dict[str, int]:

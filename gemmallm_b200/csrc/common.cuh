@@ -185,6 +185,8 @@ int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int 
                        const int32_t* expert_owner, int32_t* scratch, const float* psum_part,
                        int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
                        int64_t n_total, int32_t* status, cudaStream_t s);
+int launch_ep_return(const void* y, const int32_t* offsets_local, int E_local, const EpScatter& sc,
+                     int d, cudaStream_t s);
 int launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, int where,
                    cudaStream_t s);
 int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint32_t epoch,

@@ -288,6 +288,23 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
     st_release_sys(peers.flags[tid] + kEpFlagX * kEpMaxRanks + rank, epoch);
 }
 
+// Unfused return (MOE_B200_FLAG_EP_UNFUSED_RETURN): copy every received row's
+// output from the local sorted buffer to its token owner, one warp per row.
+__global__ void __launch_bounds__(256)
+ep_return_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ offsets_local, int E_local,
+                 const int32_t* __restrict__ meta, EpScatter sc, int row_pieces) {
+  const int rows = offsets_local[E_local];
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = warp; r < rows; r += nwarps) {
+    const int m = __ldg(&meta[r]);
+    uint4* dst = reinterpret_cast<uint4*>(sc.ret_y[(m >> 24) & 7]) + (int64_t)(m & 0xffffff) * row_pieces;
+    const uint4* src = y + (int64_t)r * row_pieces;
+    for (int i = lane; i < row_pieces; i += 32) dst[i] = __ldg(src + i);
+  }
+  __threadfence_system();
+}
+
 __global__ void ep_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, int32_t* status,
                                int where) {
   if ((int)threadIdx.x < world) wait_flag(flags + threadIdx.x, epoch, status, where);
@@ -340,6 +357,14 @@ int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int 
                   (void*)&psum_global, (void*)&offsets_local, (void*)&aux, (void*)&n_total,
                   (void*)&status};
   MOE_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem, s));
+  return 0;
+}
+
+int launch_ep_return(const void* y, const int32_t* offsets_local, int E_local, const EpScatter& sc,
+                     int d, cudaStream_t s) {
+  ep_return_kernel<<<kNumSMs * 8, 256, 0, s>>>(static_cast<const uint4*>(y), offsets_local, E_local,
+                                               sc.meta, sc, d * 2 / 16);
+  MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
 

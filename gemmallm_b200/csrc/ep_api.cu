@@ -58,6 +58,7 @@ void ws_layout(int64_t N_local, int d, int f, int E, int k, int world, size_t* o
   sizes[MOE_B200_EP_WS_OFFSETS_LOCAL] = (size_t)(E + 1) * sizeof(int32_t);
   sizes[MOE_B200_EP_WS_OWNER] = (size_t)E * sizeof(int32_t);
   sizes[MOE_B200_EP_WS_H] = cap * f * 2;
+  sizes[MOE_B200_EP_WS_Y] = cap * d * 2;
   size_t pos = 0;
   for (int i = 0; i < MOE_B200_EP_WS_NUM; ++i) {
     off[i] = pos;
@@ -108,7 +109,7 @@ int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, in
 
 int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
                         const void* residual, int64_t N_local, int d, int f, int E, int k,
-                        int dtype, int rank, int world, uint32_t epoch,
+                        int dtype, int flags, int rank, int world, uint32_t epoch,
                         const int32_t* h_expert_owner, void* const* h_symm_bases, void* workspace,
                         size_t workspace_bytes, void* out, void* stream) {
   int rc = ep_check(N_local, d, f, E, k, dtype, rank, world);
@@ -181,9 +182,21 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
   EpScatter sc;
   for (int q = 0; q < kEpMaxRanks; ++q) sc.ret_y[q] = peers.ret_y[q];
   sc.meta = peers.recv_meta[rank];
-  rc = launch_experts_tc_ep(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h, sc,
-                            status, s);
-  if (rc) return rc;
+  if (flags & MOE_B200_FLAG_EP_UNFUSED_RETURN) {
+    // expert outputs to a local buffer first, then one copy kernel over NVLink
+    void* y = ws + wo[MOE_B200_EP_WS_Y];
+    if (E_local > 0) {
+      rc = launch_experts_tc(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h, y,
+                             status, s);
+      if (rc) return rc;
+      rc = launch_ep_return(y, offsets_local, E_local, sc, d, s);
+      if (rc) return rc;
+    }
+  } else {
+    rc = launch_experts_tc_ep(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h,
+                              sc, status, s);
+    if (rc) return rc;
+  }
   rc = launch_ep_signal(peers, kEpFlagY, rank, world, epoch, s);
   if (rc) return rc;
   rc = launch_ep_wait(peers.flags[rank] + kEpFlagY * kEpMaxRanks, world, epoch, status, 23, s);

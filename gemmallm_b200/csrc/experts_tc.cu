@@ -40,6 +40,7 @@ constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 2 * BN;             // two accumulators
 constexpr uint32_t kIdesc = make_idesc(BN);
+constexpr int kStgPitch = 144;
 
 struct Control {
   uint64_t full[kStages];
@@ -50,6 +51,9 @@ struct Control {
   int abort;
   int tile_start[kMaxExperts + 1];
   int offsets[kMaxExperts + 1];  // copy of the row offsets: no global loads in the tile loops
+  // per epilogue warp: 32 rows x 64 bf16 (+16 bytes pad) to turn the scatter
+  // epilogue's row-per-thread registers into 128-byte runs per row
+  alignas(16) uint8_t stage_out[4][32 * kStgPitch];
 };
 
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + sizeof(Control);
@@ -216,11 +220,49 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
       __nv_bfloat16* orow = out + (int64_t)row * Nout + n0;
       if (SCATTER) {
-        const int meta = row_ok ? __ldg(&sc.meta[row]) : 0;
-        orow = static_cast<__nv_bfloat16*>(sc.ret_y[(meta >> 24) & 7]) +
-               (int64_t)(meta & 0xffffff) * Nout + n0;
-      }
-      if (GEGLU) {
+        // Rows go to their token owners over NVLink. Registers hold one row per
+        // thread; stage 64 columns per row in shared memory and let 8 lanes write
+        // each row's 128 bytes, so that the peer stores are 128-byte runs.
+        const int meta = row_ok ? __ldg(&sc.meta[row]) : -1;
+        uint8_t* stg = ctl->stage_out[quad];
+#pragma unroll 1
+        for (int cp = 0; cp < kTileN / 64; ++cp) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c = cp * 2 + half;
+            uint32_t v[32];
+            tc_ld32(taddr + c * 32, v);
+            tc_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int n = n0 + c * 32 + q * 8;
+              float b[8], o[8];
+              if (n < Nout) {
+                load8_ldg(bias + n, b);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) b[i] = 0.f;
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(v[q * 8 + i]) + b[i];
+              store8(reinterpret_cast<__nv_bfloat16*>(stg + lane * kStgPitch + (half * 4 + q) * 16), o);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3), piece = lane & 7;
+            const int m = __shfl_sync(0xffffffffu, meta, rr);
+            const int n = n0 + cp * 64 + piece * 8;
+            if (m >= 0 && n < Nout) {
+              const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + piece * 16);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sc.ret_y[(m >> 24) & 7]) +
+                                        (int64_t)(m & 0xffffff) * Nout + n) = val;
+            }
+          }
+          __syncwarp();
+        }
+      } else if (GEGLU) {
 #pragma unroll 1
         for (int c = 0; c < kTileN / 32; ++c) {
           uint32_t g[32], u[32];

@@ -69,6 +69,7 @@ class ExpertParallelMOE(nn.Module):
         self.d_ff = hidden_size * expansion_factor if d_ff is None else d_ff
         self.top_k = top_k
         self.epoch = 0
+        self.flags = _cabi.FLAG_DEFAULT
         self._plan = _Plan()
         self._state = None
         self.last = None
@@ -143,7 +144,7 @@ class ExpertParallelMOE(nn.Module):
             self.epoch += 1
             check(lib.moe_b200_ep_forward(
                 x.data_ptr(), self.gate.weight.data_ptr(), self.gate.bias.data_ptr(), plan, res_ptr,
-                N, d, f, E, k, dtype, self.rank, self.world, self.epoch, st["owner"], st["bases"],
+                N, d, f, E, k, dtype, self.flags, self.rank, self.world, self.epoch, st["owner"], st["bases"],
                 st["ws_base"], st["ws_bytes"], out.data_ptr(), _stream(dev)), "ep_forward")
         self.last = {
             "logits": self._ws_view("logits", torch.float32, (N, E)),

@@ -97,3 +97,17 @@ def load_into(module, params: dict, dtype: torch.dtype, device) -> None:
             ex.gate_and_up.bias.copy_(params["b1"][e])
             ex.down.weight.copy_(params["w2"][e])
             ex.down.bias.copy_(params["b2"][e])
+
+
+def make_gate(d: int, E: int, seed: int = 0, gate_bias_kind: str = "zero"):
+    """gate_w [E,d], gate_b [E]: the first draws of ``make_params`` with the same seed."""
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(E, d, generator=g) * 0.02, gate_bias(gate_bias_kind, E)
+
+
+def make_expert(d: int, f: int, e: int, seed: int = 0) -> dict:
+    """One expert's fp32 parameters from its own generator (seed, e), so that a rank
+    of the expert-parallel configuration draws only the experts it owns."""
+    g = torch.Generator().manual_seed(1000003 * (seed + 1) + e)
+    return {"w1": torch.randn(2 * f, d, generator=g) * 0.02, "b1": torch.zeros(2 * f),
+            "w2": torch.randn(d, f, generator=g) * 0.02, "b2": torch.zeros(d)}

@@ -63,7 +63,11 @@ enum {
    * arithmetic to check the tensor-core kernel against. */
   MOE_B200_FLAG_SIMT_EXPERTS = 1,
   /* never take the small-N weight-streaming path inside moe_b200_forward */
-  MOE_B200_FLAG_NO_DECODE_PATH = 2
+  MOE_B200_FLAG_NO_DECODE_PATH = 2,
+  /* expert-parallel: write the expert outputs locally and return them to the
+   * token owners with a separate copy kernel instead of from the down pass's
+   * epilogue (for comparison) */
+  MOE_B200_FLAG_EP_UNFUSED_RETURN = 4
 };
 
 /* Indices into the array filled by moe_b200_workspace_layout. */
@@ -247,7 +251,9 @@ enum {
   MOE_B200_EP_WS_AUX,          /* loss over all N_local*world tokens (model.py:213-216) */
   MOE_B200_EP_WS_SCRATCH, MOE_B200_EP_WS_CNT_SLOT0, /* int32 [E], all ranks */
   MOE_B200_EP_WS_OFFSETS_LOCAL, /* int32 [E_local+1] rows received per owned expert */
-  MOE_B200_EP_WS_OWNER, MOE_B200_EP_WS_H, MOE_B200_EP_WS_NUM
+  MOE_B200_EP_WS_OWNER, MOE_B200_EP_WS_H,
+  MOE_B200_EP_WS_Y,            /* bf16 [cap][d], used only with MOE_B200_FLAG_EP_UNFUSED_RETURN */
+  MOE_B200_EP_WS_NUM
 };
 size_t moe_b200_ep_symm_bytes(int64_t N_local, int d, int E, int k, int world);
 int moe_b200_ep_symm_layout(int64_t N_local, int d, int E, int k, int world, size_t* h_offsets);
@@ -264,7 +270,7 @@ int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, in
  * arrives makes the bounded waits run out: status word = MOE_B200_DEV_TIMEOUT. */
 int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
                         const void* residual, int64_t N_local, int d, int f, int E, int k,
-                        int dtype, int rank, int world, uint32_t epoch,
+                        int dtype, int flags, int rank, int world, uint32_t epoch,
                         const int32_t* h_expert_owner, void* const* h_symm_bases,
                         void* workspace, size_t workspace_bytes, void* out, void* stream);
 
