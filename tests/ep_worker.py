@@ -22,8 +22,8 @@ from oracle import moe_oracle  # noqa: E402
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=2048)   # total over all ranks
-    ap.add_argument("--d", type=int, default=256)
-    ap.add_argument("--f", type=int, default=384)
+    ap.add_argument("--dmodel", type=int, default=256)
+    ap.add_argument("--dff", type=int, default=384)
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--topk", type=int, default=4)
     ap.add_argument("--bias", default="zipf1.1")
@@ -33,7 +33,7 @@ def main():
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
-    N, d, f, E, k = args.tokens, args.d, args.f, args.experts, args.topk
+    N, d, f, E, k = args.tokens, args.dmodel, args.dff, args.experts, args.topk
     assert N % world == 0
     Nl = N // world
     dt = torch.bfloat16

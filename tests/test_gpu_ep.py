@@ -31,5 +31,5 @@ def test_ep_multi_gpu(cuda_device, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     run_workers(world, ["--tokens", "4096", "--experts", "16", "--topk", "4"], port=29542 + world)
-    run_workers(world, ["--tokens", "2048", "--experts", "64", "--topk", "4", "--d", "512", "--f", "704",
+    run_workers(world, ["--tokens", "2048", "--experts", "64", "--topk", "4", "--dmodel", "512", "--dff", "704",
                         "--placement", "lpt"], port=29552 + world)
