@@ -15,6 +15,7 @@ LIB_PATH = Path(os.environ.get("MOE_B200_LIB") or Path(__file__).resolve().paren
 
 F32, BF16 = 0, 1
 FLAG_DEFAULT, FLAG_SIMT_EXPERTS, FLAG_NO_DECODE_PATH, FLAG_EP_UNFUSED_RETURN = 0, 1, 2, 4
+FLAG_ONE_CTA = 8
 DEV_OK, DEV_TIMEOUT, DEV_BAD_INDEX = 0, 1, 2
 
 WS_NAMES = (

@@ -180,8 +180,12 @@ int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
   if (M == 0) return 0;
   if (!perm || !offsets || !plan || !h || !y || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
   if (!aligned16(perm) || !aligned16(h) || !aligned16(y)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
-  if (dtype == MOE_B200_BF16 && !(flags & MOE_B200_FLAG_SIMT_EXPERTS))
-    return launch_experts_tc(perm, offsets, plan, M, d, f, E, h, y, status, (cudaStream_t)stream);
+  if (dtype == MOE_B200_BF16 && !(flags & MOE_B200_FLAG_SIMT_EXPERTS)) {
+    if (flags & MOE_B200_FLAG_ONE_CTA)
+      return launch_experts_tc(perm, offsets, plan, M, d, f, E, h, y, status, (cudaStream_t)stream);
+    return launch_experts_tc2(perm, offsets, plan, M, d, f, E, h, y, nullptr, status,
+                              (cudaStream_t)stream);
+  }
   return launch_experts_simt(perm, offsets, plan, M, d, f, E, dtype, h, y, (cudaStream_t)stream);
 }
 

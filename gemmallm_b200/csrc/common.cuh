@@ -176,6 +176,9 @@ int launch_combine(const void* y, const int32_t* row_of, const float* w, const v
                    int64_t N, int d, int k, int dtype, void* out, cudaStream_t s);
 int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, int E, int d, int f,
                              void* h_tmaps /* kPlanMapsPerExpert*E*128 bytes */);
+int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
+                       int f, int E, void* h, void* y, const EpScatter* sc, int32_t* status,
+                       cudaStream_t s);
 int launch_experts_tc_ep(const void* recv_x, const int32_t* offsets, const void* plan, int64_t cap,
                          int d, int f, int E_local, void* h, const EpScatter& sc, int32_t* status,
                          cudaStream_t s);

@@ -186,15 +186,21 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
     // expert outputs to a local buffer first, then one copy kernel over NVLink
     void* y = ws + wo[MOE_B200_EP_WS_Y];
     if (E_local > 0) {
-      rc = launch_experts_tc(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h, y,
-                             status, s);
+      rc = (flags & MOE_B200_FLAG_ONE_CTA)
+               ? launch_experts_tc(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local,
+                                   h, y, status, s)
+               : launch_experts_tc2(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local,
+                                    h, y, nullptr, status, s);
       if (rc) return rc;
       rc = launch_ep_return(y, offsets_local, E_local, sc, d, s);
       if (rc) return rc;
     }
   } else {
-    rc = launch_experts_tc_ep(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h,
-                              sc, status, s);
+    rc = (flags & MOE_B200_FLAG_ONE_CTA)
+             ? launch_experts_tc_ep(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local,
+                                    h, sc, status, s)
+             : launch_experts_tc2(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h,
+                                  nullptr, &sc, status, s);
     if (rc) return rc;
   }
   rc = launch_ep_signal(peers, kEpFlagY, rank, world, epoch, s);

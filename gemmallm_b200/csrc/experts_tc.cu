@@ -7,10 +7,11 @@
 // Experts are grouped by the row offsets the dispatch kernel wrote; nothing is
 // read back to the host, every CTA derives the tile list from the offsets.
 //
-// One CTA per SM, 192 threads:
+// One CTA per SM, 320 threads:
 //   warp 0   : TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, 4 stages)
 //   warp 1   : MMA issuer    (tcgen05.mma cta_group::1 kind::f16, M=128 N=256 K=16)
-//   warps 2-5: epilogue      (tcgen05.ld 32 lanes x 32 columns, bias, GeGLU, store)
+//   warps 2-9: epilogue      (tcgen05.ld 32 lanes x 32 columns, bias, GeGLU, store);
+//              two warps per TMEM lane quadrant, each taking half of the columns
 // The 512 TMEM columns hold two 128x256 fp32 accumulators, so the epilogue of
 // one tile runs under the main loop of the next.
 //
@@ -23,6 +24,7 @@
 #include <cuda.h>
 #include "common.cuh"
 #include "tc_ptx.cuh"
+#include "tc_epilogue.cuh"
 
 namespace moe {
 
@@ -37,10 +39,9 @@ constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2;          // 16 KiB
 constexpr int kBHalfBytes = (BN / 2) * BK * 2;  // 16 KiB
 constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kTmemCols = 2 * BN;             // two accumulators
 constexpr uint32_t kIdesc = make_idesc(BN);
-constexpr int kStgPitch = 144;
 
 struct Control {
   uint64_t full[kStages];
@@ -89,7 +90,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 128); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 256); }
     ctl->abort = 0;
     int acc = 0;
     int beg = offsets[0];
@@ -197,6 +198,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ---------------- epilogue: 4 warps, one accumulator row per thread ----------------
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns
     const int r = quad * 32 + lane;
     uint32_t acc_phase = 0;
     int it = 0;
@@ -218,93 +220,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
-      __nv_bfloat16* orow = out + (int64_t)row * Nout + n0;
-      if (SCATTER) {
-        // Rows go to their token owners over NVLink. Registers hold one row per
-        // thread; stage 64 columns per row in shared memory and let 8 lanes write
-        // each row's 128 bytes, so that the peer stores are 128-byte runs.
-        const int meta = row_ok ? __ldg(&sc.meta[row]) : -1;
-        uint8_t* stg = ctl->stage_out[quad];
-#pragma unroll 1
-        for (int cp = 0; cp < kTileN / 64; ++cp) {
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int c = cp * 2 + half;
-            uint32_t v[32];
-            tc_ld32(taddr + c * 32, v);
-            tc_ld_wait();
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int n = n0 + c * 32 + q * 8;
-              float b[8], o[8];
-              if (n < Nout) {
-                load8_ldg(bias + n, b);
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) b[i] = 0.f;
-              }
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(v[q * 8 + i]) + b[i];
-              store8(reinterpret_cast<__nv_bfloat16*>(stg + lane * kStgPitch + (half * 4 + q) * 16), o);
-            }
-          }
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + (lane >> 3), piece = lane & 7;
-            const int m = __shfl_sync(0xffffffffu, meta, rr);
-            const int n = n0 + cp * 64 + piece * 8;
-            if (m >= 0 && n < Nout) {
-              const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + piece * 16);
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sc.ret_y[(m >> 24) & 7]) +
-                                        (int64_t)(m & 0xffffff) * Nout + n) = val;
-            }
-          }
-          __syncwarp();
-        }
-      } else if (GEGLU) {
-#pragma unroll 1
-        for (int c = 0; c < kTileN / 32; ++c) {
-          uint32_t g[32], u[32];
-          tc_ld32(taddr + c * 32, g);
-          tc_ld32(taddr + BN / 2 + c * 32, u);
-          tc_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int n = n0 + c * 32 + q * 8;
-            if (n < Nout) {
-              float bg[8], bu[8], o[8];
-              load8_ldg(bias + n, bg);
-              load8_ldg(bias + Nout + n, bu);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float gv = __uint_as_float(g[q * 8 + i]) + bg[i];
-                float uv = __uint_as_float(u[q * 8 + i]) + bu[i];
-                o[i] = gelu_tanh_fast(gv) * uv;
-              }
-              if (row_ok) store8(orow + c * 32 + q * 8, o);
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < kTileN / 32; ++c) {
-          uint32_t v[32];
-          tc_ld32(taddr + c * 32, v);
-          tc_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int n = n0 + c * 32 + q * 8;
-            if (n < Nout) {
-              float b[8], o[8];
-              load8_ldg(bias + n, b);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(v[q * 8 + i]) + b[i];
-              if (row_ok) store8(orow + c * 32 + q * 8, o);
-            }
-          }
-        }
-      }
+      store_tile<GEGLU, SCATTER>(taddr, row, row_ok, n0, Nout, bias, out, sc, ctl->stage_out[quad], lane, half);
       tc_fence_before();
       mbar_arrive(&ctl->tmem_empty[a]);
       if (a == 1) acc_phase ^= 1u;

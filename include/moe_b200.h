@@ -67,7 +67,10 @@ enum {
   /* expert-parallel: write the expert outputs locally and return them to the
    * token owners with a separate copy kernel instead of from the down pass's
    * epilogue (for comparison) */
-  MOE_B200_FLAG_EP_UNFUSED_RETURN = 4
+  MOE_B200_FLAG_EP_UNFUSED_RETURN = 4,
+  /* bf16 expert products on the one-CTA kernel (cta_group::1, 128-row tiles)
+   * instead of CTA pairs (cta_group::2, 256-row tiles) */
+  MOE_B200_FLAG_ONE_CTA = 8
 };
 
 /* Indices into the array filled by moe_b200_workspace_layout. */

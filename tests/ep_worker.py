@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--topk", type=int, default=4)
     ap.add_argument("--bias", default="zipf1.1")
     ap.add_argument("--placement", default="strided")
+    ap.add_argument("--flags", type=int, default=0)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -51,6 +52,7 @@ def main():
     if args.placement == "lpt":
         placement = lpt_placement([1.0 / (e + 1) ** 1.1 for e in range(E)], world)
     m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement).eval()
+    m.flags = args.flags
     m.to(device=dev, dtype=dt)
     with torch.no_grad():
         m.gate.weight.copy_(params["gate_w"])

@@ -22,8 +22,10 @@ def run_workers(world, extra=(), port=29541):
     assert r.stdout.count("EP_OK") == world, r.stdout[-3000:]
 
 
-def test_ep_world_1(cuda_device):
-    run_workers(1, ["--tokens", "1000", "--experts", "8", "--topk", "2"], port=29541)
+@pytest.mark.parametrize("flags", [0, 4, 8])   # default; unfused return; one-CTA GEMM kernel
+def test_ep_world_1(cuda_device, flags):
+    run_workers(1, ["--tokens", "1000", "--experts", "8", "--topk", "2", "--flags", str(flags)],
+                port=29541)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])

@@ -148,7 +148,7 @@ def test_experts_fp32(cuda_device, rows, d, f):
     assert (y.cpu() - y_ref).abs().max() <= 1e-4
 
 
-@pytest.mark.parametrize("flags", [_cabi.FLAG_DEFAULT, _cabi.FLAG_SIMT_EXPERTS])
+@pytest.mark.parametrize("flags", [_cabi.FLAG_DEFAULT, _cabi.FLAG_ONE_CTA, _cabi.FLAG_SIMT_EXPERTS])
 @pytest.mark.parametrize("rows,d,f", EXPERT_CASES)
 def test_experts_bf16(cuda_device, rows, d, f, flags):
     params, x, offsets = expert_inputs(rows, d, f, torch.bfloat16, seed=len(rows) + d)
