@@ -42,6 +42,8 @@ SIGNATURES = {
     "moe_b200_dispatch_static": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                                       _vp, _vp, _vp]),
     "moe_b200_experts": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "moe_b200_front_small": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
+                                  _vp, _vp, _vp, _vp]),
     "moe_b200_experts_decode": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "moe_b200_decode_splits": (_i, [_i]),
     "moe_b200_decode_max_rows": (_i64, []),

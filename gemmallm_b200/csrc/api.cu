@@ -189,6 +189,23 @@ int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
   return launch_experts_simt(perm, offsets, plan, M, d, f, E, dtype, h, y, (cudaStream_t)stream);
 }
 
+int moe_b200_front_small(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E,
+                         int k, int dtype, float* out_logits, int32_t* out_idx, float* out_w,
+                         int32_t* cnt_slot, int32_t* offsets, int32_t* row_of, void* perm,
+                         float* psum, float* aux, void* stream) {
+  int rc = check_shape(N, d, 8, E, k, dtype);
+  if (rc) return rc;
+  if (!front_small_supported(N, E, k, dtype))
+    return set_error(MOE_B200_ERR_UNSUPPORTED,
+                     "moe_b200_front_small needs bf16, 1 <= N <= 128, N*k <= 256, E <= 32");
+  if (!x || !Wg || !bg || !out_idx || !out_w || !cnt_slot || !offsets || !row_of || !perm || !psum || !aux)
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(x) || !aligned16(Wg) || !aligned16(perm))
+    return set_error(MOE_B200_ERR_ALIGN, "x, Wg and perm must be 16-byte aligned");
+  return launch_front_small(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets,
+                            row_of, perm, psum, aux, (cudaStream_t)stream);
+}
+
 int moe_b200_decode_splits(int f) { return f >= 8 ? decode_splits(f) : 0; }
 
 int64_t moe_b200_decode_max_rows(void) { return kDecodeMaxRows; }
@@ -260,11 +277,18 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
                        !(flags & (MOE_B200_FLAG_SIMT_EXPERTS | MOE_B200_FLAG_NO_DECODE_PATH));
 
   MOE_CUDA_CHECK(cudaMemsetAsync(status, 0, 16 * sizeof(int32_t), s));
-  rc = moe_b200_router(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, psum_part, status, stream);
-  if (rc) return rc;
-  rc = moe_b200_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
-                         N > 0 ? psum_part : nullptr, psum, aux, status, stream);
-  if (rc) return rc;
+  if (small_n && front_small_supported(N, E, k, dtype)) {
+    // router and dispatch of a handful of tokens in one single-block launch
+    rc = moe_b200_front_small(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, cnt_slot, offsets,
+                              row_of, perm, psum, aux, stream);
+    if (rc) return rc;
+  } else {
+    rc = moe_b200_router(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, psum_part, status, stream);
+    if (rc) return rc;
+    rc = moe_b200_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
+                           N > 0 ? psum_part : nullptr, psum, aux, status, stream);
+    if (rc) return rc;
+  }
   if (small_n) {
     // few tokens per expert: weight streaming with narrow tiles and split-K
     rc = moe_b200_experts_decode(perm, offsets, plan, N * k, d, f, E, h, part, status, stream);

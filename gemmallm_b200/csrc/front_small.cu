@@ -1,0 +1,275 @@
+// Router and dispatch of a small-N ("decode") call in ONE launch of ONE block:
+// with at most 128 tokens the separate router and cooperative dispatch kernels
+// are pure launch and barrier latency (13 + 15 us against a few us of work).
+// Covers reference model.py:206-253 for N <= 128, N*k <= 256, E <= 32, bf16:
+//   A. logits: 32 warps = (16-token group) x (slice of K); each warp forms its
+//      partial x Wg^T with mma.sync m16n8k16 exactly like router_mma_kernel
+//      (router.cu), all its loads in flight at once; partials are summed over
+//      the K slices in slice order, plus bias;
+//   B. one thread per token: fp32 softmax, k passes of arg-max ordered by
+//      (logit desc, index asc), renormalise; probabilities summed per expert in
+//      token order; loss;
+//   C. per-slot counts, offsets (scan over E), stable ranks in (token, slot)
+//      order, row copies into the sorted buffer with 16-byte accesses.
+#include "common.cuh"
+
+namespace moe {
+
+namespace {
+
+constexpr int kThreads = 1024;
+constexpr int kMaxTok = 128;
+constexpr int kMaxE = 32;
+constexpr int kMaxPairs = 256;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT>  // n-tiles of 8 experts: E <= 8*NT
+__global__ void __launch_bounds__(kThreads, 1)
+front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ Wg,
+                   const __nv_bfloat16* __restrict__ bg, int N, int d, int E, int k,
+                   float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
+                   float* __restrict__ out_w, int32_t* __restrict__ cnt_slot,
+                   int32_t* __restrict__ offsets, int32_t* __restrict__ row_of,
+                   __nv_bfloat16* __restrict__ perm, float* __restrict__ psum,
+                   float* __restrict__ aux) {
+  extern __shared__ float smem[];
+  const int ld = E + 1;
+  const int ngroups = (N + 15) >> 4;                       // 16-token groups
+  int gp2 = 1;
+  while (gp2 < ngroups) gp2 <<= 1;                         // 1, 2, 4 or 8
+  const int nslices = 32 / gp2;                            // K slices
+  float* s_part = smem;                                    // [nslices][16*gp2][8*NT]
+  float* s_logit = s_part + (size_t)nslices * 16 * gp2 * 8 * NT;   // [kMaxTok][E+1]
+  int* s_idx = reinterpret_cast<int*>(s_logit + (size_t)kMaxTok * ld);  // [kMaxPairs]
+  int* s_row = s_idx + kMaxPairs;                          // [kMaxPairs]
+  int* s_cnt = s_row + kMaxPairs;                          // [kMaxTopK][kMaxE]
+  int* s_off = s_cnt + kMaxTopK * kMaxE;                   // [kMaxE+1]
+  int* s_run = s_off + kMaxE + 1;                          // [kMaxE]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int ET = 8 * NT;
+
+  // ---- A. partial logits -----------------------------------------------------
+  {
+    const int tg = warp % gp2, ks = warp / gp2;
+    if (tg < ngroups) {
+      const int tok0 = tg * 16;
+      const int row_pieces = d >> 3;
+      const int ra = min(tok0 + g, N - 1), rb = min(tok0 + g + 8, N - 1);
+      const uint4* xa = reinterpret_cast<const uint4*>(x + (size_t)ra * d);
+      const uint4* xb = reinterpret_cast<const uint4*>(x + (size_t)rb * d);
+      const uint4* w4 = reinterpret_cast<const uint4*>(Wg);
+      const int nchunk = (d + 31) >> 5;
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      float acc[NT][4];
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+      for (int c0 = ks; c0 < nchunk; c0 += nslices * 4) {
+        uint4 A[4], B[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * nslices;
+          const int piece = 4 * c + t;
+          const bool ok = c < nchunk && piece < row_pieces;
+          A[u] = ok ? __ldg(xa + piece) : zero;
+          B[u] = ok ? __ldg(xb + piece) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * nslices;
+          const int piece = 4 * c + t;
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            const int row = 8 * j + g;
+            const uint4 w = (row < E && c < nchunk && piece < row_pieces)
+                                ? __ldg(w4 + (size_t)row * row_pieces + piece) : zero;
+            mma_bf16_16816(acc[j], A[u].x, B[u].x, A[u].y, B[u].y, w.x, w.y);
+            mma_bf16_16816(acc[j], A[u].z, B[u].z, A[u].w, B[u].w, w.z, w.w);
+          }
+        }
+      }
+      float* pp = s_part + ((size_t)ks * 16 * gp2 + tok0) * ET;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int e = 8 * j + 2 * t;
+        pp[g * ET + e] = acc[j][0];
+        pp[g * ET + e + 1] = acc[j][1];
+        pp[(g + 8) * ET + e] = acc[j][2];
+        pp[(g + 8) * ET + e + 1] = acc[j][3];
+      }
+    }
+  }
+  for (int i = tid; i < kMaxTopK * kMaxE; i += kThreads) s_cnt[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < N * E; i += kThreads) {
+    const int tok = i / E, e = i - tok * E;
+    float s = 0.f;
+    for (int ks = 0; ks < nslices; ++ks) s += s_part[((size_t)ks * 16 * gp2 + tok) * ET + e];
+    s += __bfloat162float(bg[e]);
+    s_logit[tok * ld + e] = s;
+    if (out_logits != nullptr) out_logits[i] = s;
+  }
+  __syncthreads();
+
+  // ---- B. softmax, top-k, renormalise: one thread per token --------------------
+  if (tid < N) {
+    float* lg = s_logit + tid * ld;
+    float m = -INFINITY;
+    for (int e = 0; e < E; ++e) m = fmaxf(m, lg[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) sum += expf(lg[e] - m);
+    int sel[kMaxTopK];
+    float sl[kMaxTopK], vals[kMaxTopK];
+    float total = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; ++j) {
+      if (j < k) {
+        float bl = -INFINITY;
+        int be = 0;
+        for (int e = 0; e < E; ++e) {
+          const float v = lg[e];
+          if (v > bl) { bl = v; be = e; }
+        }
+        sel[j] = be;
+        sl[j] = bl;
+        vals[j] = expf(bl - m) / sum;
+        total += vals[j];
+        lg[be] = -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxTopK; ++j) {
+      if (j < k) {
+        lg[sel[j]] = sl[j];
+        out_idx[tid * k + j] = sel[j];
+        out_w[tid * k + j] = vals[j] / total;
+        s_idx[tid * k + j] = sel[j];
+        atomicAdd(&s_cnt[j * kMaxE + sel[j]], 1);
+      }
+    }
+    for (int e = 0; e < E; ++e) lg[e] = expf(lg[e] - m) / sum;
+  }
+  __syncthreads();
+
+  // ---- C. counts, offsets, loss, ranks -----------------------------------------
+  if (tid < E) {
+    int tot = 0;
+    for (int j = 0; j < k; ++j) {
+      const int c = s_cnt[j * kMaxE + tid];
+      cnt_slot[j * E + tid] = c;
+      tot += c;
+    }
+    s_run[tid] = tot;          // total rows of this expert, until the scan below
+    float ps = 0.f;
+    for (int tok = 0; tok < N; ++tok) ps += s_logit[tok * ld + tid];
+    psum[tid] = ps;
+    s_part[tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0;
+    float a = 0.f;
+    for (int e = 0; e < E; ++e) {
+      s_off[e] = acc;
+      offsets[e] = acc;
+      acc += s_run[e];
+      a += s_part[e];
+    }
+    s_off[E] = acc;
+    offsets[E] = acc;
+    aux[0] = a / (float)E * (float)(E * E);   // model.py:213-216
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int npair = N * k;
+    for (int e = lane; e < E; e += 32) s_run[e] = 0;
+    __syncwarp();
+    for (int p0 = 0; p0 < npair; p0 += 32) {
+      const int p = p0 + lane;
+      const int e = p < npair ? s_idx[p] : -1;
+      const bool ok = e >= 0;
+      const unsigned grp = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+      int row = -1;
+      if (ok) row = s_off[e] + s_run[e] + __popc(grp & ((1u << lane) - 1u));
+      __syncwarp();
+      if (ok && (grp >> lane) == 1u) s_run[e] += __popc(grp);
+      __syncwarp();
+      if (p < npair) {
+        s_row[p] = row;
+        row_of[p] = row;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- D. copy the token rows into the sorted buffer ----------------------------
+  const int pieces = d >> 3;
+  const int items = N * pieces;
+  const uint4* src = reinterpret_cast<const uint4*>(x);
+  constexpr int kInFlight = 4;
+  for (int i0 = tid; i0 < items; i0 += kThreads * kInFlight) {
+    uint4 v[kInFlight];
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int i = i0 + u * kThreads;
+      if (i < items) v[u] = __ldg(src + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int i = i0 + u * kThreads;
+      if (i < items) {
+        const int tok = i / pieces, pc = i - tok * pieces;
+        for (int j = 0; j < k; ++j)
+          reinterpret_cast<uint4*>(perm + (size_t)s_row[tok * k + j] * d)[pc] = v[u];
+      }
+    }
+  }
+}
+
+template <int NT>
+int launch(const void* x, const void* Wg, const void* bg, int N, int d, int E, int k,
+           float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot, int32_t* offsets,
+           int32_t* row_of, void* perm, float* psum, float* aux, cudaStream_t s) {
+  const size_t smem = sizeof(float) * ((size_t)32 * 16 * 8 * NT + (size_t)kMaxTok * (E + 1)) +
+                      sizeof(int) * (2 * kMaxPairs + kMaxTopK * kMaxE + 2 * kMaxE + 1);
+  static bool attr_set = false;
+  if (!attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    attr_set = true;
+  }
+  front_small_kernel<NT><<<1, kThreads, smem, s>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
+      static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, cnt_slot,
+      offsets, row_of, static_cast<__nv_bfloat16*>(perm), psum, aux);
+  MOE_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace
+
+bool front_small_supported(int64_t N, int E, int k, int dtype) {
+  return dtype == MOE_B200_BF16 && N >= 1 && N <= kMaxTok && N * k <= kMaxPairs && E <= kMaxE;
+}
+
+int launch_front_small(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+                       float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot,
+                       int32_t* offsets, int32_t* row_of, void* perm, float* psum, float* aux,
+                       cudaStream_t s) {
+  if (E <= 8) return launch<1>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, s);
+  if (E <= 16) return launch<2>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, s);
+  return launch<4>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, s);
+}
+
+}  // namespace moe

@@ -193,6 +193,16 @@ int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
                      int64_t M, int d, int f, int E, int dtype, int flags,
                      void* h, void* y, int32_t* status, void* stream);
 
+/* Parts 1+2 for a handful of tokens in ONE single-block launch: same results as
+ * moe_b200_router followed by moe_b200_dispatch (model.py:206-253), for bf16,
+ * 1 <= N <= 128, N*k <= 256, E <= 32; other shapes return
+ * MOE_B200_ERR_UNSUPPORTED. psum [E] and aux [1] are final (no partial sums). */
+int moe_b200_front_small(const void* x, const void* Wg, const void* bg,
+                         int64_t N, int d, int E, int k, int dtype,
+                         float* out_logits, int32_t* out_idx, float* out_w,
+                         int32_t* cnt_slot, int32_t* offsets, int32_t* row_of, void* perm,
+                         float* psum, float* aux, void* stream);
+
 /* Part 3, small-N ("decode") variant, bf16 only, M <= moe_b200_decode_max_rows():
  * the same products as moe_b200_experts, arranged for weight streaming when
  * only a few rows reach each expert (the reference runs the same

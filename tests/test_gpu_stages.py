@@ -50,6 +50,44 @@ def test_router_matches_oracle(cuda_device, N, d, E, k, dtype):
     assert (idx.sort(dim=1).values.diff(dim=1) > 0).all() if k > 1 else True
 
 
+@pytest.mark.parametrize("N,d,E,k", [(1, 1024, 8, 2), (8, 1024, 8, 2), (17, 256, 16, 4), (64, 1024, 8, 2),
+                                     (100, 72, 5, 2), (128, 128, 32, 2), (33, 64, 24, 7)])
+def test_front_small_equals_router_plus_dispatch(cuda_device, N, d, E, k):
+    """The single-launch small-N front end gives what the two general kernels give."""
+    dt = torch.bfloat16
+    x, gw, gb = make_gate(N, d, E, dt, seed=N + E)
+    xd, gwd, gbd = x.to(dt).to(cuda_device), gw.to(dt).to(cuda_device), gb.to(dt).to(cuda_device)
+    logits, idx, w, psum_part = helpers.router(xd, gwd, gbd, k)
+    ref = helpers.dispatch(xd, idx, E, psum_part)
+    dev = cuda_device
+    got = {"logits": torch.empty(N, E, dtype=torch.float32, device=dev),
+           "idx": torch.empty(N, k, dtype=torch.int32, device=dev),
+           "w": torch.empty(N, k, dtype=torch.float32, device=dev),
+           "cnt_slot": torch.empty(k, E, dtype=torch.int32, device=dev),
+           "offsets": torch.empty(E + 1, dtype=torch.int32, device=dev),
+           "row_of": torch.empty(N, k, dtype=torch.int32, device=dev),
+           "perm": torch.empty(N * k, d, dtype=dt, device=dev),
+           "psum": torch.empty(E, dtype=torch.float32, device=dev),
+           "aux": torch.zeros(1, dtype=torch.float32, device=dev)}
+    helpers.check(helpers.lib.moe_b200_front_small(
+        xd.data_ptr(), gwd.data_ptr(), gbd.data_ptr(), N, d, E, k, _cabi.BF16,
+        *[got[n].data_ptr() for n in ("logits", "idx", "w", "cnt_slot", "offsets", "row_of", "perm",
+                                      "psum", "aux")], helpers.stream(dev)), "front_small")
+    torch.cuda.synchronize()
+    assert (got["logits"] - logits).abs().max() <= 2e-5 * max(1.0, float(logits.abs().max()))
+    r = moe_oracle.route_from_logits(got["logits"].cpu(), k)
+    ok = ~moe_oracle.tie_rows(r["probs"], k)
+    assert torch.equal(got["idx"].cpu()[ok].long(), r["idx"][ok])
+    assert torch.allclose(got["w"].cpu()[ok], r["w"][ok], atol=2e-6, rtol=0)
+    if torch.equal(got["idx"], idx):     # same routing (always, unless a near-tie flips): same layout
+        for name in ("cnt_slot", "offsets", "row_of", "perm"):
+            assert torch.equal(got[name], ref[name]), name
+        assert torch.allclose(got["psum"], ref["psum"], rtol=1e-5, atol=1e-6)
+        assert abs(float(got["aux"]) - float(ref["aux"])) <= 1e-5 * abs(float(ref["aux"])) + 1e-7
+    else:
+        assert torch.equal(got["cnt_slot"].cpu().long(), r["cnt_slot"])
+
+
 DISPATCH_CASES = [(1, 64, 8, 2), (2, 64, 8, 2), (63, 64, 8, 2), (64, 64, 8, 2), (65, 64, 8, 2),
                   (129, 128, 8, 2), (1000, 256, 64, 4), (5000, 512, 8, 2), (333, 72, 5, 3),
                   (4097, 64, 256, 8), (40000, 64, 8, 2)]
