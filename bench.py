@@ -29,6 +29,9 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernels per step, from the ncu
+# captures summarised under profiles/ (GEGLU pass + down pass)
+NCU_TRAFFIC_BYTES = {"c1_uniform": 429.7e6 + 405.7e6, "c2_t64": 138.2e6 + 69.1e6}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 CPU_SAMPLE_TOKENS = 4096
 
@@ -371,9 +374,9 @@ def run_ours(args, wl):
                     "mode": e2e_mode},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
-            "roofline": {"kernel": "grouped_gemm_tc_kernel (GEGLU pass + down pass)",
+            "roofline": {"kernel": "grouped_gemm_tc2_kernel (GEGLU pass + down pass, CTA pairs)",
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
                          "peak_source": f"{peak_kind} bf16 burst", "flops_per_step": flops,
                          "ms": stage_ms["experts"]},
             "stages_ms": stage_ms,
@@ -389,9 +392,10 @@ def run_ours(args, wl):
             gbs_step = nbytes_step / (ms_step * 1e-3) / 1e9
             gbs_experts = wbytes / (stage_ms["experts"] * 1e-3) / 1e9
             line["roofline"] = {
-                "kernel": "grouped_gemm_tc_kernel, 64-row tiles (GEGLU pass + split-K down pass)",
+                "kernel": "decode_gemm_kernel (GEGLU pass + split-K down pass)",
                 "bound": "hbm", "achieved": gbs_experts, "peak": hbm, "unit": "GB/s",
-                "frac": gbs_experts / hbm, "traffic": None, "peak_source": f"{peak_kind} copy",
+                "frac": gbs_experts / hbm, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
+                "peak_source": f"{peak_kind} copy",
                 "bytes_per_step": wbytes, "experts_hit": hit, "ms": stage_ms["experts"],
                 "whole_step_gbs": gbs_step, "whole_step_frac": gbs_step / hbm}
         if world == 1 and not args.no_cpu_baseline:
@@ -538,7 +542,7 @@ def run_ep(args, wl):
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": 9 * args.steps,
             "clocks": clocks.summary(),
-            "roofline": {"kernel": "grouped_gemm_tc_kernel (GEGLU pass + down pass) on the busiest rank",
+            "roofline": {"kernel": "grouped_gemm_tc2_kernel (GEGLU pass + down pass) on the busiest rank",
                          "bound": "tensor", "achieved": busiest["tflops"], "peak": peak,
                          "unit": "TFLOP/s", "frac": busiest["tflops"] / peak, "traffic": None,
                          "peak_source": f"{peak_kind} bf16 burst", "ms": busiest["gemm_ms"]},

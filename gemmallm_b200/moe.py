@@ -30,6 +30,35 @@ def _stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _merged_lora(ex):
+    """The expert's two Linears with the LoRA branch folded in, as fresh tensors:
+    W' = W + s * B A and b' = b + s * (B a + b_lora), which makes
+    x W'^T + b' = x W^T + b + s * (B (A x + a) + b_lora), the fine_tuning=True
+    expression of model.py:175-179 and 185-189. Computed in fp32, stored in the
+    parameter dtype."""
+    s = ex.lora_scale
+    out = []
+    for lin, a, b in ((ex.gate_and_up, ex.lora_gate_and_up_a, ex.lora_gate_and_up_b),
+                      (ex.down, ex.lora_down_a, ex.lora_down_b)):
+        bw, aw = b.weight.float(), a.weight.float()
+        w = lin.weight.float() + s * (bw @ aw)
+        bias = lin.bias.float() + s * (bw @ a.bias.float() + b.bias.float())
+        out += [w.to(lin.weight.dtype).contiguous(), bias.to(lin.bias.dtype).contiguous()]
+    return out
+
+
+class _MergedExpert:
+    """Stand-in with the attribute shape _Plan expects (gate_and_up/down with .weight/.bias)."""
+
+    class _Lin:
+        def __init__(self, w, b):
+            self.weight, self.bias = w, b
+
+    def __init__(self, ex):
+        w1, b1, w2, b2 = _merged_lora(ex)
+        self.gate_and_up, self.down = self._Lin(w1, b1), self._Lin(w2, b2)
+
+
 class _Plan:
     """Device copy of the experts' parameter pointers and TMA tensor maps.
 
@@ -68,9 +97,8 @@ class FeedForward(nn.Module):
     """GeGLU feed-forward expert; mirrors reference model.py:154-190.
 
     ``gate_and_up`` maps d -> 2f (rows [0,f) gate, rows [f,2f) up), ``down`` maps
-    f -> d. The LoRA tensors exist so that checkpoints load strictly; the
-    ``fine_tuning=True`` branch (model.py:175-179,185-189) is not implemented
-    and raises.
+    f -> d, plus the four LoRA Linears of the reference (rank ``lora_rank``,
+    scale ``lora_alpha / lora_rank``), used when ``fine_tuning=True``.
 
     ``d_ff`` (keyword-only) sets f directly for widths that are not an integer
     multiple of ``hidden_size``."""
@@ -89,12 +117,13 @@ class FeedForward(nn.Module):
         self.lora_down_a = nn.Linear(f, lora_rank)
         self.lora_down_b = nn.Linear(lora_rank, hidden_size)
         self._plan = _Plan()
+        self._plan_ft = _Plan()
 
     def forward(self, tensor: torch.Tensor, fine_tuning: bool = False) -> torch.Tensor:
         """y = down(gelu_tanh(gate) * up) for every row, through the grouped
-        expert kernels with a single group."""
-        if fine_tuning:
-            raise NotImplementedError("the LoRA branch (fine_tuning=True) is not implemented")
+        expert kernels with a single group. ``fine_tuning=True`` adds the LoRA
+        branch (model.py:175-179,185-189) by folding it into the two weight
+        matrices for this call; forward only (the kernels have no backward)."""
         if self.training and self.dropout.p > 0:
             raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
         if not tensor.is_cuda:
@@ -105,7 +134,8 @@ class FeedForward(nn.Module):
         M, d, f = x.shape[0], self.hidden_size, self.d_ff
         dev = x.device
         with torch.cuda.device(dev):
-            plan = self._plan.get([self], d, f, dtype, dev)
+            plan = (self._plan_ft if fine_tuning else self._plan).get(
+                [_MergedExpert(self)] if fine_tuning else [self], d, f, dtype, dev)
             offsets = torch.tensor([0, M], dtype=torch.int32, device=dev)
             status = torch.zeros(16, dtype=torch.int32, device=dev)
             h = torch.empty(M, f, dtype=x.dtype, device=dev)
@@ -140,6 +170,7 @@ class MOE(nn.Module):
         self.top_k = top_k
         self.flags = _cabi.FLAG_DEFAULT
         self._plan = _Plan()
+        self._plan_ft = _Plan()
         self._ws = None
         self._ws_key = None
         self.last = None  # views into the workspace of the most recent call
@@ -170,9 +201,9 @@ class MOE(nn.Module):
         """``tensor`` [B,S,d] -> ([B,S,d] in the input dtype, load-balancing loss).
 
         With ``residual`` (same shape and dtype) the caller's skip connection
-        (model.py:319) is added inside the combine kernel."""
-        if fine_tuning:
-            raise NotImplementedError("the LoRA branch (fine_tuning=True) is not implemented")
+        (model.py:319) is added inside the combine kernel. ``fine_tuning=True``
+        runs the experts with their LoRA branches (model.py:175-179,185-189)
+        folded into per-call merged weights; forward only."""
         if self.training and self.experts[0].dropout.p > 0:
             raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
         if not tensor.is_cuda:
@@ -196,7 +227,11 @@ class MOE(nn.Module):
             raise ValueError("gate parameters must share the input's device and dtype")
         out = torch.empty_like(x)
         with torch.cuda.device(dev):
-            plan = self._plan.get(self.experts, d, f, dtype, dev)
+            if fine_tuning:
+                merged = [_MergedExpert(ex) for ex in self.experts]   # kept alive until the call returns
+                plan = self._plan_ft.get(merged, d, f, dtype, dev)
+            else:
+                plan = self._plan.get(self.experts, d, f, dtype, dev)
             _, base, nbytes, _ = self._workspace(N, dtype, dev)
             check(lib.moe_b200_forward(x.data_ptr(), gw.data_ptr(), gb.data_ptr(), plan, res_ptr,
                                        N, d, f, E, k, dtype, self.flags, base, nbytes,

@@ -175,3 +175,41 @@ def test_state_survives_dtype_change_and_repeat_calls(cuda_device):
         c, _ = m(x.to(torch.bfloat16))
     assert c.dtype == torch.bfloat16
     assert (c.float() - a).abs().max() < 0.05 * a.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fine_tuning_lora_branch(cuda_device, dtype):
+    """fine_tuning=True (model.py:175-179,185-189): LoRA folded into merged weights."""
+    from test_oracle import lora_dicts
+    d, E, f, k, N = 128, 8, 256, 2, 600
+    params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=40), dtype)
+    x = synthetic.round_to(synthetic.make_input(N, d, seed=41), dtype)
+    torch.manual_seed(42)
+    m = build(params, d, E, f, k, dtype, cuda_device)
+    with torch.no_grad():
+        for ex in m.experts:          # LoRA tensors of a size that matters
+            for lin in (ex.lora_gate_and_up_a, ex.lora_gate_and_up_b, ex.lora_down_a, ex.lora_down_b):
+                lin.weight.normal_(0, 0.05)
+                lin.bias.normal_(0, 0.05)
+        out, aux = m(x.to(dtype).to(cuda_device).view(1, N, d), fine_tuning=True)
+        plain, _ = m(x.to(dtype).to(cuda_device).view(1, N, d))
+    torch.cuda.synchronize()
+    logits = m.last["logits"].cpu()
+    with torch.no_grad():
+        o = moe_oracle.moe_forward(x, params, k, logits=logits, lora=lora_dicts(m))
+    ok = ~moe_oracle.tie_rows(o["probs"], k)
+    err = (out.view(N, d).float().cpu() - o["out"])[ok].abs().max()
+    if dtype == torch.float32:
+        assert err <= 1e-4
+    else:
+        assert err <= 2e-2 * o["out"].abs().max()
+    assert (out.float() - plain.float()).abs().max() > 10 * err   # not the plain forward
+
+
+def test_empty_batch(cuda_device):
+    m = build(synthetic.make_params(64, 8, 128, seed=1), 64, 8, 128, 2, torch.bfloat16, cuda_device)
+    with torch.no_grad():
+        out, aux = m(torch.zeros(0, 4, 64, dtype=torch.bfloat16, device=cuda_device))
+    torch.cuda.synchronize()
+    assert out.shape == (0, 4, 64)
+    assert m.last["offsets"].cpu().tolist() == [0] * 9

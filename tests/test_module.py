@@ -66,7 +66,7 @@ def test_no_cpu_path_and_unimplemented_branches_raise():
     x = torch.zeros(1, 4, 32)
     with pytest.raises(RuntimeError, match="no CPU path"):
         m(x)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError, match="no CPU path"):
         m(x, fine_tuning=True)
     m.train()
     with pytest.raises(NotImplementedError):

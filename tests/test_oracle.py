@@ -99,3 +99,39 @@ def test_oracle_equals_reference_class():
         o = moe_oracle.moe_forward(x, params, 2)
     assert torch.equal(out.reshape(N, d), o["out"])
     assert torch.equal(aux, o["aux"])
+
+
+def lora_dicts(module):
+    """Per-expert LoRA tensors of a (reference or drop-in) MOE module, for the oracle."""
+    out = []
+    for ex in module.experts:
+        out.append({
+            "scale": ex.lora_scale,
+            "gu_a_w": ex.lora_gate_and_up_a.weight.detach().float().cpu(),
+            "gu_a_b": ex.lora_gate_and_up_a.bias.detach().float().cpu(),
+            "gu_b_w": ex.lora_gate_and_up_b.weight.detach().float().cpu(),
+            "gu_b_b": ex.lora_gate_and_up_b.bias.detach().float().cpu(),
+            "dn_a_w": ex.lora_down_a.weight.detach().float().cpu(),
+            "dn_a_b": ex.lora_down_a.bias.detach().float().cpu(),
+            "dn_b_w": ex.lora_down_b.weight.detach().float().cpu(),
+            "dn_b_b": ex.lora_down_b.bias.detach().float().cpu(),
+        })
+    return out
+
+
+@pytest.mark.skipif(not Path(REF_DIR, "model.py").exists(), reason="no reference checkout")
+def test_oracle_lora_branch_equals_reference_class():
+    sys.path.insert(0, REF_DIR)
+    from model import MOE
+    d, E, factor, N = 32, 4, 2, 64
+    params = synthetic.make_params(d, E, d * factor, seed=31)
+    x = synthetic.make_input(N, d, seed=32)
+    torch.manual_seed(33)
+    ref = MOE(d, num_experts=E, expansion_factor=factor, device="cpu").eval()   # default-initialised LoRA
+    synthetic.load_into(ref, params, torch.float32, "cpu")
+    with torch.no_grad():
+        out, aux = ref(x.reshape(2, N // 2, d), fine_tuning=True)
+        o = moe_oracle.moe_forward(x, params, 2, lora=lora_dicts(ref))
+        plain = moe_oracle.moe_forward(x, params, 2)
+    assert torch.equal(out.reshape(N, d), o["out"])
+    assert not torch.equal(o["out"], plain["out"])        # the branch does something
