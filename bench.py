@@ -102,6 +102,59 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+def pipelined_e2e(m, x_host, out_host, aux_host, N, d, dt, dev, steps, warm=3):
+    """End-to-end loop over three streams: every step copies its input from pinned host
+    memory, runs the block and copies output and loss back; copy-in of step i+1, compute
+    of step i and copy-out of step i-1 overlap, as a serving loop would. Returns the
+    CUDA-event time of `steps` steps in ms (all results on the host when it ends)."""
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_comp = torch.cuda.current_stream(dev)
+    x_bufs = [torch.empty(1, N, d, dtype=dt, device=dev) for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_done = []
+
+    def loop(n):
+        with torch.no_grad():
+            for i in range(n):
+                b = i & 1
+                with torch.cuda.stream(s_in):
+                    if i >= 2:
+                        s_in.wait_event(in_free[b])          # compute of step i-2 has read this buffer
+                    x_bufs[b].copy_(x_host.view(1, N, d), non_blocking=True)
+                    in_ready[b].record(s_in)
+                s_comp.wait_event(in_ready[b])
+                o, aux = m(x_bufs[b])
+                in_free[b].record(s_comp)
+                done = torch.cuda.Event()
+                done.record(s_comp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    out_host.copy_(o.view(N, d), non_blocking=True)
+                    aux_host.copy_(aux.view(1), non_blocking=True)
+                    o.record_stream(s_out)
+                    aux.record_stream(s_out)
+                    fin = torch.cuda.Event()
+                    fin.record(s_out)
+                out_done.append(fin)
+                if len(out_done) > 2:
+                    out_done.pop(0).synchronize()       # bounded queue: step i-2 is on the host
+                    _ = float(aux_host[0])
+            for ev in out_done:
+                ev.synchronize()
+            out_done.clear()
+
+    loop(warm)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    loop(steps)
+    torch.cuda.synchronize(dev)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1)
+
+
 def workload_config(wl, extra):
     cfg = {"workload": wl.name, "tokens": wl.tokens, "d_model": wl.d_model,
            "n_experts": wl.n_experts, "d_ff": wl.d_ff, "top_k": wl.top_k, "routing": wl.gate_bias}
@@ -293,52 +346,9 @@ def run_ours(args, wl):
             e2e_ms = max_over_ranks(e0.elapsed_time(e1))
         e2e_mode = "one CUDA graph per step, host waits for every step"
     else:
-        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        s_comp = torch.cuda.current_stream(dev)
-        x_bufs = [torch.empty(1, N, d, dtype=dt, device=dev) for _ in range(2)]
-        in_ready = [torch.cuda.Event() for _ in range(2)]
-        in_free = [torch.cuda.Event() for _ in range(2)]
-        out_done = []
-
-        def e2e_loop(steps):
-            with torch.no_grad():
-                for i in range(steps):
-                    b = i & 1
-                    with torch.cuda.stream(s_in):
-                        if i >= 2:
-                            s_in.wait_event(in_free[b])          # compute of step i-2 has read this buffer
-                        x_bufs[b].copy_(x_host.view(1, N, d), non_blocking=True)
-                        in_ready[b].record(s_in)
-                    s_comp.wait_event(in_ready[b])
-                    o, aux = m(x_bufs[b])
-                    in_free[b].record(s_comp)
-                    done = torch.cuda.Event()
-                    done.record(s_comp)
-                    with torch.cuda.stream(s_out):
-                        s_out.wait_event(done)
-                        out_host.copy_(o.view(N, d), non_blocking=True)
-                        aux_host.copy_(aux.view(1), non_blocking=True)
-                        o.record_stream(s_out)
-                        aux.record_stream(s_out)
-                        fin = torch.cuda.Event()
-                        fin.record(s_out)
-                    out_done.append(fin)
-                    if len(out_done) > 2:
-                        out_done.pop(0).synchronize()       # bounded queue: step i-2 is on the host
-                        loss = float(aux_host[0])
-                for ev in out_done:
-                    ev.synchronize()
-                out_done.clear()
-
-        e2e_loop(3)
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        e2e_loop(args.steps)
-        torch.cuda.synchronize()
-        e1.record()
+        e2e_ms = max_over_ranks(pipelined_e2e(m, x_host, out_host, aux_host, N, d, dt, dev, args.steps))
         barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1))
         e2e_mode = "three streams: copy-in, compute, copy-out of consecutive steps overlap"
     e2e_value = N * world * args.steps / (e2e_ms * 1e-3)
 
@@ -436,14 +446,20 @@ def run_ep(args, wl):
         from gemmallm_b200.ep import lpt_placement
         prior = torch.softmax(synthetic.gate_bias(wl.gate_bias, E), 0).tolist()
         placement = lpt_placement(prior, world)
-    m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement).eval()
+    replicate = None
+    if args.ep_replicate > 0:
+        # copies of the most popular experts (by the router-bias prior) on every rank
+        prior = torch.softmax(synthetic.gate_bias(wl.gate_bias, E), 0)
+        replicate = prior.topk(min(args.ep_replicate, E)).indices.tolist()
+    m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement,
+                          replicate=replicate).eval()
     m.flags = args.ep_flags
     m.to(device=dev, dtype=dt)
     gate_w, gate_b = synthetic.make_gate(d, E, 0, wl.gate_bias)
     with torch.no_grad():
         m.gate.weight.copy_(gate_w)
         m.gate.bias.copy_(gate_b)
-        for e in m.local_ids:
+        for e in sorted(set(m.local_ids)):
             p = synthetic.make_expert(d, f, e, 0)
             ex = m.experts[str(e)]
             ex.gate_and_up.weight.copy_(p["w1"])
@@ -479,22 +495,10 @@ def run_ep(args, wl):
         status = max_over_ranks(float(m.device_status()))
         if status != 0:
             raise RuntimeError(f"device status {status} after the timed region")
-        # end to end: pinned host input in, output and loss back, every step
-        x_dev = torch.empty(1, Nl, d, dtype=dt, device=dev)
-        for it in range(2 + args.steps):
-            if it == 2:
-                barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-            x_dev.copy_(x_host.view(1, Nl, d), non_blocking=True)
-            o, aux = m(x_dev)
-            out_host.copy_(o.view(Nl, d), non_blocking=True)
-            aux_host.copy_(aux.view(1), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            loss = float(aux_host[0])
-        e1.record()
+        # end to end: pinned host input in, output and loss back, every step (pipelined)
         barrier()
-        e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+        e2e_ms = max_over_ranks(pipelined_e2e(m, x_host, out_host, aux_host, Nl, d, dt, dev, args.steps))
+        barrier()
         # grouped GEMMs alone on this rank's received rows
         rows = int(m.last["offsets_local"][-1])
         st = m._state
@@ -535,11 +539,13 @@ def run_ep(args, wl):
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
             "config": workload_config(wl, {
                 "parallelism": f"ep{world}: tokens and experts sharded over {world} ranks, "
-                               f"{args.ep_placement} expert placement, peer-store all-to-all",
+                               f"{args.ep_placement} expert placement, {args.ep_replicate} hottest experts copied to every rank, "
+                               "peer-store all-to-all",
                 "l2": "per-rank working set (received rows, h, owned expert weights) exceeds the 126 MB L2"}),
             "e2e": {"value": N * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": Nl * d * es * world, "d2h_bytes_per_step": (Nl * d * es + 4) * world,
-                    "ms_per_step": e2e_ms / args.steps},
+                    "ms_per_step": e2e_ms / args.steps,
+                    "mode": "per rank three streams: copy-in, compute, copy-out of consecutive steps overlap"},
             "gpu_launches": 9 * args.steps,
             "clocks": clocks.summary(),
             "roofline": {"kernel": "grouped_gemm_tc2_kernel (GEGLU pass + down pass) on the busiest rank",
@@ -623,6 +629,9 @@ def main():
                     help="default: c1_uniform on one GPU, c4 (expert-parallel) on several")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-placement", default="strided", choices=["strided", "lpt"])
+    ap.add_argument("--ep-replicate", type=int, default=16,
+                    help="expert-parallel: copy the N most popular experts (by the router-bias prior) "
+                         "to every rank, on top of the even sharding; 0 = no copies")
     ap.add_argument("--ep-flags", type=int, default=0, help="flags for moe_b200_ep_forward")
     ap.add_argument("--no-graph", action="store_true", help="small-N workloads: time eager calls")
     ap.add_argument("--quick", action="store_true",

@@ -57,7 +57,7 @@ SIGNATURES = {
     "moe_b200_ep_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),
     "moe_b200_ep_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_ep_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
-                                 C.c_uint32, _vp, _vp, _vp, _sz, _vp, _vp]),
+                                 C.c_uint32, _i, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
     "moe_b200_read_status": (_i, [_vp, C.POINTER(C.c_int32), _vp]),
 }
 

@@ -149,7 +149,7 @@ enum { kEpFlagCnt = 0, kEpFlagX = 1, kEpFlagY = 2, kEpNumFlags = 3 };
 // Pointers into every rank's symmetric buffer (index = rank), valid on this GPU.
 struct EpPeers {
   uint32_t* flags[kEpMaxRanks];     // [kEpNumFlags][kEpMaxRanks] epoch words, one per (kind, source)
-  int32_t* cnt_all[kEpMaxRanks];    // [world][3E] per source: pair counts, slot-0 counts, psum bits
+  int32_t* cnt_all[kEpMaxRanks];    // [world][EV+2E] per source: pair counts, slot-0 counts, psum bits
   int32_t* recv_meta[kEpMaxRanks];  // [cap] return address of a received row: source << 24 | pair id
   void* recv_x[kEpMaxRanks];        // [cap][d] received token rows, grouped by owned expert
   void* ret_y[kEpMaxRanks];         // [N_local*k][d] expert outputs returned to the token owner
@@ -182,10 +182,11 @@ int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* pla
 int launch_experts_tc_ep(const void* recv_x, const int32_t* offsets, const void* plan, int64_t cap,
                          int d, int f, int E_local, void* h, const EpScatter& sc, int32_t* status,
                          cudaStream_t s);
-int64_t ep_scratch_ints(int64_t N, int E);
-int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
-                       const EpPeers& peers, int rank, int world, uint32_t epoch,
-                       const int32_t* expert_owner, int32_t* scratch, const float* psum_part,
+int64_t ep_scratch_ints(int64_t N, int EV, int E);
+int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int EV, int k,
+                       int dtype, const EpPeers& peers, int rank, int world, uint32_t epoch,
+                       const int32_t* owner, const int32_t* vmap, int32_t* scratch,
+                       const float* psum_part,
                        int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
                        int64_t n_total, int32_t* status, cudaStream_t s);
 int launch_ep_return(const void* y, const int32_t* offsets_local, int E_local, const EpScatter& sc,

@@ -3,7 +3,8 @@
 // multicast, no TMA on remote memory).
 //
 // Tokens are sharded over the G ranks (rank r owns N_local tokens), experts are
-// owned by rank expert_owner[e]; the router runs replicated on local tokens.
+// owned by ranks (optionally replicated, see ep_dispatch_kernel); the router runs
+// replicated on local tokens.
 // Every rank has one "symmetric" buffer of identical layout that its peers can
 // write (EpSymm below). Per forward, with a caller-supplied increasing epoch:
 //   1. ep_dispatch_kernel (cooperative): per-expert counts of the local
@@ -68,72 +69,83 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
   }
 }
 
+// Experts are addressed by "virtual" ids: vmap[e * world + source rank] is the
+// virtual expert that rank's pairs for expert e go to, and owner[v] the rank that
+// runs it. Without replication v == e. A popular expert can be given several
+// virtual ids owned by different ranks (same weights on each): every source rank
+// then sends its rows for that expert to one replica, which spreads the expert's
+// load and keeps part of its rows off NVLink. E counts real experts (routing
+// indices, loss); EV virtual experts (counts, layout).
 __global__ void __launch_bounds__(kThreads)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx, int64_t N, int row_pieces,
-                   int E, int k, EpPeers peers, int rank, int world, uint32_t epoch,
-                   const int32_t* __restrict__ expert_owner, int32_t* __restrict__ scratch,
-                   const float* __restrict__ psum_part, int64_t router_blocks,
-                   int32_t* __restrict__ cnt_slot0, float* __restrict__ psum_global,
-                   int32_t* __restrict__ offsets_local, float* __restrict__ aux, int64_t n_total,
-                   int32_t* __restrict__ status) {
+                   int E, int EV, int k, EpPeers peers, int rank, int world, uint32_t epoch,
+                   const int32_t* __restrict__ owner, const int32_t* __restrict__ vmap,
+                   int32_t* __restrict__ scratch, const float* __restrict__ psum_part,
+                   int64_t router_blocks, int32_t* __restrict__ cnt_slot0,
+                   float* __restrict__ psum_global, int32_t* __restrict__ offsets_local,
+                   float* __restrict__ aux, int64_t n_total, int32_t* __restrict__ status) {
   cg::grid_group grid = cg::this_grid();
   extern __shared__ int s_int[];
-  int* s_hist = s_int;                  // [E] local totals
-  int* s_base = s_hist + E;             // [E] local rows of earlier chunks
-  int* s_dest = s_base + E;             // [E] first row of (this rank, expert) at its owner
-  int* s_run = s_dest + E;              // [E]
-  int* s_owner = s_run + E;             // [E]
-  int* s_row = s_owner + E;             // [kChunk*k]
+  int* s_hist = s_int;                  // [EV] local totals per virtual expert
+  int* s_base = s_hist + EV;            // [EV] local rows of earlier chunks
+  int* s_dest = s_base + EV;            // [EV] first row of (this rank, virtual expert) at its owner
+  int* s_run = s_dest + EV;             // [EV]
+  int* s_owner = s_run + EV;            // [EV]
+  int* s_vmap = s_owner + EV;           // [E]  virtual expert of real expert e for this source rank
+  int* s_slot0 = s_vmap + E;            // [E]  slot-0 histogram (real experts)
+  int* s_row = s_slot0 + E;             // [kChunk*k]
   int* s_q = s_row + kChunk * k;        // [kChunk*k]
-  int* s_cnt = s_q + kChunk * k;        // [world][E] pair counts of every source rank
-  float* s_red = reinterpret_cast<float*>(s_cnt + world * E);  // [kThreads]
+  int* s_cnt = s_q + kChunk * k;        // [world][EV] pair counts of every source rank
+  float* s_red = reinterpret_cast<float*>(s_cnt + world * EV);  // [kThreads]
   __shared__ int s_fail;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = gridDim.x;
   const int64_t nchunk = (N + kChunk - 1) / kChunk;
-  int32_t* chunk_cnt = scratch;                       // [nchunk][E]
-  int32_t* blk_slot0 = chunk_cnt + nchunk * E;        // [G][E] slot-0 counts per block
-  const int row_ints = 3 * E;                         // published row: counts, slot-0 counts, psum bits
+  int32_t* chunk_cnt = scratch;                       // [nchunk][EV]
+  int32_t* blk_slot0 = chunk_cnt + nchunk * EV;       // [G][E] slot-0 counts per block
+  const int row_ints = EV + 2 * E;                    // published row: pair counts, slot-0 counts, psum bits
 
   // ---- phase 1: per-chunk histograms --------------------------------------
-  for (int e = tid; e < E; e += kThreads) { s_run[e] = 0; s_owner[e] = expert_owner[e]; }
+  for (int v = tid; v < EV; v += kThreads) s_owner[v] = owner[v];
+  for (int e = tid; e < E; e += kThreads) { s_slot0[e] = 0; s_vmap[e] = vmap[e * world + rank]; }
   if (tid == 0) s_fail = 0;
   __syncthreads();
   for (int64_t c = blockIdx.x; c < nchunk; c += G) {
-    for (int e = tid; e < E; e += kThreads) s_hist[e] = 0;
+    for (int v = tid; v < EV; v += kThreads) s_hist[v] = 0;
     __syncthreads();
     const int64_t t0 = c * kChunk;
     const int ntok = (int)((N - t0) < kChunk ? (N - t0) : kChunk);
     for (int p = tid; p < ntok * k; p += kThreads) {
       int e = idx[t0 * k + p];
       if ((unsigned)e >= (unsigned)E) { atomicMax(&status[0], MOE_B200_DEV_BAD_INDEX); continue; }
-      atomicAdd(&s_hist[e], 1);
-      if (p % k == 0) atomicAdd(&s_run[e], 1);   // s_run doubles as the slot-0 histogram here
+      atomicAdd(&s_hist[s_vmap[e]], 1);
+      if (p % k == 0) atomicAdd(&s_slot0[e], 1);
     }
     __syncthreads();
-    for (int e = tid; e < E; e += kThreads) chunk_cnt[c * E + e] = s_hist[e];
+    for (int v = tid; v < EV; v += kThreads) chunk_cnt[c * EV + v] = s_hist[v];
     __syncthreads();
   }
-  for (int e = tid; e < E; e += kThreads) blk_slot0[(size_t)blockIdx.x * E + e] = s_run[e];
+  for (int e = tid; e < E; e += kThreads) blk_slot0[(size_t)blockIdx.x * E + e] = s_slot0[e];
   grid.sync();
 
   // ---- phase 2: local totals; block 0 publishes this rank's row ------------
-  for (int e = tid; e < E; e += kThreads) { s_hist[e] = 0; s_base[e] = 0; }
+  for (int v = tid; v < EV; v += kThreads) { s_hist[v] = 0; s_base[v] = 0; }
   __syncthreads();
   const int64_t c0 = blockIdx.x;
-  for (int64_t i = tid; i < nchunk * E; i += kThreads) {
-    int v = __ldcg(&chunk_cnt[i]);
-    int64_t cc = i / E;
-    int e = (int)(i - cc * E);
-    if (v != 0) {
-      atomicAdd(&s_hist[e], v);
-      if (cc < c0) atomicAdd(&s_base[e], v);
+  for (int64_t i = tid; i < nchunk * EV; i += kThreads) {
+    int val = __ldcg(&chunk_cnt[i]);
+    int64_t cc = i / EV;
+    int v = (int)(i - cc * EV);
+    if (val != 0) {
+      atomicAdd(&s_hist[v], val);
+      if (cc < c0) atomicAdd(&s_base[v], val);
     }
   }
   __syncthreads();
   if (blockIdx.x == 0) {
     int32_t* my_row = peers.cnt_all[rank] + (size_t)rank * row_ints;
+    for (int v = tid; v < EV; v += kThreads) my_row[v] = s_hist[v];
     for (int e = warp; e < E; e += kThreads / 32) {
       int c0s = 0;
       for (int b = lane; b < G; b += 32) c0s += __ldcg(&blk_slot0[(size_t)b * E + e]);
@@ -145,9 +157,8 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
         ps += __shfl_xor_sync(0xffffffffu, ps, o);
       }
       if (lane == 0) {
-        my_row[e] = s_hist[e];
-        my_row[E + e] = c0s;
-        my_row[2 * E + e] = __float_as_int(ps);
+        my_row[EV + e] = c0s;
+        my_row[EV + E + e] = __float_as_int(ps);
       }
     }
     __syncthreads();
@@ -168,28 +179,28 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
   __syncthreads();
   const bool fail = s_fail != 0;
   const int32_t* all = peers.cnt_all[rank];
-  for (int i = tid; i < world * E; i += kThreads) {
-    int g = i / E, e = i - g * E;
-    s_cnt[i] = fail ? 0 : (int)__ldcv(&all[(size_t)g * row_ints + e]);
+  for (int i = tid; i < world * EV; i += kThreads) {
+    int g = i / EV, v = i - g * EV;
+    s_cnt[i] = fail ? 0 : (int)__ldcv(&all[(size_t)g * row_ints + v]);
   }
   __syncthreads();
-  for (int e = tid; e < E; e += kThreads) {
-    const int q = s_owner[e];
+  for (int v = tid; v < EV; v += kThreads) {
+    const int q = s_owner[v];
     int base = 0;
-    for (int e2 = 0; e2 < e; ++e2)
-      if (s_owner[e2] == q)
-        for (int g = 0; g < world; ++g) base += s_cnt[g * E + e2];
-    for (int g = 0; g < rank; ++g) base += s_cnt[g * E + e];
-    s_dest[e] = base;
+    for (int v2 = 0; v2 < v; ++v2)
+      if (s_owner[v2] == q)
+        for (int g = 0; g < world; ++g) base += s_cnt[g * EV + v2];
+    for (int g = 0; g < rank; ++g) base += s_cnt[g * EV + v];
+    s_dest[v] = base;
   }
   if (blockIdx.x == 0 && !fail) {
-    // rows this rank will receive, per owned expert in increasing expert id
+    // rows this rank will receive, per owned virtual expert in increasing id
     if (tid == 0) {
       int acc = 0, li = 0;
-      for (int e = 0; e < E; ++e) {
-        if (s_owner[e] != rank) continue;
+      for (int v = 0; v < EV; ++v) {
+        if (s_owner[v] != rank) continue;
         offsets_local[li++] = acc;
-        for (int g = 0; g < world; ++g) acc += s_cnt[g * E + e];
+        for (int g = 0; g < world; ++g) acc += s_cnt[g * EV + v];
       }
       offsets_local[li] = acc;
     }
@@ -200,8 +211,8 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
       int c0s = 0;
       float ps = 0.f;
       for (int g = 0; g < world; ++g) {
-        c0s += (int)__ldcv(&all[(size_t)g * row_ints + E + e]);
-        ps += __int_as_float((int)__ldcv(&all[(size_t)g * row_ints + 2 * E + e]));
+        c0s += (int)__ldcv(&all[(size_t)g * row_ints + EV + e]);
+        ps += __int_as_float((int)__ldcv(&all[(size_t)g * row_ints + EV + E + e]));
       }
       cnt_slot0[e] = c0s;
       psum_global[e] = ps;
@@ -223,20 +234,21 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
     const int ntok = (int)((N - t0) < kChunk ? (N - t0) : kChunk);
     const int npair = ntok * k;
     if (warp == 0) {
-      for (int e = lane; e < E; e += 32) s_run[e] = 0;
+      for (int v = lane; v < EV; v += 32) s_run[v] = 0;
       __syncwarp();
       for (int p0 = 0; p0 < npair; p0 += 32) {
         int p = p0 + lane;
         int e = p < npair ? idx[t0 * k + p] : -1;
         bool ok = (unsigned)e < (unsigned)E;
-        unsigned grp = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+        const int v = ok ? s_vmap[e] : -1 - lane;
+        unsigned grp = __match_any_sync(0xffffffffu, v);
         int row = -1, q = 0;
         if (ok) {
-          row = s_dest[e] + s_base[e] + s_run[e] + __popc(grp & ((1u << lane) - 1u));
-          q = s_owner[e];
+          row = s_dest[v] + s_base[v] + s_run[v] + __popc(grp & ((1u << lane) - 1u));
+          q = s_owner[v];
         }
         __syncwarp();
-        if (ok && (grp >> lane) == 1u) s_run[e] += __popc(grp);
+        if (ok && (grp >> lane) == 1u) s_run[v] += __popc(grp);
         __syncwarp();
         if (p < npair) {
           s_row[p] = row;
@@ -272,12 +284,12 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
     }
     __syncthreads();
     if (c + G >= nchunk) break;
-    for (int64_t i = tid; i < (int64_t)G * E; i += kThreads) {
-      int64_t cc = c + i / E;
-      int e = (int)(i % E);
+    for (int64_t i = tid; i < (int64_t)G * EV; i += kThreads) {
+      int64_t cc = c + i / EV;
+      int v = (int)(i % EV);
       if (cc < nchunk) {
-        int v = __ldcg(&chunk_cnt[cc * E + e]);
-        if (v != 0) atomicAdd(&s_base[e], v);
+        int val = __ldcg(&chunk_cnt[cc * EV + v]);
+        if (val != 0) atomicAdd(&s_base[v], val);
       }
     }
     __syncthreads();
@@ -321,17 +333,18 @@ int g_blocks_per_sm = 0;
 
 }  // namespace
 
-int64_t ep_scratch_ints(int64_t N, int E) {
-  return ((N + kChunk - 1) / kChunk) * E + (int64_t)kNumSMs * 2 * E;
+int64_t ep_scratch_ints(int64_t N, int EV, int E) {
+  return ((N + kChunk - 1) / kChunk) * EV + (int64_t)kNumSMs * 2 * E;
 }
 
-int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
-                       const EpPeers& peers, int rank, int world, uint32_t epoch,
-                       const int32_t* expert_owner, int32_t* scratch, const float* psum_part,
+int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int EV, int k,
+                       int dtype, const EpPeers& peers, int rank, int world, uint32_t epoch,
+                       const int32_t* owner, const int32_t* vmap, int32_t* scratch,
+                       const float* psum_part,
                        int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
                        int64_t n_total, int32_t* status, cudaStream_t s) {
   const int row_pieces = d * (dtype == MOE_B200_BF16 ? 2 : 4) / 16;
-  const size_t smem = sizeof(int) * (size_t)(5 * E + 2 * kChunk * k + world * E + kThreads);
+  const size_t smem = sizeof(int) * (size_t)(5 * EV + 2 * E + 2 * kChunk * k + world * EV + kThreads);
   const void* fn = (const void*)ep_dispatch_kernel;
   if (g_sm_count == 0) {
     int dev = 0;
@@ -351,9 +364,10 @@ int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int 
   int64_t router_blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
   const uint4* x4 = static_cast<const uint4*>(x);
   EpPeers pv = peers;
-  void* args[] = {(void*)&x4, (void*)&idx, (void*)&N, (void*)&row_pieces, (void*)&E, (void*)&k,
-                  (void*)&pv, (void*)&rank, (void*)&world, (void*)&epoch, (void*)&expert_owner,
-                  (void*)&scratch, (void*)&psum_part, (void*)&router_blocks, (void*)&cnt_slot0,
+  void* args[] = {(void*)&x4, (void*)&idx, (void*)&N, (void*)&row_pieces, (void*)&E, (void*)&EV,
+                  (void*)&k, (void*)&pv, (void*)&rank, (void*)&world, (void*)&epoch, (void*)&owner,
+                  (void*)&vmap, (void*)&scratch, (void*)&psum_part, (void*)&router_blocks,
+                  (void*)&cnt_slot0,
                   (void*)&psum_global, (void*)&offsets_local, (void*)&aux, (void*)&n_total,
                   (void*)&status};
   MOE_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem, s));

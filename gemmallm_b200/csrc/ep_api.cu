@@ -29,7 +29,7 @@ void symm_layout(int64_t N_local, int d, int E, int k, int world, size_t* off, s
   const size_t cap = (size_t)N_local * k * world;  // worst case: every pair lands on one rank
   size_t sizes[MOE_B200_EP_SYMM_NUM];
   sizes[MOE_B200_EP_SYMM_FLAGS] = sizeof(uint32_t) * kEpNumFlags * kEpMaxRanks;
-  sizes[MOE_B200_EP_SYMM_CNT_ALL] = sizeof(int32_t) * 3 * E * world;
+  sizes[MOE_B200_EP_SYMM_CNT_ALL] = sizeof(int32_t) * (kMaxExperts + 2 * E) * world;  // any EV <= 256
   sizes[MOE_B200_EP_SYMM_RECV_META] = sizeof(int32_t) * cap;
   sizes[MOE_B200_EP_SYMM_RECV_X] = cap * d * 2;
   sizes[MOE_B200_EP_SYMM_RET_Y] = (size_t)N_local * k * d * 2;
@@ -53,10 +53,10 @@ void ws_layout(int64_t N_local, int d, int f, int E, int k, int world, size_t* o
   sizes[MOE_B200_EP_WS_PSUM_PART] = rb * E * sizeof(float);
   sizes[MOE_B200_EP_WS_PSUM] = (size_t)E * sizeof(float);
   sizes[MOE_B200_EP_WS_AUX] = sizeof(float);
-  sizes[MOE_B200_EP_WS_SCRATCH] = (size_t)ep_scratch_ints(N_local, E) * sizeof(int32_t);
+  sizes[MOE_B200_EP_WS_SCRATCH] = (size_t)ep_scratch_ints(N_local, kMaxExperts, E) * sizeof(int32_t);
   sizes[MOE_B200_EP_WS_CNT_SLOT0] = (size_t)E * sizeof(int32_t);
-  sizes[MOE_B200_EP_WS_OFFSETS_LOCAL] = (size_t)(E + 1) * sizeof(int32_t);
-  sizes[MOE_B200_EP_WS_OWNER] = (size_t)E * sizeof(int32_t);
+  sizes[MOE_B200_EP_WS_OFFSETS_LOCAL] = (size_t)(kMaxExperts + 1) * sizeof(int32_t);
+  sizes[MOE_B200_EP_WS_OWNER] = (size_t)(kMaxExperts + E * kEpMaxRanks) * sizeof(int32_t);  // owner[EV], vmap[E][world]
   sizes[MOE_B200_EP_WS_H] = cap * f * 2;
   sizes[MOE_B200_EP_WS_Y] = cap * d * 2;
   size_t pos = 0;
@@ -109,20 +109,24 @@ int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, in
 
 int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
                         const void* residual, int64_t N_local, int d, int f, int E, int k,
-                        int dtype, int flags, int rank, int world, uint32_t epoch,
-                        const int32_t* h_expert_owner, void* const* h_symm_bases, void* workspace,
-                        size_t workspace_bytes, void* out, void* stream) {
+                        int dtype, int flags, int rank, int world, uint32_t epoch, int EV,
+                        const int32_t* h_owner, const int32_t* h_vmap, void* const* h_symm_bases,
+                        void* workspace, size_t workspace_bytes, void* out, void* stream) {
   int rc = ep_check(N_local, d, f, E, k, dtype, rank, world);
   if (rc) return rc;
-  if (!h_expert_owner || !h_symm_bases || !workspace) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!h_owner || !h_vmap || !h_symm_bases || !workspace) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (EV < E || EV > kMaxExperts) return set_error(MOE_B200_ERR_SHAPE, "EV must be in [E, 256]");
   if (N_local > 0 && (!x || !Wg || !bg || !out)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
   if (epoch == 0) return set_error(MOE_B200_ERR_SHAPE, "epoch must start at 1 and grow by one per call");
   int E_local = 0;
-  for (int e = 0; e < E; ++e) {
-    if (h_expert_owner[e] < 0 || h_expert_owner[e] >= world)
+  for (int v = 0; v < EV; ++v) {
+    if (h_owner[v] < 0 || h_owner[v] >= world)
       return set_error(MOE_B200_ERR_SHAPE, "expert owner out of range");
-    if (h_expert_owner[e] == rank) ++E_local;
+    if (h_owner[v] == rank) ++E_local;
   }
+  for (int i = 0; i < E * world; ++i)
+    if (h_vmap[i] < 0 || h_vmap[i] >= EV)
+      return set_error(MOE_B200_ERR_SHAPE, "virtual expert id out of range");
   if (E_local > 0 && !plan_local) return set_error(MOE_B200_ERR_NULL, "plan_local is NULL");
   size_t so[MOE_B200_EP_SYMM_NUM], wo[MOE_B200_EP_WS_NUM], stotal, wtotal;
   symm_layout(N_local, d, E, k, world, so, &stotal);
@@ -160,22 +164,27 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
   // the owner table is uploaded only when it (or the workspace) changes: a copy
   // from pageable memory would otherwise synchronise the stream on every call
   static thread_local const void* cached_ws = nullptr;
-  static thread_local int cached_E = 0;
-  static thread_local int32_t cached_owner[kMaxExperts];
-  if (cached_ws != workspace || cached_E != E ||
-      memcmp(cached_owner, h_expert_owner, sizeof(int32_t) * E) != 0) {
-    MOE_CUDA_CHECK(cudaMemcpyAsync(owner, h_expert_owner, sizeof(int32_t) * E, cudaMemcpyHostToDevice, s));
-    memcpy(cached_owner, h_expert_owner, sizeof(int32_t) * E);
+  static thread_local int cached_n = 0;
+  static thread_local int32_t cached_tab[kMaxExperts + kMaxExperts * kEpMaxRanks];
+  int32_t tab[kMaxExperts + kMaxExperts * kEpMaxRanks];
+  memset(tab, 0, sizeof(tab));
+  memcpy(tab, h_owner, sizeof(int32_t) * EV);
+  memcpy(tab + kMaxExperts, h_vmap, sizeof(int32_t) * E * world);
+  const int tab_n = kMaxExperts + E * world;
+  if (cached_ws != workspace || cached_n != tab_n || memcmp(cached_tab, tab, sizeof(int32_t) * tab_n) != 0) {
+    MOE_CUDA_CHECK(cudaMemcpyAsync(owner, tab, sizeof(int32_t) * tab_n, cudaMemcpyHostToDevice, s));
+    memcpy(cached_tab, tab, sizeof(int32_t) * tab_n);
     cached_ws = workspace;
-    cached_E = E;
+    cached_n = tab_n;
   }
+  const int32_t* vmap_dev = owner + kMaxExperts;
   if (N_local > 0) {
     rc = launch_router(x, Wg, bg, N_local, d, E, k, dtype, logits, idx, w, psum_part, status, s);
     if (rc) return rc;
   }
-  rc = launch_ep_dispatch(x, idx, N_local, d, E, k, dtype, peers, rank, world, epoch, owner, scratch,
-                          psum_part, cnt_slot0, psum, offsets_local, aux, N_local * (int64_t)world,
-                          status, s);
+  rc = launch_ep_dispatch(x, idx, N_local, d, E, EV, k, dtype, peers, rank, world, epoch, owner,
+                          vmap_dev, scratch, psum_part, cnt_slot0, psum, offsets_local, aux,
+                          N_local * (int64_t)world, status, s);
   if (rc) return rc;
   rc = launch_ep_wait(peers.flags[rank] + kEpFlagX * kEpMaxRanks, world, epoch, status, 22, s);
   if (rc) return rc;

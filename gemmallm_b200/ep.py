@@ -44,11 +44,42 @@ def lpt_placement(load: list[float], world: int) -> list[int]:
     return owner
 
 
+def virtual_experts(owner: list[int], replicate: dict[int, list[int]], world: int):
+    """Virtual expert table. ``owner[e]`` places every real expert; ``replicate[e]``
+    lists the ranks that hold a copy of expert e (its owner is added if missing).
+    Returns (v_owner, v_real, vmap): rank and real expert of every virtual id, and
+    vmap[e][r] = the virtual expert rank r sends its rows for e to — the copy on r
+    itself when there is one (those rows never leave the GPU), else the copies in
+    turn by source rank."""
+    E = len(owner)
+    v_owner, v_real = list(owner), list(range(E))
+    vmap = [[e] * world for e in range(E)]
+    for e in sorted(replicate):
+        ranks = sorted(set(replicate[e]) | {owner[e]})
+        ids = {owner[e]: e}
+        for r in ranks:
+            if r != owner[e]:
+                ids[r] = len(v_owner)
+                v_owner.append(r)
+                v_real.append(e)
+        others = [r for r in range(world) if r not in ids]
+        for r in ids:
+            vmap[e][r] = ids[r]
+        for i, r in enumerate(others):
+            vmap[e][r] = ids[ranks[i % len(ranks)]]
+    return v_owner, v_real, vmap
+
+
 class ExpertParallelMOE(nn.Module):
+    """``placement[e]``: owner rank of expert e (default strided). ``replicate``:
+    {expert: [ranks]} extra copies of popular experts; a list of expert ids means
+    "on every rank". Replicas are ordinary entries of ``experts`` under the same
+    global id, so checkpoints load the same way."""
+
     def __init__(self, hidden_size: int, num_experts: int = 8, expansion_factor: int = 4,
                  dropout_ratio: float = 0.1, lora_rank: int = 16, lora_alpha: int = 32,
                  device: str = "mps", *, top_k: int = 2, d_ff: int | None = None, group=None,
-                 placement: list[int] | None = None):
+                 placement: list[int] | None = None, replicate=None):
         super().__init__()
         import torch.distributed as dist
         self.group = group if group is not None else dist.group.WORLD
@@ -57,13 +88,22 @@ class ExpertParallelMOE(nn.Module):
         self.owner = list(placement) if placement is not None else strided_placement(num_experts, self.world)
         if len(self.owner) != num_experts or any(not 0 <= o < self.world for o in self.owner):
             raise ValueError("placement must give a rank in [0, world) for every expert")
+        if replicate is None:
+            replicate = {}
+        elif not isinstance(replicate, dict):
+            replicate = {int(e): list(range(self.world)) for e in replicate}
+        self.v_owner, self.v_real, self.vmap = virtual_experts(self.owner, replicate, self.world)
+        if len(self.v_owner) > 256:
+            raise ValueError("too many expert copies (at most 256 virtual experts)")
         self.gate = nn.Linear(hidden_size, num_experts)
         self.num_experts = num_experts
-        self.local_ids = [e for e in range(num_experts) if self.owner[e] == self.rank]
+        # virtual experts this rank runs, in increasing virtual id, and their real experts
+        self.local_virtual = [v for v, o in enumerate(self.v_owner) if o == self.rank]
+        self.local_ids = [self.v_real[v] for v in self.local_virtual]
         self.experts = nn.ModuleDict({
             str(e): FeedForward(hidden_size, expansion_factor=expansion_factor,
                                 dropout_ratio=dropout_ratio, lora_rank=lora_rank,
-                                lora_alpha=lora_alpha, d_ff=d_ff) for e in self.local_ids})
+                                lora_alpha=lora_alpha, d_ff=d_ff) for e in sorted(set(self.local_ids))})
         self.device = device
         self.hidden_size = hidden_size
         self.d_ff = hidden_size * expansion_factor if d_ff is None else d_ff
@@ -103,7 +143,8 @@ class ExpertParallelMOE(nn.Module):
             "ws": ws, "ws_base": (ws.data_ptr() + 1023) & ~1023, "ws_bytes": wbytes,
             "ws_layout": _cabi.ep_workspace_layout(N_local, d, f, E, k, G),
             "symm_layout": _cabi.ep_symm_layout(N_local, d, E, k, G),
-            "owner": (C.c_int32 * E)(*self.owner),
+            "owner": (C.c_int32 * len(self.v_owner))(*self.v_owner),
+            "vmap": (C.c_int32 * (E * G))(*[v for row in self.vmap for v in row]),
         }
         return self._state
 
@@ -144,7 +185,8 @@ class ExpertParallelMOE(nn.Module):
             self.epoch += 1
             check(lib.moe_b200_ep_forward(
                 x.data_ptr(), self.gate.weight.data_ptr(), self.gate.bias.data_ptr(), plan, res_ptr,
-                N, d, f, E, k, dtype, self.flags, self.rank, self.world, self.epoch, st["owner"], st["bases"],
+                N, d, f, E, k, dtype, self.flags, self.rank, self.world, self.epoch, len(self.v_owner),
+                st["owner"], st["vmap"], st["bases"],
                 st["ws_base"], st["ws_bytes"], out.data_ptr(), _stream(dev)), "ep_forward")
         self.last = {
             "logits": self._ws_view("logits", torch.float32, (N, E)),

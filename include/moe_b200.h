@@ -252,7 +252,7 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg,
  * process), zero-filled once before the first call. bf16 only. */
 enum {
   MOE_B200_EP_SYMM_FLAGS = 0, /* uint32 [3][8] epoch words */
-  MOE_B200_EP_SYMM_CNT_ALL,   /* int32 [world][3E] counts published by every rank */
+  MOE_B200_EP_SYMM_CNT_ALL,   /* int32 [world][256+2E] counts published by every rank */
   MOE_B200_EP_SYMM_RECV_META, /* int32 [cap] return address of each received row */
   MOE_B200_EP_SYMM_RECV_X,    /* bf16 [cap][d] received rows, cap = N_local*k*world */
   MOE_B200_EP_SYMM_RET_Y,     /* bf16 [N_local*k][d] expert outputs in (token, slot) order */
@@ -263,7 +263,7 @@ enum {
   MOE_B200_EP_WS_PSUM_PART, MOE_B200_EP_WS_PSUM, /* float [E], summed over all ranks */
   MOE_B200_EP_WS_AUX,          /* loss over all N_local*world tokens (model.py:213-216) */
   MOE_B200_EP_WS_SCRATCH, MOE_B200_EP_WS_CNT_SLOT0, /* int32 [E], all ranks */
-  MOE_B200_EP_WS_OFFSETS_LOCAL, /* int32 [E_local+1] rows received per owned expert */
+  MOE_B200_EP_WS_OFFSETS_LOCAL, /* int32 [E_local+1] rows received per owned (virtual) expert */
   MOE_B200_EP_WS_OWNER, MOE_B200_EP_WS_H,
   MOE_B200_EP_WS_Y,            /* bf16 [cap][d], used only with MOE_B200_FLAG_EP_UNFUSED_RETURN */
   MOE_B200_EP_WS_NUM
@@ -277,14 +277,19 @@ int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, in
 /* One sharded forward on this rank: router on the local tokens, count exchange,
  * dispatch push to the expert owners, grouped GEMMs on the received rows with
  * the down pass writing straight to the token owners, combine (+ residual).
- * plan_local covers the experts this rank owns, in increasing expert id.
+ * Experts are addressed by virtual ids v in [0, EV): h_owner[v] is the rank that
+ * runs v, h_vmap[e * world + r] the virtual expert that rank r's rows for expert
+ * e go to. Without replication EV = E and h_vmap[e * world + r] = e. Giving a
+ * popular expert several virtual ids on different ranks (with the same weights
+ * in each rank's plan) splits its rows between them. plan_local covers the
+ * virtual experts this rank owns, in increasing virtual id.
  * `epoch` is 1 on the first call and one more on every later call, the same on
  * all ranks. All ranks must make the same sequence of calls. A peer that never
  * arrives makes the bounded waits run out: status word = MOE_B200_DEV_TIMEOUT. */
 int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
                         const void* residual, int64_t N_local, int d, int f, int E, int k,
-                        int dtype, int flags, int rank, int world, uint32_t epoch,
-                        const int32_t* h_expert_owner, void* const* h_symm_bases,
+                        int dtype, int flags, int rank, int world, uint32_t epoch, int EV,
+                        const int32_t* h_owner, const int32_t* h_vmap, void* const* h_symm_bases,
                         void* workspace, size_t workspace_bytes, void* out, void* stream);
 
 /* Copy the 16 status words to the host after synchronising the stream.

@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--bias", default="zipf1.1")
     ap.add_argument("--placement", default="strided")
     ap.add_argument("--flags", type=int, default=0)
+    ap.add_argument("--replicate", type=int, default=0, help="copy the N most popular experts to every rank")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -51,13 +52,15 @@ def main():
     placement = None
     if args.placement == "lpt":
         placement = lpt_placement([1.0 / (e + 1) ** 1.1 for e in range(E)], world)
-    m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement).eval()
+    replicate = list(range(args.replicate)) if args.replicate else None   # Zipf bias: lowest ids are hottest
+    m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement,
+                          replicate=replicate).eval()
     m.flags = args.flags
     m.to(device=dev, dtype=dt)
     with torch.no_grad():
         m.gate.weight.copy_(params["gate_w"])
         m.gate.bias.copy_(params["gate_b"])
-        for e in m.local_ids:
+        for e in sorted(set(m.local_ids)):
             ex = m.experts[str(e)]
             ex.gate_and_up.weight.copy_(params["w1"][e])
             ex.gate_and_up.bias.copy_(params["b1"][e])
@@ -90,7 +93,13 @@ def main():
         # rows received per owned expert = global count of that expert
         total = r_all["cnt_slot"].sum(0)
         recv = m.last["offsets_local"].cpu().long().diff()
-        recv_ok = torch.equal(recv, total[m.local_ids]) if not moe_oracle.tie_rows(r_all["probs"], k).any() else True
+        if args.replicate:
+            # copies split an expert's rows; over all ranks every pair is received exactly once
+            got_rows = torch.tensor([int(recv.sum())], device=dev)
+            dist.all_reduce(got_rows)
+            recv_ok = int(got_rows) == N * k
+        else:
+            recv_ok = torch.equal(recv, total[m.local_ids]) if not moe_oracle.tie_rows(r_all["probs"], k).any() else True
         this = status == 0 and idx_ok and aux_ok and cnt0_ok and recv_ok and err <= bound
         print(f"rank {rank} call {call}: status {status} idx {idx_ok} aux {aux_ok} cnt0 {cnt0_ok} "
               f"recv {recv_ok} max-abs {err:.4g} (bound {bound:.4g}) -> {'ok' if this else 'FAIL'}", flush=True)

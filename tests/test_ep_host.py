@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from gemmallm_b200 import synthetic
-from gemmallm_b200.ep import lpt_placement, strided_placement
+from gemmallm_b200.ep import lpt_placement, strided_placement, virtual_experts
 from oracle import moe_oracle
 
 
@@ -24,6 +24,21 @@ def test_placements():
     strided = [sum(l for e, l in enumerate(load) if e % 8 == r) for r in range(8)]
     assert max(per_rank) <= max(strided) + 1e-12                         # never worse than strided
     assert max(per_rank) >= load[0]                                      # the hottest expert bounds it
+
+
+def test_virtual_experts():
+    v_owner, v_real, vmap = virtual_experts([0, 1, 0, 1], {}, 2)
+    assert v_owner == [0, 1, 0, 1] and v_real == [0, 1, 2, 3] and vmap == [[e, e] for e in range(4)]
+    # expert 0 copied to both ranks: each rank keeps its own rows of expert 0
+    v_owner, v_real, vmap = virtual_experts([0, 1, 0, 1], {0: [0, 1]}, 2)
+    assert v_owner == [0, 1, 0, 1, 1] and v_real == [0, 1, 2, 3, 0]
+    assert vmap[0] == [0, 4] and vmap[1] == [1, 1]
+    # a partial copy set: holders use their own copy, the other ranks alternate
+    v_owner, v_real, vmap = virtual_experts([0, 1, 2, 3, 0, 1, 2, 3], {1: [1, 3]}, 4)
+    assert v_owner[8] == 3 and v_real[8] == 1
+    assert vmap[1][1] == 1 and vmap[1][3] == 8 and sorted([vmap[1][0], vmap[1][2]]) == [1, 8]
+    for e in range(8):
+        assert all(v_real[v] == e for v in vmap[e])
 
 
 def dest_rows(cnt_all, owner, rank):

@@ -35,3 +35,6 @@ def test_ep_multi_gpu(cuda_device, world):
     run_workers(world, ["--tokens", "4096", "--experts", "16", "--topk", "4"], port=29542 + world)
     run_workers(world, ["--tokens", "2048", "--experts", "64", "--topk", "4", "--dmodel", "512", "--dff", "704",
                         "--placement", "lpt"], port=29552 + world)
+    # the three most popular experts copied to every rank
+    run_workers(world, ["--tokens", "4096", "--experts", "16", "--topk", "4", "--replicate", "3"],
+                port=29562 + world)

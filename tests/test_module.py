@@ -9,7 +9,8 @@ import torch
 
 from gemmallm_b200 import MOE, FeedForward
 
-REF_DIR = os.environ.get("MOE_REFERENCE_DIR", "/root/reference")
+# a reference checkout next to this repository, or wherever MOE_REFERENCE_DIR points
+REF_DIR = os.environ.get("MOE_REFERENCE_DIR", str(Path(__file__).resolve().parents[2] / "reference"))
 
 
 def expected_keys(E):

@@ -16,7 +16,8 @@ from gemmallm_b200 import synthetic
 from oracle import moe_oracle
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
-REF_DIR = os.environ.get("MOE_REFERENCE_DIR", "/root/reference")
+# a reference checkout next to this repository, or wherever MOE_REFERENCE_DIR points
+REF_DIR = os.environ.get("MOE_REFERENCE_DIR", str(Path(__file__).resolve().parents[2] / "reference"))
 
 
 def sha(t):
