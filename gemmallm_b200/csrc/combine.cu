@@ -49,7 +49,7 @@ combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ row_of,
 // Small-N variant: the down product arrives as `ksplit` fp32 partial buffers
 // part[s][M][d] without bias; sum them in order s = 0..ksplit-1, add the
 // expert's down.bias, then weight and add as above.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(64)
 combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_stride,
                       const int32_t* __restrict__ row_of, const int32_t* __restrict__ idx,
                       const float* __restrict__ w, const void* const* __restrict__ b2,
@@ -57,6 +57,7 @@ combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_s
                       __nv_bfloat16* __restrict__ out) {
   const int pieces = d >> 3;
   const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
   if (item >= N * pieces) return;
   const int64_t t = item / pieces;
   const int c = (int)(item - t * pieces) << 3;
@@ -73,12 +74,17 @@ combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_s
     float s[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) s[i] = 0.f;
-    for (int sp = 0; sp < ksplit; ++sp) {
-      float pv[8];
-      load8(part + (int64_t)sp * part_stride + (int64_t)row * d + c, pv);
+    // all partial loads in flight at once; summed in order sp = 0, 1, ...
+    float pv[8][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s[i] += pv[i];
-    }
+    for (int sp = 0; sp < 8; ++sp)
+      if (sp < ksplit) load8(part + (int64_t)sp * part_stride + (int64_t)row * d + c, pv[sp]);
+#pragma unroll
+    for (int sp = 0; sp < 8; ++sp)
+      if (sp < ksplit) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] += pv[sp][i];
+      }
     // the expert's output is rounded to bf16 before weighting, as on the large-N path
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -103,11 +109,11 @@ int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_
   if (N == 0) return 0;
   PlanView pv = plan_view(plan, E);
   const int64_t items = N * (d >> 3);
-  const int64_t blocks = (items + 255) / 256;
-  combine_decode_kernel<<<(unsigned)blocks, 256, 0, s>>>(
-      part, ksplit, M * (int64_t)d, row_of, idx, w, pv.b2,
-      static_cast<const __nv_bfloat16*>(residual), N, d, k, static_cast<__nv_bfloat16*>(out));
-  MOE_CUDA_CHECK(cudaGetLastError());
+  const int64_t blocks = (items + 63) / 64;   // small blocks: spread few items over many SMs
+  MOE_CUDA_CHECK(launch_pdl(combine_decode_kernel, dim3((unsigned)blocks), dim3(64), 0, s, part, ksplit,
+                            M * (int64_t)d, row_of, idx, w, pv.b2,
+                            static_cast<const __nv_bfloat16*>(residual), N, d, k,
+                            static_cast<__nv_bfloat16*>(out)));
   return 0;
 }
 

@@ -110,6 +110,33 @@ __device__ __forceinline__ float gelu_tanh_fast(float g) {
   return fmaf(hg, tanh_approx(inner), hg);
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl may start while
+// the kernel before it in the stream is still draining; everything it does before
+// pdl_wait() must not touch that kernel's outputs. pdl_wait() returns when the
+// earlier kernel has completed and its writes are visible; without the launch
+// attribute it returns at once. pdl_launch_dependents() lets the next kernel's
+// blocks be scheduled as soon as resources free up.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Plan buffer layout (device memory owned by the caller).
 //   [0, 4*E*8)            : W1[E], b1[E], W2[E], b2[E] device pointers
 //   then, 128-byte aligned: tensor maps (128 bytes each) W1[E], W2[E] with

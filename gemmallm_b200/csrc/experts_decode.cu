@@ -83,6 +83,18 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_tok,
       mbar_init(&ctl->up_ready[a], 64);
     }
     ctl->abort = 0;
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&ctl->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // everything above is independent of the kernels before this one in the stream
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
     int acc = 0;
     int beg = offsets[0];
     ctl->offsets[0] = beg;
@@ -96,13 +108,6 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tmap_tok,
     ctl->tile_start[E] = acc;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&ctl->tmem_base)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -267,9 +272,9 @@ int launch_one(const CUtensorMap& tm_tok, const void* tmap_w, const int32_t* off
                                         (int)kSmemBytes));
     attr_set = true;
   }
-  fn<<<sms, kThreads, kSmemBytes, s>>>(tm_tok, static_cast<const CUtensorMap*>(tmap_w), offsets,
-                                       bias, E, K, Nout, ksplit, part_stride, out, status);
-  MOE_CUDA_CHECK(cudaGetLastError());
+  MOE_CUDA_CHECK(launch_pdl(fn, dim3(sms), dim3(kThreads), kSmemBytes, s, tm_tok,
+                            static_cast<const CUtensorMap*>(tmap_w), offsets, bias, E, K, Nout, ksplit,
+                            part_stride, out, status));
   return 0;
 }
 

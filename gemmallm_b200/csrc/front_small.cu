@@ -1,6 +1,9 @@
-// Router and dispatch of a small-N ("decode") call in ONE launch of ONE block:
-// with at most 128 tokens the separate router and cooperative dispatch kernels
-// are pure launch and barrier latency (13 + 15 us against a few us of work).
+// Router and dispatch of a small-N ("decode") call in ONE launch: with at most
+// 128 tokens the separate router and cooperative dispatch kernels are pure launch
+// and barrier latency (13 + 15 us against a few us of work). A few blocks run;
+// each one derives the complete routing by itself (the same instructions on the
+// same data, so every block gets the same answer and no grid barrier is needed),
+// block 0 writes the routing results, and the row copies are split over the blocks.
 // Covers reference model.py:206-253 for N <= 128, N*k <= 256, E <= 32, bf16:
 //   A. logits: 32 warps = (16-token group) x (slice of K); each warp forms its
 //      partial x Wg^T with mma.sync m16n8k16 exactly like router_mma_kernel
@@ -57,6 +60,8 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int ET = 8 * NT;
+  pdl_wait();                 // x may come from the kernel before this one
+  pdl_launch_dependents();
 
   // ---- A. partial logits -----------------------------------------------------
   {
@@ -118,7 +123,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int ks = 0; ks < nslices; ++ks) s += s_part[((size_t)ks * 16 * gp2 + tok) * ET + e];
     s += __bfloat162float(bg[e]);
     s_logit[tok * ld + e] = s;
-    if (out_logits != nullptr) out_logits[i] = s;
+    if (out_logits != nullptr && blockIdx.x == 0) out_logits[i] = s;
   }
   __syncthreads();
 
@@ -152,8 +157,10 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int j = 0; j < kMaxTopK; ++j) {
       if (j < k) {
         lg[sel[j]] = sl[j];
-        out_idx[tid * k + j] = sel[j];
-        out_w[tid * k + j] = vals[j] / total;
+        if (blockIdx.x == 0) {
+          out_idx[tid * k + j] = sel[j];
+          out_w[tid * k + j] = vals[j] / total;
+        }
         s_idx[tid * k + j] = sel[j];
         atomicAdd(&s_cnt[j * kMaxE + sel[j]], 1);
       }
@@ -167,13 +174,13 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     int tot = 0;
     for (int j = 0; j < k; ++j) {
       const int c = s_cnt[j * kMaxE + tid];
-      cnt_slot[j * E + tid] = c;
+      if (blockIdx.x == 0) cnt_slot[j * E + tid] = c;
       tot += c;
     }
     s_run[tid] = tot;          // total rows of this expert, until the scan below
     float ps = 0.f;
     for (int tok = 0; tok < N; ++tok) ps += s_logit[tok * ld + tid];
-    psum[tid] = ps;
+    if (blockIdx.x == 0) psum[tid] = ps;
     s_part[tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
   }
   __syncthreads();
@@ -182,13 +189,15 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     float a = 0.f;
     for (int e = 0; e < E; ++e) {
       s_off[e] = acc;
-      offsets[e] = acc;
+      if (blockIdx.x == 0) offsets[e] = acc;
       acc += s_run[e];
       a += s_part[e];
     }
     s_off[E] = acc;
-    offsets[E] = acc;
-    aux[0] = a / (float)E * (float)(E * E);   // model.py:213-216
+    if (blockIdx.x == 0) {
+      offsets[E] = acc;
+      aux[0] = a / (float)E * (float)(E * E);   // model.py:213-216
+    }
   }
   __syncthreads();
   if (warp == 0) {
@@ -207,18 +216,19 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       __syncwarp();
       if (p < npair) {
         s_row[p] = row;
-        row_of[p] = row;
+        if (blockIdx.x == 0) row_of[p] = row;
       }
     }
   }
   __syncthreads();
 
-  // ---- D. copy the token rows into the sorted buffer ----------------------------
+  // ---- D. copy the token rows into the sorted buffer (split over the blocks) -----
   const int pieces = d >> 3;
   const int items = N * pieces;
   const uint4* src = reinterpret_cast<const uint4*>(x);
   constexpr int kInFlight = 4;
-  for (int i0 = tid; i0 < items; i0 += kThreads * kInFlight) {
+  for (int i0 = blockIdx.x * kThreads * kInFlight + tid; i0 < items;
+       i0 += gridDim.x * kThreads * kInFlight) {
     uint4 v[kInFlight];
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
@@ -249,11 +259,13 @@ int launch(const void* x, const void* Wg, const void* bg, int N, int d, int E, i
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     attr_set = true;
   }
-  front_small_kernel<NT><<<1, kThreads, smem, s>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
-      static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, cnt_slot,
-      offsets, row_of, static_cast<__nv_bfloat16*>(perm), psum, aux);
-  MOE_CUDA_CHECK(cudaGetLastError());
+  // one block per 16 tokens, at most 8: more blocks only repeat the routing
+  const int blocks = N <= 16 ? 1 : (N + 15) / 16;
+  MOE_CUDA_CHECK(launch_pdl(front_small_kernel<NT>, dim3(blocks), dim3(kThreads), smem, s,
+                            static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
+                            static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx,
+                            out_w, cnt_slot, offsets, row_of, static_cast<__nv_bfloat16*>(perm), psum,
+                            aux));
   return 0;
 }
 
