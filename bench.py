@@ -523,6 +523,35 @@ def run_ep(args, wl):
     info = torch.tensor([float(rows), gemm_ms], device=dev)
     gathered = [torch.empty_like(info) for _ in range(world)]
     dist.all_gather(gathered, info)
+    single = None
+    if rank == 0 and not args.quick:
+        # the same workload on this one GPU (all experts local, no exchange), for the speed-up
+        from gemmallm_b200 import MOE
+        del m
+        torch.cuda.empty_cache()
+        m1 = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda").eval()
+        m1.to(device=dev, dtype=dt)
+        with torch.no_grad():
+            m1.gate.weight.copy_(gate_w)
+            m1.gate.bias.copy_(gate_b)
+            for e, ex in enumerate(m1.experts):
+                pe = synthetic.make_expert(d, f, e, 0)
+                ex.gate_and_up.weight.copy_(pe["w1"])
+                ex.down.weight.copy_(pe["w2"])
+                ex.gate_and_up.bias.zero_()
+                ex.down.bias.zero_()
+            x1 = synthetic.make_input(N, d, seed=1).to(dt).to(dev).view(1, N, d)
+            for _ in range(3):
+                m1(x1)
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(10):
+                m1(x1)
+            t1.record()
+            torch.cuda.synchronize()
+            single = t0.elapsed_time(t1) / 10
+        del m1, x1
     if rank == 0:
         peaks, peak_kind = load_peaks()
         peak = float(peaks["bf16_tflops"])
@@ -554,7 +583,9 @@ def run_ep(args, wl):
                          "peak_source": f"{peak_kind} bf16 burst", "ms": busiest["gemm_ms"]},
             "ep": {"per_rank": per_rank, "max_rank_share_of_rows": share,
                    "balance_limited_speedup": 1.0 / share,
-                   "gemm_ms_over_step_ms": busiest["gemm_ms"] / ms_step},
+                   "gemm_ms_over_step_ms": busiest["gemm_ms"] / ms_step,
+                   "same_workload_on_one_gpu_ms_per_step": single,
+                   "speedup_vs_one_gpu": (single / ms_step) if single else None},
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -193,6 +193,10 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
     for (int g = 0; g < rank; ++g) base += s_cnt[g * EV + v];
     s_dest[v] = base;
   }
+  if (blockIdx.x == 0 && fail) {
+    // a peer never arrived: leave an empty layout so that the kernels after this one do nothing
+    for (int i = tid; i <= EV; i += kThreads) offsets_local[i] = 0;
+  }
   if (blockIdx.x == 0 && !fail) {
     // rows this rank will receive, per owned virtual expert in increasing id
     if (tid == 0) {

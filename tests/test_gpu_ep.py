@@ -38,3 +38,45 @@ def test_ep_multi_gpu(cuda_device, world):
     # the three most popular experts copied to every rank
     run_workers(world, ["--tokens", "4096", "--experts", "16", "--topk", "4", "--replicate", "3"],
                 port=29562 + world)
+
+
+def test_missing_peer_ends_in_timeout_status(cuda_device):
+    """Failure detection without any GPU fault: rank 0 of a 2-rank configuration runs
+    alone (the "peer" buffer is a second local allocation that nobody drives), so the
+    flags it waits for are never set. Every wait is bounded: the call must come back
+    with MOE_B200_DEV_TIMEOUT in the status word, and the context must stay usable."""
+    import ctypes as C
+    import helpers
+    from gemmallm_b200 import _cabi, synthetic
+    from gemmallm_b200._cabi import lib, check
+    dev = cuda_device
+    N, d, f, E, k, world = 256, 128, 256, 8, 2, 2
+    dt = torch.bfloat16
+    params = synthetic.make_params(d, E, f, seed=0)
+    owner = [e % world for e in range(E)]
+    local = [e for e in range(E) if owner[e] == 0]
+    dp = helpers.device_params(params, dt, dev)
+    plan = helpers.Plan(dp["w1"][local].contiguous(), dp["b1"][local].contiguous(),
+                        dp["w2"][local].contiguous(), dp["b2"][local].contiguous())
+    sbytes = lib.moe_b200_ep_symm_bytes(N, d, E, k, world)
+    bufs = [torch.zeros(sbytes + 1024, dtype=torch.uint8, device=dev) for _ in range(world)]
+    bases = (C.c_void_p * world)(*[(b.data_ptr() + 1023) & ~1023 for b in bufs])
+    wbytes = lib.moe_b200_ep_workspace_bytes(N, d, f, E, k, world)
+    ws = torch.empty(wbytes + 1024, dtype=torch.uint8, device=dev)
+    ws_base = (ws.data_ptr() + 1023) & ~1023
+    lay = _cabi.ep_workspace_layout(N, d, f, E, k, world)
+    x = synthetic.make_input(N, d, seed=1).to(dt).to(dev)
+    out = torch.empty_like(x)
+    vmap = (C.c_int32 * (E * world))(*[e for e in range(E) for _ in range(world)])
+    torch.cuda.synchronize()
+    check(lib.moe_b200_ep_forward(x.data_ptr(), dp["gate_w"].data_ptr(), dp["gate_b"].data_ptr(),
+                                  plan.ptr, None, N, d, f, E, k, _cabi.BF16, 0, 0, world, 1, E,
+                                  (C.c_int32 * E)(*owner), vmap, bases, ws_base, wbytes,
+                                  out.data_ptr(), helpers.stream(dev)), "ep_forward")
+    torch.cuda.synchronize()                      # returns: no wait is unbounded
+    status = _cabi.read_status(ws_base + lay["status"], helpers.stream(dev))
+    assert status[0] == _cabi.DEV_TIMEOUT
+    # the context is intact: an ordinary call still works afterwards
+    logits, idx, w, _ = helpers.router(x, dp["gate_w"], dp["gate_b"], k)
+    torch.cuda.synchronize()
+    assert int(idx.min()) >= 0
