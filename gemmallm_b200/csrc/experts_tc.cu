@@ -52,9 +52,7 @@ struct Control {
   int abort;
   int tile_start[kMaxExperts + 1];
   int offsets[kMaxExperts + 1];  // copy of the row offsets: no global loads in the tile loops
-  // per epilogue warp: 32 rows x 64 bf16 (+16 bytes pad) to turn the scatter
-  // epilogue's row-per-thread registers into 128-byte runs per row
-  alignas(16) uint8_t stage_out[4][32 * kStgPitch];
+  alignas(16) uint8_t stage_out[8][kStgBytes];  // one staging area per epilogue warp
 };
 
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + sizeof(Control);
@@ -220,7 +218,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
-      store_tile<GEGLU, SCATTER>(taddr, row, row_ok, n0, Nout, bias, out, sc, ctl->stage_out[quad], lane, half);
+      store_tile<GEGLU, SCATTER>(taddr, row, row_ok, n0, Nout, bias, out, sc, ctl->stage_out[warp - 2], lane, half);
       tc_fence_before();
       mbar_arrive(&ctl->tmem_empty[a]);
       if (a == 1) acc_phase ^= 1u;

@@ -1,6 +1,7 @@
 // Epilogue of the 128-row x 256-column accumulator tile shared by the one-CTA and
 // the CTA-pair grouped GEMM kernels: TMEM -> registers (one row per thread) ->
-// bias (+ GeGLU) -> bf16 -> global memory.
+// bias (+ GeGLU) -> bf16 -> shared-memory staging -> global memory in 128-byte
+// runs per row.
 #pragma once
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -8,19 +9,31 @@
 namespace moe {
 namespace tc {
 
-constexpr int kStgPitch = 144;  // bytes per staged row: 64 bf16 + 16 bytes pad
+// Instrumented builds only: MOE_TC_NOSTORE drops the epilogue's global stores (the
+// predicate is never true, which the compiler cannot know).
+#ifdef MOE_TC_NOSTORE
+#define MOE_TC_STORE_OK(cond) ((cond) && Nout < 0)
+#else
+#define MOE_TC_STORE_OK(cond) (cond)
+#endif
 
-// taddr: TMEM address of this warp's 32 lanes, column 0 of the accumulator.
-// row/row_ok: the sorted-buffer row this thread owns. stg: this warp's staging
-// area (32 * kStgPitch bytes), used by SCATTER only.
-//   GEGLU  : columns [0,128) gate, [128,256) up; writes 128 outputs per row.
-//   plain  : writes 256 outputs per row.
+constexpr int kStgPitch = 144;               // bytes per staged row: 64 bf16 + 16 bytes pad
+constexpr int kStgRows = 16;                 // half a warp's rows are staged at a time
+constexpr int kStgBytes = kStgRows * kStgPitch;
+
+// Registers hold one accumulator row per thread, so a direct store would send 16
+// bytes to each of 32 different rows per instruction. Instead 64 output columns
+// of 16 rows at a time go through this warp's staging area and 8 lanes write
+// each row's 128 bytes as one run (4 rows per store instruction): an eighth of
+// the memory requests, which compete with the TMA loads for the SM's path to L2,
+// and the run length NVLink wants for the expert-parallel scatter.
+//   taddr  : TMEM address of this warp's 32 lanes, column 0 of the accumulator
+//   row    : sorted-buffer row this thread owns; row_ok: inside the expert's segment
+//   half   : two warps share each TMEM lane quadrant and split the tile's columns
+//   GEGLU  : columns [0,128) gate, [128,256) up; 128 outputs per row, 64 per warp
+//   plain  : 256 outputs per row, 128 per warp (two passes)
 //   SCATTER: plain, but the row goes to sc.ret_y[meta >> 24] + (meta & 0xffffff) * Nout
-//            over NVLink; 64 columns per row are staged in shared memory so that 8
-//            lanes write each row's 128 bytes as one run.
-// half: two warps share each TMEM lane quadrant and split the tile's columns
-// (half 0 the first half of the 32-column chunks, half 1 the rest); SCATTER is
-// done by half 0 alone (its staging area is per quadrant).
+//            (the token owner's buffer, possibly on another GPU)
 template <bool GEGLU, bool SCATTER>
 __device__ __forceinline__ void store_tile(uint32_t taddr, int row, bool row_ok, int n0, int Nout,
                                            const __nv_bfloat16* __restrict__ bias,
@@ -28,23 +41,51 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, bool row_ok,
                                            uint8_t* stg, int lane, int half) {
   constexpr int BN = 256;
   constexpr int kTileN = GEGLU ? BN / 2 : BN;
-  constexpr int kChunks = kTileN / 32;
-  const int c_begin = SCATTER ? 0 : half * (kChunks / 2);
-  const int c_end = SCATTER ? kChunks : c_begin + kChunks / 2;
-  if (SCATTER && half != 0) return;
-  __nv_bfloat16* orow = out + (int64_t)row * Nout + n0;
-  if (SCATTER) {
-    // Rows go to their token owners over NVLink. Registers hold one row per
-    // thread; stage 64 columns per row in shared memory and let 8 lanes write
-    // each row's 128 bytes, so that the peer stores are 128-byte runs.
-    const int meta = row_ok ? __ldg(&sc.meta[row]) : -1;
-    #pragma unroll 1
-    for (int cp = c_begin / 2; cp < c_end / 2; ++cp) {
+  constexpr int kPasses = kTileN / 128;        // 64-column passes per warp
+  // destination of this thread's row (nullptr: nothing to store)
+  __nv_bfloat16* dst = nullptr;
+  if (MOE_TC_STORE_OK(row_ok)) {
+    if (SCATTER) {
+      const int meta = __ldg(&sc.meta[row]);
+      dst = static_cast<__nv_bfloat16*>(sc.ret_y[(meta >> 24) & 7]) + (int64_t)(meta & 0xffffff) * Nout;
+    } else {
+      dst = out + (int64_t)row * Nout;
+    }
+  }
+#pragma unroll 1
+  for (int p = 0; p < kPasses; ++p) {
+    const int col0 = (half * kPasses + p) * 64;   // first output column of this pass inside the tile
+    uint4 packed[8];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int c = cp * 2 + half;
-        uint32_t v[32];
-        tc_ld32(taddr + c * 32, v);
+    for (int hc = 0; hc < 2; ++hc) {              // two 32-column chunks
+      const int c = col0 / 32 + hc;
+      uint32_t g[32];
+      tc_ld32(taddr + c * 32, g);
+      if (GEGLU) {
+        uint32_t u[32];
+        tc_ld32(taddr + BN / 2 + c * 32, u);
+        tc_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int n = n0 + c * 32 + q * 8;
+          float bg[8], bu[8], o[8];
+          if (n < Nout) {
+            load8_ldg(bias + n, bg);
+            load8_ldg(bias + Nout + n, bu);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bg[i] = bu[i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float gv = __uint_as_float(g[q * 8 + i]) + bg[i];
+            const float uv = __uint_as_float(u[q * 8 + i]) + bu[i];
+            o[i] = gelu_tanh_fast(gv) * uv;
+          }
+          packed[hc * 4 + q] = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]),
+                                          pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+        }
+      } else {
         tc_ld_wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -57,65 +98,31 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, bool row_ok,
             for (int i = 0; i < 8; ++i) b[i] = 0.f;
           }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(v[q * 8 + i]) + b[i];
-          store8(reinterpret_cast<__nv_bfloat16*>(stg + lane * kStgPitch + (half * 4 + q) * 16), o);
+          for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(g[q * 8 + i]) + b[i];
+          packed[hc * 4 + q] = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]),
+                                          pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
         }
+      }
+    }
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {              // 16 rows at a time through the staging area
+      if ((lane >> 4) == hr) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(stg + (lane & 15) * kStgPitch + q * 16) = packed[q];
       }
       __syncwarp();
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         const int rr = i * 4 + (lane >> 3), piece = lane & 7;
-        const int m = __shfl_sync(0xffffffffu, meta, rr);
-        const int n = n0 + cp * 64 + piece * 8;
-        if (m >= 0 && n < Nout) {
-          const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + piece * 16);
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sc.ret_y[(m >> 24) & 7]) +
-                                    (int64_t)(m & 0xffffff) * Nout + n) = val;
-        }
+        __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(
+            __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst), hr * 16 + rr));
+        const int n = n0 + col0 + piece * 8;
+        if (d != nullptr && n < Nout)
+          *reinterpret_cast<uint4*>(d + n) =
+              *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + piece * 16);
       }
       __syncwarp();
-    }
-  } else if (GEGLU) {
-#pragma unroll 1
-    for (int c = c_begin; c < c_end; ++c) {
-      uint32_t g[32], u[32];
-      tc_ld32(taddr + c * 32, g);
-      tc_ld32(taddr + BN / 2 + c * 32, u);
-      tc_ld_wait();
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int n = n0 + c * 32 + q * 8;
-        if (n < Nout) {
-          float bg[8], bu[8], o[8];
-          load8_ldg(bias + n, bg);
-          load8_ldg(bias + Nout + n, bu);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float gv = __uint_as_float(g[q * 8 + i]) + bg[i];
-            float uv = __uint_as_float(u[q * 8 + i]) + bu[i];
-            o[i] = gelu_tanh_fast(gv) * uv;
-          }
-          if (row_ok) store8(orow + c * 32 + q * 8, o);
-        }
-      }
-    }
-  } else {
-#pragma unroll 1
-    for (int c = c_begin; c < c_end; ++c) {
-      uint32_t v[32];
-      tc_ld32(taddr + c * 32, v);
-      tc_ld_wait();
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int n = n0 + c * 32 + q * 8;
-        if (n < Nout) {
-          float b[8], o[8];
-          load8_ldg(bias + n, b);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(v[q * 8 + i]) + b[i];
-          if (row_ok) store8(orow + c * 32 + q * 8, o);
-        }
-      }
     }
   }
 }
