@@ -20,6 +20,7 @@ combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ row_of,
                int k, T* __restrict__ out) {
   const int pieces = d >> 3;
   const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
   if (item >= N * pieces) return;
   const int64_t t = item / pieces;
   const int c = (int)(item - t * pieces) << 3;
@@ -123,15 +124,15 @@ int launch_combine(const void* y, const int32_t* row_of, const float* w, const v
   const int64_t items = N * (d >> 3);
   const int64_t blocks = (items + 255) / 256;
   if (dtype == MOE_B200_BF16) {
-    combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(y), row_of, w,
-        static_cast<const __nv_bfloat16*>(residual), N, d, k, static_cast<__nv_bfloat16*>(out));
+    MOE_CUDA_CHECK(launch_pdl(combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
+                              static_cast<const __nv_bfloat16*>(y), row_of, w,
+                              static_cast<const __nv_bfloat16*>(residual), N, d, k,
+                              static_cast<__nv_bfloat16*>(out)));
   } else {
-    combine_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(
-        static_cast<const float*>(y), row_of, w, static_cast<const float*>(residual), N, d, k,
-        static_cast<float*>(out));
+    MOE_CUDA_CHECK(launch_pdl(combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s,
+                              static_cast<const float*>(y), row_of, w,
+                              static_cast<const float*>(residual), N, d, k, static_cast<float*>(out)));
   }
-  MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
 

@@ -126,6 +126,18 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&ctl->tmem_full[a], 1); mbar_init(&ctl->tmem_empty[a], 16); }
     ctl->abort = 0;
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&ctl->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  // everything above is independent of the kernels before this one in the stream
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
     int acc = 0;
     int beg = offsets[0];
     ctl->offsets[0] = beg;
@@ -139,13 +151,6 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ctl->tile_start[E] = acc;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&ctl->tmem_base)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -304,10 +309,9 @@ int launch_pair(const CUtensorMap& tm_a, const void* tmap_b, const int32_t* offs
                                         (int)kSmemBytes));
     attr_set = true;
   }
-  fn<<<sms & ~1, kThreads, kSmemBytes, s>>>(tm_a, static_cast<const CUtensorMap*>(tmap_b), offsets,
-                                            bias, E, K, Nout, static_cast<__nv_bfloat16*>(out), sc,
-                                            status);
-  MOE_CUDA_CHECK(cudaGetLastError());
+  MOE_CUDA_CHECK(launch_pdl(fn, dim3(sms & ~1), dim3(kThreads), kSmemBytes, s, tm_a,
+                            static_cast<const CUtensorMap*>(tmap_b), offsets, bias, E, K, Nout,
+                            static_cast<__nv_bfloat16*>(out), sc, status));
   return 0;
 }
 
