@@ -118,6 +118,7 @@ class FeedForward(nn.Module):
         self.lora_down_b = nn.Linear(lora_rank, hidden_size)
         self._plan = _Plan()
         self._plan_ft = _Plan()
+        self._offsets = None   # ((rows, device), int32 [0, rows]) of the last call
 
     def forward(self, tensor: torch.Tensor, fine_tuning: bool = False) -> torch.Tensor:
         """y = down(gelu_tanh(gate) * up) for every row, through the grouped
@@ -136,7 +137,9 @@ class FeedForward(nn.Module):
         with torch.cuda.device(dev):
             plan = (self._plan_ft if fine_tuning else self._plan).get(
                 [_MergedExpert(self)] if fine_tuning else [self], d, f, dtype, dev)
-            offsets = torch.tensor([0, M], dtype=torch.int32, device=dev)
+            if self._offsets is None or self._offsets[0] != (M, str(dev)):
+                self._offsets = ((M, str(dev)), torch.tensor([0, M], dtype=torch.int32, device=dev))
+            offsets = self._offsets[1]
             status = torch.zeros(16, dtype=torch.int32, device=dev)
             h = torch.empty(M, f, dtype=x.dtype, device=dev)
             y = torch.empty(M, d, dtype=x.dtype, device=dev)

@@ -213,3 +213,28 @@ def test_empty_batch(cuda_device):
     torch.cuda.synchronize()
     assert out.shape == (0, 4, 64)
     assert m.last["offsets"].cpu().tolist() == [0] * 9
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [1, 200, 1000])
+def test_feedforward_alone(cuda_device, dtype, rows):
+    """The expert module on its own (the reference's dense FeedForward, model.py:154-190)
+    runs through the grouped kernels with a single group."""
+    from gemmallm_b200 import FeedForward
+    d, f = 128, 384
+    p = helpers.rounded_params(synthetic.make_params(d, 1, f, seed=rows), dtype)
+    g = torch.Generator().manual_seed(rows + 1)
+    p["b1"] = synthetic.round_to(torch.randn(1, 2 * f, generator=g) * 0.05, dtype)
+    p["b2"] = synthetic.round_to(torch.randn(1, d, generator=g) * 0.05, dtype)
+    ff = FeedForward(d, d_ff=f).eval().to(device=cuda_device, dtype=dtype)
+    with torch.no_grad():
+        ff.gate_and_up.weight.copy_(p["w1"][0]); ff.gate_and_up.bias.copy_(p["b1"][0])
+        ff.down.weight.copy_(p["w2"][0]); ff.down.bias.copy_(p["b2"][0])
+        x = synthetic.round_to(synthetic.make_input(rows, d, seed=rows + 2), dtype)
+        y = ff(x.to(dtype).to(cuda_device).view(1, rows, d))
+        y2 = ff(x.to(dtype).to(cuda_device).view(1, rows, d))
+        ref = moe_oracle.expert_ffn(x, p["w1"][0], p["b1"][0], p["w2"][0], p["b2"][0])
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    err = (y.view(rows, d).float().cpu() - ref).abs().max()
+    assert err <= (1e-4 if dtype == torch.float32 else 2e-2 * ref.abs().max())
