@@ -81,13 +81,27 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
   for (int e = tid; e < E; e += kThreads) { s_hist[e] = 0; s_base[e] = 0; }
   __syncthreads();
   const int64_t c0 = blockIdx.x;
-  for (int64_t i = tid; i < nchunk * E; i += kThreads) {
-    int v = __ldcg(&chunk_cnt[i]);
-    int64_t cc = i / E;
-    int e = (int)(i - cc * E);
-    if (v != 0) {
-      atomicAdd(&s_hist[e], v);
-      if (cc < c0) atomicAdd(&s_base[e], v);
+  if (kThreads % E == 0) {
+    // every element this thread visits belongs to the same expert: sum in registers,
+    // one shared-memory atomic per thread at the end
+    const int e = tid % E;
+    int tot = 0, before = 0;
+    for (int64_t i = tid; i < nchunk * E; i += kThreads) {
+      const int v = __ldcg(&chunk_cnt[i]);
+      tot += v;
+      if (i / E < c0) before += v;
+    }
+    if (tot != 0) atomicAdd(&s_hist[e], tot);
+    if (before != 0) atomicAdd(&s_base[e], before);
+  } else {
+    for (int64_t i = tid; i < nchunk * E; i += kThreads) {
+      int v = __ldcg(&chunk_cnt[i]);
+      int64_t cc = i / E;
+      int e = (int)(i - cc * E);
+      if (v != 0) {
+        atomicAdd(&s_hist[e], v);
+        if (cc < c0) atomicAdd(&s_base[e], v);
+      }
     }
   }
   __syncthreads();

@@ -202,7 +202,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 
 constexpr int kMmaTokPerWarp = 16;
-constexpr int kMmaUnroll = 8;  // 32-element chunks in flight per lane (16 loads of 16 bytes)
+constexpr int kMmaUnroll = 4;  // 32-element chunks in flight per lane
 
 // NT = n-tiles (of 8 experts) per pass over x; E > 8*NT makes more passes.
 template <int NT>
