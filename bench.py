@@ -244,6 +244,7 @@ def run_ours(args, wl):
         params = synthetic.make_params(d, E, f, seed=0, gate_bias_kind=wl.gate_bias)
         synthetic.load_into(m, params, dt, dev)
         del params
+    m.flags = getattr(args, "flags", 0)
     # each rank owns its own token batch (seed differs per rank)
     x_host = synthetic.make_input(N, d, seed=1 + rank).to(dt).pin_memory()
     x = x_host.to(dev).view(1, N, d)
@@ -353,7 +354,8 @@ def run_ours(args, wl):
     e2e_value = N * world * args.steps / (e2e_ms * 1e-3)
 
     # ---- per-stage times through the stage entry points --------------------
-    stage_ms, launches_per_step = {}, (4 if small_n else 5)
+    two_pass = bool(m.flags & _cabi.FLAG_DECODE_TWO_PASS)
+    stage_ms, launches_per_step = {}, ((4 if two_pass else 3) if small_n else 5)
     if rank == 0:
         stage_ms = time_stages(m, x.view(N, d), wl, dev, small_n)
     peaks, peak_kind = load_peaks()
@@ -402,7 +404,7 @@ def run_ours(args, wl):
             gbs_step = nbytes_step / (ms_step * 1e-3) / 1e9
             gbs_experts = wbytes / (stage_ms["experts"] * 1e-3) / 1e9
             line["roofline"] = {
-                "kernel": "decode_gemm_kernel (GEGLU pass + split-K down pass)",
+                "kernel": "decode_fused_kernel (GEGLU tiles + split-K down tiles, one launch)",
                 "bound": "hbm", "achieved": gbs_experts, "peak": hbm, "unit": "GB/s",
                 "frac": gbs_experts / hbm, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
                 "peak_source": f"{peak_kind} copy",
@@ -630,7 +632,10 @@ def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20):
                 p["w"], p["cnt_slot"], p["offsets"], p["row_of"], p["perm"], p["psum"], p["aux"], s),
                 **calls}
         splits = lib.moe_b200_decode_splits(f)
-        calls["experts"] = lambda: lib.moe_b200_experts_decode(
+        ready = p["status"] + 4 * _cabi.READY_OFFSET
+        calls["experts"] = lambda: lib.moe_b200_experts_decode_fused(
+            p["perm"], p["offsets"], plan, N * k, d, f, E, p["h"], p["part"], ready, p["status"], s)
+        calls["experts_two_pass"] = lambda: lib.moe_b200_experts_decode(
             p["perm"], p["offsets"], plan, N * k, d, f, E, p["h"], p["part"], p["status"], s)
         calls["combine"] = lambda: lib.moe_b200_combine_decode(
             p["part"], splits, N * k, p["row_of"], p["idx"], p["w"], plan, E, None, N, d, k,
@@ -664,6 +669,7 @@ def main():
                     help="expert-parallel: copy the N most popular experts (by the router-bias prior) "
                          "to every rank, on top of the even sharding; 0 = no copies")
     ap.add_argument("--ep-flags", type=int, default=0, help="flags for moe_b200_ep_forward")
+    ap.add_argument("--flags", type=int, default=0, help="flags for moe_b200_forward (one GPU)")
     ap.add_argument("--no-graph", action="store_true", help="small-N workloads: time eager calls")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident loop only (for profiler captures): no end-to-end leg, "

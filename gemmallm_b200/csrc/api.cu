@@ -40,7 +40,7 @@ static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off
   const size_t M = (size_t)N * k;
   const size_t rb = (size_t)((N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock);
   size_t sizes[MOE_B200_WS_NUM];
-  sizes[MOE_B200_WS_STATUS] = 16 * sizeof(int32_t);
+  sizes[MOE_B200_WS_STATUS] = (MOE_B200_READY_OFFSET + MOE_B200_READY_INTS) * sizeof(int32_t);
   sizes[MOE_B200_WS_LOGITS] = (size_t)N * E * sizeof(float);
   sizes[MOE_B200_WS_IDX] = M * sizeof(int32_t);
   sizes[MOE_B200_WS_W] = M * sizeof(float);
@@ -222,6 +222,20 @@ int moe_b200_experts_decode(const void* perm, const int32_t* offsets, const void
   return launch_experts_tc_decode(perm, offsets, plan, M, d, f, E, h, part, status, (cudaStream_t)stream);
 }
 
+int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
+                                  int64_t M, int d, int f, int E, void* h, float* part,
+                                  int32_t* ready, int32_t* status, void* stream) {
+  int rc = check_shape(0, d, f, E, 1, MOE_B200_BF16);
+  if (rc) return rc;
+  if (M < 0 || M > kDecodeMaxRows) return set_error(MOE_B200_ERR_SHAPE, "M exceeds the small-N path's row limit");
+  if (M == 0) return 0;
+  if (!perm || !offsets || !plan || !h || !part || !ready || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(perm) || !aligned16(h) || !aligned16(part)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  MOE_CUDA_CHECK(cudaMemsetAsync(ready, 0, MOE_B200_READY_INTS * sizeof(int32_t), (cudaStream_t)stream));
+  return launch_experts_tc_decode_fused(perm, offsets, plan, M, d, f, E, h, part, ready, status,
+                                        (cudaStream_t)stream);
+}
+
 int moe_b200_combine_decode(const float* part, int ksplit, int64_t M, const int32_t* row_of,
                             const int32_t* idx, const float* w, const void* plan, int E,
                             const void* residual, int64_t N, int d, int k, void* out, void* stream) {
@@ -276,7 +290,9 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   const bool small_n = dtype == MOE_B200_BF16 && N * k <= kDecodeMaxRows &&
                        !(flags & (MOE_B200_FLAG_SIMT_EXPERTS | MOE_B200_FLAG_NO_DECODE_PATH));
 
-  MOE_CUDA_CHECK(cudaMemsetAsync(status, 0, 16 * sizeof(int32_t), s));
+  // status words, and (small N) the completion counters behind them, in one memset
+  MOE_CUDA_CHECK(cudaMemsetAsync(
+      status, 0, (small_n ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
   if (small_n && front_small_supported(N, E, k, dtype)) {
     // router and dispatch of a handful of tokens in one single-block launch
     rc = moe_b200_front_small(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, cnt_slot, offsets,
@@ -291,7 +307,11 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   }
   if (small_n) {
     // few tokens per expert: weight streaming with narrow tiles and split-K
-    rc = moe_b200_experts_decode(perm, offsets, plan, N * k, d, f, E, h, part, status, stream);
+    if (flags & MOE_B200_FLAG_DECODE_TWO_PASS)
+      rc = moe_b200_experts_decode(perm, offsets, plan, N * k, d, f, E, h, part, status, stream);
+    else
+      rc = launch_experts_tc_decode_fused(perm, offsets, plan, N * k, d, f, E, h, part,
+                                          status + MOE_B200_READY_OFFSET, status, s);
     if (rc) return rc;
     return moe_b200_combine_decode(part, decode_splits(f), N * k, row_of, idx, w, plan, E, residual,
                                    N, d, k, out, stream);

@@ -70,12 +70,23 @@ enum {
   MOE_B200_FLAG_EP_UNFUSED_RETURN = 4,
   /* bf16 expert products on the one-CTA kernel (cta_group::1, 128-row tiles)
    * instead of CTA pairs (cta_group::2, 256-row tiles) */
-  MOE_B200_FLAG_ONE_CTA = 8
+  MOE_B200_FLAG_ONE_CTA = 8,
+  /* small-N path of moe_b200_forward: run the GEGLU and the down product as two
+   * launches (moe_b200_experts_decode) instead of the single launch of
+   * moe_b200_experts_decode_fused */
+  MOE_B200_FLAG_DECODE_TWO_PASS = 16
 };
+
+/* Layout of the status region: word 0 = device status code, words 1..15 detail;
+ * from word MOE_B200_READY_OFFSET on, MOE_B200_READY_INTS completion counters of
+ * moe_b200_experts_decode_fused. */
+#define MOE_B200_STATUS_INTS 16
+#define MOE_B200_READY_OFFSET 64
+#define MOE_B200_READY_INTS 320
 
 /* Indices into the array filled by moe_b200_workspace_layout. */
 enum {
-  MOE_B200_WS_STATUS = 0, /* int32[16]; word 0 = device status code */
+  MOE_B200_WS_STATUS = 0, /* int32[16] status, then the counters (see MOE_B200_READY_OFFSET) */
   MOE_B200_WS_LOGITS,     /* float [N,E]   router logits (model.py:206) */
   MOE_B200_WS_IDX,        /* int32 [N,k]   chosen experts, slot 0 = best (model.py:210) */
   MOE_B200_WS_W,          /* float [N,k]   renormalised scores (model.py:219-223) */
@@ -215,6 +226,18 @@ int moe_b200_experts_decode(const void* perm, const int32_t* offsets, const void
                             int32_t* status, void* stream);
 int moe_b200_decode_splits(int f);
 int64_t moe_b200_decode_max_rows(void);
+
+/* The same results as moe_b200_experts_decode from ONE launch: the down tiles of
+ * a 32-row block start as soon as that block's GEGLU tiles have finished, while
+ * other blocks' weights are still streaming (same arithmetic, model.py:174-184).
+ * `ready`: int32[MOE_B200_READY_INTS] completion counters, zeroed by this call.
+ * The kernel's blocks wait on one another, so all of them must be resident: one
+ * block per SM of an otherwise idle GPU. If other work holds SMs for seconds,
+ * the bounded waits end with MOE_B200_DEV_TIMEOUT in status and the outputs are
+ * unspecified; the context stays usable. */
+int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
+                                  int64_t M, int d, int f, int E, void* h, float* part,
+                                  int32_t* ready, int32_t* status, void* stream);
 
 /* Parts 4+5 after moe_b200_experts_decode: y = sum_s part[s] + down.bias of
  * the row's expert (idx), rounded to bf16, then the weighted sum and residual

@@ -110,6 +110,22 @@ def experts_decode(perm, offsets, plan: Plan):
     return h, part, status
 
 
+def experts_decode_fused(perm, offsets, plan: Plan):
+    M, d = perm.shape
+    dev = perm.device
+    splits = lib.moe_b200_decode_splits(plan.f)
+    h = torch.empty(M, plan.f, dtype=perm.dtype, device=dev)
+    part = torch.full((splits, M, d), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    # stale counters on purpose: the entry point has to zero them
+    ready = torch.full((_cabi.READY_INTS,), 7, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_experts_decode_fused(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d,
+                                            plan.f, plan.E, h.data_ptr(), part.data_ptr(),
+                                            ready.data_ptr(), status.data_ptr(), stream(dev)),
+          "experts_decode_fused")
+    return h, part, status
+
+
 def combine_decode(part, row_of, idx, w, plan: Plan, residual=None):
     splits, M, d = part.shape
     N, k = row_of.shape

@@ -149,6 +149,28 @@ def test_c2_decode_shapes_bf16(cuda_device, name):
     check_against_oracle(m, params, x, wl.top_k, torch.bfloat16, cuda_device, residual=res)
 
 
+@pytest.mark.parametrize("name", ["c2_t8", "c2_t64"])
+def test_c2_single_launch_experts_equal_two_launches(cuda_device, name):
+    """Small-N forward: the default single-launch expert kernel and the two-launch
+    variant (flag) produce the same bits, call after call."""
+    wl = synthetic.WORKLOADS[name]
+    params = helpers.rounded_params(
+        synthetic.make_params(wl.d_model, wl.n_experts, wl.d_ff, seed=0), torch.bfloat16)
+    x = synthetic.round_to(synthetic.make_input(wl.tokens, wl.d_model, seed=1), torch.bfloat16)
+    xin = x.to(torch.bfloat16).to(cuda_device).view(1, wl.tokens, wl.d_model)
+    outs = []
+    for flags in (0, _cabi.FLAG_DECODE_TWO_PASS, 0):
+        m = build(params, wl.d_model, wl.n_experts, wl.d_ff, wl.top_k, torch.bfloat16, cuda_device, flags)
+        with torch.no_grad():
+            for _ in range(3):
+                out, _aux = m(xin)
+        torch.cuda.synchronize()
+        assert m.device_status() == 0
+        outs.append(out.clone())
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[2])
+
+
 def test_c4_router_pin(cuda_device):
     wl = synthetic.WORKLOADS["c4"]
     pins = json.loads((GOLDEN / "routing_pins.json").read_text())["c4"]
