@@ -53,6 +53,11 @@ static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off
   sizes[MOE_B200_WS_ROW_OF] = M * sizeof(int32_t);
   sizes[MOE_B200_WS_PERM] = M * d * es;
   sizes[MOE_B200_WS_H] = M * f * es;
+  if (dtype == MOE_B200_BF16 && decode_spec_supported(N, E, k)) {
+    // the routing-independent small-N kernel keeps one slab of h per expert
+    const size_t slabs = (size_t)E * decode_spec_rows(N) * f * es;
+    if (slabs > sizes[MOE_B200_WS_H]) sizes[MOE_B200_WS_H] = slabs;
+  }
   sizes[MOE_B200_WS_Y] = M * d * es;
   sizes[MOE_B200_WS_PART] =
       (dtype == MOE_B200_BF16 && M <= kDecodeMaxRows) ? (size_t)decode_splits(f) * M * d * sizeof(float) : 0;
@@ -236,6 +241,22 @@ int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, cons
                                         (cudaStream_t)stream);
 }
 
+int moe_b200_decode_spec_rows(int64_t N) { return decode_spec_rows(N); }
+
+int moe_b200_experts_decode_spec(const void* x, const int32_t* idx, const int32_t* offsets,
+                                 const void* plan, int64_t N, int k, int d, int f, int E,
+                                 void* h_all, float* part, int32_t* ready, int32_t* status,
+                                 void* stream) {
+  int rc = check_shape(N, d, f, E, k, MOE_B200_BF16);
+  if (rc) return rc;
+  if (!decode_spec_supported(N, E, k)) return set_error(MOE_B200_ERR_UNSUPPORTED, "needs N <= 128, E <= 32, N*k within the small-N row limit");
+  if (!x || !idx || !offsets || !plan || !h_all || !part || !ready || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(x) || !aligned16(h_all) || !aligned16(part)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  MOE_CUDA_CHECK(cudaMemsetAsync(ready, 0, MOE_B200_READY_INTS * sizeof(int32_t), (cudaStream_t)stream));
+  return launch_experts_tc_decode_spec(x, idx, offsets, plan, N, k, d, f, E, h_all, part, ready, status,
+                                       (cudaStream_t)stream);
+}
+
 int moe_b200_combine_decode(const float* part, int ksplit, int64_t M, const int32_t* row_of,
                             const int32_t* idx, const float* w, const void* plan, int E,
                             const void* residual, int64_t N, int d, int k, void* out, void* stream) {
@@ -290,6 +311,10 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   const bool small_n = dtype == MOE_B200_BF16 && N * k <= kDecodeMaxRows &&
                        !(flags & (MOE_B200_FLAG_SIMT_EXPERTS | MOE_B200_FLAG_NO_DECODE_PATH));
 
+  // most experts hit: stream all of them without waiting for the routing
+  const bool spec = small_n && front_small_supported(N, E, k, dtype) && decode_spec_supported(N, E, k) &&
+                    N * k >= 2 * (int64_t)E &&
+                    !(flags & (MOE_B200_FLAG_DECODE_TWO_PASS | MOE_B200_FLAG_DECODE_NO_SPEC));
   // status words, and (small N) the completion counters behind them, in one memset
   MOE_CUDA_CHECK(cudaMemsetAsync(
       status, 0, (small_n ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
@@ -309,6 +334,9 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
     // few tokens per expert: weight streaming with narrow tiles and split-K
     if (flags & MOE_B200_FLAG_DECODE_TWO_PASS)
       rc = moe_b200_experts_decode(perm, offsets, plan, N * k, d, f, E, h, part, status, stream);
+    else if (spec)
+      rc = launch_experts_tc_decode_spec(x, idx, offsets, plan, N, k, d, f, E, h, part,
+                                         status + MOE_B200_READY_OFFSET, status, s);
     else
       rc = launch_experts_tc_decode_fused(perm, offsets, plan, N * k, d, f, E, h, part,
                                           status + MOE_B200_READY_OFFSET, status, s);

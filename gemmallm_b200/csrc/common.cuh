@@ -230,9 +230,14 @@ int launch_front_small(const void* x, const void* Wg, const void* bg, int64_t N,
 int encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int sm_count(int* sms);
 int decode_splits(int f);
+int decode_spec_rows(int64_t N);
+bool decode_spec_supported(int64_t N, int E, int k);
+int launch_experts_tc_decode_spec(const void* x, const int32_t* idx, const int32_t* offsets,
+                                  const void* plan, int64_t N, int k, int d, int f, int E, void* h_all,
+                                  float* part, int* ready, int32_t* status, cudaStream_t s);
 int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                    int64_t M, int d, int f, int E, void* h, float* part, int* ready,
-                                   int32_t* status, cudaStream_t s);
+                                   int32_t* status, cudaStream_t s, int spec = -1);
 int launch_experts_tc_decode(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
                              int d, int f, int E, void* h, float* part, int32_t* status,
                              cudaStream_t s);

@@ -81,6 +81,15 @@ __device__ __forceinline__ Tile decode_tile(const Control* ctl, int t, int E, in
   return ti;
 }
 
+// Debug timeline (compile with -DMOE_TIMELINE): %globaltimer stamps in status words 16..
+#ifdef MOE_TIMELINE
+#define TL_FIRST(slot) do { if (blockIdx.x == 0) reinterpret_cast<unsigned long long*>(status + 16)[slot] = global_ns(); } while (0)
+#define TL_MAX(slot) atomicMax(reinterpret_cast<unsigned long long*>(status + 16) + (slot), global_ns())
+#else
+#define TL_FIRST(slot)
+#define TL_MAX(slot)
+#endif
+
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -91,6 +100,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_h,
                     const CUtensorMap* __restrict__ tmap_w1, const CUtensorMap* __restrict__ tmap_w2,
                     const int32_t* __restrict__ offsets, const void* const* __restrict__ b1_ptrs,
+                    const void* const* __restrict__ w1_ptrs, int spec_waves,
                     int E, int d, int f, int ksplit, int64_t part_stride,
                     __nv_bfloat16* __restrict__ h, float* __restrict__ part, int* __restrict__ ready,
                     int32_t* __restrict__ status) {
@@ -116,6 +126,9 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       mbar_init(&ctl->h_done[a], 128);
     }
     ctl->abort = 0;
+    TL_FIRST(0);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -124,23 +137,61 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // tensor maps into the descriptor cache: the plan is not written by earlier kernels
+  if (warp == 2) {
+    for (int e = lane; e < E; e += 32) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(tmap_w1 + e) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(tmap_w2 + e) : "memory");
+    }
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_h) : "memory");
+    }
+  }
+  // Speculation while the kernels before this one still run: if every expert gets
+  // exactly one 32-row block, tile t is (expert t / n1, n tile t % n1), so this CTA's
+  // first `spec_waves` GEGLU tiles are known before the routing is. Pull their weight
+  // rows (two runs of 64 consecutive rows) into L2. A wrong guess costs bandwidth only.
+  if (threadIdx.x == 96) {
+    const size_t row_bytes = (size_t)d * 2;
+    for (int w = 0; w < spec_waves; ++w) {
+      const int t = (int)blockIdx.x + w * (int)gridDim.x;
+      const int e = t / n1, nt = t - e * n1;
+      if (e >= E) break;
+      const char* W = static_cast<const char*>(w1_ptrs[e]);
+      const int rows = min(64, f - nt * 64);
+      for (int half = 0; half < 2; ++half) {
+        const char* p = W + (size_t)(half * f + nt * 64) * row_bytes;
+        const size_t bytes = (size_t)rows * row_bytes;
+        for (size_t o = 0; o < bytes; o += 16384) {
+          const uint32_t n = (uint32_t)min((size_t)16384, bytes - o);
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + o), "r"(n) : "memory");
+        }
+      }
+    }
+  }
   // everything above is independent of the kernels before this one in the stream
   pdl_wait();
   pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    int beg = offsets[0];
-    ctl->offsets[0] = beg;
-    for (int e = 0; e < E; ++e) {
-      ctl->tb_start[e] = acc;
-      const int end = offsets[e + 1];
-      ctl->offsets[e + 1] = end;
-      acc += (end - beg + kTok - 1) / kTok;
-      beg = end;
+  if (threadIdx.x == 0) TL_FIRST(1);
+  for (int e = threadIdx.x; e <= E; e += kThreads) ctl->offsets[e] = offsets[e];
+  __syncthreads();
+  if (warp == 0) {
+    // 32-row blocks per expert, exclusive scan over the experts
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int nb = e < E ? (ctl->offsets[e + 1] - ctl->offsets[e] + kTok - 1) / kTok : 0;
+      int incl = nb;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (e < E) ctl->tb_start[e] = carry + incl - nb;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    ctl->tb_start[E] = acc;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (lane == 0) ctl->tb_start[E] = carry;
   }
   tc_fence_before();
   __syncthreads();
@@ -185,10 +236,16 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort, status, 11)) { ok = false; break; }
           uint8_t* sw = smem + (size_t)stage * kStageBytes;
+#ifdef MOE_EXP_NOTOK
+          mbar_expect_tx(&ctl->full[stage], kWBytes);
+          tma_load_2d(sw, tw, &ctl->full[stage], kb * BK, w0);
+          tma_load_2d(sw + kWHalf, tw, &ctl->full[stage], kb * BK, w1);
+#else
           mbar_expect_tx(&ctl->full[stage], kStageBytes);
           tma_load_2d(sw, tw, &ctl->full[stage], kb * BK, w0);
           tma_load_2d(sw + kWHalf, tw, &ctl->full[stage], kb * BK, w1);
           tma_load_2d(sw + kWBytes, tt, &ctl->full[stage], kb * BK, ti.row0);
+#endif
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -212,14 +269,21 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const uint32_t tmem_d = tmem_base + (uint32_t)(a * kTok);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&ctl->full[stage], phase, &ctl->abort, status, 13)) { ok = false; break; }
+#ifdef MOE_TIMELINE
+          if (it == 0 && kb == kb0) TL_FIRST(2);
+#endif
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + (size_t)stage * kStageBytes);
           const uint64_t wdesc = make_smem_desc(sw);
           const uint64_t tdesc = make_smem_desc(sw + kWBytes);
+#ifdef MOE_EXP_NOMMA
+          if (kb == kb0) tc_mma(tmem_d, wdesc, tdesc, kIdesc, 0u);
+#else
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk)
             tc_mma(tmem_d, wdesc + (uint64_t)(kk * 2), tdesc + (uint64_t)(kk * 2), kIdesc,
                    (kb > kb0 || kk > 0) ? 1u : 0u);
+#endif
           tc_commit(&ctl->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -278,6 +342,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           if (!mbar_wait(&ctl->h_done[a], acc_phase, &ctl->abort, status, 17)) { ok = false; break; }
           __threadfence();
           atomicAdd(&ready[ti.tbg], 1);
+          TL_MAX(3);
         }
       } else if (feat_ok) {
         float* o = part + (int64_t)ti.ks * part_stride + (int64_t)ti.row0 * d + feat;
@@ -293,6 +358,9 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
   // ---------------- teardown ----------------
   __syncwarp();
+#ifdef MOE_TIMELINE
+  if (lane == 0) TL_MAX(4 + min(warp, 2));   // 4 producer, 5 MMA, 6 epilogue
+#endif
   if (*reinterpret_cast<volatile int*>(&ctl->abort)) {
     unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
@@ -309,10 +377,10 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
 }  // namespace
 
-// `ready`: int32 [kDecodeReadyInts], zeroed by the caller before this launch.
+// `ready`: int32 [MOE_B200_READY_INTS], zeroed by the caller before this launch.
 int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                    int64_t M, int d, int f, int E, void* h, float* part, int* ready,
-                                   int32_t* status, cudaStream_t s) {
+                                   int32_t* status, cudaStream_t s, int spec) {
   if (M == 0) return 0;
   PlanView pv = plan_view(plan, E);
   alignas(64) CUtensorMap tm_x, tm_h;
@@ -323,6 +391,8 @@ int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, con
   int sms = 0;
   rc = sm_count(&sms);
   if (rc) return rc;
+  // weight rows pulled into L2 ahead of the routing: only when most experts are hit
+  const int spec_waves = spec < 0 ? (M >= 4 * (int64_t)E ? 2 : (M >= E ? 1 : 0)) : spec;
   static bool attr_set = false;
   if (!attr_set) {
     MOE_CUDA_CHECK(cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -331,7 +401,8 @@ int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, con
   }
   MOE_CUDA_CHECK(launch_pdl(decode_fused_kernel, dim3(sms), dim3(kThreads), kSmemBytes, s, tm_x, tm_h,
                             static_cast<const CUtensorMap*>(pv.tmap_W1_dec),
-                            static_cast<const CUtensorMap*>(pv.tmap_W2_dec), offsets, pv.b1, E, d, f,
+                            static_cast<const CUtensorMap*>(pv.tmap_W2_dec), offsets, pv.b1, pv.W1,
+                            spec_waves, E, d, f,
                             decode_splits(f), M * (int64_t)d, static_cast<__nv_bfloat16*>(h), part,
                             ready, status));
   return 0;

@@ -9,11 +9,13 @@
 //      partial x Wg^T with mma.sync m16n8k16 exactly like router_mma_kernel
 //      (router.cu), all its loads in flight at once; partials are summed over
 //      the K slices in slice order, plus bias;
-//   B. one thread per token: fp32 softmax, k passes of arg-max ordered by
-//      (logit desc, index asc), renormalise; probabilities summed per expert in
-//      token order; loss;
-//   C. per-slot counts, offsets (scan over E), stable ranks in (token, slot)
-//      order, row copies into the sorted buffer with 16-byte accesses.
+//   B. 8, 16 or 32 lanes per token, lane e = expert e: fp32 softmax, k passes of
+//      arg-max ordered by (logit desc, index asc) with integer warp reductions
+//      on order-preserving keys, renormalise;
+//   C. warp 0: per-slot counts, offsets (scan over E), stable ranks in (token,
+//      slot) order; then row copies into the sorted buffer with 16-byte accesses
+//      (their loads were issued before B);
+//   E. block 0, after its copies: probabilities summed per expert in token order; loss.
 #include "common.cuh"
 
 namespace moe {
@@ -33,6 +35,15 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+
+// Debug timeline (compile with -DMOE_TIMELINE): %globaltimer stamps of block 0.
+#ifdef MOE_TIMELINE
+__device__ unsigned long long g_front_tl[16];
+#define FTL(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) { unsigned long long t_; \
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_front_tl[slot] = t_; } } while (0)
+#else
+#define FTL(slot)
+#endif
 
 template <int NT>  // n-tiles of 8 experts: E <= 8*NT
 __global__ void __launch_bounds__(kThreads, 1)
@@ -56,12 +67,17 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   int* s_cnt = s_row + kMaxPairs;                          // [kMaxTopK][kMaxE]
   int* s_off = s_cnt + kMaxTopK * kMaxE;                   // [kMaxE+1]
   int* s_run = s_off + kMaxE + 1;                          // [kMaxE]
+  float* s_bias = reinterpret_cast<float*>(s_run + kMaxE); // [kMaxE]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int ET = 8 * NT;
+  constexpr int ET_C = 8 * NT;
+  const int ET = ET_C;
+  FTL(0);
   pdl_wait();                 // x may come from the kernel before this one
   pdl_launch_dependents();
+  FTL(1);
+  if (tid < E) s_bias[tid] = __bfloat162float(bg[tid]);   // visible after the barrier behind part A
 
   // ---- A. partial logits -----------------------------------------------------
   {
@@ -116,94 +132,121 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   }
   for (int i = tid; i < kMaxTopK * kMaxE; i += kThreads) s_cnt[i] = 0;
+  FTL(2);
   __syncthreads();
+  FTL(3);
+  // the first batch of row copies: the loads do not depend on the routing, so they are
+  // issued now and wait in registers until the destination rows are known
+  const int pieces = d >> 3;
+  const int items = N * pieces;
+  const uint4* src = reinterpret_cast<const uint4*>(x);
+  constexpr int kInFlight = 4;
+  const int first_item = blockIdx.x * kThreads * kInFlight + tid;
+  uint4 pre[kInFlight];
+#pragma unroll
+  for (int u = 0; u < kInFlight; ++u) {
+    const int i = first_item + u * kThreads;
+    if (i < items)
+      asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(pre[u].x), "=r"(pre[u].y), "=r"(pre[u].z), "=r"(pre[u].w)
+                   : "l"(src + i)
+                   : "memory");
+  }
   for (int i = tid; i < N * E; i += kThreads) {
     const int tok = i / E, e = i - tok * E;
     float s = 0.f;
     for (int ks = 0; ks < nslices; ++ks) s += s_part[((size_t)ks * 16 * gp2 + tok) * ET + e];
-    s += __bfloat162float(bg[e]);
+    s += s_bias[e];
     s_logit[tok * ld + e] = s;
     if (out_logits != nullptr && blockIdx.x == 0) out_logits[i] = s;
   }
   __syncthreads();
+  FTL(4);
 
-  // ---- B. softmax, top-k, renormalise: one thread per token --------------------
-  if (tid < N) {
-    float* lg = s_logit + tid * ld;
-    float m = -INFINITY;
-    for (int e = 0; e < E; ++e) m = fmaxf(m, lg[e]);
-    float sum = 0.f;
-    for (int e = 0; e < E; ++e) sum += expf(lg[e] - m);
-    int sel[kMaxTopK];
-    float sl[kMaxTopK], vals[kMaxTopK];
-    float total = 0.f;
+  // ---- B. softmax, top-k, renormalise: a group of ET lanes per token, lane e = expert e ----
+  {
+    constexpr int G = ET_C;                 // 8, 16 or 32 lanes
+    constexpr int kTokPerWarp = 32 / G;
+    const int grp = lane / G, e = lane % G;
+    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (grp * G));
+    for (int tok0 = warp * kTokPerWarp; tok0 < N; tok0 += (kThreads / 32) * kTokPerWarp) {
+      const int tok = tok0 + grp;
+      const bool live = tok < N && e < E;
+      float* lg = s_logit + (size_t)min(tok, N - 1) * ld;
+      const float v = live ? lg[e] + 0.f : -INFINITY;      // + 0: no negative zero
+      // order-preserving map float -> unsigned, so that the integer warp reduction finds the maximum
+      const unsigned u = __float_as_uint(v);
+      unsigned key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+      const unsigned kmax = __reduce_max_sync(gmask, key);
+      const float m = __uint_as_float((kmax & 0x80000000u) ? (kmax & 0x7fffffffu) : ~kmax);
+      const float p = live ? expf(v - m) : 0.f;
+      float sum = p;
 #pragma unroll
-    for (int j = 0; j < kMaxTopK; ++j) {
-      if (j < k) {
-        float bl = -INFINITY;
-        int be = 0;
-        for (int e = 0; e < E; ++e) {
-          const float v = lg[e];
-          if (v > bl) { bl = v; be = e; }
+      for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(gmask, sum, o);
+      if (live) lg[e] = p / sum;            // probabilities, for the loss below
+      int sel[kMaxTopK];
+      float vals[kMaxTopK];
+      float total = 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxTopK; ++j) {
+        if (j < k) {
+          // arg-max ordered by (logit descending, index ascending)
+          const unsigned km = __reduce_max_sync(gmask, key);
+          const unsigned hit = __ballot_sync(gmask, key == km) & gmask;
+          const int winner = __ffs(hit) - 1;
+          sel[j] = winner - grp * G;
+          const float bv = __uint_as_float((km & 0x80000000u) ? (km & 0x7fffffffu) : ~km);
+          vals[j] = expf(bv - m) / sum;
+          total += vals[j];
+          if (lane == winner) key = 0u;     // below every real key
         }
-        sel[j] = be;
-        sl[j] = bl;
-        vals[j] = expf(bl - m) / sum;
-        total += vals[j];
-        lg[be] = -INFINITY;
+      }
+      if (e == 0 && tok < N) {
+#pragma unroll
+        for (int j = 0; j < kMaxTopK; ++j) {
+          if (j < k) {
+            if (blockIdx.x == 0) {
+              out_idx[tok * k + j] = sel[j];
+              out_w[tok * k + j] = vals[j] / total;
+            }
+            s_idx[tok * k + j] = sel[j];
+            atomicAdd(&s_cnt[j * kMaxE + sel[j]], 1);
+          }
+        }
       }
     }
-#pragma unroll
-    for (int j = 0; j < kMaxTopK; ++j) {
-      if (j < k) {
-        lg[sel[j]] = sl[j];
-        if (blockIdx.x == 0) {
-          out_idx[tid * k + j] = sel[j];
-          out_w[tid * k + j] = vals[j] / total;
-        }
-        s_idx[tid * k + j] = sel[j];
-        atomicAdd(&s_cnt[j * kMaxE + sel[j]], 1);
-      }
-    }
-    for (int e = 0; e < E; ++e) lg[e] = expf(lg[e] - m) / sum;
   }
   __syncthreads();
+  FTL(5);
 
-  // ---- C. counts, offsets, loss, ranks -----------------------------------------
-  if (tid < E) {
-    int tot = 0;
-    for (int j = 0; j < k; ++j) {
-      const int c = s_cnt[j * kMaxE + tid];
-      if (blockIdx.x == 0) cnt_slot[j * E + tid] = c;
-      tot += c;
-    }
-    s_run[tid] = tot;          // total rows of this expert, until the scan below
-    float ps = 0.f;
-    for (int tok = 0; tok < N; ++tok) ps += s_logit[tok * ld + tid];
-    if (blockIdx.x == 0) psum[tid] = ps;
-    s_part[tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int acc = 0;
-    float a = 0.f;
-    for (int e = 0; e < E; ++e) {
-      s_off[e] = acc;
-      if (blockIdx.x == 0) offsets[e] = acc;
-      acc += s_run[e];
-      a += s_part[e];
-    }
-    s_off[E] = acc;
-    if (blockIdx.x == 0) {
-      offsets[E] = acc;
-      aux[0] = a / (float)E * (float)(E * E);   // model.py:213-216
-    }
-  }
-  __syncthreads();
+  // ---- C. counts, offsets, ranks: warp 0 -------------------------------------------
   if (warp == 0) {
-    const int npair = N * k;
-    for (int e = lane; e < E; e += 32) s_run[e] = 0;
+    int tot = 0;
+    if (lane < E) {
+      for (int j = 0; j < k; ++j) {
+        const int c = s_cnt[j * kMaxE + lane];
+        if (blockIdx.x == 0) cnt_slot[j * E + lane] = c;
+        tot += c;
+      }
+    }
+    int incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane < E) {
+      s_off[lane] = incl - tot;
+      s_run[lane] = 0;
+      if (blockIdx.x == 0) offsets[lane] = incl - tot;
+    }
+    if (lane == 31) {
+      s_off[E] = incl;
+      if (blockIdx.x == 0) offsets[E] = incl;
+    }
     __syncwarp();
+    FTL(7);
+    const int npair = N * k;
     for (int p0 = 0; p0 < npair; p0 += 32) {
       const int p = p0 + lane;
       const int e = p < npair ? s_idx[p] : -1;
@@ -221,19 +264,16 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   }
   __syncthreads();
+  FTL(8);
 
   // ---- D. copy the token rows into the sorted buffer (split over the blocks) -----
-  const int pieces = d >> 3;
-  const int items = N * pieces;
-  const uint4* src = reinterpret_cast<const uint4*>(x);
-  constexpr int kInFlight = 4;
-  for (int i0 = blockIdx.x * kThreads * kInFlight + tid; i0 < items;
-       i0 += gridDim.x * kThreads * kInFlight) {
+  for (int i0 = first_item; i0 < items; i0 += gridDim.x * kThreads * kInFlight) {
     uint4 v[kInFlight];
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
       const int i = i0 + u * kThreads;
-      if (i < items) v[u] = __ldg(src + i);
+      if (i0 == first_item) v[u] = pre[u];
+      else if (i < items) v[u] = __ldg(src + i);
     }
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
@@ -245,6 +285,23 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       }
     }
   }
+  FTL(9);
+
+  // ---- E. the loss, off the path of the kernels that wait for the rows (model.py:213-216) ----
+  if (blockIdx.x == 0) {
+    if (tid < E) {
+      float ps = 0.f;
+      for (int tok = 0; tok < N; ++tok) ps += s_logit[tok * ld + tid];
+      psum[tid] = ps;
+      s_part[tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float a = 0.f;
+      for (int e = 0; e < E; ++e) a += s_part[e];
+      aux[0] = a / (float)E * (float)(E * E);
+    }
+  }
 }
 
 template <int NT>
@@ -252,7 +309,7 @@ int launch(const void* x, const void* Wg, const void* bg, int N, int d, int E, i
            float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot, int32_t* offsets,
            int32_t* row_of, void* perm, float* psum, float* aux, cudaStream_t s) {
   const size_t smem = sizeof(float) * ((size_t)32 * 16 * 8 * NT + (size_t)kMaxTok * (E + 1)) +
-                      sizeof(int) * (2 * kMaxPairs + kMaxTopK * kMaxE + 2 * kMaxE + 1);
+                      sizeof(int) * (2 * kMaxPairs + kMaxTopK * kMaxE + 3 * kMaxE + 1);
   static bool attr_set = false;
   if (!attr_set) {
     MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT>,
@@ -285,3 +342,9 @@ int launch_front_small(const void* x, const void* Wg, const void* bg, int64_t N,
 }
 
 }  // namespace moe
+
+#ifdef MOE_TIMELINE
+extern "C" int moe_b200_debug_front_timeline(unsigned long long* h16) {
+  return (int)cudaMemcpyFromSymbol(h16, moe::g_front_tl, sizeof(unsigned long long) * 16);
+}
+#endif

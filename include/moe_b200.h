@@ -74,7 +74,10 @@ enum {
   /* small-N path of moe_b200_forward: run the GEGLU and the down product as two
    * launches (moe_b200_experts_decode) instead of the single launch of
    * moe_b200_experts_decode_fused */
-  MOE_B200_FLAG_DECODE_TWO_PASS = 16
+  MOE_B200_FLAG_DECODE_TWO_PASS = 16,
+  /* small-N path of moe_b200_forward: never use moe_b200_experts_decode_spec (the
+   * kernel that streams every expert without waiting for the routing) */
+  MOE_B200_FLAG_DECODE_NO_SPEC = 32
 };
 
 /* Layout of the status region: word 0 = device status code, words 1..15 detail;
@@ -238,6 +241,24 @@ int64_t moe_b200_decode_max_rows(void);
 int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                   int64_t M, int d, int f, int E, void* h, float* part,
                                   int32_t* ready, int32_t* status, void* stream);
+
+/* Part 3 for small N without waiting for the routing: the same partial sums
+ * part[s][M][d] as moe_b200_experts_decode (row order of moe_b200_dispatch), but
+ * computed from the UNSORTED tokens x [N,d]: every expert's weights are streamed and
+ * multiplied with all N tokens, and only the (token, expert) pairs of idx [N,k] are
+ * stored. Nothing the kernel loads depends on idx/offsets, so under programmatic
+ * dependent launch it overlaps the routing kernel before it in the stream
+ * (model.py:174-184 per expert; the reference skips experts without tokens,
+ * model.py:256, this kernel reads their GEGLU weights anyway: worth it when most
+ * experts are hit, roughly N*k >= 2E). bf16, N <= 128, E <= 32, N*k <=
+ * moe_b200_decode_max_rows(). h_all: bf16 [E][moe_b200_decode_spec_rows(N)][f]
+ * scratch; ready: int32[MOE_B200_READY_INTS], zeroed by this call. Residency rule
+ * and timeout behaviour as for moe_b200_experts_decode_fused. */
+int moe_b200_experts_decode_spec(const void* x, const int32_t* idx, const int32_t* offsets,
+                                 const void* plan, int64_t N, int k, int d, int f, int E,
+                                 void* h_all, float* part, int32_t* ready, int32_t* status,
+                                 void* stream);
+int moe_b200_decode_spec_rows(int64_t N);
 
 /* Parts 4+5 after moe_b200_experts_decode: y = sum_s part[s] + down.bias of
  * the row's expert (idx), rounded to bf16, then the weighted sum and residual

@@ -126,6 +126,25 @@ def experts_decode_fused(perm, offsets, plan: Plan):
     return h, part, status
 
 
+def experts_decode_spec(x, idx, offsets, plan: Plan):
+    """x [N,d] unsorted tokens; returns part [splits, N*k, d] in dispatch row order."""
+    N, d = x.shape
+    k = idx.shape[1]
+    dev = x.device
+    splits = lib.moe_b200_decode_splits(plan.f)
+    NP = lib.moe_b200_decode_spec_rows(N)
+    # poisoned slabs: rows of tokens not routed to an expert are never written and must not matter
+    h_all = torch.full((plan.E, NP, plan.f), float("nan"), dtype=x.dtype, device=dev)
+    part = torch.full((splits, N * k, d), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    ready = torch.full((_cabi.READY_INTS,), 7, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_experts_decode_spec(x.data_ptr(), idx.data_ptr(), offsets.data_ptr(), plan.ptr,
+                                           N, k, d, plan.f, plan.E, h_all.data_ptr(), part.data_ptr(),
+                                           ready.data_ptr(), status.data_ptr(), stream(dev)),
+          "experts_decode_spec")
+    return h_all, part, status
+
+
 def combine_decode(part, row_of, idx, w, plan: Plan, residual=None):
     splits, M, d = part.shape
     N, k = row_of.shape

@@ -159,7 +159,7 @@ def test_c2_single_launch_experts_equal_two_launches(cuda_device, name):
     x = synthetic.round_to(synthetic.make_input(wl.tokens, wl.d_model, seed=1), torch.bfloat16)
     xin = x.to(torch.bfloat16).to(cuda_device).view(1, wl.tokens, wl.d_model)
     outs = []
-    for flags in (0, _cabi.FLAG_DECODE_TWO_PASS, 0):
+    for flags in (_cabi.FLAG_DECODE_NO_SPEC, _cabi.FLAG_DECODE_TWO_PASS, _cabi.FLAG_DECODE_NO_SPEC):
         m = build(params, wl.d_model, wl.n_experts, wl.d_ff, wl.top_k, torch.bfloat16, cuda_device, flags)
         with torch.no_grad():
             for _ in range(3):
@@ -169,6 +169,15 @@ def test_c2_single_launch_experts_equal_two_launches(cuda_device, name):
         outs.append(out.clone())
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[0], outs[2])
+    # the default (routing-independent kernel when most experts are hit): same products, other tiles
+    m = build(params, wl.d_model, wl.n_experts, wl.d_ff, wl.top_k, torch.bfloat16, cuda_device, 0)
+    with torch.no_grad():
+        for _ in range(3):
+            out, _aux = m(xin)
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    ref = outs[0].float()
+    assert (out.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
 
 
 def test_c4_router_pin(cuda_device):
