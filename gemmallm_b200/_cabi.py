@@ -18,6 +18,7 @@ FLAG_DEFAULT, FLAG_SIMT_EXPERTS, FLAG_NO_DECODE_PATH, FLAG_EP_UNFUSED_RETURN = 0
 FLAG_ONE_CTA = 8
 FLAG_DECODE_TWO_PASS = 16
 FLAG_DECODE_NO_SPEC = 32
+FLAG_WS_CLEAN = 64
 READY_OFFSET, READY_INTS = 64, 320
 DEV_OK, DEV_TIMEOUT, DEV_BAD_INDEX = 0, 1, 2
 

@@ -316,8 +316,9 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
                     N * k >= 2 * (int64_t)E &&
                     !(flags & (MOE_B200_FLAG_DECODE_TWO_PASS | MOE_B200_FLAG_DECODE_NO_SPEC));
   // status words, and (small N) the completion counters behind them, in one memset
-  MOE_CUDA_CHECK(cudaMemsetAsync(
-      status, 0, (small_n ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
+  if (!(small_n && (flags & MOE_B200_FLAG_WS_CLEAN)))
+    MOE_CUDA_CHECK(cudaMemsetAsync(
+        status, 0, (small_n ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
   if (small_n && front_small_supported(N, E, k, dtype)) {
     // router and dispatch of a handful of tokens in one single-block launch
     rc = moe_b200_front_small(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, cnt_slot, offsets,

@@ -70,6 +70,7 @@ combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_s
 #ifdef MOE_TIMELINE
   if (item == 0) { g_comb_tl[0] = comb_ns(); g_comb_tl[2] = 0; }
 #endif
+  pdl_launch_dependents();   // the next kernel may become resident; it waits before it reads
   pdl_wait();
 #ifdef MOE_TIMELINE
   if (item == 0) g_comb_tl[1] = comb_ns();

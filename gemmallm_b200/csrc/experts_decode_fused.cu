@@ -373,6 +373,16 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                  "r"(kTmemCols)
                  : "memory");
   }
+  // The last CTA to get here leaves the counters zero for the next call on this workspace:
+  // by then every CTA has read its last completion count.
+  if (threadIdx.x == 0 && !*reinterpret_cast<volatile int*>(&ctl->abort)) {
+    int* exit_count = ready + (MOE_B200_READY_INTS - 2);
+    __threadfence();
+    if (atomicAdd(exit_count, 1) == (int)gridDim.x - 1) {
+      for (int i = 0; i < token_blocks; ++i) ready[i] = 0;
+      *exit_count = 0;
+    }
+  }
 }
 
 }  // namespace

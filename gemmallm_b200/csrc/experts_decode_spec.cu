@@ -38,7 +38,8 @@ using namespace tc;
 
 constexpr int BK = 64;
 constexpr int kBox = 128 * BK * 2;   // one 128-row weight box: 16 KiB
-constexpr int kThreads = 192;
+constexpr int kEpiThreads = 256;           // 8 epilogue warps: two per TMEM lane quadrant, half the columns each
+constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kMaxStages = 6;
 constexpr int kMaxE = 32;
 constexpr int kSmemBudget = 220 * 1024;
@@ -49,10 +50,10 @@ struct Control {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t h_done[2];     // the 128 epilogue threads have stored (and fenced) a GEGLU tile
-  uint64_t route_done;    // the 128 epilogue threads have filled mask[] and offsets[]
+  uint64_t h_done[2];     // the epilogue threads have stored (and fenced) a GEGLU tile
+  uint64_t route_done;    // the epilogue threads have filled mask[] and offsets[]
   uint64_t ring_full[kRing];   // the claiming thread has written ring[slot]
-  uint64_t ring_empty[kRing];  // the MMA thread and the 128 epilogue threads have read it
+  uint64_t ring_empty[kRing];  // the MMA thread and the epilogue threads have read it
   int ring[kRing];             // claimed tile ids, -1 = no more tiles
   uint32_t tmem_base;
   int abort;
@@ -118,11 +119,11 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     for (int s = 0; s < stages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->tmem_full[a], 1);
-      mbar_init(&ctl->tmem_empty[a], 128);
-      mbar_init(&ctl->h_done[a], 128);
+      mbar_init(&ctl->tmem_empty[a], kEpiThreads);
+      mbar_init(&ctl->h_done[a], kEpiThreads);
     }
-    mbar_init(&ctl->route_done, 128);
-    for (int i = 0; i < kRing; ++i) { mbar_init(&ctl->ring_full[i], 1); mbar_init(&ctl->ring_empty[i], 129); }
+    mbar_init(&ctl->route_done, kEpiThreads);
+    for (int i = 0; i < kRing; ++i) { mbar_init(&ctl->ring_full[i], 1); mbar_init(&ctl->ring_empty[i], kEpiThreads + 1); }
     ctl->abort = 0;
     TL_FIRST(0);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -318,8 +319,10 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     }
   } else {
     // ---------------- epilogue: thread r owns feature r of the tile ----------------
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;
+    const int quad = warp & 3;                 // TMEM lanes 32*quad .. +31 (fixed by the warp's index mod 4)
+    const int half = (warp - 2) >> 2;          // which half of the tile's columns this warp handles
+    const int r = quad * 32 + lane;            // token = accumulator lane
+    const int et = threadIdx.x - 64;           // 0 .. kEpiThreads-1
     bool ok = true;
     bool routed = false;
     uint32_t acc_phase = 0;
@@ -342,12 +345,12 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           // after the dry iterations: wait for the routing kernel, then membership masks and
           // offsets into shared memory (read from the first real tile on)
           pdl_wait();
-          for (int p = r; p < N * k; p += 128) {
+          for (int p = et; p < N * k; p += kEpiThreads) {
             const int e = __ldg(&idx[p]);
             const int tok = p / k;
             if (e >= 0 && e < E) atomicOr(&ctl->mask[e][tok >> 5], 1u << (tok & 31));
           }
-          for (int e = r; e <= E; e += 128) ctl->offsets[e] = __ldg(&offsets[e]);
+          for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldg(&offsets[e]);
           mbar_arrive(&ctl->route_done);
         }
       } else {
@@ -355,7 +358,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           routed = true;
           ok = mbar_wait(&ctl->route_done, 0u, &ctl->abort, status, 27);
           if (!ok) break;
-          if (r == 0) TL_FIRST(1);
+          if (et == 0) TL_FIRST(1);
         }
         { TW_BEGIN();
         if (!mbar_wait(&ctl->ring_full[slot], rphase, &ctl->abort, status, 31)) break;
@@ -382,14 +385,14 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       // this thread's token (accumulator lane) and whether it is routed to expert e
       const uint32_t mword = dry ? 0xffffffffu : ctl->mask[e][quad];   // tokens 32*quad .. +31: this warp's lanes
       const bool routed_here = !dry && ((mword >> lane) & 1u);
-      // GEGLU biases of the tile's 128 features, fetched before the accumulator is awaited: lane l
-      // keeps features l, 32 + l, 64 + l, 96 + l; the loop below hands them round with shuffles
-      float bgv[4] = {0.f, 0.f, 0.f, 0.f}, buv[4] = {0.f, 0.f, 0.f, 0.f};
+      // GEGLU biases of this warp's 64 features, fetched before the accumulator is awaited: lane l
+      // keeps features l and 32 + l of the half; the loop below hands them round with shuffles
+      float bgv[2] = {0.f, 0.f}, buv[2] = {0.f, 0.f};
       if (!down && mword != 0u) {
         const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(b1_ptrs[e]);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int feat = nt * 128 + ch * 32 + lane;
+        for (int ch = 0; ch < 2; ++ch) {
+          const int feat = nt * 128 + (half * 2 + ch) * 32 + lane;
           if (feat < f) {
             bgv[ch] = __bfloat162float(__ldg(bias + feat));
             buv[ch] = __bfloat162float(__ldg(bias + f + feat));
@@ -410,8 +413,8 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           const int n0 = nt * 128;
           __nv_bfloat16* o = h_all + ((int64_t)e * NP + r) * f + n0;
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            const int c0 = ch * 32;
+          for (int ch = 0; ch < 2; ++ch) {
+            const int c0 = (half * 2 + ch) * 32;
             uint32_t g[32], u[32];
             tc_ld32(lane_addr + (uint32_t)c0, g);
             tc_ld32(lane_addr + (uint32_t)(128 + c0), u);
@@ -429,11 +432,11 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             }
           }
         }
-        // publish: all 128 threads have stored and fenced, then one adds to the expert's count
+        // publish: all epilogue threads have stored and fenced, then one adds to the expert's count
         if (!dry) {
           __threadfence();
           mbar_arrive(&ctl->h_done[a]);
-          if (r == 0) {
+          if (et == 0) {
             if (!mbar_wait(&ctl->h_done[a], acc_phase, &ctl->abort, status, 28)) { ok = false; break; }
             __threadfence();
             atomicAdd(&ready[e], 1);
@@ -446,7 +449,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         for (int w = 0; w < quad; ++w) row += __popc(ctl->mask[e][w]);
         float* o = part + (int64_t)ks * part_stride + (int64_t)row * d + n0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 256; c0 += 32) {
+        for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
           uint32_t v[32];
           tc_ld32(lane_addr + (uint32_t)c0, v);
           tc_ld_wait();
@@ -470,7 +473,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       if (a == 1) acc_phase ^= 1u;
       ++it;
     }
-    if (r == 0) PROF_FLUSH(19, 4);   // ring, full, geglu, down | total
+    if (et == 0) PROF_FLUSH(19, 4);   // ring, full, geglu, down | total
   }
 
   // ---------------- teardown ----------------
@@ -489,6 +492,17 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(tmem_cols)
                  : "memory");
+  }
+  // The last CTA to get here leaves the counters zero for the next call on this workspace:
+  // by then every CTA has made its last claim and read its last completion count.
+  if (threadIdx.x == 0 && !*reinterpret_cast<volatile int*>(&ctl->abort)) {
+    int* exit_count = ready + (MOE_B200_READY_INTS - 2);
+    __threadfence();
+    if (atomicAdd(exit_count, 1) == (int)gridDim.x - 1) {
+      for (int e = 0; e < E; ++e) ready[e] = 0;
+      *tile_counter = 0;
+      *exit_count = 0;
+    }
   }
 }
 

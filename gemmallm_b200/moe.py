@@ -184,7 +184,9 @@ class MOE(nn.Module):
         if key != self._ws_key:
             d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
             nbytes = _cabi.workspace_bytes(N, d, f, E, k, dtype)
-            buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+            # zeroed: the small-N kernels keep their counters in the status region and leave
+            # them zero after every call (FLAG_WS_CLEAN below)
+            buf = torch.zeros(nbytes + 1024, dtype=torch.uint8, device=device)
             base = (buf.data_ptr() + 1023) & ~1023
             self._ws = (buf, base, nbytes, _cabi.workspace_layout(N, d, f, E, k, dtype))
             self._ws_key = key
@@ -237,7 +239,7 @@ class MOE(nn.Module):
                 plan = self._plan.get(self.experts, d, f, dtype, dev)
             _, base, nbytes, _ = self._workspace(N, dtype, dev)
             check(lib.moe_b200_forward(x.data_ptr(), gw.data_ptr(), gb.data_ptr(), plan, res_ptr,
-                                       N, d, f, E, k, dtype, self.flags, base, nbytes,
+                                       N, d, f, E, k, dtype, self.flags | _cabi.FLAG_WS_CLEAN, base, nbytes,
                                        out.data_ptr(), _stream(dev)), "forward")
         self.last = {
             "logits": self._view("logits", torch.float32, (N, E)),
@@ -253,5 +255,11 @@ class MOE(nn.Module):
         return out.reshape(shape), aux
 
     def device_status(self) -> int:
-        """Status word of the most recent call (0 = ok); synchronises."""
-        return int(self.last["status"][0].item()) if self.last else 0
+        """Status word of the most recent call (0 = ok); synchronises. A non-zero status is
+        returned once: the status region is zeroed again so that later calls start clean."""
+        if not self.last:
+            return 0
+        code = int(self.last["status"][0].item())
+        if code != 0:
+            self._view("status", torch.int32, (_cabi.READY_OFFSET + _cabi.READY_INTS,)).zero_()
+        return code

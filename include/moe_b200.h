@@ -77,7 +77,14 @@ enum {
   MOE_B200_FLAG_DECODE_TWO_PASS = 16,
   /* small-N path of moe_b200_forward: never use moe_b200_experts_decode_spec (the
    * kernel that streams every expert without waiting for the routing) */
-  MOE_B200_FLAG_DECODE_NO_SPEC = 32
+  MOE_B200_FLAG_DECODE_NO_SPEC = 32,
+  /* moe_b200_forward, small-N path: the caller guarantees that the status region of
+   * `workspace` (MOE_B200_WS_STATUS, status words and counters) is all zero on entry: it
+   * was zeroed once, and every call on this workspace since then has ended with device
+   * status 0 (such calls leave the region zero). Saves the memset in front of the first
+   * kernel, which then overlaps the tail of the kernel before it. After a non-zero device
+   * status the region has to be zeroed again by the caller. */
+  MOE_B200_FLAG_WS_CLEAN = 64
 };
 
 /* Layout of the status region: word 0 = device status code, words 1..15 detail;
