@@ -31,7 +31,7 @@ sys.path.insert(0, str(ROOT))
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernels per step, from the ncu
 # captures summarised under profiles/ (GEGLU pass + down pass)
-NCU_TRAFFIC_BYTES = {"c1_uniform": 429.7e6 + 405.7e6, "c2_t64": 138.2e6 + 69.1e6}
+NCU_TRAFFIC_BYTES = {"c1_uniform": 429.7e6 + 405.7e6, "c2_t64": 204.8e6 + 3.8e6}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 CPU_SAMPLE_TOKENS = 4096
 L2_BYTES = 126e6
