@@ -115,6 +115,9 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   const int total_tiles = T1 + E * n2 * ksplit;
   int* tile_counter = ready + (MOE_B200_READY_INTS - 1);
 
+  // first tile: the claim is in flight while the barriers and the tensor memory are set up
+  int first_tile = 0;
+  if (threadIdx.x == 0) first_tile = atomicAdd(tile_counter, 1);
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
     for (int a = 0; a < 2; ++a) {
@@ -158,7 +161,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       PROF_DECL();
       // The next tile is claimed while the last few stages of the current one are still to
       // be issued: late enough that nobody hoards tiles, early enough to hide the atomic.
-      int t_cur = atomicAdd(tile_counter, 1);
+      int t_cur = first_tile;
       int t_next = -1;
       int next_ready = 0;
       int cur_ready = 0;   // completion count of t_cur's expert as read one tile earlier
