@@ -321,56 +321,36 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       PROF_FLUSH(12, 6);   // ring, tmem, full, issue, latency sum, loads | total
     }
   } else {
-    // ---------------- epilogue: thread r owns feature r of the tile ----------------
+    // ---------------- epilogue: thread = token (accumulator lane), half of the columns ----------------
     const int quad = warp & 3;                 // TMEM lanes 32*quad .. +31 (fixed by the warp's index mod 4)
     const int half = (warp - 2) >> 2;          // which half of the tile's columns this warp handles
     const int r = quad * 32 + lane;            // token = accumulator lane
     const int et = threadIdx.x - 64;           // 0 .. kEpiThreads-1
     bool ok = true;
-    bool routed = false;
     uint32_t acc_phase = 0;
     int slot = 0;
     uint32_t rphase = 0;
     int it = 0;
-    // Two dry iterations first, one shaped like a GEGLU tile and one like a down tile: they
-    // wait for nothing and store nothing; they only walk the epilogue's instructions while
-    // these warps would otherwise idle, so that the first real tile does not pay the
-    // instruction-cache misses (several microseconds each while the weight stream saturates
-    // the memory system) on the path every down tile of its expert waits for.
-    int dry_left = 2;
+    // routing: wait for the routing kernel, then membership masks and offsets into shared memory
+    pdl_wait();
+    for (int p = et; p < N * k; p += kEpiThreads) {
+      const int e = __ldg(&idx[p]);
+      const int tok = p / k;
+      if (e >= 0 && e < E) atomicOr(&ctl->mask[e][tok >> 5], 1u << (tok & 31));
+    }
+    for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldg(&offsets[e]);
+    mbar_arrive(&ctl->route_done);
+    ok = mbar_wait(&ctl->route_done, 0u, &ctl->abort, status, 27);
+    if (et == 0) TL_FIRST(1);
     PROF_DECL();
     while (ok) {
-      int t;
-      const bool dry = dry_left > 0;
-      if (dry) {
-        t = dry_left == 2 ? 0 : T1;
-        if (--dry_left == 0) {
-          // after the dry iterations: wait for the routing kernel, then membership masks and
-          // offsets into shared memory (read from the first real tile on)
-          pdl_wait();
-          for (int p = et; p < N * k; p += kEpiThreads) {
-            const int e = __ldg(&idx[p]);
-            const int tok = p / k;
-            if (e >= 0 && e < E) atomicOr(&ctl->mask[e][tok >> 5], 1u << (tok & 31));
-          }
-          for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldg(&offsets[e]);
-          mbar_arrive(&ctl->route_done);
-        }
-      } else {
-        if (!routed) {
-          routed = true;
-          ok = mbar_wait(&ctl->route_done, 0u, &ctl->abort, status, 27);
-          if (!ok) break;
-          if (et == 0) TL_FIRST(1);
-        }
-        { TW_BEGIN();
-        if (!mbar_wait(&ctl->ring_full[slot], rphase, &ctl->abort, status, 31)) break;
-        TW_END(0); }
-        t = *reinterpret_cast<volatile int*>(&ctl->ring[slot]);
-        mbar_arrive(&ctl->ring_empty[slot]);
-        if (++slot == kRing) { slot = 0; rphase ^= 1u; }
-        if (t < 0) break;
-      }
+      { TW_BEGIN();
+      if (!mbar_wait(&ctl->ring_full[slot], rphase, &ctl->abort, status, 31)) break;
+      TW_END(0); }
+      const int t = *reinterpret_cast<volatile int*>(&ctl->ring[slot]);
+      mbar_arrive(&ctl->ring_empty[slot]);
+      if (++slot == kRing) { slot = 0; rphase ^= 1u; }
+      if (t < 0) break;
       const bool down = t >= T1;
       int e, nt, ks = 0;
       if (!down) {
@@ -382,12 +362,12 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const int rest = j / ksplit;
         e = rest / n2;
         nt = rest - e * n2;
-        if (!dry && ctl->offsets[e + 1] == ctl->offsets[e]) continue;
+        if (ctl->offsets[e + 1] == ctl->offsets[e]) continue;
       }
       const int a = it & 1;
       // this thread's token (accumulator lane) and whether it is routed to expert e
-      const uint32_t mword = dry ? 0xffffffffu : ctl->mask[e][quad];   // tokens 32*quad .. +31: this warp's lanes
-      const bool routed_here = !dry && ((mword >> lane) & 1u);
+      const uint32_t mword = ctl->mask[e][quad];   // tokens 32*quad .. +31: this warp's lanes
+      const bool routed_here = (mword >> lane) & 1u;
       // GEGLU biases of this warp's 64 features, fetched before the accumulator is awaited: lane l
       // keeps features l and 32 + l of the half; the loop below hands them round with shuffles
       float bgv[2] = {0.f, 0.f}, buv[2] = {0.f, 0.f};
@@ -402,13 +382,11 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           }
         }
       }
-      if (!dry) {
-        TW_BEGIN();
-        if (!mbar_wait(&ctl->tmem_full[a], acc_phase, &ctl->abort, status, 25)) { ok = false; break; }
-        TW_END(1);
-      }
+      { TW_BEGIN();
+      if (!mbar_wait(&ctl->tmem_full[a], acc_phase, &ctl->abort, status, 25)) { ok = false; break; }
+      TW_END(1); }
       tc_fence_after();
-      const bool prof_down = down;
+      [[maybe_unused]] const bool prof_down = down;
       TW_BEGIN();
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * 256);
       if (!down) {
@@ -436,15 +414,13 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           }
         }
         // publish: all epilogue threads have stored and fenced, then one adds to the expert's count
-        if (!dry) {
+        __threadfence();
+        mbar_arrive(&ctl->h_done[a]);
+        if (et == 0) {
+          if (!mbar_wait(&ctl->h_done[a], acc_phase, &ctl->abort, status, 28)) { ok = false; break; }
           __threadfence();
-          mbar_arrive(&ctl->h_done[a]);
-          if (et == 0) {
-            if (!mbar_wait(&ctl->h_done[a], acc_phase, &ctl->abort, status, 28)) { ok = false; break; }
-            __threadfence();
-            atomicAdd(&ready[e], 1);
-            TL_MAX(3);
-          }
+          atomicAdd(&ready[e], 1);
+          TL_MAX(3);
         }
       } else if (mword != 0u) {
         const int n0 = nt * 256;
@@ -468,11 +444,9 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           }
         }
       }
-      if (dry) continue;
       tc_fence_before();
       mbar_arrive(&ctl->tmem_empty[a]);
       TW_END(prof_down ? 3 : 2);
-      (void)prof_down;
       if (a == 1) acc_phase ^= 1u;
       ++it;
     }

@@ -41,8 +41,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 __device__ unsigned long long g_front_tl[16];
 #define FTL(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) { unsigned long long t_; \
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_front_tl[slot] = t_; } } while (0)
+#define FCLK(var) const long long var = clock64()
+#define FCLK_OUT(slot, a, b) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_front_tl[slot] = (unsigned long long)((b) - (a)); } while (0)
 #else
 #define FTL(slot)
+#define FCLK(var)
+#define FCLK_OUT(slot, a, b)
 #endif
 
 template <int NT>  // n-tiles of 8 experts: E <= 8*NT
@@ -170,6 +174,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const int grp = lane / G, e = lane % G;
     const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (grp * G));
     for (int tok0 = warp * kTokPerWarp; tok0 < N; tok0 += (kThreads / 32) * kTokPerWarp) {
+      FCLK(cb0);
       const int tok = tok0 + grp;
       const bool live = tok < N && e < E;
       float* lg = s_logit + (size_t)min(tok, N - 1) * ld;
@@ -184,6 +189,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 #pragma unroll
       for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(gmask, sum, o);
       if (live) lg[e] = p / sum;            // probabilities, for the loss below
+      FCLK(cb1);
       int sel[kMaxTopK];
       float vals[kMaxTopK];
       float total = 0.f;
@@ -201,6 +207,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
           if (lane == winner) key = 0u;     // below every real key
         }
       }
+      FCLK(cb2);
       if (e == 0 && tok < N) {
 #pragma unroll
         for (int j = 0; j < kMaxTopK; ++j) {
@@ -214,9 +221,16 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
           }
         }
       }
+      FCLK(cb3);
+      FCLK_OUT(10, cb0, cb1);
+      FCLK_OUT(11, cb1, cb2);
+      FCLK_OUT(12, cb2, cb3);
     }
   }
+  FCLK(cb4);
   __syncthreads();
+  FCLK(cb5);
+  FCLK_OUT(13, cb4, cb5);
   FTL(5);
 
   // ---- C. counts, offsets, ranks: warp 0 -------------------------------------------
