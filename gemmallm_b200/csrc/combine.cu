@@ -82,10 +82,13 @@ combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_s
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   for (int j = 0; j < k; ++j) {
-    const int row = __ldg(&row_of[t * k + j]);
+    // row_of, idx and w come from the routing kernel, which may still be running when this
+    // kernel becomes resident: read them through L2 after the wait, never through the read-only
+    // path (whose loads the compiler may move above the wait)
+    const int row = __ldcg(&row_of[t * k + j]);
     if (row < 0) continue;
-    const int e = __ldg(&idx[t * k + j]);
-    const float wj = __ldg(&w[t * k + j]);
+    const int e = __ldcg(&idx[t * k + j]);
+    const float wj = __ldcg(&w[t * k + j]);
     float v[8];
     load8_ldg(static_cast<const __nv_bfloat16*>(b2[e]) + c, v);
     float s[8];

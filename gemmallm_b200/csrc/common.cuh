@@ -116,6 +116,13 @@ __device__ __forceinline__ float gelu_tanh_fast(float g) {
 // earlier kernel has completed and its writes are visible; without the launch
 // attribute it returns at once. pdl_launch_dependents() lets the next kernel's
 // blocks be scheduled as soon as resources free up.
+// Rule for loads: what a kernel that may still be running when this one starts has
+// written is read with ordinary or __ldcg loads AFTER pdl_wait(), never with __ldg /
+// ld.global.nc: those promise data that is constant over the kernel's lifetime, and
+// the compiler is free to move them above the wait (it did: two roles of one kernel
+// then disagreed about the routing). A kernel that signals its dependents only after
+// its own wait extends the guarantee to everything before it in the chain; one that
+// signals first (decode_spec_kernel, combine_decode_kernel) does not.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -176,6 +176,20 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       };
       while (ok) {
         const int t = t_cur < total_tiles ? t_cur : -1;
+        if (t >= T1) {
+          // Down tiles of an expert without tokens are dropped here, by the one thread that
+          // decides it; the other roles only ever see tiles that are processed. offsets[] is
+          // written by the routing kernel while this kernel runs: wait for that kernel, and
+          // read through L2 (the read-only path is for data constant over the kernel's life).
+          if (!routed) { pdl_wait(); routed = true; }
+          const int e = ((t - T1) / ksplit) / n2;
+          if (__ldcg(&offsets[e + 1]) == __ldcg(&offsets[e])) {
+            claim_next();
+            t_cur = t_next;
+            cur_ready = next_ready;
+            continue;
+          }
+        }
         { TW_BEGIN();
         if (!mbar_wait(&ctl->ring_empty[slot], rphase ^ 1u, &ctl->abort, status, 29)) break;
         TW_END(2); }
@@ -203,12 +217,11 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
         } else {
-          if (!routed) { pdl_wait(); routed = true; }
           const int j = t - T1;
           const int ks = j % ksplit;
           const int rest = j / ksplit;
           const int e = rest / n2, nt = rest - e * n2;
-          if (__ldg(&offsets[e + 1]) != __ldg(&offsets[e])) {   // else: expert without tokens
+          {
             // the h rows of this expert must be complete (bounded wait), and visible to TMA
             TW_BEGIN();
             if (cur_ready >= n1) {
@@ -268,7 +281,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       uint32_t rphase = 0;
       int it = 0;
       bool ok = true;
-      bool routed = false;
       PROF_DECL();
       while (ok) {
         { TW_BEGIN();
@@ -281,11 +293,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const bool down = t >= T1;
         int kb0 = 0, kb1 = kb_all1;
         if (down) {
-          if (!routed) { pdl_wait(); routed = true; }
-          const int j = t - T1;
-          const int ks = j % ksplit;
-          const int e = (j / ksplit) / n2;
-          if (__ldg(&offsets[e + 1]) == __ldg(&offsets[e])) continue;
+          const int ks = (t - T1) % ksplit;
           kb0 = ks * kb_per_split;
           kb1 = min(kb_all2, kb0 + kb_per_split);
         }
@@ -332,13 +340,14 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     uint32_t rphase = 0;
     int it = 0;
     // routing: wait for the routing kernel, then membership masks and offsets into shared memory
+    // (written while this kernel runs, so read through L2, not through the read-only path)
     pdl_wait();
     for (int p = et; p < N * k; p += kEpiThreads) {
-      const int e = __ldg(&idx[p]);
+      const int e = __ldcg(&idx[p]);
       const int tok = p / k;
       if (e >= 0 && e < E) atomicOr(&ctl->mask[e][tok >> 5], 1u << (tok & 31));
     }
-    for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldg(&offsets[e]);
+    for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldcg(&offsets[e]);
     mbar_arrive(&ctl->route_done);
     ok = mbar_wait(&ctl->route_done, 0u, &ctl->abort, status, 27);
     if (et == 0) TL_FIRST(1);
@@ -362,7 +371,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         const int rest = j / ksplit;
         e = rest / n2;
         nt = rest - e * n2;
-        if (ctl->offsets[e + 1] == ctl->offsets[e]) continue;
       }
       const int a = it & 1;
       // this thread's token (accumulator lane) and whether it is routed to expert e
@@ -393,9 +401,11 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         if (mword != 0u) {       // uniform over the warp
           const int n0 = nt * 128;
           __nv_bfloat16* o = h_all + ((int64_t)e * NP + r) * f + n0;
-#pragma unroll
+          // rolled: half the code, and this code runs from a cold instruction cache the first time
+#pragma unroll 1
           for (int ch = 0; ch < 2; ++ch) {
             const int c0 = (half * 2 + ch) * 32;
+            const float bgc = ch ? bgv[1] : bgv[0], buc = ch ? buv[1] : buv[0];
             uint32_t g[32], u[32];
             tc_ld32(lane_addr + (uint32_t)c0, g);
             tc_ld32(lane_addr + (uint32_t)(128 + c0), u);
@@ -405,8 +415,8 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
               float hv[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                const float gv = __uint_as_float(g[c8 + i]) + __shfl_sync(0xffffffffu, bgv[ch], c8 + i);
-                const float uv = __uint_as_float(u[c8 + i]) + __shfl_sync(0xffffffffu, buv[ch], c8 + i);
+                const float gv = __uint_as_float(g[c8 + i]) + __shfl_sync(0xffffffffu, bgc, c8 + i);
+                const float uv = __uint_as_float(u[c8 + i]) + __shfl_sync(0xffffffffu, buc, c8 + i);
                 hv[i] = gelu_tanh_fast(gv) * uv;
               }
               if (routed_here && n0 + c0 + c8 < f) store8(o + c0 + c8, hv);   // f is a multiple of 8

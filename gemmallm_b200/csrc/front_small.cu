@@ -107,8 +107,9 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
           const int c = c0 + u * nslices;
           const int piece = 4 * c + t;
           const bool ok = c < nchunk && piece < row_pieces;
-          A[u] = ok ? __ldg(xa + piece) : zero;
-          B[u] = ok ? __ldg(xb + piece) : zero;
+          // x may be the output of the kernel before this one: through L2, not the read-only path
+          A[u] = ok ? __ldcg(xa + piece) : zero;
+          B[u] = ok ? __ldcg(xb + piece) : zero;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -151,7 +152,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   for (int u = 0; u < kInFlight; ++u) {
     const int i = first_item + u * kThreads;
     if (i < items)
-      asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+      asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
                    : "=r"(pre[u].x), "=r"(pre[u].y), "=r"(pre[u].z), "=r"(pre[u].w)
                    : "l"(src + i)
                    : "memory");
@@ -190,36 +191,31 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(gmask, sum, o);
       if (live) lg[e] = p / sum;            // probabilities, for the loss below
       FCLK(cb1);
-      int sel[kMaxTopK];
-      float vals[kMaxTopK];
+      // k passes of arg-max ordered by (logit descending, index ascending); lane j of the group
+      // keeps slot j's result. The loop is kept rolled: this code runs once per launch, from a cold
+      // instruction cache, and every extra line of it costs a miss on the path to the next kernel.
+      int my_sel = 0;
+      float my_val = 0.f;
       float total = 0.f;
-#pragma unroll
-      for (int j = 0; j < kMaxTopK; ++j) {
-        if (j < k) {
-          // arg-max ordered by (logit descending, index ascending)
-          const unsigned km = __reduce_max_sync(gmask, key);
-          const unsigned hit = __ballot_sync(gmask, key == km) & gmask;
-          const int winner = __ffs(hit) - 1;
-          sel[j] = winner - grp * G;
-          const float bv = __uint_as_float((km & 0x80000000u) ? (km & 0x7fffffffu) : ~km);
-          vals[j] = expf(bv - m) / sum;
-          total += vals[j];
-          if (lane == winner) key = 0u;     // below every real key
-        }
+#pragma unroll 1
+      for (int j = 0; j < k; ++j) {
+        const unsigned km = __reduce_max_sync(gmask, key);
+        const unsigned hit = __ballot_sync(gmask, key == km) & gmask;
+        const int winner = __ffs(hit) - 1;
+        const float bv = __uint_as_float((km & 0x80000000u) ? (km & 0x7fffffffu) : ~km);
+        const float val = expf(bv - m) / sum;
+        total += val;
+        if (e == j) { my_sel = winner - grp * G; my_val = val; }
+        if (lane == winner) key = 0u;     // below every real key
       }
       FCLK(cb2);
-      if (e == 0 && tok < N) {
-#pragma unroll
-        for (int j = 0; j < kMaxTopK; ++j) {
-          if (j < k) {
-            if (blockIdx.x == 0) {
-              out_idx[tok * k + j] = sel[j];
-              out_w[tok * k + j] = vals[j] / total;
-            }
-            s_idx[tok * k + j] = sel[j];
-            atomicAdd(&s_cnt[j * kMaxE + sel[j]], 1);
-          }
+      if (e < k && tok < N) {
+        if (blockIdx.x == 0) {
+          out_idx[tok * k + e] = my_sel;
+          out_w[tok * k + e] = my_val / total;
         }
+        s_idx[tok * k + e] = my_sel;
+        atomicAdd(&s_cnt[e * kMaxE + my_sel], 1);
       }
       FCLK(cb3);
       FCLK_OUT(10, cb0, cb1);
@@ -287,7 +283,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int u = 0; u < kInFlight; ++u) {
       const int i = i0 + u * kThreads;
       if (i0 == first_item) v[u] = pre[u];
-      else if (i < items) v[u] = __ldg(src + i);
+      else if (i < items) v[u] = __ldcg(src + i);
     }
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {

@@ -180,6 +180,21 @@ def test_c2_single_launch_experts_equal_two_launches(cuda_device, name):
     assert (out.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
 
 
+def test_small_n_fresh_workspace_and_changing_inputs(cuda_device):
+    """The small-N expert kernel runs while the routing kernel is still writing idx/offsets, and
+    the combine may become resident before either has finished: every call on a fresh, zeroed
+    workspace, and every call whose routing differs from the call before, must still come out
+    right (a read of the routing that is served too early shows up here as a time-out or as
+    the previous call's routing)."""
+    N, d, E, f, k = 128, 64, 8, 128, 2
+    params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=0), torch.bfloat16)
+    for trial in range(12):
+        m = build(params, d, E, f, k, torch.bfloat16, cuda_device)
+        for call in range(3):
+            x = synthetic.round_to(synthetic.make_input(N, d, seed=100 * trial + call), torch.bfloat16)
+            check_against_oracle(m, params, x, k, torch.bfloat16, cuda_device)
+
+
 def test_c4_router_pin(cuda_device):
     wl = synthetic.WORKLOADS["c4"]
     pins = json.loads((GOLDEN / "routing_pins.json").read_text())["c4"]
