@@ -10,7 +10,7 @@
 //      (router.cu), all its loads in flight at once; partials are summed over
 //      the K slices in slice order, plus bias;
 //   B. 8, 16 or 32 lanes per token, lane e = expert e: fp32 softmax, k passes of
-//      arg-max ordered by (logit desc, index asc) with integer warp reductions
+//      arg-max ordered by (logit desc, index asc) with shuffle reductions
 //      on order-preserving keys, renormalise;
 //   C. warp 0: per-slot counts, offsets (scan over E), stable ranks in (token,
 //      slot) order; then row copies into the sorted buffer with 16-byte accesses
@@ -180,16 +180,20 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       const bool live = tok < N && e < E;
       float* lg = s_logit + (size_t)min(tok, N - 1) * ld;
       const float v = live ? lg[e] + 0.f : -INFINITY;      // + 0: no negative zero
-      // order-preserving map float -> unsigned, so that the integer warp reduction finds the maximum
+      // order-preserving map float -> unsigned: the maximum and its first position by integer compares
       const unsigned u = __float_as_uint(v);
       unsigned key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-      const unsigned kmax = __reduce_max_sync(gmask, key);
+      unsigned kmax = key;
+#pragma unroll
+      for (int o = G / 2; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(gmask, kmax, o));
       const float m = __uint_as_float((kmax & 0x80000000u) ? (kmax & 0x7fffffffu) : ~kmax);
       const float p = live ? expf(v - m) : 0.f;
       float sum = p;
 #pragma unroll
       for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(gmask, sum, o);
-      if (live) lg[e] = p / sum;            // probabilities, for the loss below
+      const float inv_sum = __frcp_rn(sum);  // one reciprocal per token, products below: a division
+                                             // is a long subroutine, and this code runs once, cold
+      if (live) lg[e] = p * inv_sum;        // probabilities, for the loss below
       FCLK(cb1);
       // k passes of arg-max ordered by (logit descending, index ascending); lane j of the group
       // keeps slot j's result. The loop is kept rolled: this code runs once per launch, from a cold
@@ -199,11 +203,13 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       float total = 0.f;
 #pragma unroll 1
       for (int j = 0; j < k; ++j) {
-        const unsigned km = __reduce_max_sync(gmask, key);
+        unsigned km = key;
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) km = max(km, __shfl_xor_sync(gmask, km, o));
         const unsigned hit = __ballot_sync(gmask, key == km) & gmask;
         const int winner = __ffs(hit) - 1;
         const float bv = __uint_as_float((km & 0x80000000u) ? (km & 0x7fffffffu) : ~km);
-        const float val = expf(bv - m) / sum;
+        const float val = expf(bv - m) * inv_sum;
         total += val;
         if (e == j) { my_sel = winner - grp * G; my_val = val; }
         if (lane == winner) key = 0u;     // below every real key
@@ -212,7 +218,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       if (e < k && tok < N) {
         if (blockIdx.x == 0) {
           out_idx[tok * k + e] = my_sel;
-          out_w[tok * k + e] = my_val / total;
+          out_w[tok * k + e] = my_val * __frcp_rn(total);
         }
         s_idx[tok * k + e] = my_sel;
         atomicAdd(&s_cnt[e * kMaxE + my_sel], 1);
