@@ -195,6 +195,37 @@ def test_small_n_fresh_workspace_and_changing_inputs(cuda_device):
             check_against_oracle(m, params, x, k, torch.bfloat16, cuda_device)
 
 
+@pytest.mark.parametrize("N", [4, 64])
+def test_small_n_layers_back_to_back(cuda_device, N):
+    """Several blocks launched back to back with no host synchronisation, each one's output the
+    next one's input: the first kernel of a block becomes resident while the last kernel of the
+    block before it is still running, and has to wait for it before it reads x."""
+    d, E, f, k, L = 256, 8, 512, 2, 5
+    layers, params = [], []
+    for l in range(L):
+        p = helpers.rounded_params(synthetic.make_params(d, E, f, seed=10 + l), torch.bfloat16)
+        params.append(p)
+        layers.append(build(p, d, E, f, k, torch.bfloat16, cuda_device))
+    x0 = synthetic.round_to(synthetic.make_input(N, d, seed=3), torch.bfloat16)
+    for rep in range(3):      # the first pass also creates plans and workspaces
+        xs = [(x0 * (1.0 + 0.25 * rep)).to(torch.bfloat16).to(cuda_device).view(1, N, d)]
+        with torch.no_grad():
+            for m in layers:
+                out, _aux = m(xs[-1], residual=xs[-1])
+                xs.append(out)
+        torch.cuda.synchronize()
+        for l, m in enumerate(layers):
+            assert m.device_status() == 0
+            xin = xs[l].view(N, d).float().cpu()
+            with torch.no_grad():
+                o = moe_oracle.moe_forward(xin, params[l], k, logits=m.last["logits"].cpu())
+            ok = ~moe_oracle.tie_rows(o["probs"], k)
+            assert torch.equal(m.last["idx"].cpu()[ok].long(), o["idx"][ok])
+            ref = o["out"] + xin
+            got = xs[l + 1].view(N, d).float().cpu()
+            assert (got - ref)[ok].abs().max() <= 2e-2 * ref.abs().max()
+
+
 def test_c4_router_pin(cuda_device):
     wl = synthetic.WORKLOADS["c4"]
     pins = json.loads((GOLDEN / "routing_pins.json").read_text())["c4"]
