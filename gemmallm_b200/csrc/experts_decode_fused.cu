@@ -236,16 +236,10 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort, status, 11)) { ok = false; break; }
           uint8_t* sw = smem + (size_t)stage * kStageBytes;
-#ifdef MOE_EXP_NOTOK
-          mbar_expect_tx(&ctl->full[stage], kWBytes);
-          tma_load_2d(sw, tw, &ctl->full[stage], kb * BK, w0);
-          tma_load_2d(sw + kWHalf, tw, &ctl->full[stage], kb * BK, w1);
-#else
           mbar_expect_tx(&ctl->full[stage], kStageBytes);
           tma_load_2d(sw, tw, &ctl->full[stage], kb * BK, w0);
           tma_load_2d(sw + kWHalf, tw, &ctl->full[stage], kb * BK, w1);
           tma_load_2d(sw + kWBytes, tt, &ctl->full[stage], kb * BK, ti.row0);
-#endif
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -276,14 +270,10 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           const uint32_t sw = smem_u32(smem + (size_t)stage * kStageBytes);
           const uint64_t wdesc = make_smem_desc(sw);
           const uint64_t tdesc = make_smem_desc(sw + kWBytes);
-#ifdef MOE_EXP_NOMMA
-          if (kb == kb0) tc_mma(tmem_d, wdesc, tdesc, kIdesc, 0u);
-#else
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk)
             tc_mma(tmem_d, wdesc + (uint64_t)(kk * 2), tdesc + (uint64_t)(kk * 2), kIdesc,
                    (kb > kb0 || kk > 0) ? 1u : 0u);
-#endif
           tc_commit(&ctl->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }

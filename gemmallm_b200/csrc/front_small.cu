@@ -41,12 +41,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 __device__ unsigned long long g_front_tl[16];
 #define FTL(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) { unsigned long long t_; \
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_front_tl[slot] = t_; } } while (0)
-#define FCLK(var) const long long var = clock64()
-#define FCLK_OUT(slot, a, b) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_front_tl[slot] = (unsigned long long)((b) - (a)); } while (0)
 #else
 #define FTL(slot)
-#define FCLK(var)
-#define FCLK_OUT(slot, a, b)
 #endif
 
 template <int NT>  // n-tiles of 8 experts: E <= 8*NT
@@ -175,7 +171,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const int grp = lane / G, e = lane % G;
     const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (grp * G));
     for (int tok0 = warp * kTokPerWarp; tok0 < N; tok0 += (kThreads / 32) * kTokPerWarp) {
-      FCLK(cb0);
       const int tok = tok0 + grp;
       const bool live = tok < N && e < E;
       float* lg = s_logit + (size_t)min(tok, N - 1) * ld;
@@ -194,7 +189,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       const float inv_sum = __frcp_rn(sum);  // one reciprocal per token, products below: a division
                                              // is a long subroutine, and this code runs once, cold
       if (live) lg[e] = p * inv_sum;        // probabilities, for the loss below
-      FCLK(cb1);
       // k passes of arg-max ordered by (logit descending, index ascending); lane j of the group
       // keeps slot j's result. The loop is kept rolled: this code runs once per launch, from a cold
       // instruction cache, and every extra line of it costs a miss on the path to the next kernel.
@@ -214,7 +208,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         if (e == j) { my_sel = winner - grp * G; my_val = val; }
         if (lane == winner) key = 0u;     // below every real key
       }
-      FCLK(cb2);
       if (e < k && tok < N) {
         if (blockIdx.x == 0) {
           out_idx[tok * k + e] = my_sel;
@@ -223,16 +216,9 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         s_idx[tok * k + e] = my_sel;
         atomicAdd(&s_cnt[e * kMaxE + my_sel], 1);
       }
-      FCLK(cb3);
-      FCLK_OUT(10, cb0, cb1);
-      FCLK_OUT(11, cb1, cb2);
-      FCLK_OUT(12, cb2, cb3);
     }
   }
-  FCLK(cb4);
   __syncthreads();
-  FCLK(cb5);
-  FCLK_OUT(13, cb4, cb5);
   FTL(5);
 
   // ---- C. counts, offsets, ranks: warp 0 -------------------------------------------
