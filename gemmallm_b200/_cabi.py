@@ -19,6 +19,7 @@ FLAG_ONE_CTA = 8
 FLAG_DECODE_TWO_PASS = 16
 FLAG_DECODE_NO_SPEC = 32
 FLAG_WS_CLEAN = 64
+FLAG_NO_ROWS_PATH = 128
 READY_OFFSET, READY_INTS = 64, 320
 DEV_OK, DEV_TIMEOUT, DEV_BAD_INDEX = 0, 1, 2
 
@@ -49,6 +50,8 @@ SIGNATURES = {
     "moe_b200_front_small": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _vp, _vp]),
     "moe_b200_experts_decode": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "moe_b200_experts_rows": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "moe_b200_rows_splits": (_i, [_i64, _i, _i, _i]),
     "moe_b200_experts_decode_spec": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "moe_b200_decode_spec_rows": (_i, [_i64]),
     "moe_b200_experts_decode_fused": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

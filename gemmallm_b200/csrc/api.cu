@@ -61,6 +61,8 @@ static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off
   sizes[MOE_B200_WS_Y] = M * d * es;
   sizes[MOE_B200_WS_PART] =
       (dtype == MOE_B200_BF16 && M <= kDecodeMaxRows) ? (size_t)decode_splits(f) * M * d * sizeof(float) : 0;
+  if (dtype == MOE_B200_BF16 && (int64_t)M > kDecodeMaxRows && (int64_t)M <= kRowsPathMaxRows)
+    sizes[MOE_B200_WS_PART] = (size_t)rows_splits((int64_t)M, d, f, E) * M * d * sizeof(float);
   size_t pos = 0;
   for (int i = 0; i < MOE_B200_WS_NUM; ++i) {
     off[i] = pos;
@@ -194,6 +196,24 @@ int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
   return launch_experts_simt(perm, offsets, plan, M, d, f, E, dtype, h, y, (cudaStream_t)stream);
 }
 
+int moe_b200_rows_splits(int64_t M, int d, int f, int E) { return M > 0 && f >= 8 && d >= 8 && E >= 1 ? rows_splits(M, d, f, E) : 0; }
+
+int moe_b200_experts_rows(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
+                          int d, int f, int E, int ksplit, void* h, float* part, int32_t* ready,
+                          int32_t* status, void* stream) {
+  int rc = check_shape(0, d, f, E, 1, MOE_B200_BF16);
+  if (rc) return rc;
+  if (M < 0 || M >= (int64_t)1 << 31) return set_error(MOE_B200_ERR_SHAPE, "M out of range");
+  if (M == 0) return 0;
+  if (!rows_supported(M, E)) return set_error(MOE_B200_ERR_UNSUPPORTED, "too many 128-row blocks for the completion counters");
+  if (ksplit < 1 || ksplit > 8 || ksplit > (f + 63) / 64) return set_error(MOE_B200_ERR_SHAPE, "ksplit must be in [1,8] and at most the number of 64-wide K blocks");
+  if (!perm || !offsets || !plan || !h || !part || !ready || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(perm) || !aligned16(h) || !aligned16(part)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  MOE_CUDA_CHECK(cudaMemsetAsync(ready, 0, MOE_B200_READY_INTS * sizeof(int32_t), (cudaStream_t)stream));
+  return launch_experts_tc_rows(perm, offsets, plan, M, d, f, E, ksplit, h, part, ready, status,
+                                (cudaStream_t)stream);
+}
+
 int moe_b200_front_small(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E,
                          int k, int dtype, float* out_logits, int32_t* out_idx, float* out_w,
                          int32_t* cnt_slot, int32_t* offsets, int32_t* row_of, void* perm,
@@ -315,10 +335,15 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   const bool spec = small_n && front_small_supported(N, E, k, dtype) && decode_spec_supported(N, E, k) &&
                     N * k >= 2 * (int64_t)E &&
                     !(flags & (MOE_B200_FLAG_DECODE_TWO_PASS | MOE_B200_FLAG_DECODE_NO_SPEC));
-  // status words, and (small N) the completion counters behind them, in one memset
-  if (!(small_n && (flags & MOE_B200_FLAG_WS_CLEAN)))
+  // between the decode and the prefill sizes: the streaming kernel on the sorted rows
+  const bool rows_path = dtype == MOE_B200_BF16 && !small_n && N * k <= kRowsPathMaxRows &&
+                         rows_supported(N * k, E) &&
+                         !(flags & (MOE_B200_FLAG_SIMT_EXPERTS | MOE_B200_FLAG_ONE_CTA | MOE_B200_FLAG_NO_ROWS_PATH));
+  const bool counters = small_n || rows_path;
+  // status words, and the completion counters behind them where a kernel uses them, in one memset
+  if (!(counters && (flags & MOE_B200_FLAG_WS_CLEAN)))
     MOE_CUDA_CHECK(cudaMemsetAsync(
-        status, 0, (small_n ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
+        status, 0, (counters ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
   if (small_n && front_small_supported(N, E, k, dtype)) {
     // router and dispatch of a handful of tokens in one single-block launch
     rc = moe_b200_front_small(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, cnt_slot, offsets,
@@ -344,6 +369,14 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
     if (rc) return rc;
     return moe_b200_combine_decode(part, decode_splits(f), N * k, row_of, idx, w, plan, E, residual,
                                    N, d, k, out, stream);
+  }
+  if (rows_path) {
+    const int ks = rows_splits(N * k, d, f, E);
+    rc = launch_experts_tc_rows(perm, offsets, plan, N * k, d, f, E, ks, h, part,
+                                status + MOE_B200_READY_OFFSET, status, s);
+    if (rc) return rc;
+    return moe_b200_combine_decode(part, ks, N * k, row_of, idx, w, plan, E, residual, N, d, k, out,
+                                   stream);
   }
   rc = moe_b200_experts(perm, offsets, plan, N * k, d, f, E, dtype, flags, h, y, status, stream);
   if (rc) return rc;

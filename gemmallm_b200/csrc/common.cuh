@@ -20,6 +20,7 @@ constexpr int kDispatchChunk = 64;
 
 // The small-N (weight-streaming) expert path is taken up to this many sorted rows (N*k).
 constexpr int64_t kDecodeMaxRows = 256;
+constexpr int64_t kRowsPathMaxRows = 1024;   // above: the prefill kernels (256-row tiles)
 
 int set_error(int code, const char* msg);
 int cuda_error(cudaError_t e, const char* where);
@@ -242,6 +243,11 @@ bool decode_spec_supported(int64_t N, int E, int k);
 int launch_experts_tc_decode_spec(const void* x, const int32_t* idx, const int32_t* offsets,
                                   const void* plan, int64_t N, int k, int d, int f, int E, void* h_all,
                                   float* part, int* ready, int32_t* status, cudaStream_t s);
+int rows_splits(int64_t M, int d, int f, int E);
+bool rows_supported(int64_t M, int E);
+int launch_experts_tc_rows(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
+                           int d, int f, int E, int ksplit, void* h, float* part, int* ready,
+                           int32_t* status, cudaStream_t s);
 int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                    int64_t M, int d, int f, int E, void* h, float* part, int* ready,
                                    int32_t* status, cudaStream_t s, int spec = -1);

@@ -57,9 +57,20 @@ struct Control {
   int ring[kRing];             // claimed tile ids, -1 = no more tiles
   uint32_t tmem_base;
   int abort;
-  int offsets[kMaxE + 1];
+  int offsets[kMaxExperts + 1];
+  int tb_start[kMaxExperts + 1];   // SORTED: prefix of NP-row blocks per expert
   uint32_t mask[kMaxE][4];   // bit t of mask[e]: token t is routed to expert e
 };
+
+// SORTED variant: which expert a global row block belongs to (binary search in the prefix).
+__device__ __forceinline__ int expert_of_block(const Control* ctl, int E, int u) {
+  int lo = 0, hi = E;   // invariant: tb_start[lo] <= u < tb_start[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (ctl->tb_start[mid] <= u) lo = mid; else hi = mid;
+  }
+  return lo;
+}
 
 // Debug timeline (compile with -DMOE_TIMELINE): %globaltimer stamps in status words 16..
 #ifdef MOE_TIMELINE
@@ -87,6 +98,13 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   return v;
 }
 
+// SORTED = false: the kernel described at the top of this file (all tokens against every expert,
+//   no wait for the routing). SORTED = true: the same pipeline on the rows the dispatch kernel has
+//   sorted by expert, for calls too large for the first form: the unit of work is a block of NP
+//   rows (32, 64 or 128) of one expert's segment (A = rows of perm, then of h [M,f]; lanes beyond the segment's end are
+//   other experts' rows and are not stored), every role waits for the kernels before this one
+//   first, and the partial sums go to part[ks][row][d] in the sorted order.
+template <bool SORTED>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_h,
                    const CUtensorMap* __restrict__ tmap_w1, const CUtensorMap* __restrict__ tmap_w2,
@@ -111,8 +129,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   const int kb_per_split = (kb_all2 + ksplit - 1) / ksplit;
   constexpr uint32_t idesc = make_idesc(256);
 
-  const int T1 = E * n1;                  // GEGLU tiles
-  const int total_tiles = T1 + E * n2 * ksplit;
   int* tile_counter = ready + (MOE_B200_READY_INTS - 1);
 
   // first tile: the claim is in flight while the barriers and the tensor memory are set up
@@ -144,10 +160,36 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
-  // The routing kernel before this one signals its dependents only after it has waited
-  // for ITS predecessor, so x is complete here; weights and biases are never written
+  if constexpr (SORTED) {
+    // sorted rows and offsets come from the kernels before this one: wait, then the block table
+    pdl_wait();
+    for (int e = threadIdx.x; e <= E; e += kThreads) ctl->offsets[e] = __ldcg(&offsets[e]);
+    __syncthreads();
+    if (warp == 0) {
+      int carry = 0;
+      for (int e0 = 0; e0 < E; e0 += 32) {
+        const int e = e0 + lane;
+        const int nb = e < E ? (ctl->offsets[e + 1] - ctl->offsets[e] + NP - 1) / NP : 0;
+        int incl = nb;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        if (e < E) ctl->tb_start[e] = carry + incl - nb;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) ctl->tb_start[E] = carry;
+    }
+    __syncthreads();
+  }
+  // SORTED = false: the routing kernel before this one signals its dependents only after it has
+  // waited for ITS predecessor, so x is complete here; weights and biases are never written
   // by kernels of this library. Nothing below waits for the routing until it must.
   pdl_launch_dependents();
+  const int U = SORTED ? ctl->tb_start[E] : E;     // units of work: row blocks, or experts
+  const int T1 = U * n1;                           // GEGLU tiles
+  const int total_tiles = T1 + U * n2 * ksplit;
 
   if (warp == 0) {
     // ---------------- tile claiming + TMA producer ----------------
@@ -170,13 +212,13 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         next_ready = 0;
         if (t_next >= T1 && t_next < total_tiles) {
           // the completion count the next tile will need, read early (no ordering asked here)
-          const int e_next = ((t_next - T1) / ksplit) / n2;
-          asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(next_ready) : "l"(ready + e_next) : "memory");
+          const int u_next = ((t_next - T1) / ksplit) / n2;
+          asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(next_ready) : "l"(ready + u_next) : "memory");
         }
       };
       while (ok) {
         const int t = t_cur < total_tiles ? t_cur : -1;
-        if (t >= T1) {
+        if (!SORTED && t >= T1) {
           // Down tiles of an expert without tokens are dropped here, by the one thread that
           // decides it; the other roles only ever see tiles that are processed. offsets[] is
           // written by the routing kernel while this kernel runs: wait for that kernel, and
@@ -199,7 +241,9 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         if (t < 0) break;
         t_next = -1;
         if (t < T1) {
-          const int e = t / n1, nt = t - e * n1;
+          const int u = t / n1, nt = t - u * n1;
+          const int e = SORTED ? expert_of_block(ctl, E, u) : u;
+          const int arow = SORTED ? ctl->offsets[e] + (u - ctl->tb_start[e]) * NP : 0;
           const CUtensorMap* tw = tmap_w1 + e;
           const int claim_kb = max(0, kb_all1 - 4);
           for (int kb = 0; kb < kb_all1; ++kb) {
@@ -210,7 +254,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             uint8_t* sw = smem + (size_t)stage * stage_bytes;
             TW_BEGIN();
             mbar_expect_tx(&ctl->full[stage], (uint32_t)stage_bytes);
-            tma_load_2d(sw, &tmap_x, &ctl->full[stage], kb * BK, 0);
+            tma_load_2d(sw, &tmap_x, &ctl->full[stage], kb * BK, arow);
             tma_load_2d(sw + tok_bytes, tw, &ctl->full[stage], kb * BK, nt * 128);
             tma_load_2d(sw + tok_bytes + kBox, tw, &ctl->full[stage], kb * BK, f + nt * 128);
             TW_END(3);
@@ -220,15 +264,17 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           const int j = t - T1;
           const int ks = j % ksplit;
           const int rest = j / ksplit;
-          const int e = rest / n2, nt = rest - e * n2;
+          const int u = rest / n2, nt = rest - u * n2;
+          const int e = SORTED ? expert_of_block(ctl, E, u) : u;
+          const int arow = SORTED ? ctl->offsets[e] + (u - ctl->tb_start[e]) * NP : e * NP;
           {
-            // the h rows of this expert must be complete (bounded wait), and visible to TMA
+            // the h rows of this unit must be complete (bounded wait), and visible to TMA
             TW_BEGIN();
             if (cur_ready >= n1) {
               asm volatile("fence.acq_rel.gpu;" ::: "memory");
             } else {
               const unsigned long long t0 = global_ns();
-              for (uint32_t it = 0; ld_acquire_gpu(&ready[e]) < n1; ++it) {
+              for (uint32_t it = 0; ld_acquire_gpu(&ready[u]) < n1; ++it) {
                 if ((it & 63u) == 63u) {
                   if (*reinterpret_cast<volatile int*>(&ctl->abort)) { ok = false; break; }
                   if (global_ns() - t0 > kWaitLimitNs) {
@@ -257,7 +303,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
               uint8_t* sw = smem + (size_t)stage * stage_bytes;
               TW_BEGIN();
               mbar_expect_tx(&ctl->full[stage], (uint32_t)stage_bytes);
-              tma_load_2d(sw, &tmap_h, &ctl->full[stage], kb * BK, e * NP);
+              tma_load_2d(sw, &tmap_h, &ctl->full[stage], kb * BK, arow);
               tma_load_2d(sw + tok_bytes, tw, &ctl->full[stage], kb * BK, nt * 256);
               tma_load_2d(sw + tok_bytes + kBox, tw, &ctl->full[stage], kb * BK, nt * 256 + 128);
               TW_END(3);
@@ -339,18 +385,20 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     int slot = 0;
     uint32_t rphase = 0;
     int it = 0;
-    // routing: wait for the routing kernel, then membership masks and offsets into shared memory
-    // (written while this kernel runs, so read through L2, not through the read-only path)
-    pdl_wait();
-    for (int p = et; p < N * k; p += kEpiThreads) {
-      const int e = __ldcg(&idx[p]);
-      const int tok = p / k;
-      if (e >= 0 && e < E) atomicOr(&ctl->mask[e][tok >> 5], 1u << (tok & 31));
+    if constexpr (!SORTED) {
+      // routing: wait for the routing kernel, then membership masks and offsets into shared memory
+      // (written while this kernel runs, so read through L2, not through the read-only path)
+      pdl_wait();
+      for (int p = et; p < N * k; p += kEpiThreads) {
+        const int e = __ldcg(&idx[p]);
+        const int tok = p / k;
+        if (e >= 0 && e < E) atomicOr(&ctl->mask[e][tok >> 5], 1u << (tok & 31));
+      }
+      for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldcg(&offsets[e]);
+      mbar_arrive(&ctl->route_done);
+      ok = mbar_wait(&ctl->route_done, 0u, &ctl->abort, status, 27);
+      if (et == 0) TL_FIRST(1);
     }
-    for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldcg(&offsets[e]);
-    mbar_arrive(&ctl->route_done);
-    ok = mbar_wait(&ctl->route_done, 0u, &ctl->abort, status, 27);
-    if (et == 0) TL_FIRST(1);
     PROF_DECL();
     while (ok) {
       { TW_BEGIN();
@@ -361,20 +409,30 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       if (++slot == kRing) { slot = 0; rphase ^= 1u; }
       if (t < 0) break;
       const bool down = t >= T1;
-      int e, nt, ks = 0;
+      int u, nt, ks = 0;     // unit of work: expert, or (SORTED) global row block
       if (!down) {
-        e = t / n1;
-        nt = t - e * n1;
+        u = t / n1;
+        nt = t - u * n1;
       } else {
         const int j = t - T1;
         ks = j % ksplit;
         const int rest = j / ksplit;
-        e = rest / n2;
-        nt = rest - e * n2;
+        u = rest / n2;
+        nt = rest - u * n2;
       }
+      const int e = SORTED ? expert_of_block(ctl, E, u) : u;
       const int a = it & 1;
-      // this thread's token (accumulator lane) and whether it is routed to expert e
-      const uint32_t mword = ctl->mask[e][quad];   // tokens 32*quad .. +31: this warp's lanes
+      // this thread's token (accumulator lane) and whether its result is stored: routed to expert
+      // e, or (SORTED) a row of this block, which ends where the expert's segment ends
+      int row0 = 0;
+      uint32_t mword;        // the warp's lanes 32*quad .. +31
+      if constexpr (SORTED) {
+        row0 = ctl->offsets[e] + (u - ctl->tb_start[e]) * NP;
+        const int left = min(NP, ctl->offsets[e + 1] - row0) - quad * 32;
+        mword = left >= 32 ? 0xffffffffu : (left > 0 ? (1u << left) - 1u : 0u);
+      } else {
+        mword = ctl->mask[e][quad];
+      }
       const bool routed_here = (mword >> lane) & 1u;
       // GEGLU biases of this warp's 64 features, fetched before the accumulator is awaited: lane l
       // keeps features l and 32 + l of the half; the loop below hands them round with shuffles
@@ -400,7 +458,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       if (!down) {
         if (mword != 0u) {       // uniform over the warp
           const int n0 = nt * 128;
-          __nv_bfloat16* o = h_all + ((int64_t)e * NP + r) * f + n0;
+          __nv_bfloat16* o = h_all + (SORTED ? (int64_t)(row0 + r) : (int64_t)e * NP + r) * f + n0;
           // rolled: half the code, and this code runs from a cold instruction cache the first time
 #pragma unroll 1
           for (int ch = 0; ch < 2; ++ch) {
@@ -429,13 +487,18 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         if (et == 0) {
           if (!mbar_wait(&ctl->h_done[a], acc_phase, &ctl->abort, status, 28)) { ok = false; break; }
           __threadfence();
-          atomicAdd(&ready[e], 1);
+          atomicAdd(&ready[u], 1);
           TL_MAX(3);
         }
       } else if (mword != 0u) {
         const int n0 = nt * 256;
-        int row = ctl->offsets[e] + __popc(mword & ((1u << lane) - 1u));
-        for (int w = 0; w < quad; ++w) row += __popc(ctl->mask[e][w]);
+        int row;
+        if constexpr (SORTED) {
+          row = row0 + r;
+        } else {
+          row = ctl->offsets[e] + __popc(mword & ((1u << lane) - 1u));
+          for (int w = 0; w < quad; ++w) row += __popc(ctl->mask[e][w]);
+        }
         float* o = part + (int64_t)ks * part_stride + (int64_t)row * d + n0;
 #pragma unroll 1
         for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
@@ -486,7 +549,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     int* exit_count = ready + (MOE_B200_READY_INTS - 2);
     __threadfence();
     if (atomicAdd(exit_count, 1) == (int)gridDim.x - 1) {
-      for (int e = 0; e < E; ++e) ready[e] = 0;
+      for (int i = 0; i < U; ++i) ready[i] = 0;
       *tile_counter = 0;
       *exit_count = 0;
     }
@@ -525,15 +588,78 @@ int launch_experts_tc_decode_spec(const void* x, const int32_t* idx, const int32
   const int tmem_cols = 512;   // two accumulators of 256 columns
   static bool attr_set = false;
   if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(decode_spec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(decode_spec_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBudget));
     attr_set = true;
   }
-  MOE_CUDA_CHECK(launch_pdl(decode_spec_kernel, dim3(sms), dim3(kThreads), smem, s, tm_x, tm_h,
+  MOE_CUDA_CHECK(launch_pdl(decode_spec_kernel<false>, dim3(sms), dim3(kThreads), smem, s, tm_x, tm_h,
                             static_cast<const CUtensorMap*>(pv.tmap_W1),
                             static_cast<const CUtensorMap*>(pv.tmap_W2), offsets, idx, pv.b1, (int)N, NP,
                             k, E, d, f, decode_splits(f), N * (int64_t)k * d, stages, tmem_cols,
                             static_cast<__nv_bfloat16*>(h_all), part, ready, status));
+  return 0;
+}
+
+// Rows-sorted form for calls between the decode and the prefill sizes. Rows per block: the
+// smallest of 32, 64, 128 that holds one and a half times an expert's share under balanced
+// routing (fewer token bytes per stage; a segment that is larger still takes several blocks, and
+// streams its expert's weights once per block).
+int rows_block(int64_t M, int E) {
+  const int64_t share = (3 * ((M + E - 1) / E) + 1) / 2;
+  return share <= 32 ? 32 : share <= 64 ? 64 : 128;
+}
+
+// K ranges of the down product: enough tiles for two waves of CTAs given at least
+// ceil(M / block) row blocks, each range at least 8 blocks of 64.
+int rows_splits(int64_t M, int d, int f, int E) {
+  const int NP = rows_block(M, E);
+  const int64_t blocks = (M + NP - 1) / NP;
+  const int64_t tiles = blocks * ((d + 255) / 256);
+  int64_t want = (2 * kNumSMs + tiles - 1) / tiles;
+  const int kb = (f + BK - 1) / BK;
+  if (want > kb / 8) want = kb / 8;
+  if (want > 8) want = 8;
+  return want < 1 ? 1 : (int)want;
+}
+
+// Every row block of an expert's segment needs one completion counter.
+bool rows_supported(int64_t M, int E) {
+  return M > 0 && E >= 1 && E <= kMaxExperts &&
+         (M + rows_block(M, E) - 1) / rows_block(M, E) + E <= MOE_B200_READY_INTS - 8;
+}
+
+// perm [M,d] sorted by expert, offsets [E+1]; h [M,f] and part [ksplit][M][d] are written.
+// `ready` as for launch_experts_tc_decode_spec.
+int launch_experts_tc_rows(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
+                           int d, int f, int E, int ksplit, void* h, float* part, int* ready,
+                           int32_t* status, cudaStream_t s) {
+  if (M == 0) return 0;
+  const int NP = rows_block(M, E);
+  PlanView pv = plan_view(plan, E);
+  alignas(64) CUtensorMap tm_x, tm_h;
+  int rc = encode_tmap_2d(&tm_x, perm, (uint64_t)M, (uint64_t)d, (uint32_t)NP);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tm_h, h, (uint64_t)M, (uint64_t)f, (uint32_t)NP);
+  if (rc) return rc;
+  int sms = 0;
+  rc = sm_count(&sms);
+  if (rc) return rc;
+  const int stage_bytes = 2 * kBox + NP * 128;
+  int stages = (kSmemBudget - (int)sizeof(Control) - 1024) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + sizeof(Control);
+  static bool attr_set = false;
+  if (!attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(decode_spec_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kSmemBudget));
+    attr_set = true;
+  }
+  MOE_CUDA_CHECK(launch_pdl(decode_spec_kernel<true>, dim3(sms), dim3(kThreads), smem, s, tm_x, tm_h,
+                            static_cast<const CUtensorMap*>(pv.tmap_W1),
+                            static_cast<const CUtensorMap*>(pv.tmap_W2), offsets,
+                            static_cast<const int32_t*>(nullptr), pv.b1, (int)0, NP, 1, E, d, f, ksplit,
+                            M * (int64_t)d, stages, 512, static_cast<__nv_bfloat16*>(h), part, ready,
+                            status));
   return 0;
 }
 

@@ -84,7 +84,10 @@ enum {
    * status 0 (such calls leave the region zero). Saves the memset in front of the first
    * kernel, which then overlaps the tail of the kernel before it. After a non-zero device
    * status the region has to be zeroed again by the caller. */
-  MOE_B200_FLAG_WS_CLEAN = 64
+  MOE_B200_FLAG_WS_CLEAN = 64,
+  /* moe_b200_forward: calls of 257 to 1024 rows (N*k) go through the prefill kernels instead
+   * of moe_b200_experts_rows */
+  MOE_B200_FLAG_NO_ROWS_PATH = 128
 };
 
 /* Layout of the status region: word 0 = device status code, words 1..15 detail;
@@ -213,6 +216,22 @@ int moe_b200_dispatch_static(const void* x, const int32_t* idx,
 int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
                      int64_t M, int d, int f, int E, int dtype, int flags,
                      void* h, void* y, int32_t* status, void* stream);
+
+/* Part 3 for calls between the decode and the prefill sizes (bf16): the weight-streaming
+ * pipeline of moe_b200_experts_decode_spec on the rows sorted by expert. With a few hundred
+ * rows per expert the prefill kernels' 256-row tiles are mostly padding, their token operand
+ * is as many bytes as the weights and the down product has fewer tiles than there are SMs;
+ * here the unit is a block of 32, 64 or 128 rows of one expert's segment, the weights are the wide MMA
+ * operand and the down product's K is cut into `ksplit` ranges. h [M,f] is written as by
+ * moe_b200_experts; the down product arrives as part[s][M][d] WITHOUT down.bias, for
+ * moe_b200_combine_decode (model.py:174-184 per expert, another summation order over K).
+ * ready: int32[MOE_B200_READY_INTS], zeroed by this call; moe_b200_rows_splits gives the
+ * ksplit moe_b200_forward uses. Needs (row blocks) + E <= MOE_B200_READY_INTS - 8.
+ * Residency rule and time-out behaviour as for moe_b200_experts_decode_fused. */
+int moe_b200_experts_rows(const void* perm, const int32_t* offsets, const void* plan,
+                          int64_t M, int d, int f, int E, int ksplit, void* h, float* part,
+                          int32_t* ready, int32_t* status, void* stream);
+int moe_b200_rows_splits(int64_t M, int d, int f, int E);
 
 /* Parts 1+2 for a handful of tokens in ONE single-block launch: same results as
  * moe_b200_router followed by moe_b200_dispatch (model.py:206-253), for bf16,

@@ -97,6 +97,19 @@ def rounded_params(params: dict, dtype) -> dict:
     return {n: synthetic.round_to(t, dtype) for n, t in params.items()}
 
 
+def experts_rows(perm, offsets, plan: Plan, ksplit: int):
+    M, d = perm.shape
+    dev = perm.device
+    h = torch.full((M, plan.f), float("nan"), dtype=perm.dtype, device=dev)
+    part = torch.full((ksplit, M, d), float("nan"), dtype=torch.float32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    ready = torch.full((_cabi.READY_INTS,), 7, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_experts_rows(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d, plan.f,
+                                    plan.E, ksplit, h.data_ptr(), part.data_ptr(), ready.data_ptr(),
+                                    status.data_ptr(), stream(dev)), "experts_rows")
+    return h, part, status
+
+
 def experts_decode(perm, offsets, plan: Plan):
     M, d = perm.shape
     dev = perm.device

@@ -180,6 +180,26 @@ def test_c2_single_launch_experts_equal_two_launches(cuda_device, name):
     assert (out.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
 
 
+@pytest.mark.parametrize("N,d,E,f,k", [(129, 64, 8, 128, 2), (300, 256, 8, 1024, 2), (512, 512, 8, 2048, 2),
+                                       (400, 1024, 8, 4096, 2), (250, 128, 16, 200, 4)])
+def test_mid_sizes_rows_path(cuda_device, N, d, E, f, k):
+    """Between the decode and the prefill sizes (257 to 1024 rows) the forward streams the
+    weights over the sorted rows; with the flag it takes the prefill kernels. Both meet the
+    block's tolerance, with and without a residual, call after call."""
+    params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=N), torch.bfloat16)
+    res = synthetic.round_to(synthetic.make_input(N, d, seed=N + 2), torch.bfloat16)
+    outs = []
+    for flags in (0, _cabi.FLAG_NO_ROWS_PATH):
+        m = build(params, d, E, f, k, torch.bfloat16, cuda_device, flags)
+        for call in range(2):
+            x = synthetic.round_to(synthetic.make_input(N, d, seed=N + 10 + call), torch.bfloat16)
+            check_against_oracle(m, params, x, k, torch.bfloat16, cuda_device)
+            check_against_oracle(m, params, x, k, torch.bfloat16, cuda_device, residual=res)
+        with torch.no_grad():
+            outs.append(m(x.to(torch.bfloat16).to(cuda_device).view(1, N, d))[0].float().cpu())
+    assert (outs[0] - outs[1]).abs().max() <= 1e-2 * outs[1].abs().max()
+
+
 def test_small_n_fresh_workspace_and_changing_inputs(cuda_device):
     """The small-N expert kernel runs while the routing kernel is still writing idx/offsets, and
     the combine may become resident before either has finished: every call on a fresh, zeroed
