@@ -56,3 +56,28 @@ def test_bad_shapes_are_rejected_on_the_host():
     rc = lib.moe_b200_forward(None, None, None, None, None, 16, 1024, 4096, 8, 2, _cabi.BF16, 0,
                               8, 1 << 40, None, None)
     assert rc == -3
+
+
+def test_small_and_mid_size_entry_points_check_their_arguments():
+    """The weight-streaming entry points reject what they cannot run before any launch."""
+    a = 1 << 20     # any non-NULL, 16-byte aligned address: nothing is dereferenced on these paths
+    # routing-independent kernel: N <= 128, E <= 32
+    rc = lib.moe_b200_experts_decode_spec(a, a, a, a, 129, 2, 1024, 4096, 8, a, a, a, a, None)
+    assert rc == -7 and b"128" in lib.moe_b200_last_error_string()
+    rc = lib.moe_b200_experts_decode_spec(a, a, a, a, 64, 2, 1024, 4096, 33, a, a, a, a, None)
+    assert rc == -7
+    rc = lib.moe_b200_experts_decode_spec(a, None, a, a, 64, 2, 1024, 4096, 8, a, a, a, a, None)
+    assert rc == -1
+    # sorted-rows kernel: K ranges within [1, 8] and not more than there are 64-wide K blocks
+    assert lib.moe_b200_experts_rows(a, a, a, 512, 1024, 4096, 8, 9, a, a, a, a, None) == -2
+    assert lib.moe_b200_experts_rows(a, a, a, 512, 1024, 64, 8, 2, a, a, a, a, None) == -2
+    assert lib.moe_b200_experts_rows(a, a, a, 512, 1024, 4096, 8, 4, a, a, None, a, None) == -1
+    assert lib.moe_b200_experts_rows(a + 8, a, a, 512, 1024, 4096, 8, 4, a, a, a, a, None) == -3
+    # one counter per row block: far too many rows
+    assert lib.moe_b200_experts_rows(a, a, a, 1 << 20, 1024, 4096, 8, 4, a, a, a, a, None) == -7
+    # sizes the forward uses
+    assert lib.moe_b200_decode_spec_rows(1) == 16 and lib.moe_b200_decode_spec_rows(65) == 128
+    assert lib.moe_b200_rows_splits(1024, 1024, 4096, 8) == 8
+    assert 1 <= lib.moe_b200_rows_splits(1024, 4096, 256, 8) <= 4 // 8 + 1
+    # the single-launch kernels' fused entry point: row limit
+    assert lib.moe_b200_experts_decode_fused(a, a, a, 257, 1024, 4096, 8, a, a, a, a, None) == -2
