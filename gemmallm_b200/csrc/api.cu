@@ -344,8 +344,8 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   if (!(counters && (flags & MOE_B200_FLAG_WS_CLEAN)))
     MOE_CUDA_CHECK(cudaMemsetAsync(
         status, 0, (counters ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
-  if (small_n && front_small_supported(N, E, k, dtype)) {
-    // router and dispatch of a handful of tokens in one single-block launch
+  if ((small_n || rows_path) && front_small_supported(N, E, k, dtype)) {
+    // router and dispatch of up to a few hundred tokens in one launch
     rc = moe_b200_front_small(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, cnt_slot, offsets,
                               row_of, perm, psum, aux, stream);
     if (rc) return rc;

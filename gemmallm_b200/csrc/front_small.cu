@@ -1,10 +1,10 @@
-// Router and dispatch of a small-N ("decode") call in ONE launch: with at most
-// 128 tokens the separate router and cooperative dispatch kernels are pure launch
-// and barrier latency (13 + 15 us against a few us of work). A few blocks run;
+// Router and dispatch of a small call in ONE launch: with at most a few hundred
+// tokens the separate router and cooperative dispatch kernels are pure launch
+// and barrier latency (13 + 19 us against a few us of work). A few blocks run;
 // each one derives the complete routing by itself (the same instructions on the
 // same data, so every block gets the same answer and no grid barrier is needed),
 // block 0 writes the routing results, and the row copies are split over the blocks.
-// Covers reference model.py:206-253 for N <= 128, N*k <= 256, E <= 32, bf16:
+// Covers reference model.py:206-253 for N <= 512, N*k <= 1024, E <= 32, bf16:
 //   A. logits: 32 warps = (16-token group) x (slice of K); each warp forms its
 //      partial x Wg^T with mma.sync m16n8k16 exactly like router_mma_kernel
 //      (router.cu), all its loads in flight at once; partials are summed over
@@ -23,9 +23,9 @@ namespace moe {
 namespace {
 
 constexpr int kThreads = 1024;
-constexpr int kMaxTok = 128;
+constexpr int kMaxTok = 512;
 constexpr int kMaxE = 32;
-constexpr int kMaxPairs = 256;
+constexpr int kMaxPairs = 1024;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -61,10 +61,10 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   while (gp2 < ngroups) gp2 <<= 1;                         // 1, 2, 4 or 8
   const int nslices = 32 / gp2;                            // K slices
   float* s_part = smem;                                    // [nslices][16*gp2][8*NT]
-  float* s_logit = s_part + (size_t)nslices * 16 * gp2 * 8 * NT;   // [kMaxTok][E+1]
-  int* s_idx = reinterpret_cast<int*>(s_logit + (size_t)kMaxTok * ld);  // [kMaxPairs]
-  int* s_row = s_idx + kMaxPairs;                          // [kMaxPairs]
-  int* s_cnt = s_row + kMaxPairs;                          // [kMaxTopK][kMaxE]
+  float* s_logit = s_part + (size_t)nslices * 16 * gp2 * 8 * NT;   // [N][E+1]
+  int* s_idx = reinterpret_cast<int*>(s_logit + (size_t)N * ld);   // [N*k]
+  int* s_row = s_idx + N * k;                              // [N*k]
+  int* s_cnt = s_row + N * k;                              // [kMaxTopK][kMaxE]
   int* s_off = s_cnt + kMaxTopK * kMaxE;                   // [kMaxE+1]
   int* s_run = s_off + kMaxE + 1;                          // [kMaxE]
   float* s_bias = reinterpret_cast<float*>(s_run + kMaxE); // [kMaxE]
@@ -291,16 +291,25 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 
   // ---- E. the loss, off the path of the kernels that wait for the rows (model.py:213-216) ----
   if (blockIdx.x == 0) {
+    __syncthreads();       // the partial-logit area is free again: every thread is past the reduction
+    // probabilities summed per expert: warp w takes tokens w, w + 32, ...; the 32 partial sums of
+    // an expert are then added in warp order
+    if (lane < E) {
+      float ps = 0.f;
+      for (int tok = warp; tok < N; tok += kThreads / 32) ps += s_logit[tok * ld + lane];
+      s_part[warp * 32 + lane] = ps;
+    }
+    __syncthreads();
     if (tid < E) {
       float ps = 0.f;
-      for (int tok = 0; tok < N; ++tok) ps += s_logit[tok * ld + tid];
+      for (int w = 0; w < kThreads / 32; ++w) ps += s_part[w * 32 + tid];
       psum[tid] = ps;
-      s_part[tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
+      s_part[1024 + tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
     }
     __syncthreads();
     if (tid == 0) {
       float a = 0.f;
-      for (int e = 0; e < E; ++e) a += s_part[e];
+      for (int e = 0; e < E; ++e) a += s_part[1024 + e];
       aux[0] = a / (float)E * (float)(E * E);
     }
   }
@@ -310,15 +319,15 @@ template <int NT>
 int launch(const void* x, const void* Wg, const void* bg, int N, int d, int E, int k,
            float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot, int32_t* offsets,
            int32_t* row_of, void* perm, float* psum, float* aux, cudaStream_t s) {
-  const size_t smem = sizeof(float) * ((size_t)32 * 16 * 8 * NT + (size_t)kMaxTok * (E + 1)) +
-                      sizeof(int) * (2 * kMaxPairs + kMaxTopK * kMaxE + 3 * kMaxE + 1);
+  const size_t smem = sizeof(float) * ((size_t)32 * 16 * 8 * NT + (size_t)N * (E + 1)) +
+                      sizeof(int) * (2 * (size_t)N * k + kMaxTopK * kMaxE + 3 * kMaxE + 1);
   static bool attr_set = false;
   if (!attr_set) {
     MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     attr_set = true;
   }
-  // one block per 16 tokens, at most 8: more blocks only repeat the routing
+  // one block per 16 tokens: every block repeats the routing, the row copies are split
   const int blocks = N <= 16 ? 1 : (N + 15) / 16;
   MOE_CUDA_CHECK(launch_pdl(front_small_kernel<NT>, dim3(blocks), dim3(kThreads), smem, s,
                             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),

@@ -235,7 +235,7 @@ int moe_b200_rows_splits(int64_t M, int d, int f, int E);
 
 /* Parts 1+2 for a handful of tokens in ONE single-block launch: same results as
  * moe_b200_router followed by moe_b200_dispatch (model.py:206-253), for bf16,
- * 1 <= N <= 128, N*k <= 256, E <= 32; other shapes return
+ * 1 <= N <= 512, N*k <= 1024, E <= 32; other shapes return
  * MOE_B200_ERR_UNSUPPORTED. psum [E] and aux [1] are final (no partial sums). */
 int moe_b200_front_small(const void* x, const void* Wg, const void* bg,
                          int64_t N, int d, int E, int k, int dtype,

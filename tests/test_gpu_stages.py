@@ -51,7 +51,8 @@ def test_router_matches_oracle(cuda_device, N, d, E, k, dtype):
 
 
 @pytest.mark.parametrize("N,d,E,k", [(1, 1024, 8, 2), (8, 1024, 8, 2), (17, 256, 16, 4), (64, 1024, 8, 2),
-                                     (100, 72, 5, 2), (128, 128, 32, 2), (33, 64, 24, 7)])
+                                     (100, 72, 5, 2), (128, 128, 32, 2), (33, 64, 24, 7),
+                                     (129, 256, 8, 2), (300, 1024, 8, 2), (512, 512, 32, 2), (200, 128, 16, 5)])
 def test_front_small_equals_router_plus_dispatch(cuda_device, N, d, E, k):
     """The single-launch small-N front end gives what the two general kernels give."""
     dt = torch.bfloat16
