@@ -50,6 +50,8 @@ SIGNATURES = {
     "moe_b200_front_small": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _vp, _vp]),
     "moe_b200_experts_decode": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "moe_b200_front_small_split": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i] + [_vp] * 12 + [_vp]),
+    "moe_b200_front_exchange_ints": (_i64, [_i64, _i, _i]),
     "moe_b200_experts_rows": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "moe_b200_rows_splits": (_i, [_i64, _i, _i, _i]),
     "moe_b200_experts_decode_spec": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -48,6 +48,9 @@ static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off
   sizes[MOE_B200_WS_PSUM] = (size_t)E * sizeof(float);
   sizes[MOE_B200_WS_AUX] = sizeof(float);
   sizes[MOE_B200_WS_SCRATCH] = (size_t)dispatch_scratch_ints(N, E, k) * sizeof(int32_t);
+  if (front_small_supported(N, E, k, dtype) &&
+      (size_t)front_small_exchange_ints(N, E, k) * sizeof(int32_t) > sizes[MOE_B200_WS_SCRATCH])
+    sizes[MOE_B200_WS_SCRATCH] = (size_t)front_small_exchange_ints(N, E, k) * sizeof(int32_t);
   sizes[MOE_B200_WS_CNT_SLOT] = (size_t)k * E * sizeof(int32_t);
   sizes[MOE_B200_WS_OFFSETS] = (size_t)(E + 1) * sizeof(int32_t);
   sizes[MOE_B200_WS_ROW_OF] = M * sizeof(int32_t);
@@ -222,13 +225,37 @@ int moe_b200_front_small(const void* x, const void* Wg, const void* bg, int64_t 
   if (rc) return rc;
   if (!front_small_supported(N, E, k, dtype))
     return set_error(MOE_B200_ERR_UNSUPPORTED,
-                     "moe_b200_front_small needs bf16, 1 <= N <= 128, N*k <= 256, E <= 32");
+                     "moe_b200_front_small needs bf16, 1 <= N <= 512, N*k <= 1024, E <= 32");
   if (!x || !Wg || !bg || !out_idx || !out_w || !cnt_slot || !offsets || !row_of || !perm || !psum || !aux)
     return set_error(MOE_B200_ERR_NULL, "NULL argument");
   if (!aligned16(x) || !aligned16(Wg) || !aligned16(perm))
     return set_error(MOE_B200_ERR_ALIGN, "x, Wg and perm must be 16-byte aligned");
   return launch_front_small(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets,
                             row_of, perm, psum, aux, (cudaStream_t)stream);
+}
+
+int64_t moe_b200_front_exchange_ints(int64_t N, int E, int k) {
+  return (N >= 1 && E >= 1 && k >= 1) ? front_small_exchange_ints(N, E, k) : 0;
+}
+
+int moe_b200_front_small_split(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E,
+                               int k, int dtype, float* out_logits, int32_t* out_idx, float* out_w,
+                               int32_t* cnt_slot, int32_t* offsets, int32_t* row_of, void* perm,
+                               float* psum, float* aux, int32_t* exchange, int32_t* counter,
+                               int32_t* status, void* stream) {
+  int rc = check_shape(N, d, 8, E, k, dtype);
+  if (rc) return rc;
+  if (!front_small_supported(N, E, k, dtype))
+    return set_error(MOE_B200_ERR_UNSUPPORTED,
+                     "moe_b200_front_small_split needs bf16, 1 <= N <= 512, N*k <= 1024, E <= 32");
+  if (!x || !Wg || !bg || !out_idx || !out_w || !cnt_slot || !offsets || !row_of || !perm || !psum ||
+      !aux || !exchange || !counter || !status)
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(x) || !aligned16(Wg) || !aligned16(perm))
+    return set_error(MOE_B200_ERR_ALIGN, "x, Wg and perm must be 16-byte aligned");
+  MOE_CUDA_CHECK(cudaMemsetAsync(counter, 0, sizeof(int32_t), (cudaStream_t)stream));
+  return launch_front_small(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets,
+                            row_of, perm, psum, aux, (cudaStream_t)stream, exchange, counter, status);
 }
 
 int moe_b200_decode_splits(int f) { return f >= 8 ? decode_splits(f) : 0; }
@@ -346,8 +373,10 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
         status, 0, (counters ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
   if ((small_n || rows_path) && front_small_supported(N, E, k, dtype)) {
     // router and dispatch of up to a few hundred tokens in one launch
-    rc = moe_b200_front_small(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, cnt_slot, offsets,
-                              row_of, perm, psum, aux, stream);
+    // (beyond 128 tokens its blocks share the work and meet at a counter behind the status words)
+    rc = launch_front_small(x, Wg, bg, N, d, E, k, logits, idx, w, cnt_slot, offsets, row_of, perm,
+                            psum, aux, s, scratch,
+                            status + MOE_B200_READY_OFFSET + MOE_B200_READY_INTS - 4, status);
     if (rc) return rc;
   } else {
     rc = moe_b200_router(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, psum_part, status, stream);

@@ -231,10 +231,12 @@ int launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* st
 int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint32_t epoch,
                      cudaStream_t s);
 bool front_small_supported(int64_t N, int E, int k, int dtype);
+int64_t front_small_exchange_ints(int64_t N, int E, int k);
 int launch_front_small(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                        float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot,
                        int32_t* offsets, int32_t* row_of, void* perm, float* psum, float* aux,
-                       cudaStream_t s);
+                       cudaStream_t s, int* xch = nullptr, int* counter = nullptr,
+                       int32_t* status = nullptr);
 int encode_tmap_2d(void* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 int sm_count(int* sms);
 int decode_splits(int f);

@@ -45,17 +45,41 @@ __device__ unsigned long long g_front_tl[16];
 #define FTL(slot)
 #endif
 
-template <int NT>  // n-tiles of 8 experts: E <= 8*NT
+__device__ __forceinline__ int ld_acquire_gpu_i32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// SPLIT = false: every block derives the complete routing (fastest up to about a hundred tokens).
+// SPLIT = true: block b routes tokens 16b .. 16b+15 only; the blocks then exchange their per-slot
+//   expert counts and probability sums through `xch` and meet at a counter (all blocks of the grid
+//   are resident: there are at most 32 of them; the wait is bounded and reports a time-out in
+//   `status`), and each block places and copies its own rows. Same results as the other form
+//   except for the order in which the logits' partial sums are added.
+template <int NT, bool SPLIT>  // n-tiles of 8 experts: E <= 8*NT
 __global__ void __launch_bounds__(kThreads, 1)
 front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ Wg,
-                   const __nv_bfloat16* __restrict__ bg, int N, int d, int E, int k,
+                   const __nv_bfloat16* __restrict__ bg, int Ntotal, int d, int E, int k,
                    float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
                    float* __restrict__ out_w, int32_t* __restrict__ cnt_slot,
                    int32_t* __restrict__ offsets, int32_t* __restrict__ row_of,
                    __nv_bfloat16* __restrict__ perm, float* __restrict__ psum,
-                   float* __restrict__ aux) {
+                   float* __restrict__ aux, int* __restrict__ xch, int* __restrict__ counter,
+                   int32_t* __restrict__ status) {
   extern __shared__ float smem[];
   const int ld = E + 1;
+  // SPLIT: this block's 16 tokens are "the problem" for the phases A and B below
+  const int tok_base = SPLIT ? 16 * (int)blockIdx.x : 0;
+  const int N = SPLIT ? min(16, Ntotal - tok_base) : Ntotal;
+  const bool writer = SPLIT || blockIdx.x == 0;     // this block writes the per-token results
+  if (SPLIT) {
+    x += (size_t)tok_base * d;
+    if (out_logits != nullptr) out_logits += (size_t)tok_base * E;
+    out_idx += (size_t)tok_base * k;
+    out_w += (size_t)tok_base * k;
+    row_of += (size_t)tok_base * k;
+  }
   const int ngroups = (N + 15) >> 4;                       // 16-token groups
   int gp2 = 1;
   while (gp2 < ngroups) gp2 <<= 1;                         // 1, 2, 4 or 8
@@ -142,7 +166,8 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int items = N * pieces;
   const uint4* src = reinterpret_cast<const uint4*>(x);
   constexpr int kInFlight = 4;
-  const int first_item = blockIdx.x * kThreads * kInFlight + tid;
+  const int first_item = (SPLIT ? 0 : (int)blockIdx.x * kThreads * kInFlight) + tid;
+  const int item_stride = (SPLIT ? 1 : (int)gridDim.x) * kThreads * kInFlight;
   uint4 pre[kInFlight];
 #pragma unroll
   for (int u = 0; u < kInFlight; ++u) {
@@ -159,7 +184,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int ks = 0; ks < nslices; ++ks) s += s_part[((size_t)ks * 16 * gp2 + tok) * ET + e];
     s += s_bias[e];
     s_logit[tok * ld + e] = s;
-    if (out_logits != nullptr && blockIdx.x == 0) out_logits[i] = s;
+    if (out_logits != nullptr && writer) out_logits[i] = s;
   }
   __syncthreads();
   FTL(4);
@@ -209,7 +234,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         if (lane == winner) key = 0u;     // below every real key
       }
       if (e < k && tok < N) {
-        if (blockIdx.x == 0) {
+        if (writer) {
           out_idx[tok * k + e] = my_sel;
           out_w[tok * k + e] = my_val * __frcp_rn(total);
         }
@@ -222,11 +247,55 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   FTL(5);
 
   // ---- C. counts, offsets, ranks: warp 0 -------------------------------------------
+  int* s_base = reinterpret_cast<int*>(s_bias + kMaxE);    // [kMaxE] SPLIT: rows of earlier blocks
+  int* s_tot = s_base + kMaxE;                             // [kMaxTopK][kMaxE] SPLIT: grid totals
+  if constexpr (SPLIT) {
+    const int nb = (int)gridDim.x, b = (int)blockIdx.x;
+    float* xps = reinterpret_cast<float*>(xch + nb * k * E);    // [nb][E] probability sums
+    if (tid < k * E) xch[b * k * E + tid] = s_cnt[(tid / E) * kMaxE + tid % E];
+    if (tid < E) {
+      float ps = 0.f;
+      for (int tok = 0; tok < N; ++tok) ps += s_logit[tok * ld + tid];
+      xps[b * E + tid] = ps;
+    }
+    for (int i = tid; i < kMaxE + kMaxTopK * kMaxE; i += kThreads) s_base[i] = 0;   // s_base, s_tot
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      atomicAdd(counter, 1);
+      unsigned long long t0 = 0;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+      for (uint32_t it = 0; ld_acquire_gpu_i32(counter) < nb; ++it) {
+        if ((it & 63u) == 63u) {
+          unsigned long long t1;
+          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+          if (t1 - t0 > 2000000000ull) {     // 2 s: some block of the grid never arrived
+            atomicMax(&status[0], MOE_B200_DEV_TIMEOUT);
+            status[1] = 41;
+            status[2] = b;
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    // totals per (slot, expert) and the rows that earlier blocks put in front of this block's
+    for (int i = tid; i < nb * k * E; i += kThreads) {
+      const int c = __ldcg(&xch[i]);
+      const int bb = i / (k * E), je = i - bb * (k * E);
+      const int j = je / E, e = je - j * E;
+      if (c != 0) {
+        atomicAdd(&s_tot[j * kMaxE + e], c);
+        if (bb < b) atomicAdd(&s_base[e], c);
+      }
+    }
+    __syncthreads();
+  }
   if (warp == 0) {
     int tot = 0;
     if (lane < E) {
       for (int j = 0; j < k; ++j) {
-        const int c = s_cnt[j * kMaxE + lane];
+        const int c = SPLIT ? s_tot[j * kMaxE + lane] : s_cnt[j * kMaxE + lane];
         if (blockIdx.x == 0) cnt_slot[j * E + lane] = c;
         tot += c;
       }
@@ -238,7 +307,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       if (lane >= o) incl += up;
     }
     if (lane < E) {
-      s_off[lane] = incl - tot;
+      s_off[lane] = incl - tot + (SPLIT ? s_base[lane] : 0);   // first row of this block's tokens
       s_run[lane] = 0;
       if (blockIdx.x == 0) offsets[lane] = incl - tot;
     }
@@ -261,7 +330,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       __syncwarp();
       if (p < npair) {
         s_row[p] = row;
-        if (blockIdx.x == 0) row_of[p] = row;
+        if (writer) row_of[p] = row;
       }
     }
   }
@@ -269,7 +338,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   FTL(8);
 
   // ---- D. copy the token rows into the sorted buffer (split over the blocks) -----
-  for (int i0 = first_item; i0 < items; i0 += gridDim.x * kThreads * kInFlight) {
+  for (int i0 = first_item; i0 < items; i0 += item_stride) {
     uint4 v[kInFlight];
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
@@ -292,19 +361,31 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   // ---- E. the loss, off the path of the kernels that wait for the rows (model.py:213-216) ----
   if (blockIdx.x == 0) {
     __syncthreads();       // the partial-logit area is free again: every thread is past the reduction
-    // probabilities summed per expert: warp w takes tokens w, w + 32, ...; the 32 partial sums of
-    // an expert are then added in warp order
-    if (lane < E) {
-      float ps = 0.f;
-      for (int tok = warp; tok < N; tok += kThreads / 32) ps += s_logit[tok * ld + lane];
-      s_part[warp * 32 + lane] = ps;
-    }
-    __syncthreads();
-    if (tid < E) {
-      float ps = 0.f;
-      for (int w = 0; w < kThreads / 32; ++w) ps += s_part[w * 32 + tid];
-      psum[tid] = ps;
-      s_part[1024 + tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
+    if constexpr (SPLIT) {
+      // the blocks' probability sums, added in block order
+      const int nb = (int)gridDim.x;
+      const float* xps = reinterpret_cast<const float*>(xch + nb * k * E);
+      if (tid < E) {
+        float ps = 0.f;
+        for (int bb = 0; bb < nb; ++bb) ps += __ldcg(&xps[bb * E + tid]);
+        psum[tid] = ps;
+        s_part[1024 + tid] = (ps / (float)Ntotal) * ((float)s_tot[tid] / (float)Ntotal);
+      }
+    } else {
+      // probabilities summed per expert: warp w takes tokens w, w + 32, ...; the 32 partial sums
+      // of an expert are then added in warp order
+      if (lane < E) {
+        float ps = 0.f;
+        for (int tok = warp; tok < N; tok += kThreads / 32) ps += s_logit[tok * ld + lane];
+        s_part[warp * 32 + lane] = ps;
+      }
+      __syncthreads();
+      if (tid < E) {
+        float ps = 0.f;
+        for (int w = 0; w < kThreads / 32; ++w) ps += s_part[w * 32 + tid];
+        psum[tid] = ps;
+        s_part[1024 + tid] = (ps / (float)N) * ((float)s_cnt[tid] / (float)N);
+      }
     }
     __syncthreads();
     if (tid == 0) {
@@ -313,27 +394,39 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       aux[0] = a / (float)E * (float)(E * E);
     }
   }
+  if constexpr (SPLIT) {
+    // the last block to leave puts the meeting counter back to zero for the next call
+    __syncthreads();
+    if (tid == 0 && atomicAdd(counter, 1) == 2 * (int)gridDim.x - 1) *counter = 0;
+  }
 }
 
 template <int NT>
 int launch(const void* x, const void* Wg, const void* bg, int N, int d, int E, int k,
            float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot, int32_t* offsets,
-           int32_t* row_of, void* perm, float* psum, float* aux, cudaStream_t s) {
-  const size_t smem = sizeof(float) * ((size_t)32 * 16 * 8 * NT + (size_t)N * (E + 1)) +
-                      sizeof(int) * (2 * (size_t)N * k + kMaxTopK * kMaxE + 3 * kMaxE + 1);
+           int32_t* row_of, void* perm, float* psum, float* aux, int* xch, int* counter,
+           int32_t* status, cudaStream_t s) {
+  // beyond 128 tokens repeating the routing in every block costs more than one exchange
+  const bool split = xch != nullptr && counter != nullptr && status != nullptr && N > 128;
+  const int ntok = split ? 16 : N;
+  const size_t smem = sizeof(float) * ((size_t)32 * 16 * 8 * NT + (size_t)ntok * (E + 1)) +
+                      sizeof(int) * (2 * (size_t)ntok * k + 2 * kMaxTopK * kMaxE + 4 * kMaxE + 1);
   static bool attr_set = false;
   if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT>,
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT, false>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT, true>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     attr_set = true;
   }
-  // one block per 16 tokens: every block repeats the routing, the row copies are split
+  // one block per 16 tokens
   const int blocks = N <= 16 ? 1 : (N + 15) / 16;
-  MOE_CUDA_CHECK(launch_pdl(front_small_kernel<NT>, dim3(blocks), dim3(kThreads), smem, s,
+  auto fn = split ? front_small_kernel<NT, true> : front_small_kernel<NT, false>;
+  MOE_CUDA_CHECK(launch_pdl(fn, dim3(blocks), dim3(kThreads), smem, s,
                             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
                             static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx,
                             out_w, cnt_slot, offsets, row_of, static_cast<__nv_bfloat16*>(perm), psum,
-                            aux));
+                            aux, xch, counter, status));
   return 0;
 }
 
@@ -343,19 +436,21 @@ bool front_small_supported(int64_t N, int E, int k, int dtype) {
   return dtype == MOE_B200_BF16 && N >= 1 && N <= kMaxTok && N * k <= kMaxPairs && E <= kMaxE;
 }
 
+// xch: int32 scratch of at least front_small_exchange_ints(N, E, k) words and counter: one int32
+// that is zero on entry (both only used beyond 128 tokens; without them every block repeats the
+// whole routing at every size).
+int64_t front_small_exchange_ints(int64_t N, int E, int k) {
+  const int64_t nb = (N + 15) / 16;
+  return nb * k * E + nb * E;
+}
+
 int launch_front_small(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                        float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot,
                        int32_t* offsets, int32_t* row_of, void* perm, float* psum, float* aux,
-                       cudaStream_t s) {
-  if (E <= 8) return launch<1>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, s);
-  if (E <= 16) return launch<2>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, s);
-  return launch<4>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, s);
+                       cudaStream_t s, int* xch, int* counter, int32_t* status) {
+  if (E <= 8) return launch<1>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, xch, counter, status, s);
+  if (E <= 16) return launch<2>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, xch, counter, status, s);
+  return launch<4>(x, Wg, bg, (int)N, d, E, k, out_logits, out_idx, out_w, cnt_slot, offsets, row_of, perm, psum, aux, xch, counter, status, s);
 }
 
 }  // namespace moe
-
-#ifdef MOE_TIMELINE
-extern "C" int moe_b200_debug_front_timeline(unsigned long long* h16) {
-  return (int)cudaMemcpyFromSymbol(h16, moe::g_front_tl, sizeof(unsigned long long) * 16);
-}
-#endif

@@ -243,6 +243,21 @@ int moe_b200_front_small(const void* x, const void* Wg, const void* bg,
                          int32_t* cnt_slot, int32_t* offsets, int32_t* row_of, void* perm,
                          float* psum, float* aux, void* stream);
 
+/* The same results from blocks that share the work: beyond 128 tokens every block of
+ * moe_b200_front_small would repeat the whole routing; here block b routes tokens 16b..16b+15,
+ * the blocks exchange their counts through `exchange` (int32, at least
+ * moe_b200_front_exchange_ints(N,E,k) words) and meet at `counter` (one int32, zeroed by this
+ * call; bounded wait, MOE_B200_DEV_TIMEOUT in `status` if a block never arrives). Up to 128
+ * tokens it runs exactly moe_b200_front_small. The logits differ from that function's in the
+ * order their partial sums are added; everything derived from them is derived the same way. */
+int moe_b200_front_small_split(const void* x, const void* Wg, const void* bg,
+                               int64_t N, int d, int E, int k, int dtype,
+                               float* out_logits, int32_t* out_idx, float* out_w,
+                               int32_t* cnt_slot, int32_t* offsets, int32_t* row_of, void* perm,
+                               float* psum, float* aux, int32_t* exchange, int32_t* counter,
+                               int32_t* status, void* stream);
+int64_t moe_b200_front_exchange_ints(int64_t N, int E, int k);
+
 /* Part 3, small-N ("decode") variant, bf16 only, M <= moe_b200_decode_max_rows():
  * the same products as moe_b200_experts, arranged for weight streaming when
  * only a few rows reach each expert (the reference runs the same

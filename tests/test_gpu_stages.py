@@ -53,8 +53,10 @@ def test_router_matches_oracle(cuda_device, N, d, E, k, dtype):
 @pytest.mark.parametrize("N,d,E,k", [(1, 1024, 8, 2), (8, 1024, 8, 2), (17, 256, 16, 4), (64, 1024, 8, 2),
                                      (100, 72, 5, 2), (128, 128, 32, 2), (33, 64, 24, 7),
                                      (129, 256, 8, 2), (300, 1024, 8, 2), (512, 512, 32, 2), (200, 128, 16, 5)])
-def test_front_small_equals_router_plus_dispatch(cuda_device, N, d, E, k):
-    """The single-launch small-N front end gives what the two general kernels give."""
+@pytest.mark.parametrize("split", [False, True])
+def test_front_small_equals_router_plus_dispatch(cuda_device, N, d, E, k, split):
+    """The single-launch front end gives what the two general kernels give, whether every block
+    repeats the routing or (beyond 128 tokens) the blocks share it and meet at a counter."""
     dt = torch.bfloat16
     x, gw, gb = make_gate(N, d, E, dt, seed=N + E)
     xd, gwd, gbd = x.to(dt).to(cuda_device), gw.to(dt).to(cuda_device), gb.to(dt).to(cuda_device)
@@ -70,10 +72,24 @@ def test_front_small_equals_router_plus_dispatch(cuda_device, N, d, E, k):
            "perm": torch.empty(N * k, d, dtype=dt, device=dev),
            "psum": torch.empty(E, dtype=torch.float32, device=dev),
            "aux": torch.zeros(1, dtype=torch.float32, device=dev)}
-    helpers.check(helpers.lib.moe_b200_front_small(
-        xd.data_ptr(), gwd.data_ptr(), gbd.data_ptr(), N, d, E, k, _cabi.BF16,
-        *[got[n].data_ptr() for n in ("logits", "idx", "w", "cnt_slot", "offsets", "row_of", "perm",
-                                      "psum", "aux")], helpers.stream(dev)), "front_small")
+    outs = [got[n].data_ptr() for n in ("logits", "idx", "w", "cnt_slot", "offsets", "row_of", "perm",
+                                        "psum", "aux")]
+    if split:
+        xch = torch.full((helpers.lib.moe_b200_front_exchange_ints(N, E, k),), 0x5A5A5A5A,
+                         dtype=torch.int32, device=dev)
+        counter = torch.full((1,), 77, dtype=torch.int32, device=dev)    # the call zeroes it
+        status = torch.zeros(16, dtype=torch.int32, device=dev)
+        for _ in range(2):       # twice: the counter has to be back at zero after a call
+            helpers.check(helpers.lib.moe_b200_front_small_split(
+                xd.data_ptr(), gwd.data_ptr(), gbd.data_ptr(), N, d, E, k, _cabi.BF16, *outs,
+                xch.data_ptr(), counter.data_ptr(), status.data_ptr(), helpers.stream(dev)),
+                "front_small_split")
+            torch.cuda.synchronize()
+            assert status.cpu().tolist()[0] == 0 and int(counter.item()) == 0
+    else:
+        helpers.check(helpers.lib.moe_b200_front_small(
+            xd.data_ptr(), gwd.data_ptr(), gbd.data_ptr(), N, d, E, k, _cabi.BF16, *outs,
+            helpers.stream(dev)), "front_small")
     torch.cuda.synchronize()
     assert (got["logits"] - logits).abs().max() <= 2e-5 * max(1.0, float(logits.abs().max()))
     r = moe_oracle.route_from_logits(got["logits"].cpu(), k)
