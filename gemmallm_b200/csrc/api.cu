@@ -48,7 +48,7 @@ static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off
   sizes[MOE_B200_WS_PSUM] = (size_t)E * sizeof(float);
   sizes[MOE_B200_WS_AUX] = sizeof(float);
   sizes[MOE_B200_WS_SCRATCH] = (size_t)dispatch_scratch_ints(N, E, k) * sizeof(int32_t);
-  if (front_small_supported(N, E, k, dtype) &&
+  if (front_split_supported(N, E, k, dtype) &&
       (size_t)front_small_exchange_ints(N, E, k) * sizeof(int32_t) > sizes[MOE_B200_WS_SCRATCH])
     sizes[MOE_B200_WS_SCRATCH] = (size_t)front_small_exchange_ints(N, E, k) * sizeof(int32_t);
   sizes[MOE_B200_WS_CNT_SLOT] = (size_t)k * E * sizeof(int32_t);
@@ -245,9 +245,9 @@ int moe_b200_front_small_split(const void* x, const void* Wg, const void* bg, in
                                int32_t* status, void* stream) {
   int rc = check_shape(N, d, 8, E, k, dtype);
   if (rc) return rc;
-  if (!front_small_supported(N, E, k, dtype))
+  if (!front_split_supported(N, E, k, dtype))
     return set_error(MOE_B200_ERR_UNSUPPORTED,
-                     "moe_b200_front_small_split needs bf16, 1 <= N <= 512, N*k <= 1024, E <= 32");
+                     "moe_b200_front_small_split needs bf16, 1 <= N <= 2048, E <= 32");
   if (!x || !Wg || !bg || !out_idx || !out_w || !cnt_slot || !offsets || !row_of || !perm || !psum ||
       !aux || !exchange || !counter || !status)
     return set_error(MOE_B200_ERR_NULL, "NULL argument");
@@ -371,7 +371,7 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   if (!(counters && (flags & MOE_B200_FLAG_WS_CLEAN)))
     MOE_CUDA_CHECK(cudaMemsetAsync(
         status, 0, (counters ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
-  if ((small_n || rows_path) && front_small_supported(N, E, k, dtype)) {
+  if ((small_n || rows_path) && (front_small_supported(N, E, k, dtype) || front_split_supported(N, E, k, dtype))) {
     // router and dispatch of up to a few hundred tokens in one launch
     // (beyond 128 tokens its blocks share the work and meet at a counter behind the status words)
     rc = launch_front_small(x, Wg, bg, N, d, E, k, logits, idx, w, cnt_slot, offsets, row_of, perm,

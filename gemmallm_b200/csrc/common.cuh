@@ -20,7 +20,7 @@ constexpr int kDispatchChunk = 64;
 
 // The small-N (weight-streaming) expert path is taken up to this many sorted rows (N*k).
 constexpr int64_t kDecodeMaxRows = 256;
-constexpr int64_t kRowsPathMaxRows = 1024;   // above: the prefill kernels (256-row tiles)
+constexpr int64_t kRowsPathMaxRows = 4096;   // above: the prefill kernels (256-row tiles)
 
 int set_error(int code, const char* msg);
 int cuda_error(cudaError_t e, const char* where);
@@ -232,6 +232,7 @@ int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint3
                      cudaStream_t s);
 bool front_small_supported(int64_t N, int E, int k, int dtype);
 int64_t front_small_exchange_ints(int64_t N, int E, int k);
+bool front_split_supported(int64_t N, int E, int k, int dtype);
 int launch_front_small(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                        float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot,
                        int32_t* offsets, int32_t* row_of, void* perm, float* psum, float* aux,

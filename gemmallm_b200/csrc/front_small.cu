@@ -436,6 +436,12 @@ bool front_small_supported(int64_t N, int E, int k, int dtype) {
   return dtype == MOE_B200_BF16 && N >= 1 && N <= kMaxTok && N * k <= kMaxPairs && E <= kMaxE;
 }
 
+// With the exchange buffer and the counter (blocks share the work): as many tokens as give a grid
+// whose blocks are all resident at once with room to spare.
+bool front_split_supported(int64_t N, int E, int k, int dtype) {
+  return dtype == MOE_B200_BF16 && N >= 1 && N <= 16 * 128 && E <= kMaxE && k <= kMaxTopK;
+}
+
 // xch: int32 scratch of at least front_small_exchange_ints(N, E, k) words and counter: one int32
 // that is zero on entry (both only used beyond 128 tokens; without them every block repeats the
 // whole routing at every size).

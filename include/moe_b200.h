@@ -85,7 +85,7 @@ enum {
    * kernel, which then overlaps the tail of the kernel before it. After a non-zero device
    * status the region has to be zeroed again by the caller. */
   MOE_B200_FLAG_WS_CLEAN = 64,
-  /* moe_b200_forward: calls of 257 to 1024 rows (N*k) go through the prefill kernels instead
+  /* moe_b200_forward: calls of 257 to 4096 rows (N*k) go through the prefill kernels instead
    * of moe_b200_experts_rows */
   MOE_B200_FLAG_NO_ROWS_PATH = 128
 };
@@ -247,8 +247,8 @@ int moe_b200_front_small(const void* x, const void* Wg, const void* bg,
  * moe_b200_front_small would repeat the whole routing; here block b routes tokens 16b..16b+15,
  * the blocks exchange their counts through `exchange` (int32, at least
  * moe_b200_front_exchange_ints(N,E,k) words) and meet at `counter` (one int32, zeroed by this
- * call; bounded wait, MOE_B200_DEV_TIMEOUT in `status` if a block never arrives). Up to 128
- * tokens it runs exactly moe_b200_front_small. The logits differ from that function's in the
+ * call; bounded wait, MOE_B200_DEV_TIMEOUT in `status` if a block never arrives). bf16,
+ * 1 <= N <= 2048, E <= 32. Up to 128 tokens it runs exactly moe_b200_front_small. The logits differ from that function's in the
  * order their partial sums are added; everything derived from them is derived the same way. */
 int moe_b200_front_small_split(const void* x, const void* Wg, const void* bg,
                                int64_t N, int d, int E, int k, int dtype,

@@ -181,9 +181,10 @@ def test_c2_single_launch_experts_equal_two_launches(cuda_device, name):
 
 
 @pytest.mark.parametrize("N,d,E,f,k", [(129, 64, 8, 128, 2), (300, 256, 8, 1024, 2), (512, 512, 8, 2048, 2),
-                                       (400, 1024, 8, 4096, 2), (250, 128, 16, 200, 4)])
+                                       (400, 1024, 8, 4096, 2), (250, 128, 16, 200, 4), (1500, 256, 8, 1024, 2),
+                                       (2048, 128, 8, 256, 2)])
 def test_mid_sizes_rows_path(cuda_device, N, d, E, f, k):
-    """Between the decode and the prefill sizes (257 to 1024 rows) the forward streams the
+    """Between the decode and the prefill sizes (257 to 4096 rows) the forward streams the
     weights over the sorted rows; with the flag it takes the prefill kernels. Both meet the
     block's tolerance, with and without a residual, call after call."""
     params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=N), torch.bfloat16)

@@ -52,11 +52,14 @@ def test_router_matches_oracle(cuda_device, N, d, E, k, dtype):
 
 @pytest.mark.parametrize("N,d,E,k", [(1, 1024, 8, 2), (8, 1024, 8, 2), (17, 256, 16, 4), (64, 1024, 8, 2),
                                      (100, 72, 5, 2), (128, 128, 32, 2), (33, 64, 24, 7),
-                                     (129, 256, 8, 2), (300, 1024, 8, 2), (512, 512, 32, 2), (200, 128, 16, 5)])
+                                     (129, 256, 8, 2), (300, 1024, 8, 2), (512, 512, 32, 2), (200, 128, 16, 5),
+                                     (1000, 256, 8, 2), (2048, 128, 16, 4)])
 @pytest.mark.parametrize("split", [False, True])
 def test_front_small_equals_router_plus_dispatch(cuda_device, N, d, E, k, split):
     """The single-launch front end gives what the two general kernels give, whether every block
     repeats the routing or (beyond 128 tokens) the blocks share it and meet at a counter."""
+    if N > 512 and not split:
+        pytest.skip("every block repeating the routing is limited to 512 tokens")
     dt = torch.bfloat16
     x, gw, gb = make_gate(N, d, E, dt, seed=N + E)
     xd, gwd, gbd = x.to(dt).to(cuda_device), gw.to(dt).to(cuda_device), gb.to(dt).to(cuda_device)
