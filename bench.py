@@ -264,10 +264,14 @@ def run_ours(args, wl):
         return ms
 
     small_n = wl.dtype == "bf16" and N * k <= lib.moe_b200_decode_max_rows()
+    # between the decode and the prefill sizes: the streaming kernels on sorted rows
+    mid_n = (wl.dtype == "bf16" and not small_n and N * k <= 4096 and N <= 2048 and E <= 32
+             and not (getattr(args, "flags", 0) & _cabi.FLAG_NO_ROWS_PATH))
+    streaming = small_n or mid_n      # launch-bound from Python, bound by the weight stream on the GPU
 
     def capture(fn):
         """Small-N calls are launch-bound from Python: replay them as a CUDA graph."""
-        if not small_n or args.no_graph:
+        if not streaming or args.no_graph:
             return None
         try:
             g = torch.cuda.CUDAGraph()
@@ -285,14 +289,14 @@ def run_ours(args, wl):
         for _ in range(max(args.warmup, 3)):
             m(x)
         torch.cuda.synchronize()
-        if small_n and not args.no_graph:
+        if streaming and not args.no_graph:
             # A small-N step touches only the weights of the experts it hits, which can be less
             # than the L2: rotate over copies of the block so that no step finds its weights
             # cached by the step before, and put several steps into one graph, as a decoder
             # that captures all its layers would (the gap between two graph launches is not
             # the block's).
             hit = int((m.last["cnt_slot"].sum(0) > 0).sum())
-            if N * k >= 2 * E:
+            if N * k >= 2 * E and small_n:
                 hit = E      # the routing-independent kernel streams every expert
             touched = hit * (3 * d * f + 2 * f + d) * es
             n_rep = max(1, -(-int(2 * L2_BYTES) // touched))
@@ -349,7 +353,7 @@ def run_ours(args, wl):
     # i-1 overlap, as a serving loop would); small-N calls replay one CUDA
     # graph per step and wait for it, since there latency is the point.
     aux_host = torch.zeros(1, dtype=torch.float32).pin_memory()
-    if small_n:
+    if streaming:
         x_dev = torch.empty(1, N, d, dtype=dt, device=dev)
 
         def e2e_step():
@@ -385,9 +389,9 @@ def run_ours(args, wl):
 
     # ---- per-stage times through the stage entry points --------------------
     two_pass = bool(m.flags & _cabi.FLAG_DECODE_TWO_PASS)
-    stage_ms, launches_per_step = {}, ((4 if two_pass else 3) if small_n else 5)
+    stage_ms, launches_per_step = {}, ((4 if two_pass else 3) if small_n else (3 if mid_n else 5))
     if rank == 0:
-        stage_ms = time_stages(m, x.view(N, d), wl, dev, small_n)
+        stage_ms = time_stages(m, x.view(N, d), wl, dev, small_n, mid_n=mid_n)
     peaks, peak_kind = load_peaks()
     line = None
     if rank == 0:
@@ -429,7 +433,7 @@ def run_ours(args, wl):
                                "frac": b / (stage_ms[n] * 1e-3) / 1e9 / hbm}
                            for n, b in stage_bytes.items()},
         }
-        if small_n:
+        if streaming:
             # weight streaming: bytes of the distinct experts hit, plus router weights, x in, out
             hit = int((m.last["cnt_slot"].sum(0) > 0).sum())
             wbytes = hit * (3 * d * f + 2 * f + d) * es
@@ -437,7 +441,8 @@ def run_ours(args, wl):
             gbs_step = nbytes_step / (ms_step * 1e-3) / 1e9
             gbs_experts = wbytes / (stage_ms["experts"] * 1e-3) / 1e9
             line["roofline"] = {
-                "kernel": "decode_spec_kernel / decode_fused_kernel (GEGLU + split-K down tiles, one launch)",
+                "kernel": ("decode_spec_kernel / decode_fused_kernel (GEGLU + split-K down tiles, one launch)"
+                           if small_n else "decode_spec_kernel<SORTED> (GEGLU + split-K down tiles on sorted rows)"),
                 "bound": "hbm", "achieved": gbs_experts, "peak": hbm, "unit": "GB/s",
                 "frac": gbs_experts / hbm, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
                 "peak_source": f"{peak_kind} copy",
@@ -627,7 +632,7 @@ def run_ep(args, wl):
     dist.destroy_process_group()
 
 
-def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20):
+def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: bool = False):
     """CUDA-event time of each stage, called through its own C-ABI entry point
     on the buffers of the module's workspace, on the current stream."""
     from gemmallm_b200 import _cabi
@@ -680,6 +685,24 @@ def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20):
         calls["combine"] = lambda: lib.moe_b200_combine_decode(
             p["part"], splits, N * k, p["row_of"], p["idx"], p["w"], plan, E, None, N, d, k,
             out.data_ptr(), s)
+    if mid_n:
+        # single-launch front (blocks share the routing), streaming kernel on the sorted rows,
+        # the small-N combine
+        ks = lib.moe_b200_rows_splits(N * k, d, f, E)
+        ready = p["status"] + 4 * _cabi.READY_OFFSET
+        counter = ready + 4 * (_cabi.READY_INTS - 4)
+        calls = {
+            "front": lambda: lib.moe_b200_front_small_split(
+                x2d.data_ptr(), gw.data_ptr(), gb.data_ptr(), N, d, E, k, code, p["logits"], p["idx"],
+                p["w"], p["cnt_slot"], p["offsets"], p["row_of"], p["perm"], p["psum"], p["aux"],
+                p["scratch"], counter, p["status"], s),
+            "experts": lambda: lib.moe_b200_experts_rows(
+                p["perm"], p["offsets"], plan, N * k, d, f, E, ks, p["h"], p["part"], ready,
+                p["status"], s),
+            "combine": lambda: lib.moe_b200_combine_decode(
+                p["part"], ks, N * k, p["row_of"], p["idx"], p["w"], plan, E, None, N, d, k,
+                out.data_ptr(), s),
+        }
     res = {}
     for name, fn in calls.items():
         for _ in range(3):

@@ -37,6 +37,9 @@ WORKLOADS = {
     "c2_t8": Workload("c2_t8", 8, 1024, 8, 4096, 2, "bf16"),
     "c2_t32": Workload("c2_t32", 32, 1024, 8, 4096, 2, "bf16"),
     "c2_t64": Workload("c2_t64", 64, 1024, 8, 4096, 2, "bf16"),
+    # the same block at batch sizes between decode and prefill (not BASELINE configurations)
+    "c2_t256": Workload("c2_t256", 256, 1024, 8, 4096, 2, "bf16"),
+    "c2_t1024": Workload("c2_t1024", 1024, 1024, 8, 4096, 2, "bf16"),
     # per-layer shape of the 12-layer decoder forward (batch 512 x context 64)
     "c3_layer": Workload("c3_layer", 32768, 1024, 8, 4096, 2, "bf16"),
     # expert-parallel block, Zipf(1.1) expert popularity
