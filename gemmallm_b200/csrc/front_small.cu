@@ -36,15 +36,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Debug timeline (compile with -DMOE_TIMELINE): %globaltimer stamps of block 0.
-#ifdef MOE_TIMELINE
-__device__ unsigned long long g_front_tl[16];
-#define FTL(slot) do { if (blockIdx.x == 0 && threadIdx.x == 0) { unsigned long long t_; \
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_front_tl[slot] = t_; } } while (0)
-#else
-#define FTL(slot)
-#endif
-
 __device__ __forceinline__ int ld_acquire_gpu_i32(const int* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -97,10 +88,8 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int g = lane >> 2, t = lane & 3;
   constexpr int ET_C = 8 * NT;
   const int ET = ET_C;
-  FTL(0);
   pdl_wait();                 // x may come from the kernel before this one
   pdl_launch_dependents();
-  FTL(1);
   if (tid < E) s_bias[tid] = __bfloat162float(bg[tid]);   // visible after the barrier behind part A
 
   // ---- A. partial logits -----------------------------------------------------
@@ -157,9 +146,7 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   }
   for (int i = tid; i < kMaxTopK * kMaxE; i += kThreads) s_cnt[i] = 0;
-  FTL(2);
   __syncthreads();
-  FTL(3);
   // the first batch of row copies: the loads do not depend on the routing, so they are
   // issued now and wait in registers until the destination rows are known
   const int pieces = d >> 3;
@@ -187,7 +174,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     if (out_logits != nullptr && writer) out_logits[i] = s;
   }
   __syncthreads();
-  FTL(4);
 
   // ---- B. softmax, top-k, renormalise: a group of ET lanes per token, lane e = expert e ----
   {
@@ -244,7 +230,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   }
   __syncthreads();
-  FTL(5);
 
   // ---- C. counts, offsets, ranks: warp 0 -------------------------------------------
   int* s_base = reinterpret_cast<int*>(s_bias + kMaxE);    // [kMaxE] SPLIT: rows of earlier blocks
@@ -316,7 +301,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       if (blockIdx.x == 0) offsets[E] = incl;
     }
     __syncwarp();
-    FTL(7);
     const int npair = N * k;
     for (int p0 = 0; p0 < npair; p0 += 32) {
       const int p = p0 + lane;
@@ -335,7 +319,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   }
   __syncthreads();
-  FTL(8);
 
   // ---- D. copy the token rows into the sorted buffer (split over the blocks) -----
   for (int i0 = first_item; i0 < items; i0 += item_stride) {
@@ -356,7 +339,6 @@ front_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       }
     }
   }
-  FTL(9);
 
   // ---- E. the loss, off the path of the kernels that wait for the rows (model.py:213-216) ----
   if (blockIdx.x == 0) {
