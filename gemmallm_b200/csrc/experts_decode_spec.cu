@@ -609,13 +609,17 @@ int rows_block(int64_t M, int E) {
   return share <= 32 ? 32 : share <= 64 ? 64 : 128;
 }
 
-// K ranges of the down product: enough tiles for two waves of CTAs given at least
-// ceil(M / block) row blocks, each range at least 8 blocks of 64.
+// K ranges of the down product: about one wave of CTAs' worth of tiles, given at least
+// max(ceil(M / block), min(E, M)) row blocks; each range at least 8 blocks of 64. More ranges
+// only add partial sums to write and read back (measured at d=1024, f=4096, E=8: 4 ranges are
+// best at 512 and 1024 rows, 2 at 2048, 1 or 2 at 4096).
 int rows_splits(int64_t M, int d, int f, int E) {
   const int NP = rows_block(M, E);
-  const int64_t blocks = (M + NP - 1) / NP;
+  int64_t blocks = (M + NP - 1) / NP;
+  const int64_t hit = M < E ? M : E;
+  if (blocks < hit) blocks = hit;
   const int64_t tiles = blocks * ((d + 255) / 256);
-  int64_t want = (2 * kNumSMs + tiles - 1) / tiles;
+  int64_t want = kNumSMs / tiles;
   const int kb = (f + BK - 1) / BK;
   if (want > kb / 8) want = kb / 8;
   if (want > 8) want = 8;

@@ -77,7 +77,7 @@ def test_small_and_mid_size_entry_points_check_their_arguments():
     assert lib.moe_b200_experts_rows(a, a, a, 1 << 20, 1024, 4096, 8, 4, a, a, a, a, None) == -7
     # sizes the forward uses
     assert lib.moe_b200_decode_spec_rows(1) == 16 and lib.moe_b200_decode_spec_rows(65) == 128
-    assert lib.moe_b200_rows_splits(1024, 1024, 4096, 8) == 8
+    assert lib.moe_b200_rows_splits(1024, 1024, 4096, 8) == 4
     assert 1 <= lib.moe_b200_rows_splits(1024, 4096, 256, 8) <= 4 // 8 + 1
     # shared-work front: token limit
     assert lib.moe_b200_front_small_split(a, a, a, 2049, 1024, 8, 2, _cabi.BF16, *([a] * 12), None) == -7

@@ -272,6 +272,98 @@ def test_experts_decode_path_bf16(cuda_device, rows, d, f):
     assert torch.equal(out.cpu(), (acc + res.float()).to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("rows,d,f", DECODE_CASES)
+def test_experts_decode_fused_equals_two_pass(cuda_device, rows, d, f):
+    """The single-launch small-N kernel does the same tiles with the same arithmetic as
+    the two launches: h and every partial sum bit-identical, twice in a row."""
+    params, x, offsets = expert_inputs(rows, d, f, torch.bfloat16, seed=len(rows) + f)
+    dp = helpers.device_params(params, torch.bfloat16, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    xd, od = x.to(torch.bfloat16).to(cuda_device), offsets.to(cuda_device)
+    h, part, status = helpers.experts_decode(xd, od, plan)
+    for _ in range(2):
+        hf, partf, statusf = helpers.experts_decode_fused(xd, od, plan)
+        torch.cuda.synchronize()
+        assert statusf.cpu().tolist()[0] == 0
+        assert torch.equal(hf, h)
+        assert torch.equal(partf, part)
+
+
+SPEC_CASES = [(1, 64, 128, 2, 2), (8, 1024, 4096, 8, 2), (17, 72, 264, 5, 3), (32, 256, 1408, 32, 4),
+              (64, 1024, 4096, 8, 2), (100, 128, 512, 3, 2), (128, 256, 384, 16, 2), (64, 128, 256, 8, 1)]
+
+
+@pytest.mark.parametrize("N,d,f,E,k", SPEC_CASES)
+def test_experts_decode_spec_equals_sorted_path(cuda_device, N, d, f, E, k):
+    """The routing-independent small-N kernel works on the unsorted tokens and all
+    experts; its partial sums, stored in dispatch row order, match the kernel that
+    works on the sorted rows, and sum(part)+bias matches the oracle."""
+    dt = torch.bfloat16
+    params = synthetic.make_params(d, E, f, seed=N + E)
+    g = torch.Generator().manual_seed(N + f)
+    params["b1"] = torch.randn(E, 2 * f, generator=g) * 0.05
+    params["b2"] = torch.randn(E, d, generator=g) * 0.05
+    params["w1"] *= 3.0
+    params["w2"] *= 3.0
+    params = helpers.rounded_params(params, dt)
+    x = synthetic.round_to(torch.randn(N, d, generator=g), dt)
+    # random routing with k distinct experts per token; expert E-1 never chosen when E > k
+    pool = E - 1 if E > k else E
+    idx = torch.stack([torch.randperm(pool, generator=g)[:k] for _ in range(N)]).to(torch.int32)
+    dp = helpers.device_params(params, dt, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    xd, idxd = x.to(dt).to(cuda_device), idx.to(cuda_device)
+    disp = helpers.dispatch(xd, idxd, E)
+    h, part, status = helpers.experts_decode(disp["perm"], disp["offsets"], plan)
+    for _ in range(2):
+        h_all, part_s, status_s = helpers.experts_decode_spec(xd, idxd, disp["offsets"], plan)
+        torch.cuda.synchronize()
+        assert status_s.cpu().tolist()[0] == 0
+        assert not torch.isnan(part_s).any()
+        assert (part_s.sum(0) - part.sum(0)).abs().max() <= 1e-3 * part.sum(0).abs().max()
+    # h rows of the routed pairs, against the sorted kernel's h
+    row_of = disp["row_of"].cpu().long()
+    assert h_all.shape[1] == helpers.lib.moe_b200_decode_spec_rows(N)
+    for t in range(0, N, max(1, N // 8)):
+        for j in range(k):
+            got = h_all[int(idx[t, j]), t].float().cpu()
+            ref = h[row_of[t, j]].float().cpu()
+            assert (got - ref).abs().max() <= 1e-2 * max(1e-3, float(ref.abs().max()))
+    # against the oracle
+    offsets = disp["offsets"].cpu()
+    e_of_row = torch.bucketize(torch.arange(N * k), offsets.long()[1:], right=True)
+    _, y_ref = oracle_experts(params, disp["perm"].float().cpu(), offsets)
+    y = part_s.sum(0).cpu() + params["b2"][e_of_row]
+    assert (y - y_ref).abs().max() <= 2e-2 * y_ref.abs().max()
+
+
+@pytest.mark.parametrize("rows,d,f,ksplit", [([100, 0, 300, 57], 256, 1024, 2), ([128] * 8, 1024, 4096, 8),
+                                             ([513, 1, 255, 256, 0, 700, 31, 64], 512, 2048, 4),
+                                             ([40, 50], 72, 520, 1), ([0, 0, 129], 64, 128, 2),
+                                             ([20, 33, 1, 40, 7, 64, 0, 65], 256, 1024, 3)])
+def test_experts_rows_matches_prefill_kernels(cuda_device, rows, d, f, ksplit):
+    """The streaming pipeline on sorted rows (calls between the decode and the prefill sizes):
+    h and sum(part) + bias against the prefill kernels and against the oracle, twice in a row."""
+    params, x, offsets = expert_inputs(rows, d, f, torch.bfloat16, seed=len(rows) + f)
+    dp = helpers.device_params(params, torch.bfloat16, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    xd, od = x.to(torch.bfloat16).to(cuda_device), offsets.to(cuda_device)
+    h2, y2, _ = helpers.experts(xd, od, plan)
+    M = sum(rows)
+    e_of_row = torch.bucketize(torch.arange(M), offsets.long()[1:], right=True)
+    h_ref, y_ref = oracle_experts(params, x, offsets)
+    for _ in range(2):
+        h, part, status = helpers.experts_rows(xd, od, plan, ksplit)
+        torch.cuda.synchronize()
+        assert status.cpu().tolist()[0] == 0
+        assert not torch.isnan(part).any() and not torch.isnan(h.float()).any()
+        assert (h.float() - h2.float()).abs().max() <= 1e-2 * h2.float().abs().max()
+        assert (h.float().cpu() - h_ref).abs().max() <= 2e-2 * h_ref.abs().max()
+        y = part.sum(0).cpu() + params["b2"][e_of_row]
+        assert (y - y_ref).abs().max() <= 2e-2 * y_ref.abs().max()
+        assert (y - y2.float().cpu()).abs().max() <= 1e-2 * y_ref.abs().max()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("N,d,k", [(1, 64, 2), (130, 128, 2), (1000, 512, 4), (33, 72, 1)])
 def test_combine_is_exact(cuda_device, N, d, k, dtype):
