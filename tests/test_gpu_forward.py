@@ -77,6 +77,7 @@ SMALL = [
     # N, d, E, f, k
     (1, 64, 8, 128, 2), (2, 64, 8, 128, 2), (3, 64, 8, 128, 2), (127, 64, 8, 128, 2),
     (128, 64, 8, 128, 2), (129, 64, 8, 128, 2), (1000, 128, 16, 200, 4), (513, 256, 5, 264, 3),
+    (2048, 64, 8, 128, 2), (2049, 64, 8, 128, 2),
 ]
 
 
