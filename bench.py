@@ -6,13 +6,17 @@ fraction of the measured bf16 tensor peak.
 
 One step = one forward of the block over the workload's token batch. At N=1 the
 workload is the bf16 prefill block (16384 tokens, d_model 1024, 8 experts,
-d_ff 4096, top-2, uniform routing). Under torchrun every rank runs the same
-block on its own token batch (tokens sharded, no data-path collective; weak
-scaling). Rank 0 prints one JSON line.
+d_ff 4096, top-2, uniform routing); the same line also carries the
+decode-shaped calls of that block and the expert-parallel workload on this one
+GPU. Under torchrun the default is the expert-parallel workload (65536 tokens,
+d_model 2048, 64 experts, d_ff 1408, top-4, Zipf routing): tokens and experts
+sharded over the ranks, strong scaling. Rank 0 prints one JSON line.
 
-``--impl reference`` times the CPU restatement of the reference block
-(oracle/moe_oracle.py, bit-identical to the reference class at k=2) on this
-host's cores instead.
+``--impl reference`` times the reference's own CPU implementation of the block on
+this host's cores instead: its ``model.MOE`` class (from oracle/_ref, an
+unmodified copy of the reference's model.py) where that class can express the
+workload (two slots, integer expansion factor), else the CPU restatement in
+oracle/moe_oracle.py (bit-identical to the class at two slots).
 """
 from __future__ import annotations
 
@@ -29,12 +33,16 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernels per step, from the ncu
-# captures summarised under profiles/ (GEGLU pass + down pass)
-NCU_TRAFFIC_BYTES = {"c1_uniform": 429.7e6 + 405.7e6, "c2_t64": 204.8e6 + 3.8e6}
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernels per step (GEGLU pass +
+# down pass) from the ncu captures summarised under profiles/: a static figure, not measured by
+# this run
+NCU_TRAFFIC = {
+    "c1_uniform": (429.7e6 + 405.7e6, "profiles/grouped_gemm_tc2_c1_uniform.md (static, ncu capture)"),
+    "c2_t64": (204.8e6 + 3.8e6, "profiles/decode_spec_kernel_c2_t64.md (static, ncu capture)"),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-CPU_SAMPLE_TOKENS = 4096
 L2_BYTES = 126e6
+CPU_ARM_BUDGET_S = 240.0      # the whole --impl reference run should end within a few minutes
 
 
 def load_peaks():
@@ -156,52 +164,106 @@ def pipelined_e2e(m, x_host, out_host, aux_host, N, d, dt, dev, steps, warm=3):
     return e0.elapsed_time(e1)
 
 
-def workload_config(wl, extra):
-    cfg = {"workload": wl.name, "tokens": wl.tokens, "d_model": wl.d_model,
-           "n_experts": wl.n_experts, "d_ff": wl.d_ff, "top_k": wl.top_k, "routing": wl.gate_bias}
-    cfg.update(extra)
-    return cfg
+def workload_config(wl):
+    """The same keys in both arms, so that the two lines name one configuration."""
+    return {"workload": wl.name, "tokens": wl.tokens, "d_model": wl.d_model,
+            "n_experts": wl.n_experts, "d_ff": wl.d_ff, "top_k": wl.top_k, "routing": wl.gate_bias,
+            "l2": "no flush: the working set of one step (expert weights, sorted rows, h) exceeds the "
+                  "126 MB L2; decode-shaped calls rotate over copies of the weights instead"}
 
 
-def cpu_baseline(wl, tokens, repeats, warmup):
-    """Oracle (port of the reference block) on the host cores, fp32 on
-    bf16-rounded values: the reference cannot run in bf16."""
+# ---------------------------------------------------------------------------
+# CPU arm: the reference's own block on the host cores
+# ---------------------------------------------------------------------------
+
+def cpu_block(wl):
+    """(kind, forward(x [N,d] fp32) -> None) for the workload. kind "reference": the
+    reference's model.MOE from oracle/_ref; kind "port": oracle/moe_oracle.py."""
     from gemmallm_b200 import synthetic
-    from oracle import moe_oracle
+    from oracle import make_ref, moe_oracle
+    dt = synthetic.torch_dtype(wl.dtype)
+    d, E, f, k = wl.d_model, wl.n_experts, wl.d_ff, wl.top_k
+    why = None
+    if k != 2 or f % d != 0:
+        why = "the reference class has two slots and an integer expansion factor"
+    elif not make_ref.available():
+        why = "oracle/_ref/model.py is absent"
+    if why is None:
+        try:
+            ref = make_ref.load()
+            m = ref.MOE(d, num_experts=E, expansion_factor=f // d, device="cpu").eval()
+            params = {n: synthetic.round_to(t, dt) for n, t in synthetic.make_params(
+                d, E, f, seed=0, gate_bias_kind=wl.gate_bias).items()}
+            synthetic.load_into(m, params, torch.float32, "cpu")
+            del params
+            return "reference", (lambda x: m(x.view(1, *x.shape))), None
+        except Exception as exc:       # import or construction failed on this box
+            why = f"the reference module did not load here ({type(exc).__name__}: {exc})"
+    if E > 16:
+        w1, w2 = [], []
+        for e in range(E):
+            pe = synthetic.make_expert(d, f, e, 0)
+            w1.append(synthetic.round_to(pe["w1"], dt))
+            w2.append(synthetic.round_to(pe["w2"], dt))
+        gate_w, gate_b = synthetic.make_gate(d, E, 0, wl.gate_bias)
+        params = {"gate_w": synthetic.round_to(gate_w, dt), "gate_b": synthetic.round_to(gate_b, dt),
+                  "w1": w1, "b1": torch.zeros(E, 2 * f), "w2": w2, "b2": torch.zeros(E, d)}
+    else:
+        params = {n: synthetic.round_to(t, dt) for n, t in synthetic.make_params(
+            d, E, f, seed=0, gate_bias_kind=wl.gate_bias).items()}
+    return "port", (lambda x: moe_oracle.moe_forward(x, params, k)), why
+
+
+def cpu_arm(wl, steps, warmup, budget_s):
+    """Times the CPU block: fp32 on bf16-rounded values (the reference cannot run in bf16),
+    all host threads. The sample is the whole token batch unless one step is so slow that
+    steps + warmup of them would pass `budget_s`; then the first tokens of the batch, as many
+    as fit. Returns (per-step seconds, cores, kind, sample text, tokens per step, note)."""
+    from gemmallm_b200 import synthetic
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     dt = synthetic.torch_dtype(wl.dtype)
-    params = {n: synthetic.round_to(t, dt) for n, t in synthetic.make_params(
-        wl.d_model, wl.n_experts, wl.d_ff, seed=0, gate_bias_kind=wl.gate_bias).items()}
-    x = synthetic.round_to(synthetic.make_input(tokens, wl.d_model, seed=1), dt)
+    kind, fwd, why = cpu_block(wl)
+    x_all = synthetic.round_to(synthetic.make_input(wl.tokens, wl.d_model, seed=1), dt)
+    tokens = wl.tokens
     with torch.no_grad():
-        for _ in range(warmup):
-            moe_oracle.moe_forward(x, params, wl.top_k)
+        t0 = time.perf_counter()
+        fwd(x_all)
+        first = time.perf_counter() - t0
+        total_calls = steps + max(warmup - 1, 0)
+        if first * total_calls > budget_s and tokens > 1024:
+            tokens = max(1024, int(tokens * budget_s / (first * total_calls)) // 1024 * 1024)
+        x = x_all[:tokens]
+        for _ in range(max(warmup - 1, 0)):
+            fwd(x)
         times = []
-        for _ in range(repeats):
+        for _ in range(steps):
             t0 = time.perf_counter()
-            moe_oracle.moe_forward(x, params, wl.top_k)
+            fwd(x)
             times.append(time.perf_counter() - t0)
-    return times, cores
+    sample = (f"all {tokens} tokens per step" if tokens == wl.tokens else
+              f"first {tokens} of {wl.tokens} tokens per step (the whole batch would pass the time limit)")
+    sample += ", fp32 on bf16-rounded values" if wl.dtype == "bf16" else ", fp32"
+    return times, cores, kind, sample, tokens, why
 
 
 def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tokens = min(wl.tokens, CPU_SAMPLE_TOKENS)
-    times, cores = cpu_baseline(wl, tokens, args.steps, args.warmup)
+    times, cores, kind, sample, tokens, why = cpu_arm(wl, args.steps, args.warmup, CPU_ARM_BUDGET_S)
     total = sum(times)
     value = tokens * args.steps / total
-    sample = f"first {tokens} of {wl.tokens} tokens per step, fp32 on bf16-rounded values"
     line = {
         "impl": "reference", "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
+        "scaling": "strong" if (args.gpus > 1 and wl.name == "c4") else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(wl, {"parallelism": "cpu"}),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": sample},
+        "config": workload_config(wl),
+        "run": {"parallelism": "cpu", "threads": cores},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind,
+                         "sample": sample, **({"why_port": why} if why else {})},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -209,24 +271,23 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args, wl):
-    import torch.distributed as dist
-    from gemmallm_b200 import MOE, _cabi, synthetic
-    from gemmallm_b200._cabi import lib, check
+def cpu_baseline_record(wl, reps):
+    times, cores, kind, sample, tokens, why = cpu_arm(wl, reps, 1, 30.0)
+    times.sort()
+    rec = {"value": tokens / times[len(times) // 2], "unit": "tokens/s", "cores": cores, "kind": kind,
+           "sample": f"{sample}, median of {reps}"}
+    if why:
+        rec["why_port"] = why
+    return rec
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: there is no CPU path")
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
 
-    dt = synthetic.torch_dtype(wl.dtype)
-    es = 2 if wl.dtype == "bf16" else 4
-    N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+# ---------------------------------------------------------------------------
+# our arm, one GPU (or token-sharded replicas)
+# ---------------------------------------------------------------------------
+
+def build_block(wl, dev, dt):
+    from gemmallm_b200 import MOE, synthetic
+    d, f, E, k = wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
     m = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda").eval()
     if E > 16:
         # many experts: draw them one at a time (same rule as the expert-parallel ranks)
@@ -244,8 +305,136 @@ def run_ours(args, wl):
     else:
         params = synthetic.make_params(d, E, f, seed=0, gate_bias_kind=wl.gate_bias)
         synthetic.load_into(m, params, dt, dev)
-        del params
-    m.flags = getattr(args, "flags", 0)
+    return m
+
+
+def clone_block(m, wl, dev, dt):
+    from gemmallm_b200 import MOE
+    r = MOE(wl.d_model, num_experts=wl.n_experts, d_ff=wl.d_ff, top_k=wl.top_k, device="cuda").eval()
+    r.to(device=dev, dtype=dt)
+    r.load_state_dict(m.state_dict())
+    return r
+
+
+def is_small_n(wl):
+    from gemmallm_b200._cabi import lib
+    return wl.dtype == "bf16" and wl.tokens * wl.top_k <= lib.moe_b200_decode_max_rows()
+
+
+def is_mid_n(wl):
+    return (wl.dtype == "bf16" and not is_small_n(wl) and wl.tokens * wl.top_k <= 4096
+            and wl.tokens <= 2048 and wl.n_experts <= 32)
+
+
+def streamed_bytes(m, wl, spec_all: bool):
+    """Algorithmic bytes of one small-N call: weights of the distinct experts hit (all of them
+    when the routing-independent kernel runs), router weights, x in, out."""
+    N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+    es = 2
+    hit = int((m.last["cnt_slot"].sum(0) > 0).sum())
+    wbytes = hit * (3 * d * f + 2 * f + d) * es
+    touched = (E if spec_all else hit) * (3 * d * f + 2 * f + d) * es
+    return hit, wbytes, wbytes + E * d * es + 2 * N * d * es, touched
+
+
+def time_streaming(replicas, make_replica, wl, x, steps, graphs=True):
+    """Device time per call of a small-N workload: the calls rotate over copies of the block so
+    that no call finds its weights in L2, several calls per CUDA graph (as a decoder that
+    captures all its layers would). Returns (ms per call, calls per graph, copies used)."""
+    N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+    m = replicas[0]
+    with torch.no_grad():
+        for _ in range(3):
+            m(x)
+    torch.cuda.synchronize()
+    spec_all = N * k >= 2 * E and is_small_n(wl)
+    _, _, _, touched = streamed_bytes(m, wl, spec_all)
+    n_rep = max(1, -(-int(2 * L2_BYTES) // touched))
+    while len(replicas) < n_rep:
+        replicas.append(make_replica())
+    use = replicas[:n_rep]
+    with torch.no_grad():
+        for r in use:
+            for _ in range(3):
+                r(x)
+    torch.cuda.synchronize()
+    per_graph = n_rep * max(1, 8 // n_rep)
+    graph = None
+    if graphs:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.no_grad(), torch.cuda.graph(graph):
+                for i in range(per_graph):
+                    use[i % n_rep](x)
+        except Exception as exc:
+            print(f"# CUDA graph capture failed ({exc}); timing eager calls", file=sys.stderr)
+            torch.cuda.synchronize()
+            graph = None
+
+    def eager():
+        with torch.no_grad():
+            for i in range(per_graph):
+                use[i % n_rep](x)
+
+    step = graph.replay if graph is not None else eager
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    reps = max(1, steps // per_graph)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * per_graph), per_graph, n_rep, graph is not None
+
+
+def decode_sweep(m, wl_main, dev, dt, hbm):
+    """The decode-shaped calls of the same block (1, 8, 32, 64 tokens): whole call, CUDA-event
+    time per call, algorithmic bytes over the measured HBM copy bandwidth."""
+    from gemmallm_b200 import synthetic
+    out = {}
+    replicas = [m]
+    for T in (1, 8, 32, 64):
+        wl = synthetic.WORKLOADS[f"c2_t{T}"]
+        if (wl.d_model, wl.d_ff, wl.n_experts, wl.top_k) != (wl_main.d_model, wl_main.d_ff,
+                                                             wl_main.n_experts, wl_main.top_k):
+            return None
+        x = synthetic.make_input(T, wl.d_model, seed=1).to(dt).to(dev).view(1, T, wl.d_model)
+        ms, per_graph, n_rep, graphed = time_streaming(
+            replicas, lambda: clone_block(m, wl, dev, dt), wl, x, 400)
+        for r in replicas:
+            if r.device_status() != 0:
+                raise RuntimeError(f"device status non-zero in the decode sweep at {T} tokens")
+        hit, wbytes, nbytes, _ = streamed_bytes(replicas[0], wl, False)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[f"t{T}"] = {"us": ms * 1e3, "bytes": nbytes, "experts_hit": hit, "gbs": gbs,
+                        "frac": gbs / hbm, "weight_copies_rotated": n_rep, "calls_per_graph": per_graph,
+                        "cuda_graph": graphed}
+    del replicas[1:]
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args, wl):
+    import torch.distributed as dist
+    from gemmallm_b200 import _cabi, synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU path")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dt = synthetic.torch_dtype(wl.dtype)
+    es = 2 if wl.dtype == "bf16" else 4
+    N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+    m = build_block(wl, dev, dt)
     # each rank owns its own token batch (seed differs per rank)
     x_host = synthetic.make_input(N, d, seed=1 + rank).to(dt).pin_memory()
     x = x_host.to(dev).view(1, N, d)
@@ -263,73 +452,32 @@ def run_ours(args, wl):
             return float(t)
         return ms
 
-    small_n = wl.dtype == "bf16" and N * k <= lib.moe_b200_decode_max_rows()
-    # between the decode and the prefill sizes: the streaming kernels on sorted rows
-    mid_n = (wl.dtype == "bf16" and not small_n and N * k <= 4096 and N <= 2048 and E <= 32
-             and not (getattr(args, "flags", 0) & _cabi.FLAG_NO_ROWS_PATH))
+    small_n, mid_n = is_small_n(wl), is_mid_n(wl)
     streaming = small_n or mid_n      # launch-bound from Python, bound by the weight stream on the GPU
-
-    def capture(fn):
-        """Small-N calls are launch-bound from Python: replay them as a CUDA graph."""
-        if not streaming or args.no_graph:
-            return None
-        try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                fn()
-            return g
-        except Exception as exc:  # capture unsupported: time eager calls instead
-            print(f"# CUDA graph capture failed ({exc}); timing eager calls", file=sys.stderr)
-            torch.cuda.synchronize()
-            return None
+    warm = max(args.warmup, 3)
 
     # ---- device-resident throughput -------------------------------------
-    replicas, steps_per_graph = [m], 1
-    with torch.no_grad():
-        for _ in range(max(args.warmup, 3)):
-            m(x)
-        torch.cuda.synchronize()
-        if streaming and not args.no_graph:
-            # A small-N step touches only the weights of the experts it hits, which can be less
-            # than the L2: rotate over copies of the block so that no step finds its weights
-            # cached by the step before, and put several steps into one graph, as a decoder
-            # that captures all its layers would (the gap between two graph launches is not
-            # the block's).
-            hit = int((m.last["cnt_slot"].sum(0) > 0).sum())
-            if N * k >= 2 * E and small_n:
-                hit = E      # the routing-independent kernel streams every expert
-            touched = hit * (3 * d * f + 2 * f + d) * es
-            n_rep = max(1, -(-int(2 * L2_BYTES) // touched))
-            for _ in range(n_rep - 1):
-                r = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda").eval()
-                r.to(device=dev, dtype=dt)
-                r.load_state_dict(m.state_dict())
-                r.flags = m.flags
-                replicas.append(r)
-            for r in replicas:
-                for _ in range(3):
-                    r(x)
-            torch.cuda.synchronize()
-            steps_per_graph = n_rep * max(1, 8 // n_rep)
-        graph = capture(lambda: [replicas[i % len(replicas)](x) for i in range(steps_per_graph)])
-        graph1 = capture(lambda: m(x)) if steps_per_graph > 1 else graph
-        if graph is None:
-            steps_per_graph = 1
-        step = graph.replay if graph is not None else (lambda: m(x))
-        step1 = graph1.replay if graph1 is not None else (lambda: m(x))
-        for _ in range(3):
-            step()
+    graphed, steps_per_graph, n_rep = False, 1, 1
+    if streaming:
         barrier()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clocks:
-            ev0.record()
-            for _ in range(args.steps // steps_per_graph):
-                step()
-            for _ in range(args.steps % steps_per_graph):
-                step1()
-            ev1.record()
+            ms_step, steps_per_graph, n_rep, graphed = time_streaming(
+                [m], lambda: clone_block(m, wl, dev, dt), wl, x, args.steps, graphs=not args.no_graph)
             barrier()
-        ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+        ms_total = max_over_ranks(ms_step * args.steps)
+    else:
+        with torch.no_grad():
+            for _ in range(warm):
+                m(x)
+            barrier()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(local) as clocks:
+                ev0.record()
+                for _ in range(args.steps):
+                    m(x)
+                ev1.record()
+                barrier()
+            ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     status = m.device_status()
     if status != 0:
         raise RuntimeError(f"device status {status} after the timed region")
@@ -340,7 +488,7 @@ def run_ours(args, wl):
         if rank == 0:
             print(json.dumps({"metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s",
                               "n_gpus": world, "steps": args.steps, "ms_per_step": ms_step,
-                              "quick": True, "config": workload_config(wl, {})}), flush=True)
+                              "quick": True, "config": workload_config(wl)}), flush=True)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -366,8 +514,15 @@ def run_ours(args, wl):
             for _ in range(2):
                 e2e_step()
             torch.cuda.synchronize()
-            e2e_graph = capture(e2e_step)
-            run_e2e = e2e_graph.replay if e2e_graph is not None else e2e_step
+            run_e2e = e2e_step
+            if not args.no_graph:
+                try:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        e2e_step()
+                    run_e2e = g.replay
+                except Exception:
+                    torch.cuda.synchronize()
             run_e2e()
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -375,7 +530,7 @@ def run_ours(args, wl):
             for _ in range(args.steps):
                 run_e2e()
                 torch.cuda.current_stream().synchronize()   # output and loss are on the host now
-                loss = float(aux_host[0])
+                _loss = float(aux_host[0])
             e1.record()
             barrier()
             e2e_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -388,12 +543,11 @@ def run_ours(args, wl):
     e2e_value = N * world * args.steps / (e2e_ms * 1e-3)
 
     # ---- per-stage times through the stage entry points --------------------
-    two_pass = bool(m.flags & _cabi.FLAG_DECODE_TWO_PASS)
-    stage_ms, launches_per_step = {}, ((4 if two_pass else 3) if small_n else (3 if mid_n else 5))
+    launches_per_step = 3 if streaming else 5
+    stage_ms = {}
     if rank == 0:
         stage_ms = time_stages(m, x.view(N, d), wl, dev, small_n, mid_n=mid_n)
     peaks, peak_kind = load_peaks()
-    line = None
     if rank == 0:
         flops = 6.0 * k * d * f * N
         t_gemm = stage_ms["experts"] * 1e-3
@@ -406,26 +560,25 @@ def run_ours(args, wl):
             "combine": N * k * d * es + N * d * es + N * k * 8,
         }
         stage_bytes = {n: b for n, b in stage_bytes.items() if n in stage_ms}
+        traffic, traffic_source = NCU_TRAFFIC.get(wl.name, (None, None))
         line = {
             "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic",
-            "config": workload_config(wl, {
-                "parallelism": "single" if world == 1 else f"tokens sharded over {world} ranks, experts replicated",
-                "l2": ("working set per step (expert weights streamed once per step) exceeds the 126 MB L2"
-                       if len(replicas) == 1 else
-                       f"{len(replicas)} copies of the block's weights used in rotation: the weights one step "
-                       "touches were evicted by the steps in between (together over twice the 126 MB L2)"),
-                "cuda_graph": graph is not None, "steps_per_graph": steps_per_graph}),
+            "config": workload_config(wl),
+            "run": {"parallelism": "single" if world == 1 else f"tokens sharded over {world} ranks, experts replicated",
+                    "cuda_graph": graphed, "steps_per_graph": steps_per_graph,
+                    "weight_copies_rotated": n_rep},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": N * d * es,
                     "d2h_bytes_per_step": N * d * es + 4, "ms_per_step": e2e_ms / args.steps,
                     "mode": e2e_mode},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
-            "roofline": {"kernel": "grouped_gemm_tc2_kernel (GEGLU pass + down pass, CTA pairs)",
+            "roofline": {"kernel": "grouped_gemm_tc2_kernel (GEGLU pass + down pass, CTA pairs)"
+                                   if wl.dtype == "bf16" else "grouped_ffn_kernel<float> (CUDA cores)",
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
+                         "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source,
                          "peak_source": f"{peak_kind} bf16 burst", "flops_per_step": flops,
                          "ms": stage_ms["experts"]},
             "stages_ms": stage_ms,
@@ -434,32 +587,89 @@ def run_ours(args, wl):
                            for n, b in stage_bytes.items()},
         }
         if streaming:
-            # weight streaming: bytes of the distinct experts hit, plus router weights, x in, out
-            hit = int((m.last["cnt_slot"].sum(0) > 0).sum())
-            wbytes = hit * (3 * d * f + 2 * f + d) * es
-            nbytes_step = wbytes + E * d * es + 2 * N * d * es
+            hit, wbytes, nbytes_step, _ = streamed_bytes(m, wl, False)
             gbs_step = nbytes_step / (ms_step * 1e-3) / 1e9
             gbs_experts = wbytes / (stage_ms["experts"] * 1e-3) / 1e9
             line["roofline"] = {
                 "kernel": ("decode_spec_kernel / decode_fused_kernel (GEGLU + split-K down tiles, one launch)"
                            if small_n else "decode_spec_kernel<SORTED> (GEGLU + split-K down tiles on sorted rows)"),
                 "bound": "hbm", "achieved": gbs_experts, "peak": hbm, "unit": "GB/s",
-                "frac": gbs_experts / hbm, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
+                "frac": gbs_experts / hbm, "traffic": traffic, "traffic_source": traffic_source,
                 "peak_source": f"{peak_kind} copy",
                 "bytes_per_step": wbytes, "experts_hit": hit, "ms": stage_ms["experts"],
                 "whole_step_gbs": gbs_step, "whole_step_frac": gbs_step / hbm}
+        if world == 1 and wl.name == "c1_uniform" and not args.no_extras:
+            # the other single-GPU records of the default run: the decode-shaped calls of this
+            # block, and the expert-parallel workload on this one GPU (the same-workload
+            # denominator of the multi-GPU speed-ups)
+            line["c2"] = decode_sweep(m, wl, dev, dt, hbm)
+            del m, x
+            torch.cuda.empty_cache()
+            line["c4_one_gpu"] = one_gpu_record(synthetic.WORKLOADS["c4"], dev, peak)
         if world == 1 and not args.no_cpu_baseline:
-            tokens = min(N, CPU_SAMPLE_TOKENS)
-            times, cores = cpu_baseline(wl, tokens, 3 if N > 256 else 20, 1)
-            times.sort()
-            line["cpu_baseline"] = {
-                "value": tokens / times[len(times) // 2], "unit": "tokens/s", "cores": cores,
-                "kind": "port",
-                "sample": f"first {tokens} of {N} tokens, median of 3, fp32 on bf16-rounded values"}
+            line["cpu_baseline"] = cpu_baseline_record(wl, 3 if N > 256 else 20)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def one_gpu_record(wl, dev, peak, steps=10):
+    """A workload's block on this one GPU, device-resident: ms per step, tokens/s and the
+    grouped GEMMs' share of the tensor peak."""
+    from gemmallm_b200 import synthetic
+    dt = synthetic.torch_dtype(wl.dtype)
+    N, d, f, k = wl.tokens, wl.d_model, wl.d_ff, wl.top_k
+    m = build_block(wl, dev, dt)
+    x = synthetic.make_input(N, d, seed=1).to(dt).to(dev).view(1, N, d)
+    with torch.no_grad():
+        for _ in range(3):
+            m(x)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            m(x)
+        t1.record()
+        torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    if m.device_status() != 0:
+        raise RuntimeError("device status non-zero")
+    st = time_stages(m, x.view(N, d), wl, dev, reps=5)
+    tf = 6.0 * k * d * f * N / (st["experts"] * 1e-3) / 1e12
+    return {"workload": wl.name, "ms_per_step": ms, "tokens_per_s": N / (ms * 1e-3),
+            "experts_ms": st["experts"], "experts_tflops": tf, "experts_frac": tf / peak}
+
+
+# ---------------------------------------------------------------------------
+# our arm, expert-parallel workload under torchrun
+# ---------------------------------------------------------------------------
+
+def ep_parity(m, x_host_f32, out, wl, rank, tokens=1024):
+    """After the timed region: the first `tokens` tokens of this rank's last output against the
+    CPU oracle under the kernel's own logits (tokens are independent, model.py:201)."""
+    from gemmallm_b200 import synthetic
+    from oracle import moe_oracle
+    dt = synthetic.torch_dtype(wl.dtype)
+    d, f, E, k = wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+    n = min(tokens, x_host_f32.shape[0])
+    w1, w2 = [], []
+    for e in range(E):
+        pe = synthetic.make_expert(d, f, e, 0)
+        w1.append(synthetic.round_to(pe["w1"], dt))
+        w2.append(synthetic.round_to(pe["w2"], dt))
+    gate_w, gate_b = synthetic.make_gate(d, E, 0, wl.gate_bias)
+    params = {"gate_w": synthetic.round_to(gate_w, dt), "gate_b": synthetic.round_to(gate_b, dt),
+              "w1": w1, "b1": torch.zeros(E, 2 * f), "w2": w2, "b2": torch.zeros(E, d)}
+    logits = m.last["logits"][:n].float().cpu()
+    with torch.no_grad():
+        o = moe_oracle.moe_forward(x_host_f32[:n], params, k, logits=logits)
+    good = ~moe_oracle.tie_rows(o["probs"], k)
+    idx_equal = bool(torch.equal(m.last["idx"][:n].cpu()[good].long(), o["idx"][good]))
+    got = out.view(-1, d)[:n].float().cpu()
+    err = float((got - o["out"])[good].abs().max())
+    bound = 2e-2 * float(o["out"].abs().max())
+    return idx_equal, err, bound
 
 
 def run_ep(args, wl):
@@ -493,7 +703,6 @@ def run_ep(args, wl):
         replicate = prior.topk(min(args.ep_replicate, E)).indices.tolist()
     m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement,
                           replicate=replicate).eval()
-    m.flags = args.ep_flags
     m.to(device=dev, dtype=dt)
     gate_w, gate_b = synthetic.make_gate(d, E, 0, wl.gate_bias)
     with torch.no_grad():
@@ -506,7 +715,8 @@ def run_ep(args, wl):
             ex.down.weight.copy_(p["w2"])
             ex.gate_and_up.bias.zero_()
             ex.down.bias.zero_()
-    x_host = synthetic.make_input(Nl, d, seed=1 + rank).to(dt).pin_memory()
+    x_f32 = synthetic.round_to(synthetic.make_input(Nl, d, seed=1 + rank), dt)
+    x_host = x_f32.to(dt).pin_memory()
     x = x_host.to(dev).view(1, Nl, d)
     out_host = torch.empty(Nl, d, dtype=dt).pin_memory()
     aux_host = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -520,32 +730,67 @@ def run_ep(args, wl):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
     with torch.no_grad():
         for _ in range(max(args.warmup, 3)):
-            m(x)
+            out, _aux = m(x)
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clocks:
             ev0.record()
             for _ in range(args.steps):
-                m(x)
+                out, _aux = m(x)
             ev1.record()
             barrier()
         ms_total = max_over_ranks(ev0.elapsed_time(ev1))
         status = max_over_ranks(float(m.device_status()))
         if status != 0:
             raise RuntimeError(f"device status {status} after the timed region")
+        if args.quick:
+            if rank == 0:
+                print(json.dumps({"metric": "moe_tokens_per_s", "value": N * args.steps / (ms_total * 1e-3),
+                                  "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                                  "ms_per_step": ms_total / args.steps, "quick": True,
+                                  "config": workload_config(wl)}), flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            return
+        # parity of what was just timed, outside the timed region
+        idx_equal, err, bound = ep_parity(m, x_f32, out, wl, rank)
+        par = torch.tensor([1.0 if (idx_equal and err <= bound) else 0.0, 1.0 if idx_equal else 0.0,
+                            err / bound], device=dev)
+        pars = [torch.empty_like(par) for _ in range(world)]
+        dist.all_gather(pars, par)
+        # per-stage times (events recorded by the library at the stage boundaries)
+        barrier()
+        stages = m.time_stages(x, reps=10)
+        st = torch.tensor([stages[n] for n in _cabi.EP_STAGES], device=dev)
+        sts = [torch.empty_like(st) for _ in range(world)]
+        dist.all_gather(sts, st)
+        # the same exchange through NCCL all_to_all_single (host-side baseline)
+        for _ in range(3):
+            m.forward_nccl(x)
+        nccl_ms = timed(lambda: m.forward_nccl(x), max(5, args.steps // 2)) / max(5, args.steps // 2)
         # end to end: pinned host input in, output and loss back, every step (pipelined)
         barrier()
         e2e_ms = max_over_ranks(pipelined_e2e(m, x_host, out_host, aux_host, Nl, d, dt, dev, args.steps))
         barrier()
         # grouped GEMMs alone on this rank's received rows
         rows = int(m.last["offsets_local"][-1])
-        st = m._state
-        recv_x = st["hdl"].buffer_ptrs[rank] + st["symm_layout"]["recv_x"]
-        hbuf = st["ws_base"] + st["ws_layout"]["h"]
-        offs = st["ws_base"] + st["ws_layout"]["offsets_local"]
-        stat = st["ws_base"] + st["ws_layout"]["status"]
+        stt = m._state
+        recv_x = stt["hdl"].buffer_ptrs[rank] + stt["symm_layout"]["recv_x"]
+        hbuf = stt["ws_base"] + stt["ws_layout"]["h"]
+        offs = stt["ws_base"] + stt["ws_layout"]["offsets_local"]
+        stat = stt["ws_base"] + stt["ws_layout"]["status"]
         ybuf = torch.empty(max(rows, 1), d, dtype=dt, device=dev)
         s_ = torch.cuda.current_stream(dev).cuda_stream
         call = lambda: lib.moe_b200_experts(recv_x, offs, m._plan.base, rows, d, f, len(m.local_ids),
@@ -563,54 +808,33 @@ def run_ep(args, wl):
     info = torch.tensor([float(rows), gemm_ms], device=dev)
     gathered = [torch.empty_like(info) for _ in range(world)]
     dist.all_gather(gathered, info)
-    single = None
-    if rank == 0 and not args.quick:
+    single, cpu_rec = None, None
+    peaks, peak_kind = load_peaks()
+    peak = float(peaks["bf16_tflops"])
+    if rank == 0:
         # the same workload on this one GPU (all experts local, no exchange), for the speed-up
-        from gemmallm_b200 import MOE
         del m
         torch.cuda.empty_cache()
-        m1 = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda").eval()
-        m1.to(device=dev, dtype=dt)
-        with torch.no_grad():
-            m1.gate.weight.copy_(gate_w)
-            m1.gate.bias.copy_(gate_b)
-            for e, ex in enumerate(m1.experts):
-                pe = synthetic.make_expert(d, f, e, 0)
-                ex.gate_and_up.weight.copy_(pe["w1"])
-                ex.down.weight.copy_(pe["w2"])
-                ex.gate_and_up.bias.zero_()
-                ex.down.bias.zero_()
-            x1 = synthetic.make_input(N, d, seed=1).to(dt).to(dev).view(1, N, d)
-            for _ in range(3):
-                m1(x1)
-            torch.cuda.synchronize()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record()
-            for _ in range(10):
-                m1(x1)
-            t1.record()
-            torch.cuda.synchronize()
-            single = t0.elapsed_time(t1) / 10
-        del m1, x1
+        single = one_gpu_record(wl, dev, peak)
+        if not args.no_cpu_baseline:
+            cpu_rec = cpu_baseline_record(wl, 1)
     if rank == 0:
-        peaks, peak_kind = load_peaks()
-        peak = float(peaks["bf16_tflops"])
         es = 2
         per_rank = [{"rows": int(g[0]), "gemm_ms": float(g[1]),
                      "tflops": 6.0 * d * f * float(g[0]) / (float(g[1]) * 1e-3) / 1e12} for g in gathered]
         busiest = max(per_rank, key=lambda r: r["gemm_ms"])
         share = max(r["rows"] for r in per_rank) / float(N * k)
         ms_step = ms_total / args.steps
+        ranks_ok = int(sum(float(p[0]) for p in pars))
         line = {
             "metric": "moe_tokens_per_s", "value": N * args.steps / (ms_total * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": workload_config(wl, {
-                "parallelism": f"ep{world}: tokens and experts sharded over {world} ranks, "
-                               f"{args.ep_placement} expert placement, {args.ep_replicate} hottest experts copied to every rank, "
-                               "peer-store all-to-all",
-                "l2": "per-rank working set (received rows, h, owned expert weights) exceeds the 126 MB L2"}),
+            "config": workload_config(wl),
+            "run": {"parallelism": f"ep{world}: tokens and experts sharded over {world} ranks, "
+                                   f"{args.ep_placement} expert placement, {args.ep_replicate} hottest experts "
+                                   "copied to every rank, peer-store all-to-all inside the kernels"},
             "e2e": {"value": N * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": Nl * d * es * world, "d2h_bytes_per_step": (Nl * d * es + 4) * world,
                     "ms_per_step": e2e_ms / args.steps,
@@ -621,15 +845,34 @@ def run_ep(args, wl):
                          "bound": "tensor", "achieved": busiest["tflops"], "peak": peak,
                          "unit": "TFLOP/s", "frac": busiest["tflops"] / peak, "traffic": None,
                          "peak_source": f"{peak_kind} bf16 burst", "ms": busiest["gemm_ms"]},
+            "parity": {"checked": "first 1024 tokens of every rank's last timed output against the CPU "
+                                  "oracle under the kernel's logits",
+                       "idx_equal": all(float(p[1]) == 1.0 for p in pars),
+                       "max_abs_over_bound": max(float(p[2]) for p in pars),
+                       "bound": "2e-2 * max|reference|", "ranks_ok": ranks_ok},
+            "stages_ms": {"rank0": {n: float(sts[0][i]) for i, n in enumerate(_cabi.EP_STAGES)},
+                          "max_over_ranks": {n: max(float(s[i]) for s in sts)
+                                             for i, n in enumerate(_cabi.EP_STAGES)}},
+            "nccl_baseline": {"ms_per_step": nccl_ms, "tokens_per_s": N / (nccl_ms * 1e-3),
+                              "what": "same router, expert and combine kernels; dispatch and return as "
+                                      "torch.distributed all_to_all_single with host-side split sizes"},
             "ep": {"per_rank": per_rank, "max_rank_share_of_rows": share,
                    "balance_limited_speedup": 1.0 / share,
                    "gemm_ms_over_step_ms": busiest["gemm_ms"] / ms_step,
-                   "same_workload_on_one_gpu_ms_per_step": single,
-                   "speedup_vs_one_gpu": (single / ms_step) if single else None},
+                   "same_workload_on_one_gpu": single,
+                   "speedup_vs_one_gpu": (single["ms_per_step"] / ms_step) if single else None},
         }
+        if cpu_rec:
+            line["cpu_baseline"] = cpu_rec
         print(json.dumps(line), flush=True)
+        if ranks_ok != world:
+            print(f"# parity failed on {world - ranks_ok} rank(s)", file=sys.stderr)
+    ok = torch.tensor([1.0 if (idx_equal and err <= bound) else 0.0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     dist.barrier()
     dist.destroy_process_group()
+    if float(ok) != 1.0:
+        sys.exit(1)
 
 
 def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: bool = False):
@@ -655,33 +898,29 @@ def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: b
                                                   p["row_of"], p["perm"], p["psum_part"], p["psum"],
                                                   p["aux"], p["status"], s),
         "experts": lambda: lib.moe_b200_experts(p["perm"], p["offsets"], plan, N * k, d, f, E, code,
-                                                m.flags, p["h"], p["y"], p["status"], s),
+                                                0, p["h"], p["y"], p["status"], s),
         "combine": lambda: lib.moe_b200_combine(p["y"], p["row_of"], p["w"], None, N, d, k, code,
                                                 out.data_ptr(), s),
     }
     if small_n:
         # the small-N path replaces router + dispatch by one single-block launch
-        if lib.moe_b200_front_small(x2d.data_ptr(), gw.data_ptr(), gb.data_ptr(), N, d, E, k, code,
-                                    p["logits"], p["idx"], p["w"], p["cnt_slot"], p["offsets"],
-                                    p["row_of"], p["perm"], p["psum"], p["aux"], s) == 0:
+        front = lambda: lib.moe_b200_front_small(
+            x2d.data_ptr(), gw.data_ptr(), gb.data_ptr(), N, d, E, k, code, p["logits"], p["idx"],
+            p["w"], p["cnt_slot"], p["offsets"], p["row_of"], p["perm"], p["psum"], p["aux"], s)
+        if front() == 0:
             del calls["router"], calls["dispatch"]
-            calls = {"front": lambda: lib.moe_b200_front_small(
-                x2d.data_ptr(), gw.data_ptr(), gb.data_ptr(), N, d, E, k, code, p["logits"], p["idx"],
-                p["w"], p["cnt_slot"], p["offsets"], p["row_of"], p["perm"], p["psum"], p["aux"], s),
-                **calls}
+            calls = {"front": front, **calls}
         splits = lib.moe_b200_decode_splits(f)
         ready = p["status"] + 4 * _cabi.READY_OFFSET
         calls["experts"] = lambda: lib.moe_b200_experts_decode_fused(
             p["perm"], p["offsets"], plan, N * k, d, f, E, p["h"], p["part"], ready, p["status"], s)
-        if N * k >= 2 * E and N <= 128 and E <= 32 and not (m.flags & (_cabi.FLAG_DECODE_NO_SPEC | _cabi.FLAG_DECODE_TWO_PASS)):
+        if N * k >= 2 * E and N <= 128 and E <= 32:
             # the kernel the forward uses when most experts are hit (timed here without its overlap
             # with the routing kernel); "experts_sorted" is the kernel for a few hit experts
             calls["experts_sorted"] = calls["experts"]
             calls["experts"] = lambda: lib.moe_b200_experts_decode_spec(
                 x2d.data_ptr(), p["idx"], p["offsets"], plan, N, k, d, f, E, p["h"], p["part"], ready,
                 p["status"], s)
-        calls["experts_two_pass"] = lambda: lib.moe_b200_experts_decode(
-            p["perm"], p["offsets"], plan, N * k, d, f, E, p["h"], p["part"], p["status"], s)
         calls["combine"] = lambda: lib.moe_b200_combine_decode(
             p["part"], splits, N * k, p["row_of"], p["idx"], p["w"], plan, E, None, N, d, k,
             out.data_ptr(), s)
@@ -715,6 +954,8 @@ def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: b
         e1.record()
         torch.cuda.synchronize()
         res[name] = e0.elapsed_time(e1) / reps
+    # the stage calls above share the workspace's status region with the forward: leave it clean
+    m._view("status", torch.int32, (_cabi.READY_OFFSET + _cabi.READY_INTS,)).zero_()
     return res
 
 
@@ -727,12 +968,13 @@ def main():
     ap.add_argument("--workload", default=None,
                     help="default: c1_uniform on one GPU, c4 (expert-parallel) on several")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="one GPU, default workload: skip the decode-shaped sweep and the "
+                         "expert-parallel workload on this GPU")
     ap.add_argument("--ep-placement", default="strided", choices=["strided", "lpt"])
     ap.add_argument("--ep-replicate", type=int, default=16,
                     help="expert-parallel: copy the N most popular experts (by the router-bias prior) "
                          "to every rank, on top of the even sharding; 0 = no copies")
-    ap.add_argument("--ep-flags", type=int, default=0, help="flags for moe_b200_ep_forward")
-    ap.add_argument("--flags", type=int, default=0, help="flags for moe_b200_forward (one GPU)")
     ap.add_argument("--no-graph", action="store_true", help="small-N workloads: time eager calls")
     ap.add_argument("--quick", action="store_true",
                     help="device-resident loop only (for profiler captures): no end-to-end leg, "

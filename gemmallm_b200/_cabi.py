@@ -7,19 +7,13 @@ fallback and importing this module raises. Build it with
 from __future__ import annotations
 
 import ctypes as C
-import os
 from pathlib import Path
 
-# MOE_B200_LIB selects another build of the same library (e.g. an instrumented one)
-LIB_PATH = Path(os.environ.get("MOE_B200_LIB") or Path(__file__).resolve().parent / "libmoe_b200.so")
+LIB_PATH = Path(__file__).resolve().parent / "libmoe_b200.so"
+ABI_VERSION = 2
 
 F32, BF16 = 0, 1
-FLAG_DEFAULT, FLAG_SIMT_EXPERTS, FLAG_NO_DECODE_PATH, FLAG_EP_UNFUSED_RETURN = 0, 1, 2, 4
-FLAG_ONE_CTA = 8
-FLAG_DECODE_TWO_PASS = 16
-FLAG_DECODE_NO_SPEC = 32
-FLAG_WS_CLEAN = 64
-FLAG_NO_ROWS_PATH = 128
+FLAG_DEFAULT, FLAG_WS_CLEAN = 0, 1
 READY_OFFSET, READY_INTS = 64, 320
 DEV_OK, DEV_TIMEOUT, DEV_BAD_INDEX = 0, 1, 2
 
@@ -49,7 +43,6 @@ SIGNATURES = {
     "moe_b200_experts": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "moe_b200_front_small": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _vp, _vp]),
-    "moe_b200_experts_decode": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "moe_b200_front_small_split": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i] + [_vp] * 12 + [_vp]),
     "moe_b200_front_exchange_ints": (_i64, [_i64, _i, _i]),
     "moe_b200_experts_rows": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
@@ -68,8 +61,9 @@ SIGNATURES = {
     "moe_b200_ep_symm_layout": (_i, [_i64, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_ep_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),
     "moe_b200_ep_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
+    "moe_b200_ep_setup": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "moe_b200_ep_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
-                                 C.c_uint32, _i, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
+                                 C.c_uint32, _i, _i, _vp, _vp, _sz, _vp, _vp, _vp]),
     "moe_b200_read_status": (_i, [_vp, C.POINTER(C.c_int32), _vp]),
 }
 
@@ -88,7 +82,7 @@ def _load() -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
         fn.restype = res
         fn.argtypes = args
-    if lib.moe_b200_version() != 1:
+    if lib.moe_b200_version() != ABI_VERSION:
         raise MoeB200Error("libmoe_b200.so ABI version mismatch; rebuild it")
     return lib
 
@@ -118,9 +112,10 @@ def workspace_layout(N: int, d: int, f: int, E: int, k: int, dtype: int) -> dict
     return {name: int(arr[i]) for i, name in enumerate(WS_NAMES)}
 
 
+EP_STAGES = ("router", "dispatch", "arrived", "experts", "returned", "combine")
 EP_SYMM_NAMES = ("flags", "cnt_all", "recv_meta", "recv_x", "ret_y")
 EP_WS_NAMES = ("status", "logits", "idx", "w", "psum_part", "psum", "aux", "scratch", "cnt_slot0",
-               "offsets_local", "owner", "h", "y")
+               "offsets_local", "owner", "h")
 
 
 def ep_symm_layout(N_local: int, d: int, E: int, k: int, world: int) -> dict[str, int]:

@@ -190,12 +190,10 @@ int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
   if (M == 0) return 0;
   if (!perm || !offsets || !plan || !h || !y || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
   if (!aligned16(perm) || !aligned16(h) || !aligned16(y)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
-  if (dtype == MOE_B200_BF16 && !(flags & MOE_B200_FLAG_SIMT_EXPERTS)) {
-    if (flags & MOE_B200_FLAG_ONE_CTA)
-      return launch_experts_tc(perm, offsets, plan, M, d, f, E, h, y, status, (cudaStream_t)stream);
+  if (flags != 0) return set_error(MOE_B200_ERR_UNSUPPORTED, "flags must be 0");
+  if (dtype == MOE_B200_BF16)
     return launch_experts_tc2(perm, offsets, plan, M, d, f, E, h, y, nullptr, status,
                               (cudaStream_t)stream);
-  }
   return launch_experts_simt(perm, offsets, plan, M, d, f, E, dtype, h, y, (cudaStream_t)stream);
 }
 
@@ -261,18 +259,6 @@ int moe_b200_front_small_split(const void* x, const void* Wg, const void* bg, in
 int moe_b200_decode_splits(int f) { return f >= 8 ? decode_splits(f) : 0; }
 
 int64_t moe_b200_decode_max_rows(void) { return kDecodeMaxRows; }
-
-int moe_b200_experts_decode(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
-                            int d, int f, int E, void* h, float* part, int32_t* status,
-                            void* stream) {
-  int rc = check_shape(0, d, f, E, 1, MOE_B200_BF16);
-  if (rc) return rc;
-  if (M < 0 || M > kDecodeMaxRows) return set_error(MOE_B200_ERR_SHAPE, "M exceeds the small-N path's row limit");
-  if (M == 0) return 0;
-  if (!perm || !offsets || !plan || !h || !part || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
-  if (!aligned16(perm) || !aligned16(h) || !aligned16(part)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
-  return launch_experts_tc_decode(perm, offsets, plan, M, d, f, E, h, part, status, (cudaStream_t)stream);
-}
 
 int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                   int64_t M, int d, int f, int E, void* h, float* part,
@@ -355,17 +341,16 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   void* y = ws + off[MOE_B200_WS_Y];
   float* part = reinterpret_cast<float*>(ws + off[MOE_B200_WS_PART]);
   cudaStream_t s = (cudaStream_t)stream;
-  const bool small_n = dtype == MOE_B200_BF16 && N * k <= kDecodeMaxRows &&
-                       !(flags & (MOE_B200_FLAG_SIMT_EXPERTS | MOE_B200_FLAG_NO_DECODE_PATH));
+  if (flags & ~MOE_B200_FLAG_WS_CLEAN) return set_error(MOE_B200_ERR_UNSUPPORTED, "unknown flag");
+  // a size switch, not a backend switch: up to 256 rows the weight-streaming kernels
+  const bool small_n = dtype == MOE_B200_BF16 && N * k <= kDecodeMaxRows;
 
   // most experts hit: stream all of them without waiting for the routing
   const bool spec = small_n && front_small_supported(N, E, k, dtype) && decode_spec_supported(N, E, k) &&
-                    N * k >= 2 * (int64_t)E &&
-                    !(flags & (MOE_B200_FLAG_DECODE_TWO_PASS | MOE_B200_FLAG_DECODE_NO_SPEC));
+                    N * k >= 2 * (int64_t)E;
   // between the decode and the prefill sizes: the streaming kernel on the sorted rows
   const bool rows_path = dtype == MOE_B200_BF16 && !small_n && N * k <= kRowsPathMaxRows &&
-                         rows_supported(N * k, E) &&
-                         !(flags & (MOE_B200_FLAG_SIMT_EXPERTS | MOE_B200_FLAG_ONE_CTA | MOE_B200_FLAG_NO_ROWS_PATH));
+                         rows_supported(N * k, E);
   const bool counters = small_n || rows_path;
   // status words, and the completion counters behind them where a kernel uses them, in one memset
   if (!(counters && (flags & MOE_B200_FLAG_WS_CLEAN)))
@@ -387,9 +372,7 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   }
   if (small_n) {
     // few tokens per expert: weight streaming with narrow tiles and split-K
-    if (flags & MOE_B200_FLAG_DECODE_TWO_PASS)
-      rc = moe_b200_experts_decode(perm, offsets, plan, N * k, d, f, E, h, part, status, stream);
-    else if (spec)
+    if (spec)
       rc = launch_experts_tc_decode_spec(x, idx, offsets, plan, N, k, d, f, E, h, part,
                                          status + MOE_B200_READY_OFFSET, status, s);
     else
@@ -407,7 +390,7 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
     return moe_b200_combine_decode(part, ks, N * k, row_of, idx, w, plan, E, residual, N, d, k, out,
                                    stream);
   }
-  rc = moe_b200_experts(perm, offsets, plan, N * k, d, f, E, dtype, flags, h, y, status, stream);
+  rc = moe_b200_experts(perm, offsets, plan, N * k, d, f, E, dtype, 0, h, y, status, stream);
   if (rc) return rc;
   return moe_b200_combine(y, row_of, w, residual, N, d, k, dtype, out, stream);
 }

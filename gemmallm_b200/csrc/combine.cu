@@ -47,14 +47,6 @@ combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ row_of,
   store8(out + t * d + c, acc);
 }
 
-#ifdef MOE_TIMELINE
-__device__ unsigned long long g_comb_tl[4];
-__device__ __forceinline__ unsigned long long comb_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#endif
 
 // Small-N variant: the down product arrives as `ksplit` fp32 partial buffers
 // part[s][M][d] without bias; sum them in order s = 0..ksplit-1, add the
@@ -67,14 +59,8 @@ combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_s
                       __nv_bfloat16* __restrict__ out) {
   const int pieces = d >> 3;
   const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-#ifdef MOE_TIMELINE
-  if (item == 0) { g_comb_tl[0] = comb_ns(); g_comb_tl[2] = 0; }
-#endif
   pdl_launch_dependents();   // the next kernel may become resident; it waits before it reads
   pdl_wait();
-#ifdef MOE_TIMELINE
-  if (item == 0) g_comb_tl[1] = comb_ns();
-#endif
   if (item >= N * pieces) return;
   const int64_t t = item / pieces;
   const int c = (int)(item - t * pieces) << 3;
@@ -119,9 +105,6 @@ combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_s
     for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
   }
   store8(out + t * d + c, acc);
-#ifdef MOE_TIMELINE
-  atomicMax(&g_comb_tl[2], comb_ns());
-#endif
 }
 
 }  // namespace
@@ -160,8 +143,3 @@ int launch_combine(const void* y, const int32_t* row_of, const float* w, const v
 
 }  // namespace moe
 
-#ifdef MOE_TIMELINE
-extern "C" int moe_b200_debug_combine_timeline(unsigned long long* h4) {
-  return (int)cudaMemcpyFromSymbol(h4, moe::g_comb_tl, sizeof(unsigned long long) * 4);
-}
-#endif

@@ -33,6 +33,32 @@ int cuda_error(cudaError_t e, const char* where);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Function attributes, occupancy results and SM counts belong to a device, and one
+// process may drive several: every cache of them is indexed by the device that is
+// current at the call.
+constexpr int kMaxDevices = 64;
+inline int device_slot(int* slot) {
+  int dev = 0;
+  MOE_CUDA_CHECK(cudaGetDevice(&dev));
+  *slot = (dev >= 0 && dev < kMaxDevices) ? dev : -1;
+  return 0;
+}
+struct PerDeviceOnce {
+  bool done[kMaxDevices] = {};
+};
+// Raise a kernel's dynamic shared-memory limit once per device.
+template <typename Fn>
+inline int ensure_dynamic_smem(PerDeviceOnce& once, Fn fn, size_t bytes) {
+  int slot = -1;
+  int rc = device_slot(&slot);
+  if (rc) return rc;
+  if (slot < 0 || !once.done[slot]) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (slot >= 0) once.done[slot] = true;
+  }
+  return 0;
+}
+
 // ---- device helpers -------------------------------------------------------
 
 template <typename T> struct Vec8;  // 8 consecutive elements of a row, as fp32
@@ -205,8 +231,6 @@ int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, 
                     cudaStream_t s);
 int launch_experts_simt(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
                         int d, int f, int E, int dtype, void* h, void* y, cudaStream_t s);
-int launch_experts_tc(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
-                      int f, int E, void* h, void* y, int32_t* status, cudaStream_t s);
 int launch_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
                    int64_t N, int d, int k, int dtype, void* out, cudaStream_t s);
 int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, int E, int d, int f,
@@ -214,9 +238,6 @@ int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, i
 int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                        int f, int E, void* h, void* y, const EpScatter* sc, int32_t* status,
                        cudaStream_t s);
-int launch_experts_tc_ep(const void* recv_x, const int32_t* offsets, const void* plan, int64_t cap,
-                         int d, int f, int E_local, void* h, const EpScatter& sc, int32_t* status,
-                         cudaStream_t s);
 int64_t ep_scratch_ints(int64_t N, int EV, int E);
 int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int EV, int k,
                        int dtype, const EpPeers& peers, int rank, int world, uint32_t epoch,
@@ -224,8 +245,6 @@ int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int 
                        const float* psum_part,
                        int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
                        int64_t n_total, int32_t* status, cudaStream_t s);
-int launch_ep_return(const void* y, const int32_t* offsets_local, int E_local, const EpScatter& sc,
-                     int d, cudaStream_t s);
 int launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, int where,
                    cudaStream_t s);
 int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint32_t epoch,
@@ -254,9 +273,6 @@ int launch_experts_tc_rows(const void* perm, const int32_t* offsets, const void*
 int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                    int64_t M, int d, int f, int E, void* h, float* part, int* ready,
                                    int32_t* status, cudaStream_t s, int spec = -1);
-int launch_experts_tc_decode(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
-                             int d, int f, int E, void* h, float* part, int32_t* status,
-                             cudaStream_t s);
 int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_t* row_of,
                           const int32_t* idx, const float* w, const void* plan, int E,
                           const void* residual, int64_t N, int d, int k, void* out, cudaStream_t s);

@@ -248,9 +248,6 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
   }
 }
 
-int g_sm_count = 0;
-int g_blocks_per_sm[2] = {0, 0};
-
 }  // namespace
 
 int64_t dispatch_scratch_ints(int64_t N, int E, int k) {
@@ -265,18 +262,15 @@ int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, 
       sizeof(int) * (size_t)(4 * E + 1 + k * E + kChunk * k) + sizeof(float) * kThreads;
   const int ti = dtype == MOE_B200_BF16 ? 1 : 0;
   const void* fn = ti ? (const void*)dispatch_kernel<__nv_bfloat16> : (const void*)dispatch_kernel<float>;
-  if (g_sm_count == 0) {
-    int dev = 0;
-    MOE_CUDA_CHECK(cudaGetDevice(&dev));
-    MOE_CUDA_CHECK(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
-  }
-  if (g_blocks_per_sm[ti] == 0) {
-    int per_sm = 0;
-    MOE_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
-    g_blocks_per_sm[ti] = per_sm < 1 ? 1 : per_sm;
-  }
-  int per_sm = g_blocks_per_sm[ti] > 2 ? 2 : g_blocks_per_sm[ti];
-  int64_t grid = (int64_t)g_sm_count * per_sm;
+  // a cooperative grid must be resident at once: SM count of the current device, and the
+  // occupancy for this call's shared-memory size (a host-side computation, no GPU work)
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc) return rc;
+  int per_sm = 0;
+  MOE_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 2 ? 2 : per_sm);
+  int64_t grid = (int64_t)sms * per_sm;
   if (grid > (int64_t)kNumSMs * 2) grid = (int64_t)kNumSMs * 2;
   int64_t nchunk = num_chunks(N);
   if (nchunk < 1) nchunk = 1;
@@ -314,7 +308,6 @@ int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, 
 namespace moe {
 namespace {
 constexpr int64_t kStaticScratchInts = 262144;  // 1 MiB
-constexpr int kMaxDevices = 64;
 static __device__ __align__(256) int32_t g_static_scratch[kStaticScratchInts];
 // g_static_scratch names a host-side shadow here; the device address has to be
 // asked for, once per device, with that device current.

@@ -16,7 +16,7 @@
 //      return address (source rank, pair id) with 16-byte peer stores; raises
 //      flag X on every destination.
 //   2. ep_wait_kernel on flag X; the grouped GEMMs run on the receive buffer
-//      (experts_tc.cu). The down pass stores its output rows straight into the
+//      (experts_tc2.cu). The down pass stores its output rows straight into the
 //      token owners' ret_y through peer pointers (scatter epilogue), so the
 //      return transfer overlaps the math tile by tile.
 //   3. ep_signal_kernel raises flag Y on every rank; ep_wait_kernel on flag Y;
@@ -107,9 +107,20 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
   const int row_ints = EV + 2 * E;                    // published row: pair counts, slot-0 counts, psum bits
 
   // ---- phase 1: per-chunk histograms --------------------------------------
-  for (int v = tid; v < EV; v += kThreads) s_owner[v] = owner[v];
-  for (int e = tid; e < E; e += kThreads) { s_slot0[e] = 0; s_vmap[e] = vmap[e * world + rank]; }
+  // the tables come from the workspace (moe_b200_ep_setup): an entry outside its range would
+  // turn into a wild peer store, so it is clamped and reported instead
   if (tid == 0) s_fail = 0;
+  for (int v = tid; v < EV; v += kThreads) {
+    int o = owner[v];
+    if ((unsigned)o >= (unsigned)world) { atomicMax(&status[0], MOE_B200_DEV_BAD_INDEX); o = rank; }
+    s_owner[v] = o;
+  }
+  for (int e = tid; e < E; e += kThreads) {
+    s_slot0[e] = 0;
+    int v = vmap[e * world + rank];
+    if ((unsigned)v >= (unsigned)EV) { atomicMax(&status[0], MOE_B200_DEV_BAD_INDEX); v = 0; }
+    s_vmap[e] = v;
+  }
   __syncthreads();
   for (int64_t c = blockIdx.x; c < nchunk; c += G) {
     for (int v = tid; v < EV; v += kThreads) s_hist[v] = 0;
@@ -304,23 +315,6 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
     st_release_sys(peers.flags[tid] + kEpFlagX * kEpMaxRanks + rank, epoch);
 }
 
-// Unfused return (MOE_B200_FLAG_EP_UNFUSED_RETURN): copy every received row's
-// output from the local sorted buffer to its token owner, one warp per row.
-__global__ void __launch_bounds__(256)
-ep_return_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ offsets_local, int E_local,
-                 const int32_t* __restrict__ meta, EpScatter sc, int row_pieces) {
-  const int rows = offsets_local[E_local];
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  for (int r = warp; r < rows; r += nwarps) {
-    const int m = __ldg(&meta[r]);
-    uint4* dst = reinterpret_cast<uint4*>(sc.ret_y[(m >> 24) & 7]) + (int64_t)(m & 0xffffff) * row_pieces;
-    const uint4* src = y + (int64_t)r * row_pieces;
-    for (int i = lane; i < row_pieces; i += 32) dst[i] = __ldg(src + i);
-  }
-  __threadfence_system();
-}
-
 __global__ void ep_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, int32_t* status,
                                int where) {
   if ((int)threadIdx.x < world) wait_flag(flags + threadIdx.x, epoch, status, where);
@@ -331,9 +325,6 @@ __global__ void ep_signal_kernel(EpPeers peers, int which, int rank, int world, 
   if ((int)threadIdx.x < world)
     st_release_sys(peers.flags[threadIdx.x] + which * kEpMaxRanks + rank, epoch);
 }
-
-int g_sm_count = 0;
-int g_blocks_per_sm = 0;
 
 }  // namespace
 
@@ -350,17 +341,15 @@ int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int 
   const int row_pieces = d * (dtype == MOE_B200_BF16 ? 2 : 4) / 16;
   const size_t smem = sizeof(int) * (size_t)(5 * EV + 2 * E + 2 * kChunk * k + world * EV + kThreads);
   const void* fn = (const void*)ep_dispatch_kernel;
-  if (g_sm_count == 0) {
-    int dev = 0;
-    MOE_CUDA_CHECK(cudaGetDevice(&dev));
-    MOE_CUDA_CHECK(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
-  }
-  if (g_blocks_per_sm == 0) {
-    int per_sm = 0;
-    MOE_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
-    g_blocks_per_sm = per_sm < 1 ? 1 : per_sm;
-  }
-  int64_t grid = (int64_t)g_sm_count * (g_blocks_per_sm > 2 ? 2 : g_blocks_per_sm);
+  // a cooperative grid must be resident at once: SM count of the current device, occupancy
+  // for this call's shared-memory size
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc) return rc;
+  int per_sm = 0;
+  MOE_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 2 ? 2 : per_sm);
+  int64_t grid = (int64_t)sms * per_sm;
   if (grid > (int64_t)kNumSMs * 2) grid = (int64_t)kNumSMs * 2;
   int64_t nchunk = (N + kChunk - 1) / kChunk;
   if (nchunk < 1) nchunk = 1;
@@ -375,14 +364,6 @@ int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int 
                   (void*)&psum_global, (void*)&offsets_local, (void*)&aux, (void*)&n_total,
                   (void*)&status};
   MOE_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem, s));
-  return 0;
-}
-
-int launch_ep_return(const void* y, const int32_t* offsets_local, int E_local, const EpScatter& sc,
-                     int d, cudaStream_t s) {
-  ep_return_kernel<<<kNumSMs * 8, 256, 0, s>>>(static_cast<const uint4*>(y), offsets_local, E_local,
-                                               sc.meta, sc, d * 2 / 16);
-  MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
 

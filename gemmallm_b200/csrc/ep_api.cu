@@ -58,7 +58,6 @@ void ws_layout(int64_t N_local, int d, int f, int E, int k, int world, size_t* o
   sizes[MOE_B200_EP_WS_OFFSETS_LOCAL] = (size_t)(kMaxExperts + 1) * sizeof(int32_t);
   sizes[MOE_B200_EP_WS_OWNER] = (size_t)(kMaxExperts + E * kEpMaxRanks) * sizeof(int32_t);  // owner[EV], vmap[E][world]
   sizes[MOE_B200_EP_WS_H] = cap * f * 2;
-  sizes[MOE_B200_EP_WS_Y] = cap * d * 2;
   size_t pos = 0;
   for (int i = 0; i < MOE_B200_EP_WS_NUM; ++i) {
     off[i] = pos;
@@ -107,26 +106,51 @@ int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, in
   return 0;
 }
 
-int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
-                        const void* residual, int64_t N_local, int d, int f, int E, int k,
-                        int dtype, int flags, int rank, int world, uint32_t epoch, int EV,
-                        const int32_t* h_owner, const int32_t* h_vmap, void* const* h_symm_bases,
-                        void* workspace, size_t workspace_bytes, void* out, void* stream) {
-  int rc = ep_check(N_local, d, f, E, k, dtype, rank, world);
+int moe_b200_ep_setup(const int32_t* h_owner, const int32_t* h_vmap, int64_t N_local, int d, int f,
+                      int E, int k, int world, int EV, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+  int rc = ep_check(N_local, d, f, E, k, MOE_B200_BF16, 0, world);
   if (rc) return rc;
-  if (!h_owner || !h_vmap || !h_symm_bases || !workspace) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!h_owner || !h_vmap || !workspace) return set_error(MOE_B200_ERR_NULL, "NULL argument");
   if (EV < E || EV > kMaxExperts) return set_error(MOE_B200_ERR_SHAPE, "EV must be in [E, 256]");
-  if (N_local > 0 && (!x || !Wg || !bg || !out)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
-  if (epoch == 0) return set_error(MOE_B200_ERR_SHAPE, "epoch must start at 1 and grow by one per call");
-  int E_local = 0;
-  for (int v = 0; v < EV; ++v) {
+  for (int v = 0; v < EV; ++v)
     if (h_owner[v] < 0 || h_owner[v] >= world)
       return set_error(MOE_B200_ERR_SHAPE, "expert owner out of range");
-    if (h_owner[v] == rank) ++E_local;
-  }
   for (int i = 0; i < E * world; ++i)
     if (h_vmap[i] < 0 || h_vmap[i] >= EV)
       return set_error(MOE_B200_ERR_SHAPE, "virtual expert id out of range");
+  size_t wo[MOE_B200_EP_WS_NUM], wtotal;
+  ws_layout(N_local, d, f, E, k, world, wo, &wtotal);
+  if (workspace_bytes < wtotal) return set_error(MOE_B200_ERR_WORKSPACE, "workspace too small");
+  if ((uintptr_t)workspace & 1023) return set_error(MOE_B200_ERR_ALIGN, "workspace must be 1024-byte aligned");
+  char* ws = static_cast<char*>(workspace);
+  cudaStream_t s = (cudaStream_t)stream;
+  int32_t tab[kMaxExperts + kMaxExperts * kEpMaxRanks];
+  memset(tab, 0, sizeof(tab));
+  memcpy(tab, h_owner, sizeof(int32_t) * EV);
+  memcpy(tab + kMaxExperts, h_vmap, sizeof(int32_t) * E * world);
+  MOE_CUDA_CHECK(cudaMemsetAsync(ws + wo[MOE_B200_EP_WS_STATUS], 0, 16 * sizeof(int32_t), s));
+  MOE_CUDA_CHECK(cudaMemcpyAsync(ws + wo[MOE_B200_EP_WS_OWNER], tab,
+                                 sizeof(int32_t) * (kMaxExperts + E * world), cudaMemcpyHostToDevice, s));
+  // `tab` lives on this stack frame
+  MOE_CUDA_CHECK(cudaStreamSynchronize(s));
+  return 0;
+}
+
+int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
+                        const void* residual, int64_t N_local, int d, int f, int E, int k,
+                        int dtype, int flags, int rank, int world, uint32_t epoch, int EV,
+                        int E_local, void* const* h_symm_bases,
+                        void* workspace, size_t workspace_bytes, void* out,
+                        void* const* h_stage_events, void* stream) {
+  int rc = ep_check(N_local, d, f, E, k, dtype, rank, world);
+  if (rc) return rc;
+  if (!h_symm_bases || !workspace) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (flags != 0) return set_error(MOE_B200_ERR_UNSUPPORTED, "flags must be 0");
+  if (EV < E || EV > kMaxExperts) return set_error(MOE_B200_ERR_SHAPE, "EV must be in [E, 256]");
+  if (E_local < 0 || E_local > EV) return set_error(MOE_B200_ERR_SHAPE, "E_local must be in [0, EV]");
+  if (N_local > 0 && (!x || !Wg || !bg || !out)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (epoch == 0) return set_error(MOE_B200_ERR_SHAPE, "epoch must start at 1 and grow by one per call");
   if (E_local > 0 && !plan_local) return set_error(MOE_B200_ERR_NULL, "plan_local is NULL");
   size_t so[MOE_B200_EP_SYMM_NUM], wo[MOE_B200_EP_WS_NUM], stotal, wtotal;
   symm_layout(N_local, d, E, k, world, so, &stotal);
@@ -155,68 +179,48 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
   int32_t* scratch = reinterpret_cast<int32_t*>(ws + wo[MOE_B200_EP_WS_SCRATCH]);
   int32_t* cnt_slot0 = reinterpret_cast<int32_t*>(ws + wo[MOE_B200_EP_WS_CNT_SLOT0]);
   int32_t* offsets_local = reinterpret_cast<int32_t*>(ws + wo[MOE_B200_EP_WS_OFFSETS_LOCAL]);
-  int32_t* owner = reinterpret_cast<int32_t*>(ws + wo[MOE_B200_EP_WS_OWNER]);
+  const int32_t* owner = reinterpret_cast<const int32_t*>(ws + wo[MOE_B200_EP_WS_OWNER]);
+  const int32_t* vmap_dev = owner + kMaxExperts;
   void* h = ws + wo[MOE_B200_EP_WS_H];
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t cap = N_local * (int64_t)k * world;
 
+  auto stamp = [&](int which) -> int {
+    if (h_stage_events == nullptr) return 0;
+    MOE_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(h_stage_events[which]), s));
+    return 0;
+  };
   MOE_CUDA_CHECK(cudaMemsetAsync(status, 0, 16 * sizeof(int32_t), s));
-  // the owner table is uploaded only when it (or the workspace) changes: a copy
-  // from pageable memory would otherwise synchronise the stream on every call
-  static thread_local const void* cached_ws = nullptr;
-  static thread_local int cached_n = 0;
-  static thread_local int32_t cached_tab[kMaxExperts + kMaxExperts * kEpMaxRanks];
-  int32_t tab[kMaxExperts + kMaxExperts * kEpMaxRanks];
-  memset(tab, 0, sizeof(tab));
-  memcpy(tab, h_owner, sizeof(int32_t) * EV);
-  memcpy(tab + kMaxExperts, h_vmap, sizeof(int32_t) * E * world);
-  const int tab_n = kMaxExperts + E * world;
-  if (cached_ws != workspace || cached_n != tab_n || memcmp(cached_tab, tab, sizeof(int32_t) * tab_n) != 0) {
-    MOE_CUDA_CHECK(cudaMemcpyAsync(owner, tab, sizeof(int32_t) * tab_n, cudaMemcpyHostToDevice, s));
-    memcpy(cached_tab, tab, sizeof(int32_t) * tab_n);
-    cached_ws = workspace;
-    cached_n = tab_n;
-  }
-  const int32_t* vmap_dev = owner + kMaxExperts;
+  if ((rc = stamp(MOE_B200_EP_EV_START))) return rc;
   if (N_local > 0) {
     rc = launch_router(x, Wg, bg, N_local, d, E, k, dtype, logits, idx, w, psum_part, status, s);
     if (rc) return rc;
   }
+  if ((rc = stamp(MOE_B200_EP_EV_ROUTER))) return rc;
   rc = launch_ep_dispatch(x, idx, N_local, d, E, EV, k, dtype, peers, rank, world, epoch, owner,
                           vmap_dev, scratch, psum_part, cnt_slot0, psum, offsets_local, aux,
                           N_local * (int64_t)world, status, s);
   if (rc) return rc;
+  if ((rc = stamp(MOE_B200_EP_EV_DISPATCH))) return rc;
   rc = launch_ep_wait(peers.flags[rank] + kEpFlagX * kEpMaxRanks, world, epoch, status, 22, s);
   if (rc) return rc;
+  if ((rc = stamp(MOE_B200_EP_EV_ARRIVED))) return rc;
+  // the down pass stores its rows straight into the token owners' ret_y
   EpScatter sc;
   for (int q = 0; q < kEpMaxRanks; ++q) sc.ret_y[q] = peers.ret_y[q];
   sc.meta = peers.recv_meta[rank];
-  if (flags & MOE_B200_FLAG_EP_UNFUSED_RETURN) {
-    // expert outputs to a local buffer first, then one copy kernel over NVLink
-    void* y = ws + wo[MOE_B200_EP_WS_Y];
-    if (E_local > 0) {
-      rc = (flags & MOE_B200_FLAG_ONE_CTA)
-               ? launch_experts_tc(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local,
-                                   h, y, status, s)
-               : launch_experts_tc2(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local,
-                                    h, y, nullptr, status, s);
-      if (rc) return rc;
-      rc = launch_ep_return(y, offsets_local, E_local, sc, d, s);
-      if (rc) return rc;
-    }
-  } else {
-    rc = (flags & MOE_B200_FLAG_ONE_CTA)
-             ? launch_experts_tc_ep(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local,
-                                    h, sc, status, s)
-             : launch_experts_tc2(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h,
-                                  nullptr, &sc, status, s);
-    if (rc) return rc;
-  }
+  rc = launch_experts_tc2(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h,
+                          nullptr, &sc, status, s);
+  if (rc) return rc;
+  if ((rc = stamp(MOE_B200_EP_EV_EXPERTS))) return rc;
   rc = launch_ep_signal(peers, kEpFlagY, rank, world, epoch, s);
   if (rc) return rc;
   rc = launch_ep_wait(peers.flags[rank] + kEpFlagY * kEpMaxRanks, world, epoch, status, 23, s);
   if (rc) return rc;
-  return launch_combine(peers.ret_y[rank], nullptr, w, residual, N_local, d, k, dtype, out, s);
+  if ((rc = stamp(MOE_B200_EP_EV_RETURNED))) return rc;
+  rc = launch_combine(peers.ret_y[rank], nullptr, w, residual, N_local, d, k, dtype, out, s);
+  if (rc) return rc;
+  return stamp(MOE_B200_EP_EV_COMBINE);
 }
 
 }  // extern "C"

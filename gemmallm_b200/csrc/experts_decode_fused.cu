@@ -1,5 +1,6 @@
-// Small-N expert feed-forward, both products in ONE launch: the GEGLU tiles and the
-// split-K down tiles of experts_decode.cu walked as one tile list by one persistent
+// Small-N expert feed-forward, both products in ONE launch: the GEGLU tiles (128 weight
+// rows = 64 gate + 64 up, as the A operand, against a block of up to 32 tokens as the B
+// operand) and the split-K down tiles walked as one tile list by one persistent
 // grid, so that the down pass's weight stream starts the moment a CTA runs out of
 // GEGLU tiles instead of after a kernel boundary (launch, ramp, tail). A down tile
 // needs the h rows of its 32-token block complete: every GEGLU tile, after its
@@ -9,8 +10,7 @@
 // for nothing and every CTA finishes its GEGLU tiles before its first down tile,
 // so the waits always end provided the grid's CTAs are resident together (one CTA
 // per SM, grid = SM count); if they are not, the bounded waits report
-// MOE_B200_DEV_TIMEOUT instead of hanging. Operand roles, tile shapes and
-// epilogues are those of experts_decode.cu (reference model.py:174,180-184).
+// MOE_B200_DEV_TIMEOUT instead of hanging (reference model.py:174,180-184).
 #include <cuda.h>
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -81,15 +81,6 @@ __device__ __forceinline__ Tile decode_tile(const Control* ctl, int t, int E, in
   return ti;
 }
 
-// Debug timeline (compile with -DMOE_TIMELINE): %globaltimer stamps in status words 16..
-#ifdef MOE_TIMELINE
-#define TL_FIRST(slot) do { if (blockIdx.x == 0) reinterpret_cast<unsigned long long*>(status + 16)[slot] = global_ns(); } while (0)
-#define TL_MAX(slot) atomicMax(reinterpret_cast<unsigned long long*>(status + 16) + (slot), global_ns())
-#else
-#define TL_FIRST(slot)
-#define TL_MAX(slot)
-#endif
-
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -126,7 +117,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       mbar_init(&ctl->h_done[a], 128);
     }
     ctl->abort = 0;
-    TL_FIRST(0);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -173,7 +163,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   // everything above is independent of the kernels before this one in the stream
   pdl_wait();
   pdl_launch_dependents();
-  if (threadIdx.x == 0) TL_FIRST(1);
   for (int e = threadIdx.x; e <= E; e += kThreads) ctl->offsets[e] = offsets[e];
   __syncthreads();
   if (warp == 0) {
@@ -263,9 +252,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         const uint32_t tmem_d = tmem_base + (uint32_t)(a * kTok);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&ctl->full[stage], phase, &ctl->abort, status, 13)) { ok = false; break; }
-#ifdef MOE_TIMELINE
-          if (it == 0 && kb == kb0) TL_FIRST(2);
-#endif
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + (size_t)stage * kStageBytes);
           const uint64_t wdesc = make_smem_desc(sw);
@@ -332,7 +318,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           if (!mbar_wait(&ctl->h_done[a], acc_phase, &ctl->abort, status, 17)) { ok = false; break; }
           __threadfence();
           atomicAdd(&ready[ti.tbg], 1);
-          TL_MAX(3);
         }
       } else if (feat_ok) {
         float* o = part + (int64_t)ti.ks * part_stride + (int64_t)ti.row0 * d + feat;
@@ -348,9 +333,6 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
   // ---------------- teardown ----------------
   __syncwarp();
-#ifdef MOE_TIMELINE
-  if (lane == 0) TL_MAX(4 + min(warp, 2));   // 4 producer, 5 MMA, 6 epilogue
-#endif
   if (*reinterpret_cast<volatile int*>(&ctl->abort)) {
     unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
@@ -377,6 +359,13 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
 }  // namespace
 
+// K of the down product is cut into this many ranges (each at least 8 blocks of 64).
+int decode_splits(int f) {
+  const int kb = (f + BK - 1) / BK;
+  int s = kb / 8;
+  return s < 1 ? 1 : (s > 8 ? 8 : s);
+}
+
 // `ready`: int32 [MOE_B200_READY_INTS], zeroed by the caller before this launch.
 int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                    int64_t M, int d, int f, int E, void* h, float* part, int* ready,
@@ -393,12 +382,9 @@ int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, con
   if (rc) return rc;
   // weight rows pulled into L2 ahead of the routing: only when most experts are hit
   const int spec_waves = spec < 0 ? (M >= 4 * (int64_t)E ? 2 : (M >= E ? 1 : 0)) : spec;
-  static bool attr_set = false;
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)kSmemBytes));
-    attr_set = true;
-  }
+  static PerDeviceOnce once;
+  rc = ensure_dynamic_smem(once, decode_fused_kernel, kSmemBytes);
+  if (rc) return rc;
   MOE_CUDA_CHECK(launch_pdl(decode_fused_kernel, dim3(sms), dim3(kThreads), kSmemBytes, s, tm_x, tm_h,
                             static_cast<const CUtensorMap*>(pv.tmap_W1_dec),
                             static_cast<const CUtensorMap*>(pv.tmap_W2_dec), offsets, pv.b1, pv.W1,

@@ -72,25 +72,6 @@ __device__ __forceinline__ int expert_of_block(const Control* ctl, int E, int u)
   return lo;
 }
 
-// Debug timeline (compile with -DMOE_TIMELINE): %globaltimer stamps in status words 16..
-#ifdef MOE_TIMELINE
-#define TL_FIRST(slot) do { if (blockIdx.x == 0) reinterpret_cast<unsigned long long*>(status + 16)[slot] = global_ns(); } while (0)
-#define TL_MAX(slot) atomicMax(reinterpret_cast<unsigned long long*>(status + 16) + (slot), global_ns())
-// cycles spent per activity, kept in registers (array prof[] of the role) and written by
-// block 0 when the role ends: slots 7.. producer, 12.. MMA, 19.. epilogue
-#define PROF_DECL() long long prof[6] = {0, 0, 0, 0, 0, 0}; const long long prof_start = clock64()
-#define TW_BEGIN() const long long tw0_ = clock64()
-#define TW_END(k) prof[k] += clock64() - tw0_
-#define PROF_FLUSH(base, n) do { if (blockIdx.x == 0) { unsigned long long* tl_ = reinterpret_cast<unsigned long long*>(status + 16); \
-    for (int q_ = 0; q_ < (n); ++q_) tl_[(base) + q_] = (unsigned long long)prof[q_]; tl_[(base) + (n)] = (unsigned long long)(clock64() - prof_start); } } while (0)
-#else
-#define PROF_DECL()
-#define TW_BEGIN()
-#define TW_END(k)
-#define PROF_FLUSH(base, n)
-#define TL_FIRST(slot)
-#define TL_MAX(slot)
-#endif
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
@@ -144,7 +125,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     mbar_init(&ctl->route_done, kEpiThreads);
     for (int i = 0; i < kRing; ++i) { mbar_init(&ctl->ring_full[i], 1); mbar_init(&ctl->ring_empty[i], kEpiThreads + 1); }
     ctl->abort = 0;
-    TL_FIRST(0);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -200,7 +180,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       uint32_t rphase = 0;
       bool ok = true;
       bool routed = false;
-      PROF_DECL();
       // The next tile is claimed while the last few stages of the current one are still to
       // be issued: late enough that nobody hoards tiles, early enough to hide the atomic.
       int t_cur = first_tile;
@@ -232,9 +211,7 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             continue;
           }
         }
-        { TW_BEGIN();
         if (!mbar_wait(&ctl->ring_empty[slot], rphase ^ 1u, &ctl->abort, status, 29)) break;
-        TW_END(2); }
         ctl->ring[slot] = t;
         mbar_arrive(&ctl->ring_full[slot]);
         if (++slot == kRing) { slot = 0; rphase ^= 1u; }
@@ -248,16 +225,12 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           const int claim_kb = max(0, kb_all1 - 4);
           for (int kb = 0; kb < kb_all1; ++kb) {
             if (kb == claim_kb) claim_next();
-            { TW_BEGIN();
             if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort, status, 21)) { ok = false; break; }
-            TW_END(0); }
             uint8_t* sw = smem + (size_t)stage * stage_bytes;
-            TW_BEGIN();
             mbar_expect_tx(&ctl->full[stage], (uint32_t)stage_bytes);
             tma_load_2d(sw, &tmap_x, &ctl->full[stage], kb * BK, arow);
             tma_load_2d(sw + tok_bytes, tw, &ctl->full[stage], kb * BK, nt * 128);
             tma_load_2d(sw + tok_bytes + kBox, tw, &ctl->full[stage], kb * BK, f + nt * 128);
-            TW_END(3);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
         } else {
@@ -269,7 +242,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           const int arow = SORTED ? ctl->offsets[e] + (u - ctl->tb_start[e]) * NP : e * NP;
           {
             // the h rows of this unit must be complete (bounded wait), and visible to TMA
-            TW_BEGIN();
             if (cur_ready >= n1) {
               asm volatile("fence.acq_rel.gpu;" ::: "memory");
             } else {
@@ -290,23 +262,18 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
               if (!ok) break;
             }
             asm volatile("fence.proxy.async;" ::: "memory");
-            TW_END(1);
             const CUtensorMap* tw = tmap_w2 + e;
             const int kb0 = ks * kb_per_split;
             const int kb1 = min(kb_all2, kb0 + kb_per_split);
             const int claim_kb = max(kb0, kb1 - 4);
             for (int kb = kb0; kb < kb1; ++kb) {
               if (kb == claim_kb) claim_next();
-              { TW_BEGIN();
               if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort, status, 22)) { ok = false; break; }
-              TW_END(0); }
               uint8_t* sw = smem + (size_t)stage * stage_bytes;
-              TW_BEGIN();
               mbar_expect_tx(&ctl->full[stage], (uint32_t)stage_bytes);
               tma_load_2d(sw, &tmap_h, &ctl->full[stage], kb * BK, arow);
               tma_load_2d(sw + tok_bytes, tw, &ctl->full[stage], kb * BK, nt * 256);
               tma_load_2d(sw + tok_bytes + kBox, tw, &ctl->full[stage], kb * BK, nt * 256 + 128);
-              TW_END(3);
               if (++stage == stages) { stage = 0; phase ^= 1u; }
             }
           }
@@ -315,7 +282,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         t_cur = t_next;
         cur_ready = next_ready;
       }
-      PROF_FLUSH(7, 4);    // empty, ready, ring, (unused) | total
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -327,11 +293,8 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       uint32_t rphase = 0;
       int it = 0;
       bool ok = true;
-      PROF_DECL();
       while (ok) {
-        { TW_BEGIN();
         if (!mbar_wait(&ctl->ring_full[slot], rphase, &ctl->abort, status, 30)) break;
-        TW_END(0); }
         const int t = *reinterpret_cast<volatile int*>(&ctl->ring[slot]);
         mbar_arrive(&ctl->ring_empty[slot]);
         if (++slot == kRing) { slot = 0; rphase ^= 1u; }
@@ -344,17 +307,12 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           kb1 = min(kb_all2, kb0 + kb_per_split);
         }
         const int a = it & 1;
-        { TW_BEGIN();
         if (!mbar_wait(&ctl->tmem_empty[a], acc_phase ^ 1u, &ctl->abort, status, 23)) { ok = false; break; }
-        TW_END(1); }
         tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)(a * 256);
         for (int kb = kb0; kb < kb1; ++kb) {
-          { TW_BEGIN();
           if (!mbar_wait(&ctl->full[stage], phase, &ctl->abort, status, 24)) { ok = false; break; }
-          TW_END(2); }
           tc_fence_after();
-          TW_BEGIN();
           const uint32_t sw = smem_u32(smem + (size_t)stage * stage_bytes);
           // A: 128 token rows from the stage base (only NP of them loaded); B: 256 weight rows
           const uint64_t adesc = make_smem_desc(sw);
@@ -364,7 +322,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             tc_mma(acc, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
                    (kb > kb0 || kk > 0) ? 1u : 0u);
           tc_commit(&ctl->empty[stage]);
-          TW_END(3);
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -372,7 +329,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         if (a == 1) acc_phase ^= 1u;
         ++it;
       }
-      PROF_FLUSH(12, 6);   // ring, tmem, full, issue, latency sum, loads | total
     }
   } else {
     // ---------------- epilogue: thread = token (accumulator lane), half of the columns ----------------
@@ -397,13 +353,9 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       for (int e = et; e <= E; e += kEpiThreads) ctl->offsets[e] = __ldcg(&offsets[e]);
       mbar_arrive(&ctl->route_done);
       ok = mbar_wait(&ctl->route_done, 0u, &ctl->abort, status, 27);
-      if (et == 0) TL_FIRST(1);
     }
-    PROF_DECL();
     while (ok) {
-      { TW_BEGIN();
       if (!mbar_wait(&ctl->ring_full[slot], rphase, &ctl->abort, status, 31)) break;
-      TW_END(0); }
       const int t = *reinterpret_cast<volatile int*>(&ctl->ring[slot]);
       mbar_arrive(&ctl->ring_empty[slot]);
       if (++slot == kRing) { slot = 0; rphase ^= 1u; }
@@ -448,12 +400,8 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           }
         }
       }
-      { TW_BEGIN();
       if (!mbar_wait(&ctl->tmem_full[a], acc_phase, &ctl->abort, status, 25)) { ok = false; break; }
-      TW_END(1); }
       tc_fence_after();
-      [[maybe_unused]] const bool prof_down = down;
-      TW_BEGIN();
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * 256);
       if (!down) {
         if (mword != 0u) {       // uniform over the warp
@@ -488,7 +436,6 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
           if (!mbar_wait(&ctl->h_done[a], acc_phase, &ctl->abort, status, 28)) { ok = false; break; }
           __threadfence();
           atomicAdd(&ready[u], 1);
-          TL_MAX(3);
         }
       } else if (mword != 0u) {
         const int n0 = nt * 256;
@@ -519,18 +466,13 @@ decode_spec_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
       }
       tc_fence_before();
       mbar_arrive(&ctl->tmem_empty[a]);
-      TW_END(prof_down ? 3 : 2);
       if (a == 1) acc_phase ^= 1u;
       ++it;
     }
-    if (et == 0) PROF_FLUSH(19, 4);   // ring, full, geglu, down | total
   }
 
   // ---------------- teardown ----------------
   __syncwarp();
-#ifdef MOE_TIMELINE
-  if (lane == 0) TL_MAX(4 + min(warp, 2));   // 4 producer, 5 MMA, 6 epilogue
-#endif
   if (*reinterpret_cast<volatile int*>(&ctl->abort)) {
     unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
@@ -586,12 +528,9 @@ int launch_experts_tc_decode_spec(const void* x, const int32_t* idx, const int32
   if (stages > kMaxStages) stages = kMaxStages;
   const size_t smem = 1024 + (size_t)stages * stage_bytes + sizeof(Control);
   const int tmem_cols = 512;   // two accumulators of 256 columns
-  static bool attr_set = false;
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(decode_spec_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kSmemBudget));
-    attr_set = true;
-  }
+  static PerDeviceOnce once;
+  rc = ensure_dynamic_smem(once, decode_spec_kernel<false>, kSmemBudget);
+  if (rc) return rc;
   MOE_CUDA_CHECK(launch_pdl(decode_spec_kernel<false>, dim3(sms), dim3(kThreads), smem, s, tm_x, tm_h,
                             static_cast<const CUtensorMap*>(pv.tmap_W1),
                             static_cast<const CUtensorMap*>(pv.tmap_W2), offsets, idx, pv.b1, (int)N, NP,
@@ -652,12 +591,9 @@ int launch_experts_tc_rows(const void* perm, const int32_t* offsets, const void*
   int stages = (kSmemBudget - (int)sizeof(Control) - 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   const size_t smem = 1024 + (size_t)stages * stage_bytes + sizeof(Control);
-  static bool attr_set = false;
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(decode_spec_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kSmemBudget));
-    attr_set = true;
-  }
+  static PerDeviceOnce once;
+  rc = ensure_dynamic_smem(once, decode_spec_kernel<true>, kSmemBudget);
+  if (rc) return rc;
   MOE_CUDA_CHECK(launch_pdl(decode_spec_kernel<true>, dim3(sms), dim3(kThreads), smem, s, tm_x, tm_h,
                             static_cast<const CUtensorMap*>(pv.tmap_W1),
                             static_cast<const CUtensorMap*>(pv.tmap_W2), offsets,

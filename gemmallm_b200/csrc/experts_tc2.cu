@@ -4,9 +4,9 @@
 // pass CTA 0 holds the 128 gate rows, CTA 1 the 128 up rows); the pair's MMA
 // (M=256, N=256, K=16), issued by the even CTA, reads both halves, and each
 // CTA's TMEM receives the 128x256 accumulator of its own rows. Per 128x256x64
-// step a CTA therefore pulls 32 KiB from L2 and shared memory instead of 48 KiB:
-// operand delivery, not the tensor pipe, is what bounded the one-CTA kernel
-// (experts_tc.cu), which stays as the fallback and the reference for tests.
+// step a CTA therefore pulls 32 KiB from L2 and shared memory instead of the
+// 48 KiB a single CTA with a 128x256 tile would need: operand delivery, not the
+// tensor pipe, is what bounds a one-CTA kernel of this shape.
 //
 // Synchronisation inside the pair (all mbarriers, all waits bounded):
 //   full[s]       lives in the even CTA; both CTAs' TMA loads complete on it
@@ -16,8 +16,7 @@
 //   tmem_full[a]  one per CTA, committed the same way;
 //   tmem_empty[a] in the even CTA; the 16 epilogue warps of the pair arrive on
 //                 it (the odd CTA's warps through the cluster-mapped address).
-// Same math and epilogue (tc_epilogue.cuh) as experts_tc.cu:
-// reference model.py:174,180-184.
+// Math and epilogue (tc_epilogue.cuh): reference model.py:174,180-184.
 #include <cuda.h>
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -158,10 +157,6 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
   const int total_tiles = ctl->tile_start[E];
-#ifdef MOE_TC_PROFILE
-  constexpr int kProfBase = GEGLU ? 0 : 8;
-  const long long prof_kernel_t0 = clock64();
-#endif
 
   if (warp == 0) {
     // ---------------- TMA producer (each CTA loads its own rows and its half of B) -------------
@@ -180,9 +175,7 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const CUtensorMap* tb = tmap_b + e;
         for (int kb = 0; kb < k_blocks; ++kb) {
           {
-            PROF_T0();
             if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort, status, 31)) { ok = false; break; }
-            PROF_ADD(0);
           }
           uint8_t* sa = smem + (size_t)stage * kStageBytes;
           const uint32_t full0 = map_to_cta(smem_u32(&ctl->full[stage]), 0);
@@ -204,28 +197,22 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int t = pair; ok && t < total_tiles; t += num_pairs, ++it) {
         const int a = it & 1;
         {
-          PROF_T0();
           if (!mbar_wait(&ctl->tmem_empty[a], acc_phase ^ 1u, &ctl->abort, status, 32)) { ok = false; break; }
-          PROF_ADD(1);
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
         for (int kb = 0; kb < k_blocks; ++kb) {
           {
-            PROF_T0();
             if (!mbar_wait(&ctl->full[stage], phase, &ctl->abort, status, 33)) { ok = false; break; }
-            PROF_ADD(2);
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(sa + kABytes);
-#ifndef MOE_TC_NOMMA
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk)
             tc_mma_pair(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), kIdesc2,
                         (kb | kk) != 0 ? 1u : 0u);
-#endif
           // the stage is free in both CTAs once these MMAs have read it
           const uint32_t e_local = smem_u32(&ctl->empty[stage]);
           tc_commit_pair(map_to_cta(e_local, 0));
@@ -258,15 +245,11 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(bias_ptrs[e]);
       const int a = it & 1;
       {
-        PROF_T0();
         if (!mbar_wait(&ctl->tmem_full[a], acc_phase, &ctl->abort, status, 34)) { ok = false; break; }
-        if (threadIdx.x == 64) PROF_ADD(3);
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
-#ifndef MOE_TC_NOEPI
       store_tile<GEGLU, SCATTER>(taddr, row, row_ok, n0, Nout, bias, out, sc, ctl->stage_out[warp - 2], lane, half);
-#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->tmem_empty[a]), 0));
@@ -275,12 +258,6 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (SCATTER) __threadfence_system();
   }
 
-#ifdef MOE_TC_PROFILE
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    g_prof[4 + kProfBase] = clock64() - prof_kernel_t0;
-    g_prof[5 + kProfBase] = total_tiles;
-  }
-#endif
   // ---------------- teardown ----------------
   __syncwarp();
   if (*reinterpret_cast<volatile int*>(&ctl->abort)) {
@@ -302,13 +279,10 @@ template <bool GEGLU, bool SCATTER>
 int launch_pair(const CUtensorMap& tm_a, const void* tmap_b, const int32_t* offsets,
                 const void* const* bias, int E, int K, int Nout, void* out, const EpScatter& sc,
                 int32_t* status, int sms, cudaStream_t s) {
-  static bool attr_set = false;
+  static PerDeviceOnce once;
   auto fn = grouped_gemm_tc2_kernel<GEGLU, SCATTER>;
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)kSmemBytes));
-    attr_set = true;
-  }
+  int rc = ensure_dynamic_smem(once, fn, kSmemBytes);
+  if (rc) return rc;
   MOE_CUDA_CHECK(launch_pdl(fn, dim3(sms & ~1), dim3(kThreads), kSmemBytes, s, tm_a,
                             static_cast<const CUtensorMap*>(tmap_b), offsets, bias, E, K, Nout,
                             static_cast<__nv_bfloat16*>(out), sc, status));
@@ -317,16 +291,6 @@ int launch_pair(const CUtensorMap& tm_a, const void* tmap_b, const int32_t* offs
 
 }  // namespace
 
-#ifdef MOE_TC_PROFILE
-extern "C" void moe_b200_prof_read2(long long* out, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, tc::g_prof, sizeof(long long) * 16);
-  if (reset) {
-    long long z[16] = {0};
-    cudaMemcpyToSymbol(tc::g_prof, z, sizeof(z));
-  }
-}
-#endif
 
 int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                        int f, int E, void* h, void* y, const EpScatter* sc, int32_t* status,

@@ -393,14 +393,11 @@ int launch(const void* x, const void* Wg, const void* bg, int N, int d, int E, i
   const int ntok = split ? 16 : N;
   const size_t smem = sizeof(float) * ((size_t)32 * 16 * 8 * NT + (size_t)ntok * (E + 1)) +
                       sizeof(int) * (2 * (size_t)ntok * k + 2 * kMaxTopK * kMaxE + 4 * kMaxE + 1);
-  static bool attr_set = false;
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT, false>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(front_small_kernel<NT, true>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-    attr_set = true;
-  }
+  static PerDeviceOnce once_whole, once_split;
+  int rc = ensure_dynamic_smem(once_whole, front_small_kernel<NT, false>, 160 * 1024);
+  if (rc) return rc;
+  rc = ensure_dynamic_smem(once_split, front_small_kernel<NT, true>, 160 * 1024);
+  if (rc) return rc;
   // one block per 16 tokens
   const int blocks = N <= 16 ? 1 : (N + 15) / 16;
   auto fn = split ? front_small_kernel<NT, true> : front_small_kernel<NT, false>;

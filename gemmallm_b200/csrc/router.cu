@@ -342,11 +342,10 @@ int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, 
                float* out_logits, int32_t* out_idx, float* out_w, float* psum_part, cudaStream_t s) {
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
   const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E);
-  static bool attr_set = false;
-  if (smem > 48 * 1024 && !attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(router_mma_kernel<NT>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
-    attr_set = true;
+  static PerDeviceOnce once;
+  if (smem > 48 * 1024) {
+    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT>, 80 * 1024);
+    if (rc) return rc;
   }
   router_mma_kernel<NT><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),

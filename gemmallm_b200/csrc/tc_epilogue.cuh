@@ -1,5 +1,5 @@
-// Epilogue of the 128-row x 256-column accumulator tile shared by the one-CTA and
-// the CTA-pair grouped GEMM kernels: TMEM -> registers (one row per thread) ->
+// Epilogue of one CTA's 128-row x 256-column accumulator tile in the CTA-pair
+// grouped GEMM kernel: TMEM -> registers (one row per thread) ->
 // bias (+ GeGLU) -> bf16 -> shared-memory staging -> global memory in 128-byte
 // runs per row.
 #pragma once
@@ -8,14 +8,6 @@
 
 namespace moe {
 namespace tc {
-
-// Instrumented builds only: MOE_TC_NOSTORE drops the epilogue's global stores (the
-// predicate is never true, which the compiler cannot know).
-#ifdef MOE_TC_NOSTORE
-#define MOE_TC_STORE_OK(cond) ((cond) && Nout < 0)
-#else
-#define MOE_TC_STORE_OK(cond) (cond)
-#endif
 
 constexpr int kStgPitch = 144;               // bytes per staged row: 64 bf16 + 16 bytes pad
 constexpr int kStgRows = 16;                 // half a warp's rows are staged at a time
@@ -44,7 +36,7 @@ __device__ __forceinline__ void store_tile(uint32_t taddr, int row, bool row_ok,
   constexpr int kPasses = kTileN / 128;        // 64-column passes per warp
   // destination of this thread's row (nullptr: nothing to store)
   __nv_bfloat16* dst = nullptr;
-  if (MOE_TC_STORE_OK(row_ok)) {
+  if (row_ok) {
     if (SCATTER) {
       const int meta = __ldg(&sc.meta[row]);
       dst = static_cast<__nv_bfloat16*>(sc.ret_y[(meta >> 24) & 7]) + (int64_t)(meta & 0xffffff) * Nout;

@@ -10,9 +10,6 @@ namespace tc {
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
-#ifdef MOE_TC_PROFILE
-static __device__ long long g_prof[16];
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -44,13 +41,6 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-#ifdef MOE_TC_PROFILE
-#define PROF_T0() long long prof_t0 = clock64()
-#define PROF_ADD(slot) do { if (blockIdx.x == 0) atomicAdd((unsigned long long*)&g_prof[(slot) + kProfBase], (unsigned long long)(clock64() - prof_t0)); } while (0)
-#else
-#define PROF_T0()
-#define PROF_ADD(slot)
-#endif
 
 // Bounded wait. False when the limit passed or another role gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* abort_flag,

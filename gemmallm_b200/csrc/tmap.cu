@@ -67,14 +67,18 @@ int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, i
   return 0;
 }
 
+// SM count of the current device (cached per device).
 int sm_count(int* sms) {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0;
-    MOE_CUDA_CHECK(cudaGetDevice(&dev));
-    MOE_CUDA_CHECK(cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev));
+  static int cached[kMaxDevices] = {};
+  int dev = 0;
+  MOE_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    MOE_CUDA_CHECK(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+    return 0;
   }
-  *sms = cached;
+  if (cached[dev] == 0)
+    MOE_CUDA_CHECK(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+  *sms = cached[dev];
   return 0;
 }
 

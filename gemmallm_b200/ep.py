@@ -109,9 +109,9 @@ class ExpertParallelMOE(nn.Module):
         self.d_ff = hidden_size * expansion_factor if d_ff is None else d_ff
         self.top_k = top_k
         self.epoch = 0
-        self.flags = _cabi.FLAG_DEFAULT
         self._plan = _Plan()
         self._state = None
+        self._stage_events = None    # ctypes array of cudaEvent_t, see time_stages()
         self.last = None
 
     def _setup(self, N_local: int, dev: torch.device):
@@ -136,15 +136,19 @@ class ExpertParallelMOE(nn.Module):
         dist.barrier(group=self.group)
         bases = [int(p) for p in hdl.buffer_ptrs]
         wbytes = lib.moe_b200_ep_workspace_bytes(N_local, d, f, E, k, G)
-        ws = torch.empty(wbytes + 1024, dtype=torch.uint8, device=dev)
+        ws = torch.zeros(wbytes + 1024, dtype=torch.uint8, device=dev)
+        ws_base = (ws.data_ptr() + 1023) & ~1023
+        owner = (C.c_int32 * len(self.v_owner))(*self.v_owner)
+        vmap = (C.c_int32 * (E * G))(*[v for row in self.vmap for v in row])
+        # the placement tables live in the workspace: uploaded here, once per workspace
+        check(lib.moe_b200_ep_setup(owner, vmap, N_local, d, f, E, k, G, len(self.v_owner), ws_base,
+                                    wbytes, _stream(dev)), "ep_setup")
         self.epoch = 0
         self._state = {
             "key": key, "symm": symm, "hdl": hdl, "bases": (C.c_void_p * G)(*bases),
-            "ws": ws, "ws_base": (ws.data_ptr() + 1023) & ~1023, "ws_bytes": wbytes,
+            "ws": ws, "ws_base": ws_base, "ws_bytes": wbytes,
             "ws_layout": _cabi.ep_workspace_layout(N_local, d, f, E, k, G),
             "symm_layout": _cabi.ep_symm_layout(N_local, d, E, k, G),
-            "owner": (C.c_int32 * len(self.v_owner))(*self.v_owner),
-            "vmap": (C.c_int32 * (E * G))(*[v for row in self.vmap for v in row]),
         }
         return self._state
 
@@ -185,9 +189,10 @@ class ExpertParallelMOE(nn.Module):
             self.epoch += 1
             check(lib.moe_b200_ep_forward(
                 x.data_ptr(), self.gate.weight.data_ptr(), self.gate.bias.data_ptr(), plan, res_ptr,
-                N, d, f, E, k, dtype, self.flags, self.rank, self.world, self.epoch, len(self.v_owner),
-                st["owner"], st["vmap"], st["bases"],
-                st["ws_base"], st["ws_bytes"], out.data_ptr(), _stream(dev)), "ep_forward")
+                N, d, f, E, k, dtype, 0, self.rank, self.world, self.epoch, len(self.v_owner),
+                len(self.local_virtual), st["bases"],
+                st["ws_base"], st["ws_bytes"], out.data_ptr(), self._stage_events, _stream(dev)),
+                "ep_forward")
         self.last = {
             "logits": self._ws_view("logits", torch.float32, (N, E)),
             "idx": self._ws_view("idx", torch.int32, (N, k)),
@@ -199,6 +204,113 @@ class ExpertParallelMOE(nn.Module):
         }
         aux = self._ws_view("aux", torch.float32, (1,))[0].clone()
         return out.reshape(shape), aux
+
+    def forward_nccl(self, tensor: torch.Tensor, *, residual: torch.Tensor | None = None):
+        """The same sharded forward with the two exchange steps done by NCCL
+        (``all_to_all_single`` with split sizes read back to the host) instead of peer stores
+        inside the kernels: the baseline the in-kernel exchange is timed against. Router, expert
+        and combine kernels are the library's; the permutations around the collectives are plain
+        torch index operations, as a host-side implementation would write them."""
+        import torch.distributed as dist
+        dtype = _dtype_code(tensor)
+        shape = tensor.shape
+        d, f, E, k, G = self.hidden_size, self.d_ff, self.num_experts, self.top_k, self.world
+        x = tensor.reshape(-1, d).contiguous()
+        N = x.shape[0]
+        dev = x.device
+        EV = len(self.v_owner)
+        with torch.cuda.device(dev):
+            s = _stream(dev)
+            logits = torch.empty(N, E, dtype=torch.float32, device=dev)
+            idx = torch.empty(N, k, dtype=torch.int32, device=dev)
+            w = torch.empty(N, k, dtype=torch.float32, device=dev)
+            psum_part = torch.empty(max(1, lib.moe_b200_router_blocks(N)), E, dtype=torch.float32, device=dev)
+            status = torch.zeros(16, dtype=torch.int32, device=dev)
+            check(lib.moe_b200_router(x.data_ptr(), self.gate.weight.data_ptr(), self.gate.bias.data_ptr(),
+                                      N, d, E, k, dtype, logits.data_ptr(), idx.data_ptr(), w.data_ptr(),
+                                      psum_part.data_ptr(), status.data_ptr(), s), "router")
+            if getattr(self, "_nccl_tables", None) is None or self._nccl_tables[0].device != dev:
+                vmap_r = torch.tensor([self.vmap[e][self.rank] for e in range(E)], device=dev)
+                v_owner = torch.tensor(self.v_owner, device=dev)
+                # position of a virtual expert in the send order: by owner, then by virtual id
+                order = sorted(range(EV), key=lambda v: (self.v_owner[v], v))
+                vpos = torch.empty(EV, dtype=torch.long)
+                vpos[torch.tensor(order)] = torch.arange(EV)
+                self._nccl_tables = (vmap_r, v_owner, vpos.to(dev), torch.tensor(order, device=dev))
+            vmap_r, v_owner, vpos, order = self._nccl_tables
+            v_pair = vmap_r[idx.long().view(-1)]                      # [N*k] virtual expert of each pair
+            key = vpos[v_pair]
+            sort = torch.argsort(key, stable=True)                    # pairs in send order
+            cnt = torch.bincount(key, minlength=EV)                   # per virtual expert, in send order
+            cnt_all = torch.empty(G, EV, dtype=cnt.dtype, device=dev)
+            dist.all_gather_into_tensor(cnt_all, cnt, group=self.group)
+            owner_sorted = v_owner[order]                             # owner of each send-order slot
+            mine = (owner_sorted == self.rank)
+            send_splits = torch.zeros(G, dtype=cnt.dtype, device=dev).index_add_(0, owner_sorted, cnt).tolist()
+            recv_cnt = cnt_all[:, mine]                               # [G, E_local] rows from each source
+            recv_splits = recv_cnt.sum(1).tolist()
+            rows = int(sum(recv_splits))
+            send = x[(sort // k)]
+            recv = torch.empty(rows, d, dtype=x.dtype, device=dev)
+            dist.all_to_all_single(recv, send, recv_splits, send_splits, group=self.group)
+            # received order is (source, expert); the grouped kernels want (expert, source)
+            E_local = recv_cnt.shape[1]
+            start_se = torch.cumsum(recv_cnt.reshape(-1), 0) - recv_cnt.reshape(-1)     # [G*E_local]
+            cnt_es = recv_cnt.t().contiguous()                        # [E_local, G]
+            start_es = (torch.cumsum(cnt_es.reshape(-1), 0) - cnt_es.reshape(-1)).view(E_local, G)
+            seg_src = start_se.view(G, E_local).t()                   # [E_local, G]
+            rep = cnt_es.reshape(-1)
+            src_start = torch.repeat_interleave(seg_src.reshape(-1), rep, output_size=rows)
+            dst_start = torch.repeat_interleave(start_es.reshape(-1), rep, output_size=rows)
+            gather = src_start + (torch.arange(rows, device=dev) - dst_start)          # row r of (expert, source) order
+            xs = recv[gather]
+            offsets = torch.zeros(E_local + 1, dtype=torch.int32, device=dev)
+            offsets[1:] = torch.cumsum(cnt_es.sum(1), 0).to(torch.int32)
+            h = torch.empty(max(rows, 1), f, dtype=x.dtype, device=dev)
+            y = torch.empty(max(rows, 1), d, dtype=x.dtype, device=dev)
+            if rows > 0 and E_local > 0:
+                local = [self.experts[str(e)] for e in self.local_ids]
+                plan = self._plan.get(local, d, f, dtype, dev)
+                check(lib.moe_b200_experts(xs.data_ptr(), offsets.data_ptr(), plan, rows, d, f, E_local,
+                                           dtype, 0, h.data_ptr(), y.data_ptr(), status.data_ptr(), s),
+                      "experts")
+            back = torch.empty(rows, d, dtype=x.dtype, device=dev)
+            back[gather] = y[:rows]
+            ret = torch.empty(N * k, d, dtype=x.dtype, device=dev)
+            dist.all_to_all_single(ret, back, send_splits, recv_splits, group=self.group)
+            row_of = torch.empty(N * k, dtype=torch.int32, device=dev)
+            row_of[sort] = torch.arange(N * k, dtype=torch.int32, device=dev)
+            out = torch.empty_like(x)
+            res_ptr = None if residual is None else residual.reshape(-1, d).contiguous().data_ptr()
+            check(lib.moe_b200_combine(ret.data_ptr(), row_of.data_ptr(), w.data_ptr(), res_ptr, N, d, k,
+                                       dtype, out.data_ptr(), s), "combine")
+        return out.reshape(shape)
+
+    def time_stages(self, tensor: torch.Tensor, reps: int = 10) -> dict:
+        """CUDA-event time (ms, mean over ``reps`` calls) of each stage of the sharded forward on
+        this rank: the library records an event at every stage boundary of the call. The waits
+        on peers belong to the stages they end ("arrived", "returned"), so a rank that is ahead
+        of its peers shows its lead there. All ranks must call this together."""
+        n = len(_cabi.EP_STAGES) + 1
+        sets = []
+        for _ in range(reps):
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+            for e in evs:
+                e.record()          # creates the underlying cudaEvent_t
+            sets.append(evs)
+        torch.cuda.synchronize(tensor.device)
+        with torch.no_grad():
+            for evs in sets:
+                self._stage_events = (C.c_void_p * n)(*[e.cuda_event for e in evs])
+                try:
+                    self.forward(tensor)
+                finally:
+                    self._stage_events = None
+        torch.cuda.synchronize(tensor.device)
+        out = {}
+        for i, name in enumerate(_cabi.EP_STAGES):
+            out[name] = sum(evs[i].elapsed_time(evs[i + 1]) for evs in sets) / reps
+        return out
 
     def device_status(self) -> int:
         return int(self.last["status"][0].item()) if self.last else 0

@@ -171,7 +171,6 @@ class MOE(nn.Module):
         self.hidden_size = hidden_size
         self.d_ff = self.experts[0].d_ff
         self.top_k = top_k
-        self.flags = _cabi.FLAG_DEFAULT
         self._plan = _Plan()
         self._plan_ft = _Plan()
         self._ws = None
@@ -239,7 +238,7 @@ class MOE(nn.Module):
                 plan = self._plan.get(self.experts, d, f, dtype, dev)
             _, base, nbytes, _ = self._workspace(N, dtype, dev)
             check(lib.moe_b200_forward(x.data_ptr(), gw.data_ptr(), gb.data_ptr(), plan, res_ptr,
-                                       N, d, f, E, k, dtype, self.flags | _cabi.FLAG_WS_CLEAN, base, nbytes,
+                                       N, d, f, E, k, dtype, _cabi.FLAG_WS_CLEAN, base, nbytes,
                                        out.data_ptr(), _stream(dev)), "forward")
         self.last = {
             "logits": self._view("logits", torch.float32, (N, E)),

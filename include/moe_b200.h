@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define MOE_B200_ABI_VERSION 1
+#define MOE_B200_ABI_VERSION 2
 
 enum { MOE_B200_F32 = 0, MOE_B200_BF16 = 1 };
 
@@ -55,39 +55,17 @@ enum {
   MOE_B200_DEV_BAD_INDEX = 2  /* an expert index outside [0,E) was seen */
 };
 
-/* flags for moe_b200_experts / moe_b200_forward */
+/* flags for moe_b200_forward */
 enum {
   MOE_B200_FLAG_DEFAULT = 0,
-  /* run the expert products on the plain CUDA-core kernel even for bf16 (the
-   * fp32 dtype always uses it). For tests: a second implementation of the same
-   * arithmetic to check the tensor-core kernel against. */
-  MOE_B200_FLAG_SIMT_EXPERTS = 1,
-  /* never take the small-N weight-streaming path inside moe_b200_forward */
-  MOE_B200_FLAG_NO_DECODE_PATH = 2,
-  /* expert-parallel: write the expert outputs locally and return them to the
-   * token owners with a separate copy kernel instead of from the down pass's
-   * epilogue (for comparison) */
-  MOE_B200_FLAG_EP_UNFUSED_RETURN = 4,
-  /* bf16 expert products on the one-CTA kernel (cta_group::1, 128-row tiles)
-   * instead of CTA pairs (cta_group::2, 256-row tiles) */
-  MOE_B200_FLAG_ONE_CTA = 8,
-  /* small-N path of moe_b200_forward: run the GEGLU and the down product as two
-   * launches (moe_b200_experts_decode) instead of the single launch of
-   * moe_b200_experts_decode_fused */
-  MOE_B200_FLAG_DECODE_TWO_PASS = 16,
-  /* small-N path of moe_b200_forward: never use moe_b200_experts_decode_spec (the
-   * kernel that streams every expert without waiting for the routing) */
-  MOE_B200_FLAG_DECODE_NO_SPEC = 32,
-  /* moe_b200_forward, small-N path: the caller guarantees that the status region of
-   * `workspace` (MOE_B200_WS_STATUS, status words and counters) is all zero on entry: it
-   * was zeroed once, and every call on this workspace since then has ended with device
-   * status 0 (such calls leave the region zero). Saves the memset in front of the first
-   * kernel, which then overlaps the tail of the kernel before it. After a non-zero device
-   * status the region has to be zeroed again by the caller. */
-  MOE_B200_FLAG_WS_CLEAN = 64,
-  /* moe_b200_forward: calls of 257 to 4096 rows (N*k) go through the prefill kernels instead
-   * of moe_b200_experts_rows */
-  MOE_B200_FLAG_NO_ROWS_PATH = 128
+  /* The caller guarantees that the status region of `workspace`
+   * (MOE_B200_WS_STATUS, status words and counters) is all zero on entry: it was
+   * zeroed once, and every call on this workspace since then has ended with
+   * device status 0 (such calls leave the region zero). Saves the memset in
+   * front of the first kernel of calls of up to 4096 rows, which then overlaps
+   * the tail of the kernel before it. After a non-zero device status the region
+   * has to be zeroed again by the caller. */
+  MOE_B200_FLAG_WS_CLEAN = 1
 };
 
 /* Layout of the status region: word 0 = device status code, words 1..15 detail;
@@ -194,7 +172,9 @@ size_t moe_b200_dispatch_scratch_bytes(int64_t N, int E, int k);
  * tensors). No counterpart in the reference. Same arguments and results as
  * moe_b200_dispatch without `scratch`: the counters live in a 1 MiB array
  * built into the library (held by every GPU that loads it until the process
- * exits). It allocates nothing and calls no allocating routine.
+ * exits). After the first call on a device it takes no device memory and calls
+ * no allocating routine; that first call loads the library's kernels on the
+ * device and looks the array's address up (so make it once at start-up).
  *   - Limit: moe_b200_dispatch_scratch_bytes(N,E,k) <= 1 MiB (e.g. N=65536,
  *     E=64, k=4 fits); larger shapes return MOE_B200_ERR_WORKSPACE.
  *   - The first call on each device looks up the array's device address; make
@@ -212,7 +192,8 @@ int moe_b200_dispatch_static(const void* x, const int32_t* idx,
  * of perm: h = gelu_tanh(x W1g^T + b1g) * (x W1u^T + b1u), y = h W2^T + b2
  * (FeedForward.forward, model.py:173-190 with fine_tuning=False, dropout in
  * eval mode). M = N*k rows. bf16 runs on tcgen05 tensor cores with fp32
- * accumulation; fp32 runs on CUDA cores. h [M,f] and y [M,d] are outputs. */
+ * accumulation; fp32 runs on CUDA cores. h [M,f] and y [M,d] are outputs.
+ * flags: reserved, pass 0. */
 int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan,
                      int64_t M, int d, int f, int E, int dtype, int flags,
                      void* h, void* y, int32_t* status, void* stream);
@@ -261,19 +242,12 @@ int64_t moe_b200_front_exchange_ints(int64_t N, int E, int k);
 /* Part 3, small-N ("decode") variant, bf16 only, M <= moe_b200_decode_max_rows():
  * the same products as moe_b200_experts, arranged for weight streaming when
  * only a few rows reach each expert (the reference runs the same
- * FeedForward.forward whatever the row count, model.py:256-257). h [M,f] is
+ * FeedForward.forward whatever the row count, model.py:256-257), in ONE launch:
+ * the down tiles of a 32-row block start as soon as that block's GEGLU tiles
+ * have finished, while other blocks' weights are still streaming. h [M,f] is
  * written as usual; the down product is split over K into
  * moe_b200_decode_splits(f) fp32 buffers part[s][M][d] WITHOUT down.bias;
- * moe_b200_combine_decode sums them. */
-int moe_b200_experts_decode(const void* perm, const int32_t* offsets, const void* plan,
-                            int64_t M, int d, int f, int E, void* h, float* part,
-                            int32_t* status, void* stream);
-int moe_b200_decode_splits(int f);
-int64_t moe_b200_decode_max_rows(void);
-
-/* The same results as moe_b200_experts_decode from ONE launch: the down tiles of
- * a 32-row block start as soon as that block's GEGLU tiles have finished, while
- * other blocks' weights are still streaming (same arithmetic, model.py:174-184).
+ * moe_b200_combine_decode sums them.
  * `ready`: int32[MOE_B200_READY_INTS] completion counters, zeroed by this call.
  * The kernel's blocks wait on one another, so all of them must be resident: one
  * block per SM of an otherwise idle GPU. If other work holds SMs for seconds,
@@ -282,9 +256,11 @@ int64_t moe_b200_decode_max_rows(void);
 int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, const void* plan,
                                   int64_t M, int d, int f, int E, void* h, float* part,
                                   int32_t* ready, int32_t* status, void* stream);
+int moe_b200_decode_splits(int f);
+int64_t moe_b200_decode_max_rows(void);
 
 /* Part 3 for small N without waiting for the routing: the same partial sums
- * part[s][M][d] as moe_b200_experts_decode (row order of moe_b200_dispatch), but
+ * part[s][M][d] as moe_b200_experts_decode_fused (row order of moe_b200_dispatch), but
  * computed from the UNSORTED tokens x [N,d]: every expert's weights are streamed and
  * multiplied with all N tokens, and only the (token, expert) pairs of idx [N,k] are
  * stored. Nothing the kernel loads depends on idx/offsets, so under programmatic
@@ -301,7 +277,7 @@ int moe_b200_experts_decode_spec(const void* x, const int32_t* idx, const int32_
                                  void* stream);
 int moe_b200_decode_spec_rows(int64_t N);
 
-/* Parts 4+5 after moe_b200_experts_decode: y = sum_s part[s] + down.bias of
+/* Parts 4+5 after the small-N expert kernels: y = sum_s part[s] + down.bias of
  * the row's expert (idx), rounded to bf16, then the weighted sum and residual
  * of moe_b200_combine (model.py:184, 264-271, 319). */
 int moe_b200_combine_decode(const float* part, int ksplit, int64_t M,
@@ -349,8 +325,8 @@ enum {
   MOE_B200_EP_WS_AUX,          /* loss over all N_local*world tokens (model.py:213-216) */
   MOE_B200_EP_WS_SCRATCH, MOE_B200_EP_WS_CNT_SLOT0, /* int32 [E], all ranks */
   MOE_B200_EP_WS_OFFSETS_LOCAL, /* int32 [E_local+1] rows received per owned (virtual) expert */
-  MOE_B200_EP_WS_OWNER, MOE_B200_EP_WS_H,
-  MOE_B200_EP_WS_Y,            /* bf16 [cap][d], used only with MOE_B200_FLAG_EP_UNFUSED_RETURN */
+  MOE_B200_EP_WS_OWNER,        /* int32 owner[256], vmap[E][world]: written by moe_b200_ep_setup */
+  MOE_B200_EP_WS_H,            /* bf16 [cap][f] */
   MOE_B200_EP_WS_NUM
 };
 size_t moe_b200_ep_symm_bytes(int64_t N_local, int d, int E, int k, int world);
@@ -359,23 +335,45 @@ size_t moe_b200_ep_workspace_bytes(int64_t N_local, int d, int f, int E, int k, 
 int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, int world,
                                  size_t* h_offsets);
 
+/* Expert placement, uploaded once into the workspace (synchronous; call it again
+ * when the placement changes or the workspace is a new allocation). Experts are
+ * addressed by virtual ids v in [0, EV): h_owner[v] is the rank that runs v,
+ * h_vmap[e * world + r] the virtual expert that rank r's rows for expert e go to.
+ * Without replication EV = E and h_vmap[e * world + r] = e. Giving a popular
+ * expert several virtual ids on different ranks (with the same weights in each
+ * rank's plan) splits its rows between them. Also zeroes the status words. */
+int moe_b200_ep_setup(const int32_t* h_owner, const int32_t* h_vmap, int64_t N_local, int d, int f,
+                      int E, int k, int world, int EV, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
 /* One sharded forward on this rank: router on the local tokens, count exchange,
  * dispatch push to the expert owners, grouped GEMMs on the received rows with
  * the down pass writing straight to the token owners, combine (+ residual).
- * Experts are addressed by virtual ids v in [0, EV): h_owner[v] is the rank that
- * runs v, h_vmap[e * world + r] the virtual expert that rank r's rows for expert
- * e go to. Without replication EV = E and h_vmap[e * world + r] = e. Giving a
- * popular expert several virtual ids on different ranks (with the same weights
- * in each rank's plan) splits its rows between them. plan_local covers the
- * virtual experts this rank owns, in increasing virtual id.
+ * The workspace must have been prepared by moe_b200_ep_setup with the same
+ * shape. plan_local covers the E_local virtual experts this rank owns, in
+ * increasing virtual id. flags: reserved, pass 0.
+ * h_stage_events: NULL, or MOE_B200_EP_EV_NUM cudaEvent_t handles that the call
+ * records on `stream` at the stage boundaries (for per-stage timing; the waits
+ * on peers are part of the stages they end).
  * `epoch` is 1 on the first call and one more on every later call, the same on
  * all ranks. All ranks must make the same sequence of calls. A peer that never
  * arrives makes the bounded waits run out: status word = MOE_B200_DEV_TIMEOUT. */
 int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
                         const void* residual, int64_t N_local, int d, int f, int E, int k,
                         int dtype, int flags, int rank, int world, uint32_t epoch, int EV,
-                        const int32_t* h_owner, const int32_t* h_vmap, void* const* h_symm_bases,
-                        void* workspace, size_t workspace_bytes, void* out, void* stream);
+                        int E_local, void* const* h_symm_bases,
+                        void* workspace, size_t workspace_bytes, void* out,
+                        void* const* h_stage_events, void* stream);
+enum {
+  MOE_B200_EP_EV_START = 0, /* before the router */
+  MOE_B200_EP_EV_ROUTER,    /* router done */
+  MOE_B200_EP_EV_DISPATCH,  /* counts exchanged, own rows pushed to their owners */
+  MOE_B200_EP_EV_ARRIVED,   /* every source's rows have landed here */
+  MOE_B200_EP_EV_EXPERTS,   /* both grouped GEMMs done, outputs stored to the token owners */
+  MOE_B200_EP_EV_RETURNED,  /* every owner's outputs for the local tokens have landed */
+  MOE_B200_EP_EV_COMBINE,   /* combine done */
+  MOE_B200_EP_EV_NUM
+};
 
 /* Copy the 16 status words to the host after synchronising the stream.
  * Returns h_status[0]. Synchronous. */

@@ -28,8 +28,9 @@ def main():
     ap.add_argument("--topk", type=int, default=4)
     ap.add_argument("--bias", default="zipf1.1")
     ap.add_argument("--placement", default="strided")
-    ap.add_argument("--flags", type=int, default=0)
     ap.add_argument("--replicate", type=int, default=0, help="copy the N most popular experts to every rank")
+    ap.add_argument("--check-tokens", type=int, default=0,
+                    help="compare only the first N tokens of every rank with the oracle (0 = all)")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -55,7 +56,6 @@ def main():
     replicate = list(range(args.replicate)) if args.replicate else None   # Zipf bias: lowest ids are hottest
     m = ExpertParallelMOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda", placement=placement,
                           replicate=replicate).eval()
-    m.flags = args.flags
     m.to(device=dev, dtype=dt)
     with torch.no_grad():
         m.gate.weight.copy_(params["gate_w"])
@@ -78,16 +78,19 @@ def main():
         gathered = [torch.empty_like(logits) for _ in range(world)]
         dist.all_gather(gathered, logits)
         logits_all = torch.cat(gathered).cpu()
+        c = min(args.check_tokens, Nl) if args.check_tokens else Nl    # tokens are independent
         with torch.no_grad():
-            o = moe_oracle.moe_forward(x, params, k, logits=logits.cpu())
+            o = moe_oracle.moe_forward(x[:c], params, k, logits=logits.cpu()[:c])
             r_all = moe_oracle.route_from_logits(logits_all, k)
-        ref = o["out"] if residual is None else o["out"] + res
-        got = out.view(Nl, d).float().cpu()
+            r_own = moe_oracle.route_from_logits(logits.cpu(), k)
+        ref = o["out"] if residual is None else o["out"] + res[:c]
+        got = out.view(Nl, d).float().cpu()[:c]
         ties = moe_oracle.tie_rows(o["probs"], k)
         good = ~ties
         err = float((got - ref)[good].abs().max())
         bound = 2e-2 * float(ref.abs().max())
-        idx_ok = torch.equal(m.last["idx"].cpu()[good].long(), o["idx"][good])
+        good_all = ~moe_oracle.tie_rows(r_own["probs"], k)
+        idx_ok = torch.equal(m.last["idx"].cpu()[good_all].long(), r_own["idx"][good_all])
         aux_ok = abs(float(aux) - float(r_all["aux"])) <= 1e-5 * abs(float(r_all["aux"])) + 1e-7
         cnt0_ok = torch.equal(m.last["cnt_slot0"].cpu().long(), r_all["cnt_slot"][0])
         # rows received per owned expert = global count of that expert
@@ -104,6 +107,14 @@ def main():
         print(f"rank {rank} call {call}: status {status} idx {idx_ok} aux {aux_ok} cnt0 {cnt0_ok} "
               f"recv {recv_ok} max-abs {err:.4g} (bound {bound:.4g}) -> {'ok' if this else 'FAIL'}", flush=True)
         ok = ok and this
+        if call == 2:
+            # the NCCL all-to-all baseline computes the same block
+            with torch.no_grad():
+                out_n = m.forward_nccl(xd)
+            torch.cuda.synchronize()
+            err_n = float((out_n.view(Nl, d).float().cpu()[:c] - ref)[good].abs().max())
+            print(f"rank {rank} nccl baseline: max-abs {err_n:.4g} (bound {bound:.4g})", flush=True)
+            ok = ok and err_n <= bound
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.barrier()

@@ -67,14 +67,14 @@ class Plan:
                                       CODE[w1.dtype], self.ptr, nbytes, stream(dev)), "plan_build")
 
 
-def experts(perm, offsets, plan: Plan, flags=0):
+def experts(perm, offsets, plan: Plan):
     M, d = perm.shape
     dev = perm.device
     h = torch.empty(M, plan.f, dtype=perm.dtype, device=dev)
     y = torch.empty(M, d, dtype=perm.dtype, device=dev)
     status = torch.zeros(16, dtype=torch.int32, device=dev)
     check(lib.moe_b200_experts(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d, plan.f, plan.E,
-                               CODE[perm.dtype], flags, h.data_ptr(), y.data_ptr(),
+                               CODE[perm.dtype], 0, h.data_ptr(), y.data_ptr(),
                                status.data_ptr(), stream(dev)), "experts")
     return h, y, status
 
@@ -107,19 +107,6 @@ def experts_rows(perm, offsets, plan: Plan, ksplit: int):
     check(lib.moe_b200_experts_rows(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d, plan.f,
                                     plan.E, ksplit, h.data_ptr(), part.data_ptr(), ready.data_ptr(),
                                     status.data_ptr(), stream(dev)), "experts_rows")
-    return h, part, status
-
-
-def experts_decode(perm, offsets, plan: Plan):
-    M, d = perm.shape
-    dev = perm.device
-    splits = lib.moe_b200_decode_splits(plan.f)
-    h = torch.empty(M, plan.f, dtype=perm.dtype, device=dev)
-    part = torch.full((splits, M, d), float("nan"), dtype=torch.float32, device=dev)
-    status = torch.zeros(16, dtype=torch.int32, device=dev)
-    check(lib.moe_b200_experts_decode(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d, plan.f,
-                                      plan.E, h.data_ptr(), part.data_ptr(), status.data_ptr(),
-                                      stream(dev)), "experts_decode")
     return h, part, status
 
 

@@ -26,7 +26,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 
 def test_version_and_sizes():
-    assert lib.moe_b200_version() == 1
+    assert lib.moe_b200_version() == _cabi.ABI_VERSION
     n = _cabi.workspace_bytes(16384, 1024, 4096, 8, 2, _cabi.BF16)
     # perm + y (N*k*d) and h (N*k*f) dominate
     assert n > 2 * 16384 * (2 * 1024 + 4096) * 2

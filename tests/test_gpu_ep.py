@@ -22,10 +22,19 @@ def run_workers(world, extra=(), port=29541):
     assert r.stdout.count("EP_OK") == world, r.stdout[-3000:]
 
 
-@pytest.mark.parametrize("flags", [0, 4, 8])   # default; unfused return; one-CTA GEMM kernel
-def test_ep_world_1(cuda_device, flags):
-    run_workers(1, ["--tokens", "1000", "--experts", "8", "--topk", "2", "--flags", str(flags)],
-                port=29541)
+C4_SHAPE = ["--experts", "64", "--topk", "4", "--dmodel", "2048", "--dff", "1408", "--replicate", "16",
+            "--check-tokens", "1024"]
+
+
+def test_ep_world_1(cuda_device):
+    run_workers(1, ["--tokens", "1000", "--experts", "8", "--topk", "2"], port=29541)
+
+
+def test_ep_world_1_at_the_benchmarked_shape(cuda_device):
+    """The expert-parallel workload's own shape (d 2048, f 1408: 11 GEGLU tiles, not a multiple of
+    256; 64 experts, top-4, Zipf popularity, the 16 hottest experts copied) with one rank's
+    share of the tokens, through the expert-parallel entry point on one GPU."""
+    run_workers(1, ["--tokens", "8192", *C4_SHAPE], port=29540)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -38,6 +47,8 @@ def test_ep_multi_gpu(cuda_device, world):
     # the three most popular experts copied to every rank
     run_workers(world, ["--tokens", "4096", "--experts", "16", "--topk", "4", "--replicate", "3"],
                 port=29562 + world)
+    # the configuration bench.py --gpus N times: real d/f/E/k, 8192 tokens per rank, 16 copies
+    run_workers(world, ["--tokens", str(8192 * world), *C4_SHAPE], port=29572 + world)
 
 
 def test_missing_peer_ends_in_timeout_status(cuda_device):
@@ -62,17 +73,19 @@ def test_missing_peer_ends_in_timeout_status(cuda_device):
     bufs = [torch.zeros(sbytes + 1024, dtype=torch.uint8, device=dev) for _ in range(world)]
     bases = (C.c_void_p * world)(*[(b.data_ptr() + 1023) & ~1023 for b in bufs])
     wbytes = lib.moe_b200_ep_workspace_bytes(N, d, f, E, k, world)
-    ws = torch.empty(wbytes + 1024, dtype=torch.uint8, device=dev)
+    ws = torch.zeros(wbytes + 1024, dtype=torch.uint8, device=dev)
     ws_base = (ws.data_ptr() + 1023) & ~1023
     lay = _cabi.ep_workspace_layout(N, d, f, E, k, world)
     x = synthetic.make_input(N, d, seed=1).to(dt).to(dev)
     out = torch.empty_like(x)
     vmap = (C.c_int32 * (E * world))(*[e for e in range(E) for _ in range(world)])
+    check(lib.moe_b200_ep_setup((C.c_int32 * E)(*owner), vmap, N, d, f, E, k, world, E, ws_base, wbytes,
+                                helpers.stream(dev)), "ep_setup")
     torch.cuda.synchronize()
     check(lib.moe_b200_ep_forward(x.data_ptr(), dp["gate_w"].data_ptr(), dp["gate_b"].data_ptr(),
                                   plan.ptr, None, N, d, f, E, k, _cabi.BF16, 0, 0, world, 1, E,
-                                  (C.c_int32 * E)(*owner), vmap, bases, ws_base, wbytes,
-                                  out.data_ptr(), helpers.stream(dev)), "ep_forward")
+                                  len(local), bases, ws_base, wbytes,
+                                  out.data_ptr(), None, helpers.stream(dev)), "ep_forward")
     torch.cuda.synchronize()                      # returns: no wait is unbounded
     status = _cabi.read_status(ws_base + lay["status"], helpers.stream(dev))
     assert status[0] == _cabi.DEV_TIMEOUT
