@@ -19,11 +19,11 @@ DEV_OK, DEV_TIMEOUT, DEV_BAD_INDEX = 0, 1, 2
 
 WS_NAMES = (
     "status", "logits", "idx", "w", "psum_part", "psum", "aux", "scratch",
-    "cnt_slot", "offsets", "row_of", "perm", "h", "y", "part",
+    "cnt_slot", "offsets", "row_of", "perm", "h", "y", "part", "norm_w", "norm_c", "stats", "xn",
 )
 WS_NUM = len(WS_NAMES)
 
-_vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+_vp, _i, _i64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float
 
 # name -> (restype, argtypes); every symbol include/moe_b200.h declares
 SIGNATURES = {
@@ -33,6 +33,7 @@ SIGNATURES = {
     "moe_b200_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_plan_bytes": (_sz, [_i]),
     "moe_b200_plan_build": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "moe_b200_lora_merge": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _vp, _vp, _vp]),
     "moe_b200_router": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "moe_b200_router_blocks": (_i64, [_i64]),
     "moe_b200_dispatch": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
@@ -55,8 +56,14 @@ SIGNATURES = {
     "moe_b200_combine_decode": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _vp, _i64, _i, _i, _vp,
                                      _vp]),
     "moe_b200_combine": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
-    "moe_b200_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _sz,
-                              _vp, _vp]),
+    "moe_b200_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i64, _i, _i, _i, _i, _i, _i, _vp,
+                              _sz, _vp, _vp]),
+    "moe_b200_norm_fold": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "moe_b200_router_norm": (_i, [_vp, _vp, _vp, _f, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
+                                  _vp]),
+    "moe_b200_dispatch_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
+                                    _vp, _vp, _vp, _vp, _vp, _vp]),
+    "moe_b200_layernorm": (_i, [_vp, _vp, _vp, _f, _i64, _i, _i, _vp, _vp]),
     "moe_b200_ep_symm_bytes": (_sz, [_i64, _i, _i, _i, _i]),
     "moe_b200_ep_symm_layout": (_i, [_i64, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_ep_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),

@@ -66,6 +66,10 @@ static void layout(int64_t N, int d, int f, int E, int k, int dtype, size_t* off
       (dtype == MOE_B200_BF16 && M <= kDecodeMaxRows) ? (size_t)decode_splits(f) * M * d * sizeof(float) : 0;
   if (dtype == MOE_B200_BF16 && (int64_t)M > kDecodeMaxRows && (int64_t)M <= kRowsPathMaxRows)
     sizes[MOE_B200_WS_PART] = (size_t)rows_splits((int64_t)M, d, f, E) * M * d * sizeof(float);
+  sizes[MOE_B200_WS_NORM_W] = (size_t)E * d * es;
+  sizes[MOE_B200_WS_NORM_C] = (size_t)2 * E * sizeof(float);
+  sizes[MOE_B200_WS_STATS] = (size_t)N * 2 * sizeof(float);
+  sizes[MOE_B200_WS_XN] = (int64_t)M <= kRowsPathMaxRows ? (size_t)N * d * es : 0;
   size_t pos = 0;
   for (int i = 0; i < MOE_B200_WS_NUM; ++i) {
     off[i] = pos;
@@ -179,6 +183,58 @@ int moe_b200_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E
   if (!aligned16(x) || !aligned16(perm)) return set_error(MOE_B200_ERR_ALIGN, "x and perm must be 16-byte aligned");
   return launch_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
                          psum_part, psum, aux, status, (cudaStream_t)stream);
+}
+
+int moe_b200_norm_fold(const void* Wg, const void* bg, const void* norm_weight, const void* norm_bias,
+                       int E, int d, int dtype, void* out_Wn, float* out_c, void* stream) {
+  int rc = check_shape(0, d, 8, E, 1, dtype);
+  if (rc) return rc;
+  if (!Wg || !bg || !norm_weight || !norm_bias || !out_Wn || !out_c)
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  return launch_norm_fold(Wg, bg, norm_weight, norm_bias, E, d, dtype, out_Wn, out_c, (cudaStream_t)stream);
+}
+
+int moe_b200_router_norm(const void* x, const void* Wn, const float* c, float eps, int64_t N, int d,
+                         int E, int k, int dtype, float* out_logits, int32_t* out_idx, float* out_w,
+                         float* psum_part, float* out_stats, int32_t* status, void* stream) {
+  int rc = check_shape(N, d, 8, E, k, dtype);
+  if (rc) return rc;
+  if (N == 0) return 0;
+  if (!x || !Wn || !c || !out_idx || !out_w || !psum_part || !out_stats)
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!(eps >= 0.f)) return set_error(MOE_B200_ERR_SHAPE, "eps must be non-negative");
+  if (!aligned16(x) || !aligned16(Wn)) return set_error(MOE_B200_ERR_ALIGN, "x and Wn must be 16-byte aligned");
+  return launch_router(x, Wn, nullptr, N, d, E, k, dtype, out_logits, out_idx, out_w, psum_part, status,
+                       (cudaStream_t)stream, c, eps, out_stats);
+}
+
+int moe_b200_dispatch_norm(const void* x, const int32_t* idx, const float* stats,
+                           const void* norm_weight, const void* norm_bias, int64_t N, int d, int E,
+                           int k, int dtype, int32_t* scratch, int32_t* cnt_slot, int32_t* offsets,
+                           int32_t* row_of, void* perm, const float* psum_part, float* psum,
+                           float* aux, int32_t* status, void* stream) {
+  int rc = check_shape(N, d, 8, E, k, dtype);
+  if (rc) return rc;
+  if (!scratch || !cnt_slot || !offsets || !status) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (N > 0 && (!x || !idx || !row_of || !perm || !stats || !norm_weight || !norm_bias))
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (psum_part && (!psum || !aux)) return set_error(MOE_B200_ERR_NULL, "psum and aux are required with psum_part");
+  if (!aligned16(x) || !aligned16(perm)) return set_error(MOE_B200_ERR_ALIGN, "x and perm must be 16-byte aligned");
+  return launch_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
+                         psum_part, psum, aux, status, (cudaStream_t)stream, stats, norm_weight,
+                         norm_bias);
+}
+
+int moe_b200_layernorm(const void* x, const void* norm_weight, const void* norm_bias, float eps,
+                       int64_t N, int d, int dtype, void* out, void* stream) {
+  int rc = check_shape(N, d, 8, 1, 1, dtype);
+  if (rc) return rc;
+  if (N == 0) return 0;
+  if (!x || !norm_weight || !norm_bias || !out) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(x) || !aligned16(out) || !aligned16(norm_weight) || !aligned16(norm_bias))
+    return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  return launch_layernorm_rows(x, norm_weight, norm_bias, eps, N, d, dtype, out, nullptr,
+                               (cudaStream_t)stream);
 }
 
 int moe_b200_experts(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
@@ -314,8 +370,9 @@ int moe_b200_combine(const void* y, const int32_t* row_of, const float* w, const
 }
 
 int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* plan,
-                     const void* residual, int64_t N, int d, int f, int E, int k, int dtype,
-                     int flags, void* workspace, size_t workspace_bytes, void* out, void* stream) {
+                     const void* residual, const void* norm_weight, const void* norm_bias,
+                     float norm_eps, int64_t N, int d, int f, int E, int k, int dtype, int flags,
+                     void* workspace, size_t workspace_bytes, void* out, void* stream) {
   int rc = check_shape(N, d, f, E, k, dtype);
   if (rc) return rc;
   if (!workspace) return set_error(MOE_B200_ERR_NULL, "workspace is NULL");
@@ -324,6 +381,9 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   if (workspace_bytes < total) return set_error(MOE_B200_ERR_WORKSPACE, "workspace too small");
   if (((uintptr_t)workspace & 1023)) return set_error(MOE_B200_ERR_ALIGN, "workspace must be 1024-byte aligned");
   if (N > 0 && (!x || !Wg || !bg || !plan || !out)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  const bool norm = norm_weight != nullptr;
+  if (norm && (!norm_bias || !aligned16(norm_weight) || !aligned16(norm_bias) || !(norm_eps >= 0.f)))
+    return set_error(MOE_B200_ERR_NULL, "norm_bias (16-byte aligned) and a non-negative eps are required with norm_weight");
   char* ws = static_cast<char*>(workspace);
   int32_t* status = reinterpret_cast<int32_t*>(ws + off[MOE_B200_WS_STATUS]);
   float* logits = reinterpret_cast<float*>(ws + off[MOE_B200_WS_LOGITS]);
@@ -356,7 +416,18 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   if (!(counters && (flags & MOE_B200_FLAG_WS_CLEAN)))
     MOE_CUDA_CHECK(cudaMemsetAsync(
         status, 0, (counters ? MOE_B200_READY_OFFSET + MOE_B200_READY_INTS : MOE_B200_STATUS_INTS) * sizeof(int32_t), s));
-  if ((small_n || rows_path) && (front_small_supported(N, E, k, dtype) || front_split_supported(N, E, k, dtype))) {
+  const bool front = (small_n || rows_path) &&
+                     (front_small_supported(N, E, k, dtype) || front_split_supported(N, E, k, dtype));
+  float* stats = reinterpret_cast<float*>(ws + off[MOE_B200_WS_STATS]);
+  if (norm && N > 0 && (front || small_n || rows_path)) {
+    // up to 4096 rows the kernels read x through TMA: normalise the few rows once
+    void* xn = ws + off[MOE_B200_WS_XN];
+    rc = launch_layernorm_rows(x, norm_weight, norm_bias, norm_eps, N, d, dtype, xn, nullptr, s);
+    if (rc) return rc;
+    x = xn;
+  }
+  const bool fold = norm && N > 0 && x != ws + off[MOE_B200_WS_XN];
+  if (front) {
     // router and dispatch of up to a few hundred tokens in one launch
     // (beyond 128 tokens its blocks share the work and meet at a counter behind the status words)
     rc = launch_front_small(x, Wg, bg, N, d, E, k, logits, idx, w, cnt_slot, offsets, row_of, perm,
@@ -364,11 +435,24 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
                             status + MOE_B200_READY_OFFSET + MOE_B200_READY_INTS - 4, status);
     if (rc) return rc;
   } else {
-    rc = moe_b200_router(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, psum_part, status, stream);
-    if (rc) return rc;
-    rc = moe_b200_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
-                           N > 0 ? psum_part : nullptr, psum, aux, status, stream);
-    if (rc) return rc;
+    if (fold) {
+      void* wn = ws + off[MOE_B200_WS_NORM_W];
+      float* nc = reinterpret_cast<float*>(ws + off[MOE_B200_WS_NORM_C]);
+      rc = launch_norm_fold(Wg, bg, norm_weight, norm_bias, E, d, dtype, wn, nc, s);
+      if (rc) return rc;
+      rc = moe_b200_router_norm(x, wn, nc, norm_eps, N, d, E, k, dtype, logits, idx, w, psum_part,
+                                stats, status, stream);
+      if (rc) return rc;
+      rc = moe_b200_dispatch_norm(x, idx, stats, norm_weight, norm_bias, N, d, E, k, dtype, scratch,
+                                  cnt_slot, offsets, row_of, perm, psum_part, psum, aux, status, stream);
+      if (rc) return rc;
+    } else {
+      rc = moe_b200_router(x, Wg, bg, N, d, E, k, dtype, logits, idx, w, psum_part, status, stream);
+      if (rc) return rc;
+      rc = moe_b200_dispatch(x, idx, N, d, E, k, dtype, scratch, cnt_slot, offsets, row_of, perm,
+                             N > 0 ? psum_part : nullptr, psum, aux, status, stream);
+      if (rc) return rc;
+    }
   }
   if (small_n) {
     // few tokens per expert: weight streaming with narrow tiles and split-K

@@ -224,11 +224,17 @@ struct EpScatter {
 // ---- launchers implemented in the other translation units -----------------
 int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                   int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
-                  int32_t* status, cudaStream_t s);
+                  int32_t* status, cudaStream_t s, const float* norm_c = nullptr, float eps = 0.f,
+                  float* stats = nullptr);
 int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
                     int32_t* chunk_cnt, int32_t* cnt_slot, int32_t* offsets, int32_t* row_of,
                     void* perm, const float* psum_part, float* psum, float* aux, int32_t* status,
-                    cudaStream_t s);
+                    cudaStream_t s, const float* norm_stats = nullptr, const void* gamma = nullptr,
+                    const void* beta = nullptr);
+int launch_norm_fold(const void* Wg, const void* bg, const void* gamma, const void* beta, int E,
+                     int d, int dtype, void* Wn, float* c, cudaStream_t s);
+int launch_layernorm_rows(const void* x, const void* gamma, const void* beta, float eps, int64_t N,
+                          int d, int dtype, void* out, float* stats, cudaStream_t s);
 int launch_experts_simt(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
                         int d, int f, int E, int dtype, void* h, void* y, cudaStream_t s);
 int launch_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,

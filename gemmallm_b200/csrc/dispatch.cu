@@ -11,6 +11,9 @@
 // offsets, those before its own chunk for its base), ranks its chunk's
 // (token, slot) pairs in token order, and copies the rows. Rows of one expert
 // therefore stay in token order whatever the grid size.
+// With the caller's LayerNorm folded in (norm_stats != nullptr, see norm.cu) a row is
+// copied as (x - mean) * rstd * gamma + beta, with (mean, rstd) from the router
+// (reference model.py:311-312).
 #include <cooperative_groups.h>
 #include <stdio.h>
 #include "common.cuh"
@@ -33,7 +36,9 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
                 int k, int32_t* __restrict__ scratch, int32_t* __restrict__ cnt_slot,
                 int32_t* __restrict__ offsets, int32_t* __restrict__ row_of, T* __restrict__ perm,
                 const float* __restrict__ psum_part, int64_t router_blocks,
-                float* __restrict__ psum, float* __restrict__ aux, int32_t* __restrict__ status) {
+                float* __restrict__ psum, float* __restrict__ aux, int32_t* __restrict__ status,
+                const float* __restrict__ norm_stats, const T* __restrict__ gamma,
+                const T* __restrict__ beta) {
   cg::grid_group grid = cg::this_grid();
   extern __shared__ int s_int[];
   int* s_hist = s_int;             // [E]  chunk histogram, later totals
@@ -182,6 +187,18 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
         const int i = i0 + u * kThreads;
         if (i < items) {
           const int tl = i / pieces, pc = i - tl * pieces;
+          if (norm_stats != nullptr) {
+            // 16 bytes = 4 fp32 or 8 bf16 elements of row t0 + tl, columns from pc * kVec
+            const float mean = __ldg(&norm_stats[2 * (t0 + tl)]);
+            const float rstd = __ldg(&norm_stats[2 * (t0 + tl) + 1]);
+            T* e = reinterpret_cast<T*>(&v[u]);
+#pragma unroll
+            for (int q = 0; q < kVec; ++q) {
+              const float y = fmaf((to_f32(e[q]) - mean) * rstd, to_f32(__ldg(&gamma[pc * kVec + q])),
+                                   to_f32(__ldg(&beta[pc * kVec + q])));
+              from_f32(e[q], y);
+            }
+          }
           for (int j = 0; j < k; ++j) {
             const int row = s_row[tl * k + j];
             if (row >= 0) __stcs(reinterpret_cast<uint4*>(perm + (int64_t)row * d) + pc, v[u]);
@@ -257,7 +274,7 @@ int64_t dispatch_scratch_ints(int64_t N, int E, int k) {
 int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,
                     int32_t* scratch, int32_t* cnt_slot, int32_t* offsets, int32_t* row_of,
                     void* perm, const float* psum_part, float* psum, float* aux, int32_t* status,
-                    cudaStream_t s) {
+                    cudaStream_t s, const float* norm_stats, const void* gamma, const void* beta) {
   const size_t smem =
       sizeof(int) * (size_t)(4 * E + 1 + k * E + kChunk * k) + sizeof(float) * kThreads;
   const int ti = dtype == MOE_B200_BF16 ? 1 : 0;
@@ -279,7 +296,8 @@ int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, 
   void* args[] = {(void*)&x,        (void*)&idx,     (void*)&N,       (void*)&d,
                   (void*)&E,        (void*)&k,       (void*)&scratch, (void*)&cnt_slot,
                   (void*)&offsets,  (void*)&row_of,  (void*)&perm,    (void*)&psum_part,
-                  (void*)&router_blocks, (void*)&psum, (void*)&aux,   (void*)&status};
+                  (void*)&router_blocks, (void*)&psum, (void*)&aux,   (void*)&status,
+                  (void*)&norm_stats, (void*)&gamma, (void*)&beta};
   MOE_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem, s));
   return 0;
 }

@@ -13,6 +13,11 @@
 //   fp32: router_kernel. CUDA-core FMA (TF32 would perturb the logits), four
 //     tokens x eight experts per warp pass, warp-shuffle reductions, softmax and
 //     top-k with one expert slice per lane.
+// With the caller's LayerNorm folded in (NORM, norm.cu): Wg is the folded weight
+// Wn = Wg * gamma, the same pass over x also forms sum(x - x0) and sum((x - x0)^2)
+// per row (x0 = the row's first element: a shift that keeps the one-pass variance
+// well conditioned), and logits = rstd * (x . Wn - mean * c1) + c2. (mean, rstd)
+// go to `stats` for the dispatch kernel (reference model.py:311-312, 206).
 #include "common.cuh"
 
 namespace moe {
@@ -29,7 +34,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 router_kernel(const T* __restrict__ x, const T* __restrict__ Wg, const T* __restrict__ bg,
               int64_t N, int d, int E, int k, float* __restrict__ out_logits,
               int32_t* __restrict__ out_idx, float* __restrict__ out_w,
-              float* __restrict__ psum_part) {
+              float* __restrict__ psum_part, const float* __restrict__ norm_c, float eps,
+              float* __restrict__ stats) {
   extern __shared__ float smem[];
   float* s_logits = smem;                                     // [64][E]
   float* s_psum = smem + (size_t)kRouterTokensPerBlock * E;   // [kWarps][E]
@@ -49,6 +55,14 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ Wg, const T* __rest
       int64_t tt = t0 + t < N ? t0 + t : N - 1;  // clamp: duplicates are discarded below
       xrow[t] = x + tt * d;
     }
+    // LayerNorm statistics of the four rows, formed in the first pass over them
+    float shift[kTokGroup], mean[kTokGroup], rstd[kTokGroup];
+#pragma unroll
+    for (int t = 0; t < kTokGroup; ++t) {
+      shift[t] = norm_c != nullptr ? to_f32(xrow[t][0]) : 0.f;
+      mean[t] = 0.f;
+      rstd[t] = 1.f;
+    }
     for (int e0 = 0; e0 < E; e0 += kExpGroup) {
       float acc[kTokGroup][kExpGroup];
 #pragma unroll
@@ -56,10 +70,24 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ Wg, const T* __rest
 #pragma unroll
         for (int e = 0; e < kExpGroup; ++e) acc[t][e] = 0.f;
 
+      const bool first_pass = norm_c != nullptr && e0 == 0;
+      float s1[kTokGroup], s2[kTokGroup];
+#pragma unroll
+      for (int t = 0; t < kTokGroup; ++t) s1[t] = s2[t] = 0.f;
       for (int c = lane * 8; c < d; c += 256) {
         float xv[kTokGroup][8];
 #pragma unroll
         for (int t = 0; t < kTokGroup; ++t) load8(xrow[t] + c, xv[t]);
+        if (first_pass) {
+#pragma unroll
+          for (int t = 0; t < kTokGroup; ++t)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float dv = xv[t][i] - shift[t];
+              s1[t] += dv;
+              s2[t] = fmaf(dv, dv, s2[t]);
+            }
+        }
 #pragma unroll
         for (int e = 0; e < kExpGroup; ++e) {
           if (e0 + e < E) {
@@ -81,6 +109,24 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ Wg, const T* __rest
           for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
           acc[t][e] = v;
         }
+      if (first_pass) {
+#pragma unroll
+        for (int t = 0; t < kTokGroup; ++t) {
+          float a = s1[t], b = s2[t];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            a += __shfl_xor_sync(0xffffffffu, a, o);
+            b += __shfl_xor_sync(0xffffffffu, b, o);
+          }
+          const float m1 = a / (float)d;
+          mean[t] = shift[t] + m1;
+          rstd[t] = rsqrtf(fmaxf(b / (float)d - m1 * m1, 0.f) + eps);
+          if (lane == 0 && t0 + t < N) {
+            stats[2 * (t0 + t)] = mean[t];
+            stats[2 * (t0 + t) + 1] = rstd[t];
+          }
+        }
+      }
       if (lane == 0) {
 #pragma unroll
         for (int t = 0; t < kTokGroup; ++t)
@@ -88,7 +134,9 @@ router_kernel(const T* __restrict__ x, const T* __restrict__ Wg, const T* __rest
           for (int e = 0; e < kExpGroup; ++e)
             if (e0 + e < E)
               s_logits[(size_t)(warp * kTokPerWarp + g * kTokGroup + t) * E + e0 + e] =
-                  acc[t][e] + to_f32(bg[e0 + e]);
+                  norm_c != nullptr
+                      ? rstd[t] * (acc[t][e] - mean[t] * norm_c[e0 + e]) + norm_c[E + e0 + e]
+                      : acc[t][e] + to_f32(bg[e0 + e]);
       }
     }
   }
@@ -205,12 +253,23 @@ constexpr int kMmaTokPerWarp = 16;
 constexpr int kMmaUnroll = 4;  // 32-element chunks in flight per lane
 
 // NT = n-tiles (of 8 experts) per pass over x; E > 8*NT makes more passes.
-template <int NT>
+__device__ __forceinline__ void shifted_sums(const uint4& v, float shift, float& s1, float& s2) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = bf16_lo(w[i]) - shift, b = bf16_hi(w[i]) - shift;
+    s1 += a + b;
+    s2 = fmaf(a, a, fmaf(b, b, s2));
+  }
+}
+
+template <int NT, bool NORM>
 __global__ void __launch_bounds__(kWarps * 32)
 router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ Wg,
                   const __nv_bfloat16* __restrict__ bg, int64_t N, int d, int E, int k,
                   float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
-                  float* __restrict__ out_w, float* __restrict__ psum_part) {
+                  float* __restrict__ out_w, float* __restrict__ psum_part,
+                  const float* __restrict__ norm_c, float eps, float* __restrict__ stats) {
   extern __shared__ float smem[];
   const int ld = E + 1;                                           // row pitch: no bank conflicts
   float* s_logits = smem;                                          // [64][E+1]
@@ -231,6 +290,13 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     const uint4* w4 = reinterpret_cast<const uint4*>(Wg);
     const int nchunk = (d + 31) >> 5;
     const uint4 zero = make_uint4(0, 0, 0, 0);
+    // LayerNorm statistics of rows g and g+8: this lane's pieces, then the quad's four lanes
+    float sha = 0.f, shb = 0.f, s1a = 0.f, s2a = 0.f, s1b = 0.f, s2b = 0.f;
+    float mean_a = 0.f, rstd_a = 1.f, mean_b = 0.f, rstd_b = 1.f;
+    if (NORM) {
+      sha = __bfloat162float(x[ra * d]);
+      shb = __bfloat162float(x[rb * d]);
+    }
     for (int e_base = 0; e_base < E; e_base += 8 * NT) {
       float acc[NT][4];
 #pragma unroll
@@ -245,6 +311,10 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
           const bool ok = piece < row_pieces;
           A[u] = ok ? xa[piece] : zero;
           B[u] = ok ? xb[piece] : zero;
+          if (NORM && e_base == 0 && ok) {
+            shifted_sums(A[u], sha, s1a, s2a);
+            shifted_sums(B[u], shb, s1b, s2b);
+          }
         }
 #pragma unroll
         for (int u = 0; u < kMmaUnroll; ++u) {
@@ -259,19 +329,41 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
           }
         }
       }
+      if (NORM && e_base == 0) {
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+          s1a += __shfl_xor_sync(0xffffffffu, s1a, o);
+          s2a += __shfl_xor_sync(0xffffffffu, s2a, o);
+          s1b += __shfl_xor_sync(0xffffffffu, s1b, o);
+          s2b += __shfl_xor_sync(0xffffffffu, s2b, o);
+        }
+        const float ma = s1a / (float)d, mb = s1b / (float)d;
+        mean_a = sha + ma;
+        mean_b = shb + mb;
+        rstd_a = rsqrtf(fmaxf(s2a / (float)d - ma * ma, 0.f) + eps);
+        rstd_b = rsqrtf(fmaxf(s2b / (float)d - mb * mb, 0.f) + eps);
+        if (t == 0) {
+          if (tok0 + g < N) { stats[2 * (tok0 + g)] = mean_a; stats[2 * (tok0 + g) + 1] = rstd_a; }
+          if (tok0 + g + 8 < N) { stats[2 * (tok0 + g + 8)] = mean_b; stats[2 * (tok0 + g + 8) + 1] = rstd_b; }
+        }
+      }
       // accumulator layout: c0,c1 -> token g, experts 2t,2t+1; c2,c3 -> token g+8
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        const int e = e_base + 8 * j + 2 * t;
-        if (e < E) {
-          const float b = __bfloat162float(bg[e]);
-          my_logits[g * ld + e] = acc[j][0] + b;
-          my_logits[(g + 8) * ld + e] = acc[j][2] + b;
-        }
-        if (e + 1 < E) {
-          const float b = __bfloat162float(bg[e + 1]);
-          my_logits[g * ld + e + 1] = acc[j][1] + b;
-          my_logits[(g + 8) * ld + e + 1] = acc[j][3] + b;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int e = e_base + 8 * j + 2 * t + h;
+          if (e < E) {
+            if (NORM) {
+              const float c1 = norm_c[e], c2 = norm_c[E + e];
+              my_logits[g * ld + e] = rstd_a * (acc[j][h] - mean_a * c1) + c2;
+              my_logits[(g + 8) * ld + e] = rstd_b * (acc[j][2 + h] - mean_b * c1) + c2;
+            } else {
+              const float b = __bfloat162float(bg[e]);
+              my_logits[g * ld + e] = acc[j][h] + b;
+              my_logits[(g + 8) * ld + e] = acc[j][2 + h] + b;
+            }
+          }
         }
       }
     }
@@ -337,42 +429,54 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   }
 }
 
-template <int NT>
+template <int NT, bool NORM>
 int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
-               float* out_logits, int32_t* out_idx, float* out_w, float* psum_part, cudaStream_t s) {
+               float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+               const float* norm_c, float eps, float* stats, cudaStream_t s) {
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
   const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E);
   static PerDeviceOnce once;
   if (smem > 48 * 1024) {
-    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT>, 80 * 1024);
+    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM>, 80 * 1024);
     if (rc) return rc;
   }
-  router_mma_kernel<NT><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
+  router_mma_kernel<NT, NORM><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
-      static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part);
+      static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part,
+      norm_c, eps, stats);
   MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
 
+template <bool NORM>
+int launch_mma_nt(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+                  float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+                  const float* norm_c, float eps, float* stats, cudaStream_t s) {
+  if (E <= 8) return launch_mma<1, NORM>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, norm_c, eps, stats, s);
+  if (E <= 16) return launch_mma<2, NORM>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, norm_c, eps, stats, s);
+  if (E <= 32) return launch_mma<4, NORM>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, norm_c, eps, stats, s);
+  return launch_mma<8, NORM>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, norm_c, eps, stats, s);
+}
+
 }  // namespace
 
+// norm_c == nullptr: logits = x Wg^T + bg. Otherwise Wg is the folded weight of norm.cu,
+// norm_c its [2E] constants, and (mean, rstd) of every row is written to stats [N][2].
 int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                   int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
-                  int32_t* status, cudaStream_t s) {
+                  int32_t* status, cudaStream_t s, const float* norm_c, float eps, float* stats) {
   (void)status;
   if (N == 0) return 0;
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
   const size_t smem = sizeof(float) * (size_t)(kRouterTokensPerBlock + kWarps) * E;
   if (dtype == MOE_B200_BF16) {
-    if (E <= 8) return launch_mma<1>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
-    if (E <= 16) return launch_mma<2>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
-    if (E <= 32) return launch_mma<4>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
-    return launch_mma<8>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, s);
-  } else {
-    router_kernel<float><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
-        static_cast<const float*>(x), static_cast<const float*>(Wg), static_cast<const float*>(bg),
-        N, d, E, k, out_logits, out_idx, out_w, psum_part);
+    if (norm_c != nullptr)
+      return launch_mma_nt<true>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, norm_c, eps, stats, s);
+    return launch_mma_nt<false>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, nullptr, 0.f, nullptr, s);
   }
+  router_kernel<float><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
+      static_cast<const float*>(x), static_cast<const float*>(Wg), static_cast<const float*>(bg),
+      N, d, E, k, out_logits, out_idx, out_w, psum_part, norm_c, eps, stats);
   MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

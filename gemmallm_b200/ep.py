@@ -20,7 +20,7 @@ import torch.nn as nn
 
 from . import _cabi
 from ._cabi import lib, check
-from .moe import FeedForward, _Plan, _dtype_code, _stream
+from .moe import FeedForward, _MergedLora, _Plan, _dtype_code, _stream
 
 
 def strided_placement(num_experts: int, world: int) -> list[int]:
@@ -110,6 +110,8 @@ class ExpertParallelMOE(nn.Module):
         self.top_k = top_k
         self.epoch = 0
         self._plan = _Plan()
+        self._plan_ft = _Plan()
+        self._lora = _MergedLora()
         self._state = None
         self._stage_events = None    # ctypes array of cudaEvent_t, see time_stages()
         self.last = None
@@ -164,9 +166,8 @@ class ExpertParallelMOE(nn.Module):
     def forward(self, tensor: torch.Tensor, fine_tuning: bool = False, *,
                 residual: torch.Tensor | None = None):
         """Local tokens [B,S,d] (bf16, same count on every rank) ->
-        ([B,S,d], load-balancing loss over the tokens of all ranks)."""
-        if fine_tuning:
-            raise NotImplementedError("the LoRA branch (fine_tuning=True) is not implemented")
+        ([B,S,d], load-balancing loss over the tokens of all ranks). ``fine_tuning=True``
+        runs the owned experts with their LoRA branches folded in, as ``MOE.forward`` does."""
         if self.training and len(self.experts) and next(iter(self.experts.values())).dropout.p > 0:
             raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
         if not tensor.is_cuda:
@@ -185,7 +186,15 @@ class ExpertParallelMOE(nn.Module):
         with torch.cuda.device(dev):
             st = self._setup(N, dev)
             local = [self.experts[str(e)] for e in self.local_ids]
-            plan = self._plan.get(local, d, f, dtype, dev) if local else None
+            if not local:
+                plan = None
+            elif fine_tuning:
+                # LoRA branches (model.py:175-179,185-189) folded into merged copies of the owned experts
+                uniq = sorted(set(self.local_ids))
+                merged = dict(zip(uniq, self._lora.get([self.experts[str(e)] for e in uniq], dtype, dev)))
+                plan = self._plan_ft.get([merged[e] for e in self.local_ids], d, f, dtype, dev)
+            else:
+                plan = self._plan.get(local, d, f, dtype, dev)
             self.epoch += 1
             check(lib.moe_b200_ep_forward(
                 x.data_ptr(), self.gate.weight.data_ptr(), self.gate.bias.data_ptr(), plan, res_ptr,

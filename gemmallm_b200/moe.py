@@ -30,33 +30,62 @@ def _stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _merged_lora(ex):
-    """The expert's two Linears with the LoRA branch folded in, as fresh tensors:
-    W' = W + s * B A and b' = b + s * (B a + b_lora), which makes
-    x W'^T + b' = x W^T + b + s * (B (A x + a) + b_lora), the fine_tuning=True
-    expression of model.py:175-179 and 185-189. Computed in fp32, stored in the
-    parameter dtype."""
-    s = ex.lora_scale
-    out = []
-    for lin, a, b in ((ex.gate_and_up, ex.lora_gate_and_up_a, ex.lora_gate_and_up_b),
-                      (ex.down, ex.lora_down_a, ex.lora_down_b)):
-        bw, aw = b.weight.float(), a.weight.float()
-        w = lin.weight.float() + s * (bw @ aw)
-        bias = lin.bias.float() + s * (bw @ a.bias.float() + b.bias.float())
-        out += [w.to(lin.weight.dtype).contiguous(), bias.to(lin.bias.dtype).contiguous()]
-    return out
+_LORA_NAMES = ("gate_and_up", "down", "lora_gate_and_up_a", "lora_gate_and_up_b", "lora_down_a",
+               "lora_down_b")
 
 
 class _MergedExpert:
-    """Stand-in with the attribute shape _Plan expects (gate_and_up/down with .weight/.bias)."""
+    """An expert's two Linears with the LoRA branch folded in (moe_b200_lora_merge):
+    W' = W + s * B A and b' = b + s * (B a + b_lora), which makes
+    x W'^T + b' = x W^T + b + s * (B (A x + a) + b_lora), the fine_tuning=True
+    expression of model.py:175-179 and 185-189. Has the attribute shape _Plan expects
+    (gate_and_up/down with .weight/.bias); the buffers are written in place on every
+    refresh, so a plan built on them stays valid."""
 
     class _Lin:
         def __init__(self, w, b):
             self.weight, self.bias = w, b
 
     def __init__(self, ex):
-        w1, b1, w2, b2 = _merged_lora(ex)
-        self.gate_and_up, self.down = self._Lin(w1, b1), self._Lin(w2, b2)
+        self.gate_and_up = self._Lin(torch.empty_like(ex.gate_and_up.weight), torch.empty_like(ex.gate_and_up.bias))
+        self.down = self._Lin(torch.empty_like(ex.down.weight), torch.empty_like(ex.down.bias))
+
+    def refresh(self, ex, dtype: int, stream: int) -> None:
+        for lin, a, b, out in ((ex.gate_and_up, ex.lora_gate_and_up_a, ex.lora_gate_and_up_b, self.gate_and_up),
+                               (ex.down, ex.lora_down_a, ex.lora_down_b, self.down)):
+            check(lib.moe_b200_lora_merge(
+                lin.weight.data_ptr(), lin.bias.data_ptr(), a.weight.data_ptr(), a.bias.data_ptr(),
+                b.weight.data_ptr(), b.bias.data_ptr(), float(ex.lora_scale), lin.out_features,
+                lin.in_features, a.out_features, dtype, out.weight.data_ptr(), out.bias.data_ptr(),
+                stream), "lora_merge")
+
+
+class _MergedLora:
+    """Merged copies of a list of experts, refreshed only when one of their twelve tensors
+    was replaced or written since the last call (data pointer and torch's version counter),
+    so that a fine_tuning=True forward on unchanged parameters launches no merge kernel and
+    rebuilds no plan."""
+
+    def __init__(self):
+        self.key = None
+        self.merged = None
+
+    def get(self, experts, dtype: int, device: torch.device):
+        params = [p for ex in experts for n in _LORA_NAMES
+                  for p in (getattr(ex, n).weight, getattr(ex, n).bias)]
+        for p in params:
+            if p.device != device or _dtype_code(p) != dtype or not p.is_contiguous():
+                raise ValueError("expert and LoRA parameters must be contiguous and share the "
+                                 "input's device and dtype")
+        shape_key = (dtype, str(device), tuple(tuple(p.shape) for p in params))
+        key = (shape_key, tuple((p.data_ptr(), p._version) for p in params))
+        if self.key is None or self.key[0] != shape_key:
+            self.merged = [_MergedExpert(ex) for ex in experts]
+        if key != self.key:
+            for ex, mg in zip(experts, self.merged):
+                mg.refresh(ex, dtype, _stream(device))
+            self.key = key
+        return self.merged
 
 
 class _Plan:
@@ -118,13 +147,14 @@ class FeedForward(nn.Module):
         self.lora_down_b = nn.Linear(lora_rank, hidden_size)
         self._plan = _Plan()
         self._plan_ft = _Plan()
+        self._lora = _MergedLora()
         self._offsets = None   # ((rows, device), int32 [0, rows]) of the last call
 
     def forward(self, tensor: torch.Tensor, fine_tuning: bool = False) -> torch.Tensor:
         """y = down(gelu_tanh(gate) * up) for every row, through the grouped
         expert kernels with a single group. ``fine_tuning=True`` adds the LoRA
-        branch (model.py:175-179,185-189) by folding it into the two weight
-        matrices for this call; forward only (the kernels have no backward)."""
+        branch (model.py:175-179,185-189) folded into merged copies of the two weight
+        matrices (refreshed when a parameter changes); forward only."""
         if self.training and self.dropout.p > 0:
             raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
         if not tensor.is_cuda:
@@ -136,7 +166,7 @@ class FeedForward(nn.Module):
         dev = x.device
         with torch.cuda.device(dev):
             plan = (self._plan_ft if fine_tuning else self._plan).get(
-                [_MergedExpert(self)] if fine_tuning else [self], d, f, dtype, dev)
+                self._lora.get([self], dtype, dev) if fine_tuning else [self], d, f, dtype, dev)
             if self._offsets is None or self._offsets[0] != (M, str(dev)):
                 self._offsets = ((M, str(dev)), torch.tensor([0, M], dtype=torch.int32, device=dev))
             offsets = self._offsets[1]
@@ -173,6 +203,7 @@ class MOE(nn.Module):
         self.top_k = top_k
         self._plan = _Plan()
         self._plan_ft = _Plan()
+        self._lora = _MergedLora()
         self._ws = None
         self._ws_key = None
         self.last = None  # views into the workspace of the most recent call
@@ -201,13 +232,18 @@ class MOE(nn.Module):
         return buf[start:start + nbytes].view(dtype).view(*shape)
 
     def forward(self, tensor: torch.Tensor, fine_tuning: bool = False, *,
-                residual: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+                residual: torch.Tensor | None = None,
+                norm: nn.LayerNorm | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         """``tensor`` [B,S,d] -> ([B,S,d] in the input dtype, load-balancing loss).
 
         With ``residual`` (same shape and dtype) the caller's skip connection
-        (model.py:319) is added inside the combine kernel. ``fine_tuning=True``
+        (model.py:319) is added inside the combine kernel. With ``norm`` (the caller's
+        ``norm2``, model.py:298,312) ``tensor`` is the tensor BEFORE that LayerNorm: the
+        block normalises it on the fly in its router and dispatch kernels, so
+        ``moe(x, residual=x, norm=layer.norm2)`` replaces model.py:311-319. ``fine_tuning=True``
         runs the experts with their LoRA branches (model.py:175-179,185-189)
-        folded into per-call merged weights; forward only."""
+        folded into merged copies of their weights (refreshed when a parameter
+        changes); forward only."""
         if self.training and self.experts[0].dropout.p > 0:
             raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
         if not tensor.is_cuda:
@@ -229,16 +265,23 @@ class MOE(nn.Module):
         gw, gb = self.gate.weight, self.gate.bias
         if gw.device != dev or _dtype_code(gw) != dtype:
             raise ValueError("gate parameters must share the input's device and dtype")
+        nw = nb = None
+        eps = 0.0
+        if norm is not None:
+            if (tuple(norm.normalized_shape) != (d,) or norm.weight is None or norm.bias is None
+                    or norm.weight.device != dev or _dtype_code(norm.weight) != dtype):
+                raise ValueError("norm must be an affine LayerNorm over the last dimension with "
+                                 "the input's device and dtype")
+            nw, nb, eps = norm.weight.data_ptr(), norm.bias.data_ptr(), float(norm.eps)
         out = torch.empty_like(x)
         with torch.cuda.device(dev):
             if fine_tuning:
-                merged = [_MergedExpert(ex) for ex in self.experts]   # kept alive until the call returns
-                plan = self._plan_ft.get(merged, d, f, dtype, dev)
+                plan = self._plan_ft.get(self._lora.get(list(self.experts), dtype, dev), d, f, dtype, dev)
             else:
                 plan = self._plan.get(self.experts, d, f, dtype, dev)
             _, base, nbytes, _ = self._workspace(N, dtype, dev)
             check(lib.moe_b200_forward(x.data_ptr(), gw.data_ptr(), gb.data_ptr(), plan, res_ptr,
-                                       N, d, f, E, k, dtype, _cabi.FLAG_WS_CLEAN, base, nbytes,
+                                       nw, nb, eps, N, d, f, E, k, dtype, _cabi.FLAG_WS_CLEAN, base, nbytes,
                                        out.data_ptr(), _stream(dev)), "forward")
         self.last = {
             "logits": self._view("logits", torch.float32, (N, E)),

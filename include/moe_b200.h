@@ -93,6 +93,10 @@ enum {
   MOE_B200_WS_Y,          /* T [N*k, d]    expert outputs, sorted order (model.py:184) */
   MOE_B200_WS_PART,       /* float [splits, N*k, d] split-K partial sums of the small-N path
                            * (present when N*k <= moe_b200_decode_max_rows(), bf16) */
+  MOE_B200_WS_NORM_W,     /* T [E,d]       gate.weight * norm weight (moe_b200_norm_fold) */
+  MOE_B200_WS_NORM_C,     /* float [2E]    constants of the folded router */
+  MOE_B200_WS_STATS,      /* float [N,2]   mean and 1/std of every row of x */
+  MOE_B200_WS_XN,         /* T [N,d]       normalised rows, calls of up to 4096 rows only */
   MOE_B200_WS_NUM
 };
 
@@ -125,6 +129,17 @@ int moe_b200_plan_build(const void* const* h_W1, const void* const* h_b1,
                         const void* const* h_W2, const void* const* h_b2,
                         int E, int d, int f, int dtype,
                         void* plan, size_t plan_bytes, void* stream);
+
+/* An expert Linear with its LoRA branch folded in (fine_tuning=True,
+ * model.py:175-179 and 185-189): out_W = W + scale * B A, out_b = b + scale *
+ * (B a_bias + b_lora), so that x out_W^T + out_b = x W^T + b + scale * (B (A x +
+ * a_bias) + b_lora). W [out,in], A [rank,in] (lora_*_a.weight), a_bias [rank],
+ * B [out,rank] (lora_*_b.weight), b_lora [out]; fp32 arithmetic, one rounding.
+ * The merged tensors go into a plan like any other parameters. */
+int moe_b200_lora_merge(const void* W, const void* b, const void* A, const void* a_bias,
+                        const void* B, const void* b_lora, float scale,
+                        int out_features, int in_features, int rank, int dtype,
+                        void* out_W, void* out_b, void* stream);
 
 /* Part 1 — router: logits = x Wg^T + bg (model.py:206), fp32 softmax
  * (model.py:207), top-k (model.py:210), renormalise (model.py:219-223), and
@@ -292,12 +307,52 @@ int moe_b200_combine(const void* y, const int32_t* row_of, const float* w,
                      const void* residual, int64_t N, int d, int k, int dtype,
                      void* out, void* stream);
 
+/* ---- The caller's LayerNorm folded into the block -----------------------------
+ * In the reference the block's input is LayerNorm(x) (norm2, model.py:298,311-312).
+ * With norm_weight/norm_bias [d] given, x is the tensor BEFORE that norm: the
+ * router forms the row statistics in its own pass over x and computes the logits
+ * of the normalised row from folded weights, the dispatch normalises the rows
+ * while it copies them, and the normalised tensor is never written to memory.
+ * (eps inside the square root, biased variance: torch.nn.LayerNorm.) */
+
+/* Wn [E,d] = Wg * norm_weight (rounded to T), c [2E]: c[e] = sum_j Wn[e][j],
+ * c[E+e] = sum_j norm_bias[j] * Wg[e][j] + bg[e]; then
+ * LayerNorm(x) . Wg[e] + bg[e] = rstd * (x . Wn[e] - mean * c[e]) + c[E+e]. */
+int moe_b200_norm_fold(const void* Wg, const void* bg, const void* norm_weight,
+                       const void* norm_bias, int E, int d, int dtype,
+                       void* out_Wn, float* out_c, void* stream);
+
+/* moe_b200_router on LayerNorm(x) (model.py:311-312, 206-223): Wn and c from
+ * moe_b200_norm_fold; out_stats float [N,2] receives (mean, 1/std) of every row. */
+int moe_b200_router_norm(const void* x, const void* Wn, const float* c, float eps,
+                         int64_t N, int d, int E, int k, int dtype,
+                         float* out_logits, int32_t* out_idx, float* out_w,
+                         float* psum_part, float* out_stats, int32_t* status, void* stream);
+
+/* moe_b200_dispatch that writes LayerNorm(x) rows into perm: stats from
+ * moe_b200_router_norm, norm_weight/norm_bias [d]. */
+int moe_b200_dispatch_norm(const void* x, const int32_t* idx, const float* stats,
+                           const void* norm_weight, const void* norm_bias,
+                           int64_t N, int d, int E, int k, int dtype,
+                           int32_t* scratch, int32_t* cnt_slot, int32_t* offsets,
+                           int32_t* row_of, void* perm,
+                           const float* psum_part, float* psum, float* aux,
+                           int32_t* status, void* stream);
+
+/* out [N,d] = LayerNorm(x) row by row (model.py:298,312); what moe_b200_forward
+ * runs in front of calls of up to 4096 rows, whose kernels read x through TMA. */
+int moe_b200_layernorm(const void* x, const void* norm_weight, const void* norm_bias, float eps,
+                       int64_t N, int d, int dtype, void* out, void* stream);
+
 /* The whole block: MOE.forward (model.py:200-276) for x [N,d] -> out [N,d],
  * with the optional fused residual. Wg [E,d], bg [E] are gate.weight/bias
- * (model.py:195). After it the workspace holds logits, idx, w, counts,
+ * (model.py:195). norm_weight/norm_bias: NULL, or the LayerNorm in front of the
+ * block (see above; x is then the un-normalised tensor, which is usually also
+ * the residual). After it the workspace holds logits, idx, w, counts,
  * offsets, psum and the loss (see moe_b200_workspace_layout). */
 int moe_b200_forward(const void* x, const void* Wg, const void* bg,
                      const void* plan, const void* residual,
+                     const void* norm_weight, const void* norm_bias, float norm_eps,
                      int64_t N, int d, int f, int E, int k, int dtype, int flags,
                      void* workspace, size_t workspace_bytes,
                      void* out, void* stream);

@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--bias", default="zipf1.1")
     ap.add_argument("--placement", default="strided")
     ap.add_argument("--replicate", type=int, default=0, help="copy the N most popular experts to every rank")
+    ap.add_argument("--lora", action="store_true", help="fine_tuning=True with random LoRA tensors")
     ap.add_argument("--check-tokens", type=int, default=0,
                     help="compare only the first N tokens of every rank with the oracle (0 = all)")
     args = ap.parse_args()
@@ -66,12 +67,31 @@ def main():
             ex.gate_and_up.bias.copy_(params["b1"][e])
             ex.down.weight.copy_(params["w2"][e])
             ex.down.bias.copy_(params["b2"][e])
+    lora = None
+    if args.lora:
+        # every expert's LoRA tensors from its own seed, so that the oracle (all experts) and the
+        # ranks (their own experts) agree
+        lora = []
+        for e in range(E):
+            ge = torch.Generator().manual_seed(900 + e)
+            rnd = lambda *shape: synthetic.round_to(torch.randn(*shape, generator=ge) * 0.05, dt)
+            lora.append({"scale": 2.0, "gu_a_w": rnd(16, d), "gu_a_b": rnd(16), "gu_b_w": rnd(2 * f, 16),
+                         "gu_b_b": rnd(2 * f), "dn_a_w": rnd(16, f), "dn_a_b": rnd(16),
+                         "dn_b_w": rnd(d, 16), "dn_b_b": rnd(d)})
+        with torch.no_grad():
+            for e in sorted(set(m.local_ids)):
+                ex, l = m.experts[str(e)], lora[e]
+                assert ex.lora_scale == l["scale"]
+                ex.lora_gate_and_up_a.weight.copy_(l["gu_a_w"]); ex.lora_gate_and_up_a.bias.copy_(l["gu_a_b"])
+                ex.lora_gate_and_up_b.weight.copy_(l["gu_b_w"]); ex.lora_gate_and_up_b.bias.copy_(l["gu_b_b"])
+                ex.lora_down_a.weight.copy_(l["dn_a_w"]); ex.lora_down_a.bias.copy_(l["dn_a_b"])
+                ex.lora_down_b.weight.copy_(l["dn_b_w"]); ex.lora_down_b.bias.copy_(l["dn_b_b"])
     xd = x.to(dt).to(dev).view(1, Nl, d)
     rd = res.to(dt).to(dev).view(1, Nl, d)
     ok = True
     for call, residual in enumerate((None, rd, None)):
         with torch.no_grad():
-            out, aux = m(xd, residual=residual)
+            out, aux = m(xd, fine_tuning=args.lora, residual=residual)
         torch.cuda.synchronize()
         status = m.device_status()
         logits = m.last["logits"].clone()
@@ -80,7 +100,7 @@ def main():
         logits_all = torch.cat(gathered).cpu()
         c = min(args.check_tokens, Nl) if args.check_tokens else Nl    # tokens are independent
         with torch.no_grad():
-            o = moe_oracle.moe_forward(x[:c], params, k, logits=logits.cpu()[:c])
+            o = moe_oracle.moe_forward(x[:c], params, k, logits=logits.cpu()[:c], lora=lora)
             r_all = moe_oracle.route_from_logits(logits_all, k)
             r_own = moe_oracle.route_from_logits(logits.cpu(), k)
         ref = o["out"] if residual is None else o["out"] + res[:c]
@@ -107,7 +127,7 @@ def main():
         print(f"rank {rank} call {call}: status {status} idx {idx_ok} aux {aux_ok} cnt0 {cnt0_ok} "
               f"recv {recv_ok} max-abs {err:.4g} (bound {bound:.4g}) -> {'ok' if this else 'FAIL'}", flush=True)
         ok = ok and this
-        if call == 2:
+        if call == 2 and not args.lora:
             # the NCCL all-to-all baseline computes the same block
             with torch.no_grad():
                 out_n = m.forward_nccl(xd)

@@ -49,11 +49,11 @@ def test_bad_shapes_are_rejected_on_the_host():
     assert lib.moe_b200_workspace_bytes(16, 1024, 4096, 8, 2, 7) == 0             # dtype
     assert b"dtype" in lib.moe_b200_last_error_string()
     # NULL workspace: error code, nothing launched
-    rc = lib.moe_b200_forward(None, None, None, None, None, 16, 1024, 4096, 8, 2, _cabi.BF16, 0,
+    rc = lib.moe_b200_forward(None, None, None, None, None, None, None, 0.0, 16, 1024, 4096, 8, 2, _cabi.BF16, 0,
                               None, 0, None, None)
     assert rc == -1
     # misaligned workspace
-    rc = lib.moe_b200_forward(None, None, None, None, None, 16, 1024, 4096, 8, 2, _cabi.BF16, 0,
+    rc = lib.moe_b200_forward(None, None, None, None, None, None, None, 0.0, 16, 1024, 4096, 8, 2, _cabi.BF16, 0,
                               8, 1 << 40, None, None)
     assert rc == -3
 

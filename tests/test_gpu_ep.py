@@ -30,6 +30,11 @@ def test_ep_world_1(cuda_device):
     run_workers(1, ["--tokens", "1000", "--experts", "8", "--topk", "2"], port=29541)
 
 
+def test_ep_world_1_with_lora_branches(cuda_device):
+    """fine_tuning=True through the expert-parallel module (model.py:175-179,185-189)."""
+    run_workers(1, ["--tokens", "1024", "--experts", "8", "--topk", "2", "--lora"], port=29539)
+
+
 def test_ep_world_1_at_the_benchmarked_shape(cuda_device):
     """The expert-parallel workload's own shape (d 2048, f 1408: 11 GEGLU tiles, not a multiple of
     256; 64 experts, top-4, Zipf popularity, the 16 hottest experts copied) with one rank's
@@ -47,6 +52,7 @@ def test_ep_multi_gpu(cuda_device, world):
     # the three most popular experts copied to every rank
     run_workers(world, ["--tokens", "4096", "--experts", "16", "--topk", "4", "--replicate", "3"],
                 port=29562 + world)
+    run_workers(world, ["--tokens", "2048", "--experts", "16", "--topk", "4", "--lora"], port=29582 + world)
     # the configuration bench.py --gpus N times: real d/f/E/k, 8192 tokens per rank, 16 copies
     run_workers(world, ["--tokens", str(8192 * world), *C4_SHAPE], port=29572 + world)
 

@@ -276,6 +276,56 @@ def test_c4_shape_bf16(cuda_device):
     assert len(set(o["idx"].flatten().tolist())) >= 48      # the slice reaches the tail experts
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N,d,E,f,k", [(5000, 256, 8, 512, 2), (3000, 1024, 64, 264, 4), (100, 128, 8, 256, 2),
+                                       (1, 64, 8, 128, 2), (1500, 512, 16, 384, 2)])
+def test_layernorm_folded_into_the_block(cuda_device, N, d, E, f, k, dtype):
+    """The caller's norm2 (model.py:298,311-312) inside the block: the router forms the row
+    statistics and the logits of the normalised row, the dispatch normalises while it copies
+    (calls of up to 4096 rows normalise their few rows in a kernel of their own). Reference:
+    F.layer_norm in fp32 on the same values, then the oracle; the residual is the tensor
+    before the norm (model.py:310,319). Input rows get a mean far from zero and a per-row
+    scale, as a residual stream has."""
+    import torch.nn.functional as F
+    params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=N + 3), dtype)
+    params["w1"] *= 2.0
+    g = torch.Generator().manual_seed(N + d)
+    x = synthetic.make_input(N, d, seed=N + 4) * (0.5 + 2.0 * torch.rand(N, 1, generator=g)) \
+        + 3.0 * torch.randn(N, 1, generator=g)
+    x = synthetic.round_to(x, dtype)
+    gamma = synthetic.round_to(1.0 + 0.2 * torch.randn(d, generator=g), dtype)
+    beta = synthetic.round_to(0.1 * torch.randn(d, generator=g), dtype)
+    m = build(params, d, E, f, k, dtype, cuda_device)
+    norm = torch.nn.LayerNorm(d, eps=1e-5).to(device=cuda_device, dtype=dtype)
+    with torch.no_grad():
+        norm.weight.copy_(gamma)
+        norm.bias.copy_(beta)
+        xin = x.to(dtype).to(cuda_device).view(1, N, d)
+        out, aux = m(xin, residual=xin, norm=norm)
+        out2, _ = m(xin, residual=xin, norm=norm)
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    assert torch.equal(out, out2)
+    xn = F.layer_norm(x, (d,), gamma, beta, 1e-5)
+    last = {n: t.cpu() for n, t in m.last.items()}
+    # the kernel's logits against the logits of the fp32-normalised rows
+    ref_logits = F.linear(xn, params["gate_w"], params["gate_b"])
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    assert (last["logits"] - ref_logits).abs().max() <= tol * max(1.0, float(ref_logits.abs().max()))
+    with torch.no_grad():
+        o = moe_oracle.moe_forward(xn, params, k, logits=last["logits"])
+    ok = ~moe_oracle.tie_rows(o["probs"], k)
+    assert torch.equal(last["idx"][ok].long(), o["idx"][ok])
+    ref = o["out"] + x
+    got = out.view(N, d).float().cpu()
+    err = (got - ref)[ok].abs().max()
+    if dtype == torch.float32:
+        assert err <= 1e-4 * max(1.0, float(ref.abs().max())), f"max-abs {err}"
+    else:
+        assert err <= 2e-2 * ref.abs().max(), f"max-abs {err} vs scale {ref.abs().max()}"
+        assert (got - ref)[ok].norm() <= 2e-2 * ref[ok].norm()
+
+
 def test_state_survives_dtype_change_and_repeat_calls(cuda_device):
     d, E, f, k, N = 64, 8, 128, 2, 200
     params = synthetic.make_params(d, E, f, seed=9)

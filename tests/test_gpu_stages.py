@@ -7,6 +7,7 @@ import torch.nn.functional as F
 import helpers
 from gemmallm_b200 import _cabi, synthetic
 from oracle import moe_oracle
+from gemmallm_b200._cabi import lib, check  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
@@ -380,3 +381,70 @@ def test_combine_is_exact(cuda_device, N, d, k, dtype):
                               None if residual is None else residual.to(cuda_device))
         torch.cuda.synchronize()
         assert torch.equal(out.cpu(), expect.to(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N,d,E,k", [(777, 256, 8, 2), (64, 1024, 64, 4), (4100, 72, 5, 3)])
+def test_layernorm_stage_entry_points(cuda_device, N, d, E, k, dtype):
+    """moe_b200_norm_fold + moe_b200_router_norm + moe_b200_dispatch_norm against
+    F.layer_norm: row statistics, logits, and the normalised rows in the sorted buffer;
+    moe_b200_layernorm against F.layer_norm."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(N + d + E)
+    x = synthetic.round_to(torch.randn(N, d, generator=g) * (0.3 + torch.rand(N, 1, generator=g) * 3)
+                           + 5.0 * torch.randn(N, 1, generator=g), dtype)
+    gw = synthetic.round_to(torch.randn(E, d, generator=g) * 0.05, dtype)
+    gb = synthetic.round_to(torch.randn(E, generator=g) * 0.1, dtype)
+    gamma = synthetic.round_to(1.0 + 0.3 * torch.randn(d, generator=g), dtype)
+    beta = synthetic.round_to(0.2 * torch.randn(d, generator=g), dtype)
+    dev = cuda_device
+    xd, gwd, gbd, gd, bd = (t.to(dtype).to(dev) for t in (x, gw, gb, gamma, beta))
+    code = helpers.CODE[dtype]
+    s = helpers.stream(dev)
+    wn = torch.empty(E, d, dtype=dtype, device=dev)
+    c = torch.empty(2 * E, dtype=torch.float32, device=dev)
+    check(lib.moe_b200_norm_fold(gwd.data_ptr(), gbd.data_ptr(), gd.data_ptr(), bd.data_ptr(), E, d, code,
+                                 wn.data_ptr(), c.data_ptr(), s), "norm_fold")
+    logits = torch.empty(N, E, dtype=torch.float32, device=dev)
+    idx = torch.empty(N, k, dtype=torch.int32, device=dev)
+    w = torch.empty(N, k, dtype=torch.float32, device=dev)
+    psum_part = torch.empty(max(1, lib.moe_b200_router_blocks(N)), E, dtype=torch.float32, device=dev)
+    stats = torch.empty(N, 2, dtype=torch.float32, device=dev)
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    check(lib.moe_b200_router_norm(xd.data_ptr(), wn.data_ptr(), c.data_ptr(), 1e-5, N, d, E, k, code,
+                                   logits.data_ptr(), idx.data_ptr(), w.data_ptr(), psum_part.data_ptr(),
+                                   stats.data_ptr(), status.data_ptr(), s), "router_norm")
+    torch.cuda.synchronize()
+    mean = x.mean(1)
+    rstd = torch.rsqrt(x.var(1, unbiased=False) + 1e-5)
+    assert torch.allclose(stats[:, 0].cpu(), mean, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(stats[:, 1].cpu(), rstd, rtol=2e-5, atol=0)
+    xn = F.layer_norm(x, (d,), gamma, beta, 1e-5)
+    ref_logits = F.linear(xn, gw, gb)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    assert (logits.cpu() - ref_logits).abs().max() <= tol * max(1.0, float(ref_logits.abs().max()))
+    r = moe_oracle.route_from_logits(logits.cpu(), k)
+    good = ~moe_oracle.tie_rows(r["probs"], k)
+    assert torch.equal(idx.cpu()[good].long(), r["idx"][good])
+    # dispatch: rows of the sorted buffer are the normalised rows
+    nbytes = lib.moe_b200_dispatch_scratch_bytes(N, E, k)
+    scratch = torch.empty(nbytes // 4, dtype=torch.int32, device=dev)
+    cnt_slot = torch.empty(k, E, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    row_of = torch.empty(N, k, dtype=torch.int32, device=dev)
+    perm = torch.empty(N * k, d, dtype=dtype, device=dev)
+    check(lib.moe_b200_dispatch_norm(xd.data_ptr(), idx.data_ptr(), stats.data_ptr(), gd.data_ptr(),
+                                     bd.data_ptr(), N, d, E, k, code, scratch.data_ptr(), cnt_slot.data_ptr(),
+                                     offsets.data_ptr(), row_of.data_ptr(), perm.data_ptr(), None, None, None,
+                                     status.data_ptr(), s), "dispatch_norm")
+    out = torch.empty(N, d, dtype=dtype, device=dev)
+    check(lib.moe_b200_layernorm(xd.data_ptr(), gd.data_ptr(), bd.data_ptr(), 1e-5, N, d, code, out.data_ptr(), s),
+          "layernorm")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    rtol = 2e-5 if dtype == torch.float32 else 1e-2
+    scale = float(xn.abs().max())
+    assert (out.float().cpu() - xn).abs().max() <= rtol * scale
+    ro = row_of.cpu().long()
+    for j in range(k):
+        assert (perm.float().cpu()[ro[:, j]] - xn).abs().max() <= rtol * scale
