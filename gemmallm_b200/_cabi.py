@@ -64,6 +64,13 @@ SIGNATURES = {
     "moe_b200_dispatch_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
                                     _vp, _vp, _vp, _vp, _vp, _vp]),
     "moe_b200_layernorm": (_i, [_vp, _vp, _vp, _f, _i64, _i, _i, _vp, _vp]),
+    "moe_b200_train_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),
+    "moe_b200_train_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
+    "moe_b200_train_setup": (_i, [_i64, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "moe_b200_forward_train": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _f, C.c_uint64,
+                                    _vp, _sz, _vp, _sz, _vp, _vp]),
+    "moe_b200_backward": (_i, [_vp, _vp, _vp, _vp, _f, _i64, _i, _i, _i, _i, _i, _f, C.c_uint64,
+                               _vp, _sz, _vp, _sz, _vp, _vp]),
     "moe_b200_ep_symm_bytes": (_sz, [_i64, _i, _i, _i, _i]),
     "moe_b200_ep_symm_layout": (_i, [_i64, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_ep_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),
@@ -117,6 +124,16 @@ def workspace_layout(N: int, d: int, f: int, E: int, k: int, dtype: int) -> dict
     arr = (_sz * WS_NUM)()
     check(lib.moe_b200_workspace_layout(N, d, f, E, k, dtype, arr), "workspace_layout")
     return {name: int(arr[i]) for i, name in enumerate(WS_NAMES)}
+
+
+TWS_NAMES = ("gu", "pair_of", "koff", "dy", "dh", "dxs", "w1t", "w2t", "tmaps", "xt", "ht", "dyt", "dgut",
+             "dl", "dw", "ones", "dwg_f32", "dxr", "g_wg", "g_bg", "g_w1", "g_b1", "g_w2", "g_b2")
+
+
+def train_workspace_layout(N: int, d: int, f: int, E: int, k: int, dtype: int) -> dict[str, int]:
+    arr = (_sz * len(TWS_NAMES))()
+    check(lib.moe_b200_train_workspace_layout(N, d, f, E, k, dtype, arr), "train_workspace_layout")
+    return {name: int(arr[i]) for i, name in enumerate(TWS_NAMES)}
 
 
 EP_STAGES = ("router", "dispatch", "arrived", "experts", "returned", "combine")

@@ -221,6 +221,19 @@ struct EpScatter {
   const int32_t* meta;
 };
 
+// Training-mode extras of the GEGLU pass (reference model.py:164,183: nn.Dropout on h, and
+// what the backward pass needs): the pre-activations gate/up with their biases go to
+// gu [M, 2f] (columns [0,f) gate, [f,2f) up), and h is multiplied by the dropout mask of its
+// (token, slot) pair: element (pair, c) is kept iff its Philox word (philox.cuh) is >= thresh,
+// and scaled by `scale` = 1 / (1 - p).
+struct TrainArgs {
+  __nv_bfloat16* gu;
+  const int32_t* pair_of;   // [M] token * k + slot of every sorted row
+  uint32_t thresh;          // p * 2^32; 0 keeps everything
+  float scale;
+  uint32_t seed_lo, seed_hi;
+};
+
 // ---- launchers implemented in the other translation units -----------------
 int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                   int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
@@ -243,7 +256,17 @@ int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, i
                              void* h_tmaps /* kPlanMapsPerExpert*E*128 bytes */);
 int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                        int f, int E, void* h, void* y, const EpScatter* sc, int32_t* status,
-                       cudaStream_t s);
+                       cudaStream_t s, const TrainArgs* train = nullptr);
+// One grouped product out[rows of e] = A[rows of e] . B_e^T (+ bias_e), B_e given by the e-th
+// tensor map of tmaps_b ([Nout, K] row-major, 128-row boxes); bias may be nullptr.
+int launch_grouped_rows(const void* A, int64_t M, int K, const void* tmaps_b, const int32_t* offsets,
+                        const void* const* bias, int E, int Nout, void* out, int32_t* status,
+                        cudaStream_t s);
+// Grouped over the contraction index: out_e [Ra, Rb] = At[:, K_e] . Bt[:, K_e]^T for the column
+// ranges K_e = [koff[e], koff[e+1]) (multiples of 64) of At [Ra, Kpad] and Bt [Rb, Kpad];
+// out [E][Ra][Rb]. Experts with an empty range are skipped (their slice is left untouched).
+int launch_grouped_cols(const void* At, const void* Bt, int64_t Kpad, int Ra, int Rb,
+                        const int32_t* koff, void* out, int E, int32_t* status, cudaStream_t s);
 int64_t ep_scratch_ints(int64_t N, int EV, int E);
 int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int EV, int k,
                        int dtype, const EpPeers& peers, int rank, int world, uint32_t epoch,
@@ -282,5 +305,22 @@ int launch_experts_tc_decode_fused(const void* perm, const int32_t* offsets, con
 int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_t* row_of,
                           const int32_t* idx, const float* w, const void* plan, int E,
                           const void* residual, int64_t N, int d, int k, void* out, cudaStream_t s);
+
+// ---- backward.cu ----
+int launch_pair_of(const int32_t* row_of, int64_t M, int32_t* pair_of, cudaStream_t s);
+int launch_pad_offsets(const int32_t* offsets, int E, int32_t* koff, cudaStream_t s);
+int launch_combine_bwd(const void* dout, const void* y, const int32_t* pair_of, const float* w,
+                       int64_t M, int d, int k, void* dy, float* dw, cudaStream_t s);
+int launch_router_bwd(const float* logits, const int32_t* idx, const float* w, const float* dw,
+                      const int32_t* cnt0, float grad_aux, const void* x, const void* Wg, int64_t N,
+                      int d, int E, int k, float* dl, float* dWg_f32, float* dbg_f32, void* dWg,
+                      void* dbg, void* dxr, cudaStream_t s);
+int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t s);
+int launch_geglu_bwd(const void* dh, void* gu, const int32_t* pair_of, int64_t M, int f,
+                     uint32_t thresh, float scale, uint32_t seed_lo, uint32_t seed_hi, cudaStream_t s);
+int launch_transpose_weights(const void* const* src_ptrs, int E, int R, int C, void* dst, cudaStream_t s);
+int launch_transpose_pad(const void* src, const int32_t* offsets, const int32_t* koff, int E, int C,
+                         int64_t Kpad, void* dst, cudaStream_t s);
+int launch_colsum(const void* src, const int32_t* offsets, int E, int C, void* db, cudaStream_t s);
 
 }  // namespace moe

@@ -17,6 +17,12 @@
 //   tmem_empty[a] in the even CTA; the 16 epilogue warps of the pair arrive on
 //                 it (the odd CTA's warps through the cluster-mapped address).
 // Math and epilogue (tc_epilogue.cuh): reference model.py:174,180-184.
+//
+// The same kernel serves the backward pass (the reference trains through this block with
+// torch.autograd, train.py:140): the input gradients are two more row-grouped products
+// against transposed weights; the weight gradients dW_e = dY_e^T X_e contract over an
+// expert's rows, so there (COLS) a group is a range of the contraction index of two
+// transposed activation buffers and every expert has the same output tiles.
 #include <cuda.h>
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -99,14 +105,18 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
                : "memory");
 }
 
-template <bool GEGLU, bool SCATTER>
+// COLS = false: groups are row ranges [offsets[e], offsets[e+1]) of A; B_e = tmap_b[e]; K fixed.
+// COLS = true : groups are ranges [offsets[e], offsets[e+1]) (multiples of 64) of the contraction
+//               index; A has Ra rows, B (one map, tmap_bc) has Nout rows; out [E][Ra][Nout].
+template <bool GEGLU, bool SCATTER, bool TRAIN, bool COLS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_bc,
                         const CUtensorMap* __restrict__ tmap_b,  // [E], 128-row boxes
                         const int32_t* __restrict__ offsets,
                         const void* const* __restrict__ bias_ptrs, int E, int K, int Nout,
-                        __nv_bfloat16* __restrict__ out, const EpScatter sc,
-                        int32_t* __restrict__ status) {
+                        __nv_bfloat16* __restrict__ out, const EpScatter sc, const TrainArgs tr,
+                        int Ra, int32_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -119,7 +129,8 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_pairs = gridDim.x >> 1;
   constexpr int kTileN = GEGLU ? BN / 2 : BN;
   const int n_tiles = (Nout + kTileN - 1) / kTileN;
-  const int k_blocks = (K + BK - 1) / BK;
+  const int k_blocks_rows = (K + BK - 1) / BK;
+  const int m_tiles_cols = (Ra + kPairRows - 1) / kPairRows;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
@@ -144,7 +155,8 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ctl->tile_start[e] = acc;
       const int end = offsets[e + 1];
       ctl->offsets[e + 1] = end;
-      acc += ((end - beg + kPairRows - 1) / kPairRows) * n_tiles;
+      acc += COLS ? (end > beg ? m_tiles_cols * n_tiles : 0)
+                  : ((end - beg + kPairRows - 1) / kPairRows) * n_tiles;
       beg = end;
     }
     ctl->tile_start[E] = acc;
@@ -169,10 +181,12 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
         while (t >= ctl->tile_start[e + 1]) ++e;
         const int local = t - ctl->tile_start[e];
         const int mt = local / n_tiles, nt = local - mt * n_tiles;
-        const int row0 = ctl->offsets[e] + mt * kPairRows + (int)cta * BM;
+        const int row0 = (COLS ? 0 : ctl->offsets[e]) + mt * kPairRows + (int)cta * BM;
         const int brow = GEGLU ? (cta == 0 ? nt * kTileN : Nout + nt * kTileN)
                                : nt * kTileN + (int)cta * (BN / 2);
-        const CUtensorMap* tb = tmap_b + e;
+        const CUtensorMap* tb = COLS ? &tmap_bc : tmap_b + e;
+        const int k0 = COLS ? ctl->offsets[e] : 0;
+        const int k_blocks = COLS ? (ctl->offsets[e + 1] - k0) / BK : k_blocks_rows;
         for (int kb = 0; kb < k_blocks; ++kb) {
           {
             if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort, status, 31)) { ok = false; break; }
@@ -180,8 +194,8 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* sa = smem + (size_t)stage * kStageBytes;
           const uint32_t full0 = map_to_cta(smem_u32(&ctl->full[stage]), 0);
           if (cta == 0) mbar_expect_tx(&ctl->full[stage], 2 * kStageBytes);
-          tma_load_2d_pair(sa, &tmap_a, full0, kb * BK, row0);
-          tma_load_2d_pair(sa + kABytes, tb, full0, kb * BK, brow);
+          tma_load_2d_pair(sa, &tmap_a, full0, k0 + kb * BK, row0);
+          tma_load_2d_pair(sa + kABytes, tb, full0, k0 + kb * BK, brow);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -193,9 +207,15 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       uint32_t acc_phase = 0;
       int it = 0;
+      int e = 0;
       bool ok = true;
       for (int t = pair; ok && t < total_tiles; t += num_pairs, ++it) {
         const int a = it & 1;
+        int k_blocks = k_blocks_rows;
+        if (COLS) {
+          while (t >= ctl->tile_start[e + 1]) ++e;
+          k_blocks = (ctl->offsets[e + 1] - ctl->offsets[e]) / BK;
+        }
         {
           if (!mbar_wait(&ctl->tmem_empty[a], acc_phase ^ 1u, &ctl->abort, status, 32)) { ok = false; break; }
         }
@@ -239,17 +259,20 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
       while (t >= ctl->tile_start[e + 1]) ++e;
       const int local = t - ctl->tile_start[e];
       const int mt = local / n_tiles, nt = local - mt * n_tiles;
-      const int row = ctl->offsets[e] + mt * kPairRows + (int)cta * BM + r;
-      const bool row_ok = row < ctl->offsets[e + 1];
+      const int row = (COLS ? 0 : ctl->offsets[e]) + mt * kPairRows + (int)cta * BM + r;
+      const bool row_ok = COLS ? row < Ra : row < ctl->offsets[e + 1];
       const int n0 = nt * kTileN;
-      const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(bias_ptrs[e]);
+      const __nv_bfloat16* bias =
+          bias_ptrs != nullptr ? static_cast<const __nv_bfloat16*>(bias_ptrs[e]) : nullptr;
+      __nv_bfloat16* out_e = COLS ? out + (size_t)e * Ra * Nout : out;
       const int a = it & 1;
       {
         if (!mbar_wait(&ctl->tmem_full[a], acc_phase, &ctl->abort, status, 34)) { ok = false; break; }
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
-      store_tile<GEGLU, SCATTER>(taddr, row, row_ok, n0, Nout, bias, out, sc, ctl->stage_out[warp - 2], lane, half);
+      store_tile<GEGLU, SCATTER, TRAIN>(taddr, row, row_ok, n0, Nout, bias, out_e, sc, tr,
+                                        ctl->stage_out[warp - 2], lane, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->tmem_empty[a]), 0));
@@ -275,26 +298,25 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <bool GEGLU, bool SCATTER>
-int launch_pair(const CUtensorMap& tm_a, const void* tmap_b, const int32_t* offsets,
+template <bool GEGLU, bool SCATTER, bool TRAIN, bool COLS>
+int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_bc, const void* tmap_b, const int32_t* offsets,
                 const void* const* bias, int E, int K, int Nout, void* out, const EpScatter& sc,
-                int32_t* status, int sms, cudaStream_t s) {
+                const TrainArgs& tr, int Ra, int32_t* status, int sms, cudaStream_t s) {
   static PerDeviceOnce once;
-  auto fn = grouped_gemm_tc2_kernel<GEGLU, SCATTER>;
+  auto fn = grouped_gemm_tc2_kernel<GEGLU, SCATTER, TRAIN, COLS>;
   int rc = ensure_dynamic_smem(once, fn, kSmemBytes);
   if (rc) return rc;
-  MOE_CUDA_CHECK(launch_pdl(fn, dim3(sms & ~1), dim3(kThreads), kSmemBytes, s, tm_a,
+  MOE_CUDA_CHECK(launch_pdl(fn, dim3(sms & ~1), dim3(kThreads), kSmemBytes, s, tm_a, tm_bc,
                             static_cast<const CUtensorMap*>(tmap_b), offsets, bias, E, K, Nout,
-                            static_cast<__nv_bfloat16*>(out), sc, status));
+                            static_cast<__nv_bfloat16*>(out), sc, tr, Ra, status));
   return 0;
 }
 
 }  // namespace
 
-
 int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                        int f, int E, void* h, void* y, const EpScatter* sc, int32_t* status,
-                       cudaStream_t s) {
+                       cudaStream_t s, const TrainArgs* train) {
   if (M == 0 || E == 0) return 0;
   PlanView pv = plan_view(plan, E);
   alignas(64) CUtensorMap tm_x, tm_h;
@@ -306,12 +328,52 @@ int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* pla
   rc = sm_count(&sms);
   if (rc) return rc;
   const EpScatter none = {};
-  rc = launch_pair<true, false>(tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, none, status, sms, s);
+  const TrainArgs eval = {};
+  if (train != nullptr)
+    rc = launch_pair<true, false, true, false>(tm_x, tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, none, *train,
+                                               0, status, sms, s);
+  else
+    rc = launch_pair<true, false, false, false>(tm_x, tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, none, eval,
+                                                0, status, sms, s);
   if (rc) return rc;
   if (sc != nullptr)
-    return launch_pair<false, true>(tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, nullptr, *sc, status,
-                                    sms, s);
-  return launch_pair<false, false>(tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, y, none, status, sms, s);
+    return launch_pair<false, true, false, false>(tm_h, tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, nullptr, *sc,
+                                                  eval, 0, status, sms, s);
+  return launch_pair<false, false, false, false>(tm_h, tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, y, none, eval,
+                                                 0, status, sms, s);
+}
+
+int launch_grouped_rows(const void* A, int64_t M, int K, const void* tmaps_b, const int32_t* offsets,
+                        const void* const* bias, int E, int Nout, void* out, int32_t* status,
+                        cudaStream_t s) {
+  if (M == 0 || E == 0) return 0;
+  alignas(64) CUtensorMap tm_a;
+  int rc = encode_tmap_2d(&tm_a, A, (uint64_t)M, (uint64_t)K, BM);
+  if (rc) return rc;
+  int sms = 0;
+  rc = sm_count(&sms);
+  if (rc) return rc;
+  const EpScatter none = {};
+  const TrainArgs eval = {};
+  return launch_pair<false, false, false, false>(tm_a, tm_a, tmaps_b, offsets, bias, E, K, Nout, out, none,
+                                                 eval, 0, status, sms, s);
+}
+
+int launch_grouped_cols(const void* At, const void* Bt, int64_t Kpad, int Ra, int Rb,
+                        const int32_t* koff, void* out, int E, int32_t* status, cudaStream_t s) {
+  if (Kpad == 0 || E == 0) return 0;
+  alignas(64) CUtensorMap tm_a, tm_b;
+  int rc = encode_tmap_2d(&tm_a, At, (uint64_t)Ra, (uint64_t)Kpad, BM);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tm_b, Bt, (uint64_t)Rb, (uint64_t)Kpad, BM);
+  if (rc) return rc;
+  int sms = 0;
+  rc = sm_count(&sms);
+  if (rc) return rc;
+  const EpScatter none = {};
+  const TrainArgs eval = {};
+  return launch_pair<false, false, false, true>(tm_a, tm_b, nullptr, koff, nullptr, E, 0, Rb, out,
+                                                none, eval, Ra, status, sms, s);
 }
 
 }  // namespace moe

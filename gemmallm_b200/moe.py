@@ -122,6 +122,31 @@ class _Plan:
         return self.base
 
 
+class _TrainFn(torch.autograd.Function):
+    """MOE.forward in training mode as one autograd node: moe_b200_forward_train /
+    moe_b200_backward (dropout on h, model.py:183; gradients of model.py:200-276)."""
+
+    @staticmethod
+    def forward(ctx, module, x, residual, seed, *params):
+        out, aux = module._forward_train(x, residual, seed)
+        ctx.module, ctx.seed, ctx.gen = module, seed, module._train_gen
+        ctx.has_residual = residual is not None
+        ctx.save_for_backward(x)
+        return out, aux
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_aux):
+        m = ctx.module
+        if ctx.gen != m._train_gen:
+            raise RuntimeError("this block ran another training forward before the backward of this "
+                               "one: its workspace holds the later call's tensors")
+        (x,) = ctx.saved_tensors
+        grads = m._backward_train(x, grad_out.contiguous(), float(grad_aux), ctx.seed)
+        grad_x = grads.pop(0)
+        grad_res = grad_out if ctx.has_residual else None
+        return (None, grad_x, grad_res, None, *grads)
+
+
 class FeedForward(nn.Module):
     """GeGLU feed-forward expert; mirrors reference model.py:154-190.
 
@@ -206,6 +231,9 @@ class MOE(nn.Module):
         self._lora = _MergedLora()
         self._ws = None
         self._ws_key = None
+        self._tws = None
+        self._tws_key = None
+        self._train_gen = 0
         self.last = None  # views into the workspace of the most recent call
 
     # -- workspace ---------------------------------------------------------
@@ -244,10 +272,20 @@ class MOE(nn.Module):
         runs the experts with their LoRA branches (model.py:175-179,185-189)
         folded into merged copies of their weights (refreshed when a parameter
         changes); forward only."""
-        if self.training and self.experts[0].dropout.p > 0:
-            raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
         if not tensor.is_cuda:
             raise RuntimeError("libmoe_b200 runs on CUDA tensors only; there is no CPU path")
+        if self.training and (torch.is_grad_enabled() or self.experts[0].dropout.p > 0):
+            # training mode: dropout on h (model.py:183) and a backward pass
+            if fine_tuning or norm is not None:
+                raise NotImplementedError("training mode runs the plain block: LoRA branches and the "
+                                          "folded LayerNorm have no backward pass here")
+            if tensor.dtype != torch.bfloat16:
+                raise NotImplementedError("training mode computes in bfloat16")
+            seed = int(torch.randint(0, 2 ** 62, (1,), dtype=torch.int64).item())   # torch's CPU generator
+            params = [self.gate.weight, self.gate.bias]
+            for ex in self.experts:
+                params += [ex.gate_and_up.weight, ex.gate_and_up.bias, ex.down.weight, ex.down.bias]
+            return _TrainFn.apply(self, tensor, residual, seed, *params)
         dtype = _dtype_code(tensor)
         shape = tensor.shape
         d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
@@ -295,6 +333,98 @@ class MOE(nn.Module):
         }
         aux = self._view("aux", torch.float32, (1,))[0].clone()
         return out.reshape(shape), aux
+
+    # -- training mode -------------------------------------------------------
+    def _train_workspace(self, N: int, dtype: int, device: torch.device):
+        key = (N, dtype, str(device))
+        if key != self._tws_key:
+            d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
+            nbytes = lib.moe_b200_train_workspace_bytes(N, d, f, E, k, dtype)
+            if nbytes == 0:
+                raise _cabi.MoeB200Error(lib.moe_b200_last_error_string().decode())
+            buf = torch.zeros(nbytes + 1024, dtype=torch.uint8, device=device)
+            base = (buf.data_ptr() + 1023) & ~1023
+            check(lib.moe_b200_train_setup(N, d, f, E, k, dtype, base, nbytes, _stream(device)), "train_setup")
+            self._tws = (buf, base, nbytes, _cabi.train_workspace_layout(N, d, f, E, k, dtype))
+            self._tws_key = key
+        return self._tws
+
+    def _tws_view(self, name: str, shape) -> torch.Tensor:
+        buf, base, _, layout = self._tws
+        start = base - buf.data_ptr() + layout[name]
+        n = 2
+        for s in shape:
+            n *= s
+        return buf[start:start + n].view(torch.bfloat16).view(*shape)
+
+    def _forward_train(self, tensor, residual, seed: int):
+        dtype = _dtype_code(tensor)
+        shape = tensor.shape
+        d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
+        if shape[-1] != d:
+            raise ValueError(f"last dimension {shape[-1]} != hidden_size {d}")
+        x = tensor.reshape(-1, d).contiguous()
+        N = x.shape[0]
+        dev = x.device
+        res_ptr = None
+        if residual is not None:
+            if residual.shape != shape or residual.dtype != tensor.dtype or residual.device != dev:
+                raise ValueError("residual must match the input's shape, dtype and device")
+            res_ptr = residual.reshape(-1, d).contiguous().data_ptr()
+        out = torch.empty_like(x)
+        with torch.cuda.device(dev):
+            plan = self._plan.get(self.experts, d, f, dtype, dev)
+            _, base, nbytes, _ = self._workspace(N, dtype, dev)
+            _, tbase, tbytes, _ = self._train_workspace(N, dtype, dev)
+            check(lib.moe_b200_forward_train(
+                x.data_ptr(), self.gate.weight.data_ptr(), self.gate.bias.data_ptr(), plan, res_ptr,
+                N, d, f, E, k, dtype, float(self.experts[0].dropout.p), seed, base, nbytes, tbase, tbytes,
+                out.data_ptr(), _stream(dev)), "forward_train")
+        self._train_gen += 1
+        self.last = {
+            "logits": self._view("logits", torch.float32, (N, E)),
+            "idx": self._view("idx", torch.int32, (N, k)),
+            "w": self._view("w", torch.float32, (N, k)),
+            "cnt_slot": self._view("cnt_slot", torch.int32, (k, E)),
+            "offsets": self._view("offsets", torch.int32, (E + 1,)),
+            "psum": self._view("psum", torch.float32, (E,)),
+            "row_of": self._view("row_of", torch.int32, (N, k)),
+            "status": self._view("status", torch.int32, (16,)),
+            "seed": seed,
+        }
+        aux = self._view("aux", torch.float32, (1,))[0].clone()
+        return out.reshape(shape), aux
+
+    def _backward_train(self, tensor, grad_out, grad_aux: float, seed: int):
+        """[grad_x, grad gate.weight, grad gate.bias, then per expert the gradients of
+        gate_and_up.weight, gate_and_up.bias, down.weight, down.bias]."""
+        dtype = _dtype_code(tensor)
+        shape = tensor.shape
+        d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
+        x = tensor.reshape(-1, d).contiguous()
+        N = x.shape[0]
+        dev = x.device
+        g = grad_out.reshape(-1, d).contiguous()
+        if g.dtype != tensor.dtype:
+            g = g.to(tensor.dtype)
+        grad_x = torch.empty_like(x)
+        with torch.cuda.device(dev):
+            plan = self._plan.get(self.experts, d, f, dtype, dev)
+            _, base, nbytes, _ = self._workspace(N, dtype, dev)
+            _, tbase, tbytes, _ = self._train_workspace(N, dtype, dev)
+            check(lib.moe_b200_backward(
+                x.data_ptr(), self.gate.weight.data_ptr(), plan, g.data_ptr(), grad_aux, N, d, f, E, k, dtype,
+                float(self.experts[0].dropout.p), seed, base, nbytes, tbase, tbytes, grad_x.data_ptr(),
+                _stream(dev)), "backward")
+        # copies: the workspace is overwritten by the next backward
+        grads = [grad_x.reshape(shape), self._tws_view("g_wg", (E, d)).clone(), self._tws_view("g_bg", (E,)).clone()]
+        g_w1 = self._tws_view("g_w1", (E, 2 * f, d)).clone()
+        g_b1 = self._tws_view("g_b1", (E, 2 * f)).clone()
+        g_w2 = self._tws_view("g_w2", (E, d, f)).clone()
+        g_b2 = self._tws_view("g_b2", (E, d)).clone()
+        for e in range(E):
+            grads += [g_w1[e], g_b1[e], g_w2[e], g_b2[e]]
+        return grads
 
     def device_status(self) -> int:
         """Status word of the most recent call (0 = ok); synchronises. A non-zero status is

@@ -357,6 +357,65 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg,
                      void* workspace, size_t workspace_bytes,
                      void* out, void* stream);
 
+/* ---- Training mode ---------------------------------------------------------------
+ * The reference trains through this block (loss.backward(), train.py:140-141): under
+ * .train() FeedForward.forward applies nn.Dropout to h (model.py:164,183), and
+ * torch.autograd differentiates model.py:200-276 and 173-190. These entry points are
+ * that forward and its backward pass for bf16. Both work on the block's ordinary
+ * workspace (which the forward fills and the backward reads: call the backward before
+ * the next forward on the same workspace) plus a training workspace for the saved
+ * pre-activations, the transposed operands and the parameter gradients. */
+enum {
+  MOE_B200_TWS_GU = 0,   /* bf16 [N*k, 2f] gate/up pre-activations; (dg, du) after the backward */
+  MOE_B200_TWS_PAIR_OF,  /* int32 [N*k]    token * k + slot of every sorted row */
+  MOE_B200_TWS_KOFF,     /* int32 [E+1]    expert starts, each padded to a multiple of 64 */
+  MOE_B200_TWS_DY, MOE_B200_TWS_DH, MOE_B200_TWS_DXS,   /* gradients of y, h, sorted x */
+  MOE_B200_TWS_W1T, MOE_B200_TWS_W2T,                   /* transposed weights [E][d][2f], [E][f][d] */
+  MOE_B200_TWS_TMAPS,    /* tensor maps of W1T[e], W2T[e] (moe_b200_train_setup) */
+  MOE_B200_TWS_XT, MOE_B200_TWS_HT, MOE_B200_TWS_DYT, MOE_B200_TWS_DGUT, /* [cols][padded rows] */
+  MOE_B200_TWS_DL,       /* float [N,E]   gradient of the router logits */
+  MOE_B200_TWS_DW,       /* float [N,k]   gradient of the renormalised scores */
+  MOE_B200_TWS_ONES,     /* float [N,k]   ones (moe_b200_train_setup) */
+  MOE_B200_TWS_DWG_F32,  /* float [E*d + E] accumulators of the gate gradients */
+  MOE_B200_TWS_DXR,      /* bf16 [N,d]    the router's share of grad_x */
+  /* results of moe_b200_backward, bf16: */
+  MOE_B200_TWS_G_WG,     /* [E,d]      gradient of gate.weight */
+  MOE_B200_TWS_G_BG,     /* [E]        gate.bias */
+  MOE_B200_TWS_G_W1,     /* [E,2f,d]   experts.e.gate_and_up.weight */
+  MOE_B200_TWS_G_B1,     /* [E,2f]     experts.e.gate_and_up.bias */
+  MOE_B200_TWS_G_W2,     /* [E,d,f]    experts.e.down.weight */
+  MOE_B200_TWS_G_B2,     /* [E,d]      experts.e.down.bias */
+  MOE_B200_TWS_NUM
+};
+size_t moe_b200_train_workspace_bytes(int64_t N, int d, int f, int E, int k, int dtype);
+int moe_b200_train_workspace_layout(int64_t N, int d, int f, int E, int k, int dtype,
+                                    size_t* h_offsets);
+/* Once per training workspace (synchronous): tensor maps of its transposed-weight
+ * buffers, constants. */
+int moe_b200_train_setup(int64_t N, int d, int f, int E, int k, int dtype, void* train_ws,
+                         size_t train_ws_bytes, void* stream);
+
+/* MOE.forward in training mode (model.py:200-276 with model.py:183 active): as
+ * moe_b200_forward on the large-N kernels at every N, with dropout on h. The mask is
+ * counter-based: element (token * k + slot, column c) of h is dropped iff word c % 4 of
+ * Philox4x32-10(counter = (c / 4, token * k + slot, 0, 0), key = seed) is below
+ * dropout_p * 2^32; kept elements are scaled by 1 / (1 - dropout_p). The same
+ * dropout_p and seed must be given to moe_b200_backward. */
+int moe_b200_forward_train(const void* x, const void* Wg, const void* bg, const void* plan,
+                           const void* residual, int64_t N, int d, int f, int E, int k, int dtype,
+                           float dropout_p, uint64_t seed, void* workspace, size_t workspace_bytes,
+                           void* train_ws, size_t train_ws_bytes, void* out, void* stream);
+
+/* Backward of moe_b200_forward_train: grad_out [N,d] = gradient of the block's output,
+ * grad_aux = gradient of the load-balancing loss (a host scalar). Writes grad_x [N,d]
+ * (gradient of x; a fused residual's gradient is grad_out itself) and the parameter
+ * gradients into the MOE_B200_TWS_G_* regions. The expert counts inside the loss carry
+ * no gradient (torch.bincount, model.py:213). */
+int moe_b200_backward(const void* x, const void* Wg, const void* plan, const void* grad_out,
+                      float grad_aux, int64_t N, int d, int f, int E, int k, int dtype,
+                      float dropout_p, uint64_t seed, void* workspace, size_t workspace_bytes,
+                      void* train_ws, size_t train_ws_bytes, void* grad_x, void* stream);
+
 /* ---- Expert-parallel configuration ------------------------------------------
  * Tokens are sharded over `world` ranks (one process per GPU, rank r owns
  * N_local tokens) and experts are owned by rank h_expert_owner[e]; the

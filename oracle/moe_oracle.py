@@ -24,13 +24,16 @@ import torch
 import torch.nn.functional as F
 
 
-def expert_ffn(x, w1, b1, w2, b2, lora=None):
+def expert_ffn(x, w1, b1, w2, b2, lora=None, h_mask=None):
     """One expert on rows ``x`` [n,d]: model.py:174 (gate_and_up), :180 (chunk),
     :181 (tanh GELU on the gate half), :182 (product), :184 (down).
 
     ``lora`` (the fine_tuning=True branch, model.py:175-179 and 185-189): dict with
     ``scale`` and the eight tensors ``gu_a_w, gu_a_b, gu_b_w, gu_b_b, dn_a_w, dn_a_b,
-    dn_b_w, dn_b_b`` of this expert's four LoRA Linears."""
+    dn_b_w, dn_b_b`` of this expert's four LoRA Linears.
+
+    ``h_mask`` [n,f]: multiplier applied to h where the reference applies nn.Dropout in
+    training mode (model.py:183): 0 for dropped elements, 1/(1-p) for kept ones."""
     gu = F.linear(x, w1, b1)
     if lora is not None:
         t = F.linear(x, lora["gu_a_w"], lora["gu_a_b"])
@@ -38,6 +41,8 @@ def expert_ffn(x, w1, b1, w2, b2, lora=None):
         gu = gu + t * lora["scale"]
     gate, up = gu.chunk(2, dim=-1)
     h = F.gelu(gate, approximate="tanh") * up
+    if h_mask is not None:
+        h = h * h_mask
     y = F.linear(h, w2, b2)
     if lora is not None:
         t = F.linear(h, lora["dn_a_w"], lora["dn_a_b"])
@@ -77,12 +82,13 @@ def tie_rows(probs: torch.Tensor, k: int) -> torch.Tensor:
 
 
 def moe_forward(x: torch.Tensor, params: dict, k: int = 2, logits: torch.Tensor | None = None,
-                lora: list | None = None):
+                lora: list | None = None, h_mask: torch.Tensor | None = None):
     """The whole block on x [N,d] (fp32, CPU). ``params`` as produced by
     gemmallm_b200.synthetic.make_params (fp32). With ``logits`` given, routing
     is derived from them instead of from x (used to impose the CUDA router's
     own logits, so that outputs are compared under identical routing). ``lora``: one
-    dict per expert (see expert_ffn) for the fine_tuning=True forward.
+    dict per expert (see expert_ffn) for the fine_tuning=True forward. ``h_mask``
+    [N,k,f]: the training-mode dropout multiplier of every (token, slot) pair's h row.
 
     Per slot, as model.py:226-268: sort token ids by chosen expert, run each
     non-empty expert on its rows, concatenate, scatter back with index_copy_
@@ -100,8 +106,9 @@ def moe_forward(x: torch.Tensor, params: dict, k: int = 2, logits: torch.Tensor 
         counts = r["cnt_slot"][j].tolist()
         rows = x[order]
         pieces = torch.split(rows, counts, dim=0)
+        masks = [None] * E if h_mask is None else torch.split(h_mask[order, j], counts, dim=0)
         outs = [expert_ffn(pieces[e], params["w1"][e], params["b1"][e], params["w2"][e],
-                           params["b2"][e], None if lora is None else lora[e])
+                           params["b2"][e], None if lora is None else lora[e], masks[e])
                 if counts[e] > 0 else torch.zeros(0, d)
                 for e in range(E)]
         buf = torch.zeros(N, d, dtype=torch.float32)

@@ -1,0 +1,140 @@
+"""Training mode: dropout on h (model.py:164,183) with a mask the CPU oracle can reproduce,
+and the backward pass against torch.autograd on the oracle (the reference trains through this
+block with loss.backward(), train.py:140-141)."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import philox_ref
+from gemmallm_b200 import MOE, synthetic
+from oracle import moe_oracle
+
+DT = torch.bfloat16
+
+
+def test_philox_known_answer():
+    """Published Philox4x32-10 vectors (Random123 kat_vectors): zero counter and key; all-ones
+    counter and key."""
+    z = np.zeros(1, np.uint64)
+    got = [int(a[0]) for a in philox_ref.philox4x32_10(z, z, 0, 0)]
+    assert got == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+
+
+def make_block(d, E, f, k, p, dev, seed):
+    params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=seed), DT)
+    g = torch.Generator().manual_seed(seed + 1)
+    params["w1"] = synthetic.round_to(params["w1"] * 2.0, DT)
+    params["b1"] = synthetic.round_to(torch.randn(E, 2 * f, generator=g) * 0.05, DT)
+    params["b2"] = synthetic.round_to(torch.randn(E, d, generator=g) * 0.05, DT)
+    params["gate_w"] = synthetic.round_to(params["gate_w"] * 10.0, DT)   # routing with real preferences
+    m = MOE(d, num_experts=E, d_ff=f, top_k=k, dropout_ratio=p, device="cuda")
+    synthetic.load_into(m, params, DT, dev)
+    return m, params
+
+
+def oracle_run(x, params, k, mask, grad_out, grad_aux):
+    """fp32 forward and torch.autograd backward of the oracle; returns outputs and gradients."""
+    leaves = {n: t.clone().requires_grad_(True) for n, t in params.items()}
+    xl = x.clone().requires_grad_(True)
+    o = moe_oracle.moe_forward(xl, leaves, k, h_mask=mask)
+    loss = (o["out"] * grad_out).sum() + grad_aux * o["aux"]
+    loss.backward()
+    return o, xl.grad, {n: t.grad for n, t in leaves.items()}
+
+
+def close(got, ref, rel, what):
+    got, ref = got.float().cpu(), ref.float()
+    scale = float(ref.abs().max())
+    err = float((got - ref).abs().max())
+    assert err <= rel * scale + 1e-6, f"{what}: max-abs {err:.4g} vs scale {scale:.4g}"
+    assert float((got - ref).norm()) <= rel * float(ref.norm()) + 1e-6, f"{what}: Frobenius"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,d,E,f,k,p", [(300, 128, 8, 256, 2, 0.1), (1000, 256, 4, 264, 2, 0.25),
+                                         (64, 64, 8, 128, 2, 0.0), (700, 128, 16, 192, 4, 0.1)])
+def test_training_forward_applies_the_reproducible_dropout_mask(cuda_device, N, d, E, f, k, p):
+    m, params = make_block(d, E, f, k, p, cuda_device, seed=N)
+    m.train()
+    x = synthetic.round_to(synthetic.make_input(N, d, seed=N + 5), DT)
+    with torch.no_grad():
+        out, aux = m(x.to(DT).to(cuda_device).view(1, N, d))
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    seed = m.last["seed"]
+    mult = torch.from_numpy(philox_ref.dropout_multiplier(N * k, f, p, seed)).view(N, k, f)
+    if p > 0:
+        kept = float((mult > 0).float().mean())
+        assert abs(kept - (1 - p)) < 0.01
+    logits = m.last["logits"].cpu()
+    with torch.no_grad():
+        o = moe_oracle.moe_forward(x, params, k, logits=logits, h_mask=mult)
+        plain = moe_oracle.moe_forward(x, params, k, logits=logits)
+    ok = ~moe_oracle.tie_rows(o["probs"], k)
+    assert torch.equal(m.last["idx"].cpu()[ok].long(), o["idx"][ok])
+    got = out.view(N, d).float().cpu()
+    err = (got - o["out"])[ok].abs().max()
+    assert err <= 2e-2 * o["out"].abs().max()
+    if p > 0:   # and it is not the forward without dropout
+        assert (got - plain["out"])[ok].abs().max() > 5 * err
+    # eval mode: no mask
+    m.eval()
+    with torch.no_grad():
+        out_e, _ = m(x.to(DT).to(cuda_device).view(1, N, d))
+    torch.cuda.synchronize()
+    assert (out_e.view(N, d).float().cpu() - plain["out"])[ok].abs().max() <= 2e-2 * plain["out"].abs().max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,d,E,f,k,p", [(600, 128, 8, 256, 2, 0.1), (1500, 256, 4, 264, 2, 0.0),
+                                         (320, 64, 8, 128, 4, 0.2), (2500, 512, 8, 1024, 2, 0.1)])
+def test_backward_matches_autograd_on_the_oracle(cuda_device, N, d, E, f, k, p):
+    """All gradients of the block (input, gate, both expert Linears with their biases) against
+    torch.autograd on the fp32 oracle with the same dropout mask, the same output gradient
+    and a load-balancing loss weight. bf16 storage of the intermediate gradients: relative 3e-2."""
+    m, params = make_block(d, E, f, k, p, cuda_device, seed=N + 1)
+    m.train()
+    x = synthetic.round_to(synthetic.make_input(N, d, seed=N + 6), DT)
+    g = torch.Generator().manual_seed(N + 7)
+    grad_out = synthetic.round_to(torch.randn(N, d, generator=g), DT)
+    grad_aux = 0.5
+    xd = x.to(DT).to(cuda_device).view(1, N, d).requires_grad_(True)
+    res = synthetic.round_to(synthetic.make_input(N, d, seed=N + 8), DT).to(DT).to(cuda_device).view(1, N, d)
+    res.requires_grad_(True)
+    out, aux = m(xd, residual=res)
+    loss = (out.float() * grad_out.to(cuda_device).view(1, N, d)).sum() + grad_aux * aux
+    loss.backward()
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    seed = m.last["seed"]
+    mult = torch.from_numpy(philox_ref.dropout_multiplier(N * k, f, p, seed)).view(N, k, f)
+    o, gx, gp = oracle_run(x, params, k, mult, grad_out, grad_aux)
+    # the gradients only compare under the same routing: the seeds are chosen so that it is
+    assert torch.equal(m.last["idx"].cpu().long(), o["idx"]), "routing differs from the oracle's own"
+    close(out.view(N, d) - res.view(N, d), o["out"].detach(), 2e-2, "forward")
+    assert torch.equal(res.grad.view(N, d).float().cpu(), grad_out)          # the residual's gradient
+    close(xd.grad.view(N, d), gx, 3e-2, "grad x")
+    close(m.gate.weight.grad, gp["gate_w"], 3e-2, "grad gate.weight")
+    close(m.gate.bias.grad, gp["gate_b"], 3e-2, "grad gate.bias")
+    for e, ex in enumerate(m.experts):
+        close(ex.gate_and_up.weight.grad, gp["w1"][e], 3e-2, f"grad experts.{e}.gate_and_up.weight")
+        close(ex.gate_and_up.bias.grad, gp["b1"][e], 3e-2, f"grad experts.{e}.gate_and_up.bias")
+        close(ex.down.weight.grad, gp["w2"][e], 3e-2, f"grad experts.{e}.down.weight")
+        close(ex.down.bias.grad, gp["b2"][e], 3e-2, f"grad experts.{e}.down.bias")
+    # a second step on the same module: buffers are reused, gradients accumulate
+    out2, aux2 = m(xd, residual=res)
+    ((out2.float() * grad_out.to(cuda_device).view(1, N, d)).sum() + grad_aux * aux2).backward()
+    torch.cuda.synchronize()
+    assert torch.isfinite(m.experts[0].down.weight.grad.float()).all()
+
+
+@pytest.mark.gpu
+def test_training_mode_limits(cuda_device):
+    m, _ = make_block(64, 8, 128, 2, 0.1, cuda_device, seed=3)
+    m.train()
+    x = torch.zeros(1, 16, 64, dtype=DT, device=cuda_device)
+    with pytest.raises(NotImplementedError):
+        m(x, fine_tuning=True)
+    with pytest.raises(NotImplementedError):
+        m.float()(x.float())
