@@ -77,7 +77,7 @@ SIGNATURES = {
     "moe_b200_ep_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_ep_setup": (_i, [_vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "moe_b200_ep_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _i, _i,
-                                 C.c_uint32, _i, _i, _vp, _vp, _sz, _vp, _vp, _vp]),
+                                 _i, _i, _vp, _vp, _sz, _vp, _vp, _vp]),
     "moe_b200_read_status": (_i, [_vp, C.POINTER(C.c_int32), _vp]),
 }
 
@@ -136,7 +136,7 @@ def train_workspace_layout(N: int, d: int, f: int, E: int, k: int, dtype: int) -
     return {name: int(arr[i]) for i, name in enumerate(TWS_NAMES)}
 
 
-EP_STAGES = ("router", "dispatch", "arrived", "experts", "returned", "combine")
+EP_STAGES = ("router", "dispatch", "experts", "combine")
 EP_SYMM_NAMES = ("flags", "cnt_all", "recv_meta", "recv_x", "ret_y")
 EP_WS_NAMES = ("status", "logits", "idx", "w", "psum_part", "psum", "aux", "scratch", "cnt_slot0",
                "offsets_local", "owner", "h")

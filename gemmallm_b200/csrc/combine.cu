@@ -8,6 +8,7 @@
 // HBM-bound gather (no atomics, deterministic): each thread produces eight
 // consecutive output elements from k 16-byte (bf16) or 32-byte (fp32) loads.
 #include "common.cuh"
+#include "ep_sync.cuh"
 
 namespace moe {
 
@@ -17,10 +18,12 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ row_of,
                const float* __restrict__ w, const T* __restrict__ residual, int64_t N, int d,
-               int k, T* __restrict__ out) {
+               int k, T* __restrict__ out, const EpSync sy, int32_t* __restrict__ status) {
   const int pieces = d >> 3;
   const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_wait();
+  // expert-parallel: y is the return buffer the expert owners store into; wait for all of them
+  if (!epsync::block_wait(sy, status, 25)) return;
   if (item >= N * pieces) return;
   const int64_t t = item / pieces;
   const int c = (int)(item - t * pieces) << 3;
@@ -124,19 +127,23 @@ int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_
 }
 
 int launch_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
-                   int64_t N, int d, int k, int dtype, void* out, cudaStream_t s) {
+                   int64_t N, int d, int k, int dtype, void* out, cudaStream_t s,
+                   const EpSync* ep_wait, int32_t* status) {
   if (N == 0) return 0;
+  const EpSync nosync = {};
+  const EpSync& sy = ep_wait != nullptr ? *ep_wait : nosync;
   const int64_t items = N * (d >> 3);
   const int64_t blocks = (items + 255) / 256;
   if (dtype == MOE_B200_BF16) {
     MOE_CUDA_CHECK(launch_pdl(combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
                               static_cast<const __nv_bfloat16*>(y), row_of, w,
                               static_cast<const __nv_bfloat16*>(residual), N, d, k,
-                              static_cast<__nv_bfloat16*>(out)));
+                              static_cast<__nv_bfloat16*>(out), sy, status));
   } else {
     MOE_CUDA_CHECK(launch_pdl(combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s,
                               static_cast<const float*>(y), row_of, w,
-                              static_cast<const float*>(residual), N, d, k, static_cast<float*>(out)));
+                              static_cast<const float*>(residual), N, d, k, static_cast<float*>(out),
+                              sy, status));
   }
   return 0;
 }

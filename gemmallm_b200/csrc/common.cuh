@@ -215,6 +215,22 @@ struct EpPeers {
   void* recv_x[kEpMaxRanks];        // [cap][d] received token rows, grouped by owned expert
   void* ret_y[kEpMaxRanks];         // [N_local*k][d] expert outputs returned to the token owner
 };
+// Expert-parallel hand-shakes folded into the neighbouring kernels. Epochs only grow; a flag
+// word holds the epoch of the last call that raised it. `epoch` points to the call's epoch in
+// the workspace (written by ep_begin_kernel at the head of the call).
+//   wait_flags != nullptr: before touching its inputs the kernel waits (bounded) until
+//     wait_flags[0 .. world) have reached *epoch;
+//   done_counter != nullptr: the last block of the grid to finish raises signal_flags[q] + rank
+//     on every rank q (after a system-scope fence: its own and, through the counter, every
+//     other block's peer stores are visible first).
+struct EpSync {
+  const uint32_t* epoch;
+  const uint32_t* wait_flags;
+  uint32_t* done_counter;
+  uint32_t* signal_flags[kEpMaxRanks];   // per destination rank: word this rank raises there
+  int world;
+};
+
 // Destination of the down pass's rows in the expert-parallel configuration.
 struct EpScatter {
   void* ret_y[kEpMaxRanks];
@@ -251,12 +267,14 @@ int launch_layernorm_rows(const void* x, const void* gamma, const void* beta, fl
 int launch_experts_simt(const void* perm, const int32_t* offsets, const void* plan, int64_t M,
                         int d, int f, int E, int dtype, void* h, void* y, cudaStream_t s);
 int launch_combine(const void* y, const int32_t* row_of, const float* w, const void* residual,
-                   int64_t N, int d, int k, int dtype, void* out, cudaStream_t s);
+                   int64_t N, int d, int k, int dtype, void* out, cudaStream_t s,
+                   const EpSync* ep_wait = nullptr, int32_t* status = nullptr);
 int build_weight_tensor_maps(const void* const* h_W1, const void* const* h_W2, int E, int d, int f,
                              void* h_tmaps /* kPlanMapsPerExpert*E*128 bytes */);
 int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                        int f, int E, void* h, void* y, const EpScatter* sc, int32_t* status,
-                       cudaStream_t s, const TrainArgs* train = nullptr);
+                       cudaStream_t s, const TrainArgs* train = nullptr, const EpSync* ep_wait = nullptr,
+                       const EpSync* ep_signal = nullptr);
 // One grouped product out[rows of e] = A[rows of e] . B_e^T (+ bias_e), B_e given by the e-th
 // tensor map of tmaps_b ([Nout, K] row-major, 128-row boxes); bias may be nullptr.
 int launch_grouped_rows(const void* A, int64_t M, int K, const void* tmaps_b, const int32_t* offsets,
@@ -268,16 +286,13 @@ int launch_grouped_rows(const void* A, int64_t M, int K, const void* tmaps_b, co
 int launch_grouped_cols(const void* At, const void* Bt, int64_t Kpad, int Ra, int Rb,
                         const int32_t* koff, void* out, int E, int32_t* status, cudaStream_t s);
 int64_t ep_scratch_ints(int64_t N, int EV, int E);
+int launch_ep_begin(uint32_t* epoch, uint32_t* done_counter, int32_t* status, cudaStream_t s);
 int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int EV, int k,
-                       int dtype, const EpPeers& peers, int rank, int world, uint32_t epoch,
+                       int dtype, const EpPeers& peers, int rank, int world, const uint32_t* epoch,
                        const int32_t* owner, const int32_t* vmap, int32_t* scratch,
                        const float* psum_part,
                        int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
                        int64_t n_total, int32_t* status, cudaStream_t s);
-int launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, int where,
-                   cudaStream_t s);
-int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint32_t epoch,
-                     cudaStream_t s);
 bool front_small_supported(int64_t N, int E, int k, int dtype);
 int64_t front_small_exchange_ints(int64_t N, int E, int k);
 bool front_split_supported(int64_t N, int E, int k, int dtype);

@@ -6,7 +6,9 @@
 // owned by ranks (optionally replicated, see ep_dispatch_kernel); the router runs
 // replicated on local tokens.
 // Every rank has one "symmetric" buffer of identical layout that its peers can
-// write (EpSymm below). Per forward, with a caller-supplied increasing epoch:
+// write. Per forward (the call's epoch is a device-side counter that ep_begin_kernel
+// advances, so the whole call can be captured in a CUDA graph and replayed):
+//   0. ep_begin_kernel: epoch += 1, status words and the completion counter cleared.
 //   1. ep_dispatch_kernel (cooperative): per-expert counts of the local
 //      (token, slot) pairs, published to every rank's cnt_all[r] together with
 //      the slot-0 counts and the softmax sums the loss needs; waits for all G
@@ -15,18 +17,20 @@
 //      token, so the layout is deterministic); pushes the token rows and a
 //      return address (source rank, pair id) with 16-byte peer stores; raises
 //      flag X on every destination.
-//   2. ep_wait_kernel on flag X; the grouped GEMMs run on the receive buffer
-//      (experts_tc2.cu). The down pass stores its output rows straight into the
-//      token owners' ret_y through peer pointers (scatter epilogue), so the
-//      return transfer overlaps the math tile by tile.
-//   3. ep_signal_kernel raises flag Y on every rank; ep_wait_kernel on flag Y;
-//      the combine kernel reads ret_y in (token, slot) order.
+//   2. The grouped GEMMs (experts_tc2.cu) wait for flag X from every source at their
+//      head and run on the receive buffer. The down pass stores its output rows
+//      straight into the token owners' ret_y through peer pointers (scatter
+//      epilogue), so the return transfer overlaps the math tile by tile; its last
+//      block raises flag Y on every rank.
+//   3. The combine kernel waits for flag Y from every owner at its head and reads
+//      ret_y in (token, slot) order.
 // Every wait on a peer's flag is bounded (2 s) and reports
 // MOE_B200_DEV_TIMEOUT through the status word instead of hanging.
 // Replaces, for the sharded configuration, reference model.py:226-268.
 #include <cooperative_groups.h>
 #include <stdio.h>
 #include "common.cuh"
+#include "ep_sync.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -36,38 +40,9 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kChunk = kDispatchChunk;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Bounded wait until *flag >= epoch (epochs only grow). False on timeout.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, int32_t* status,
-                                          int where) {
-  if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-  const unsigned long long t0 = global_ns();
-  for (uint32_t it = 1;; ++it) {
-    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    if ((it & 63u) == 0) {
-      if (global_ns() - t0 > kWaitLimitNs) {
-        atomicMax(&status[0], MOE_B200_DEV_TIMEOUT);
-        status[1] = where;
-        return false;
-      }
-      __nanosleep(200);
-    }
-  }
-}
+using epsync::ld_acquire_sys;
+using epsync::st_release_sys;
+using epsync::wait_flag;
 
 // Experts are addressed by "virtual" ids: vmap[e * world + source rank] is the
 // virtual expert that rank's pairs for expert e go to, and owner[v] the rank that
@@ -78,13 +53,15 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
 // indices, loss); EV virtual experts (counts, layout).
 __global__ void __launch_bounds__(kThreads)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx, int64_t N, int row_pieces,
-                   int E, int EV, int k, EpPeers peers, int rank, int world, uint32_t epoch,
+                   int E, int EV, int k, EpPeers peers, int rank, int world,
+                   const uint32_t* __restrict__ epoch_ptr,
                    const int32_t* __restrict__ owner, const int32_t* __restrict__ vmap,
                    int32_t* __restrict__ scratch, const float* __restrict__ psum_part,
                    int64_t router_blocks, int32_t* __restrict__ cnt_slot0,
                    float* __restrict__ psum_global, int32_t* __restrict__ offsets_local,
                    float* __restrict__ aux, int64_t n_total, int32_t* __restrict__ status) {
   cg::grid_group grid = cg::this_grid();
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(epoch_ptr);
   extern __shared__ int s_int[];
   int* s_hist = s_int;                  // [EV] local totals per virtual expert
   int* s_base = s_hist + EV;            // [EV] local rows of earlier chunks
@@ -315,15 +292,14 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ idx,
     st_release_sys(peers.flags[tid] + kEpFlagX * kEpMaxRanks + rank, epoch);
 }
 
-__global__ void ep_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, int32_t* status,
-                               int where) {
-  if ((int)threadIdx.x < world) wait_flag(flags + threadIdx.x, epoch, status, where);
-}
-
-__global__ void ep_signal_kernel(EpPeers peers, int which, int rank, int world, uint32_t epoch) {
-  __threadfence_system();
-  if ((int)threadIdx.x < world)
-    st_release_sys(peers.flags[threadIdx.x] + which * kEpMaxRanks + rank, epoch);
+// Head of a call: the epoch advances, the status words and the down pass's completion counter
+// start at zero.
+__global__ void ep_begin_kernel(uint32_t* epoch, uint32_t* done_counter, int32_t* status) {
+  if (threadIdx.x == 0) {
+    *epoch = *epoch + 1u;
+    *done_counter = 0u;
+  }
+  if (threadIdx.x < MOE_B200_STATUS_INTS) status[threadIdx.x] = 0;
 }
 
 }  // namespace
@@ -333,7 +309,7 @@ int64_t ep_scratch_ints(int64_t N, int EV, int E) {
 }
 
 int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int EV, int k,
-                       int dtype, const EpPeers& peers, int rank, int world, uint32_t epoch,
+                       int dtype, const EpPeers& peers, int rank, int world, const uint32_t* epoch,
                        const int32_t* owner, const int32_t* vmap, int32_t* scratch,
                        const float* psum_part,
                        int32_t* cnt_slot0, float* psum_global, int32_t* offsets_local, float* aux,
@@ -367,16 +343,8 @@ int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int 
   return 0;
 }
 
-int launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, int where,
-                   cudaStream_t s) {
-  ep_wait_kernel<<<1, 32, 0, s>>>(flags, world, epoch, status, where);
-  MOE_CUDA_CHECK(cudaGetLastError());
-  return 0;
-}
-
-int launch_ep_signal(const EpPeers& peers, int which, int rank, int world, uint32_t epoch,
-                     cudaStream_t s) {
-  ep_signal_kernel<<<1, 32, 0, s>>>(peers, which, rank, world, epoch);
+int launch_ep_begin(uint32_t* epoch, uint32_t* done_counter, int32_t* status, cudaStream_t s) {
+  ep_begin_kernel<<<1, 32, 0, s>>>(epoch, done_counter, status);
   MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

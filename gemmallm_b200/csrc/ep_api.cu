@@ -46,7 +46,7 @@ void ws_layout(int64_t N_local, int d, int f, int E, int k, int world, size_t* o
   const size_t cap = M * world;
   const size_t rb = (size_t)((N_local + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock);
   size_t sizes[MOE_B200_EP_WS_NUM];
-  sizes[MOE_B200_EP_WS_STATUS] = 16 * sizeof(int32_t);
+  sizes[MOE_B200_EP_WS_STATUS] = 32 * sizeof(int32_t);   // 16 status words, then epoch, completion counter
   sizes[MOE_B200_EP_WS_LOGITS] = (size_t)N_local * E * sizeof(float);
   sizes[MOE_B200_EP_WS_IDX] = M * sizeof(int32_t);
   sizes[MOE_B200_EP_WS_W] = M * sizeof(float);
@@ -129,7 +129,8 @@ int moe_b200_ep_setup(const int32_t* h_owner, const int32_t* h_vmap, int64_t N_l
   memset(tab, 0, sizeof(tab));
   memcpy(tab, h_owner, sizeof(int32_t) * EV);
   memcpy(tab + kMaxExperts, h_vmap, sizeof(int32_t) * E * world);
-  MOE_CUDA_CHECK(cudaMemsetAsync(ws + wo[MOE_B200_EP_WS_STATUS], 0, 16 * sizeof(int32_t), s));
+  // status words, the epoch (calls count from 1) and the completion counter
+  MOE_CUDA_CHECK(cudaMemsetAsync(ws + wo[MOE_B200_EP_WS_STATUS], 0, 32 * sizeof(int32_t), s));
   MOE_CUDA_CHECK(cudaMemcpyAsync(ws + wo[MOE_B200_EP_WS_OWNER], tab,
                                  sizeof(int32_t) * (kMaxExperts + E * world), cudaMemcpyHostToDevice, s));
   // `tab` lives on this stack frame
@@ -139,7 +140,7 @@ int moe_b200_ep_setup(const int32_t* h_owner, const int32_t* h_vmap, int64_t N_l
 
 int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
                         const void* residual, int64_t N_local, int d, int f, int E, int k,
-                        int dtype, int flags, int rank, int world, uint32_t epoch, int EV,
+                        int dtype, int flags, int rank, int world, int EV,
                         int E_local, void* const* h_symm_bases,
                         void* workspace, size_t workspace_bytes, void* out,
                         void* const* h_stage_events, void* stream) {
@@ -150,7 +151,6 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
   if (EV < E || EV > kMaxExperts) return set_error(MOE_B200_ERR_SHAPE, "EV must be in [E, 256]");
   if (E_local < 0 || E_local > EV) return set_error(MOE_B200_ERR_SHAPE, "E_local must be in [0, EV]");
   if (N_local > 0 && (!x || !Wg || !bg || !out)) return set_error(MOE_B200_ERR_NULL, "NULL argument");
-  if (epoch == 0) return set_error(MOE_B200_ERR_SHAPE, "epoch must start at 1 and grow by one per call");
   if (E_local > 0 && !plan_local) return set_error(MOE_B200_ERR_NULL, "plan_local is NULL");
   size_t so[MOE_B200_EP_SYMM_NUM], wo[MOE_B200_EP_WS_NUM], stotal, wtotal;
   symm_layout(N_local, d, E, k, world, so, &stotal);
@@ -190,7 +190,11 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
     MOE_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(h_stage_events[which]), s));
     return 0;
   };
-  MOE_CUDA_CHECK(cudaMemsetAsync(status, 0, 16 * sizeof(int32_t), s));
+  uint32_t* epoch = reinterpret_cast<uint32_t*>(status + 16);
+  uint32_t* done_counter = reinterpret_cast<uint32_t*>(status + 17);
+  // the call's epoch lives on the device, so the same launches can be replayed from a CUDA graph
+  rc = launch_ep_begin(epoch, done_counter, status, s);
+  if (rc) return rc;
   if ((rc = stamp(MOE_B200_EP_EV_START))) return rc;
   if (N_local > 0) {
     rc = launch_router(x, Wg, bg, N_local, d, E, k, dtype, logits, idx, w, psum_part, status, s);
@@ -202,23 +206,25 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
                           N_local * (int64_t)world, status, s);
   if (rc) return rc;
   if ((rc = stamp(MOE_B200_EP_EV_DISPATCH))) return rc;
-  rc = launch_ep_wait(peers.flags[rank] + kEpFlagX * kEpMaxRanks, world, epoch, status, 22, s);
-  if (rc) return rc;
-  if ((rc = stamp(MOE_B200_EP_EV_ARRIVED))) return rc;
-  // the down pass stores its rows straight into the token owners' ret_y
+  // the GEGLU pass waits for every source's rows at its head; the down pass stores its rows
+  // straight into the token owners' ret_y and its last block raises the return flag everywhere;
+  // the combine waits for every owner's return flag at its head
   EpScatter sc;
   for (int q = 0; q < kEpMaxRanks; ++q) sc.ret_y[q] = peers.ret_y[q];
   sc.meta = peers.recv_meta[rank];
+  EpSync wait_x = {}, signal_y = {}, wait_y = {};
+  wait_x.epoch = signal_y.epoch = wait_y.epoch = epoch;
+  wait_x.world = signal_y.world = wait_y.world = world;
+  wait_x.wait_flags = peers.flags[rank] + kEpFlagX * kEpMaxRanks;
+  wait_y.wait_flags = peers.flags[rank] + kEpFlagY * kEpMaxRanks;
+  signal_y.done_counter = done_counter;
+  for (int q = 0; q < world; ++q) signal_y.signal_flags[q] = peers.flags[q] + kEpFlagY * kEpMaxRanks + rank;
   rc = launch_experts_tc2(peers.recv_x[rank], offsets_local, plan_local, cap, d, f, E_local, h,
-                          nullptr, &sc, status, s);
+                          nullptr, &sc, status, s, nullptr, &wait_x, &signal_y);
   if (rc) return rc;
   if ((rc = stamp(MOE_B200_EP_EV_EXPERTS))) return rc;
-  rc = launch_ep_signal(peers, kEpFlagY, rank, world, epoch, s);
-  if (rc) return rc;
-  rc = launch_ep_wait(peers.flags[rank] + kEpFlagY * kEpMaxRanks, world, epoch, status, 23, s);
-  if (rc) return rc;
-  if ((rc = stamp(MOE_B200_EP_EV_RETURNED))) return rc;
-  rc = launch_combine(peers.ret_y[rank], nullptr, w, residual, N_local, d, k, dtype, out, s);
+  rc = launch_combine(peers.ret_y[rank], nullptr, w, residual, N_local, d, k, dtype, out, s, &wait_y,
+                      status);
   if (rc) return rc;
   return stamp(MOE_B200_EP_EV_COMBINE);
 }

@@ -27,6 +27,7 @@
 #include "common.cuh"
 #include "tc_ptx.cuh"
 #include "tc_epilogue.cuh"
+#include "ep_sync.cuh"
 
 namespace moe {
 
@@ -116,7 +117,7 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const int32_t* __restrict__ offsets,
                         const void* const* __restrict__ bias_ptrs, int E, int K, int Nout,
                         __nv_bfloat16* __restrict__ out, const EpScatter sc, const TrainArgs tr,
-                        int Ra, int32_t* __restrict__ status) {
+                        const EpSync sy, int Ra, int32_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -147,6 +148,10 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // everything above is independent of the kernels before this one in the stream
   pdl_wait();
   pdl_launch_dependents();
+  // expert-parallel: the rows this kernel reads were pushed by the other ranks; wait for all of
+  // them (bounded), then order those peer writes before this CTA's TMA reads
+  const bool arrived = epsync::block_wait(sy, status, 24);
+  if (sy.wait_flags != nullptr) asm volatile("fence.proxy.async;" ::: "memory");
   if (threadIdx.x == 0) {
     int acc = 0;
     int beg = offsets[0];
@@ -159,7 +164,7 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   : ((end - beg + kPairRows - 1) / kPairRows) * n_tiles;
       beg = end;
     }
-    ctl->tile_start[E] = acc;
+    ctl->tile_start[E] = arrived ? acc : 0;   // a peer never arrived: nothing to do
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -280,6 +285,9 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     if (SCATTER) __threadfence_system();
   }
+  // expert-parallel down pass: the last CTA to get here tells every rank that this rank's
+  // outputs have been stored
+  epsync::grid_signal(sy);
 
   // ---------------- teardown ----------------
   __syncwarp();
@@ -301,14 +309,14 @@ grouped_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
 template <bool GEGLU, bool SCATTER, bool TRAIN, bool COLS>
 int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_bc, const void* tmap_b, const int32_t* offsets,
                 const void* const* bias, int E, int K, int Nout, void* out, const EpScatter& sc,
-                const TrainArgs& tr, int Ra, int32_t* status, int sms, cudaStream_t s) {
+                const TrainArgs& tr, const EpSync& sy, int Ra, int32_t* status, int sms, cudaStream_t s) {
   static PerDeviceOnce once;
   auto fn = grouped_gemm_tc2_kernel<GEGLU, SCATTER, TRAIN, COLS>;
   int rc = ensure_dynamic_smem(once, fn, kSmemBytes);
   if (rc) return rc;
   MOE_CUDA_CHECK(launch_pdl(fn, dim3(sms & ~1), dim3(kThreads), kSmemBytes, s, tm_a, tm_bc,
                             static_cast<const CUtensorMap*>(tmap_b), offsets, bias, E, K, Nout,
-                            static_cast<__nv_bfloat16*>(out), sc, tr, Ra, status));
+                            static_cast<__nv_bfloat16*>(out), sc, tr, sy, Ra, status));
   return 0;
 }
 
@@ -316,31 +324,37 @@ int launch_pair(const CUtensorMap& tm_a, const CUtensorMap& tm_bc, const void* t
 
 int launch_experts_tc2(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                        int f, int E, void* h, void* y, const EpScatter* sc, int32_t* status,
-                       cudaStream_t s, const TrainArgs* train) {
-  if (M == 0 || E == 0) return 0;
+                       cudaStream_t s, const TrainArgs* train, const EpSync* ep_wait,
+                       const EpSync* ep_signal) {
+  // expert-parallel ranks take part in the hand-shakes even when they own no rows
+  if ((M == 0 || E == 0) && ep_wait == nullptr && ep_signal == nullptr) return 0;
   PlanView pv = plan_view(plan, E);
   alignas(64) CUtensorMap tm_x, tm_h;
-  int rc = encode_tmap_2d(&tm_x, perm, (uint64_t)M, (uint64_t)d, BM);
+  const uint64_t rows = M > 0 ? (uint64_t)M : 1;   // a rank without rows still launches (hand-shakes)
+  int rc = encode_tmap_2d(&tm_x, perm, rows, (uint64_t)d, BM);
   if (rc) return rc;
-  rc = encode_tmap_2d(&tm_h, h, (uint64_t)M, (uint64_t)f, BM);
+  rc = encode_tmap_2d(&tm_h, h, rows, (uint64_t)f, BM);
   if (rc) return rc;
   int sms = 0;
   rc = sm_count(&sms);
   if (rc) return rc;
   const EpScatter none = {};
   const TrainArgs eval = {};
+  const EpSync nosync = {};
+  const EpSync& sy1 = ep_wait != nullptr ? *ep_wait : nosync;
+  const EpSync& sy2 = ep_signal != nullptr ? *ep_signal : nosync;
   if (train != nullptr)
     rc = launch_pair<true, false, true, false>(tm_x, tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, none, *train,
-                                               0, status, sms, s);
+                                               sy1, 0, status, sms, s);
   else
     rc = launch_pair<true, false, false, false>(tm_x, tm_x, pv.tmap_W1, offsets, pv.b1, E, d, f, h, none, eval,
-                                                0, status, sms, s);
+                                                sy1, 0, status, sms, s);
   if (rc) return rc;
   if (sc != nullptr)
     return launch_pair<false, true, false, false>(tm_h, tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, nullptr, *sc,
-                                                  eval, 0, status, sms, s);
+                                                  eval, sy2, 0, status, sms, s);
   return launch_pair<false, false, false, false>(tm_h, tm_h, pv.tmap_W2, offsets, pv.b2, E, f, d, y, none, eval,
-                                                 0, status, sms, s);
+                                                 sy2, 0, status, sms, s);
 }
 
 int launch_grouped_rows(const void* A, int64_t M, int K, const void* tmaps_b, const int32_t* offsets,
@@ -355,8 +369,9 @@ int launch_grouped_rows(const void* A, int64_t M, int K, const void* tmaps_b, co
   if (rc) return rc;
   const EpScatter none = {};
   const TrainArgs eval = {};
+  const EpSync nosync = {};
   return launch_pair<false, false, false, false>(tm_a, tm_a, tmaps_b, offsets, bias, E, K, Nout, out, none,
-                                                 eval, 0, status, sms, s);
+                                                 eval, nosync, 0, status, sms, s);
 }
 
 int launch_grouped_cols(const void* At, const void* Bt, int64_t Kpad, int Ra, int Rb,
@@ -372,8 +387,9 @@ int launch_grouped_cols(const void* At, const void* Bt, int64_t Kpad, int Ra, in
   if (rc) return rc;
   const EpScatter none = {};
   const TrainArgs eval = {};
+  const EpSync nosync = {};
   return launch_pair<false, false, false, true>(tm_a, tm_b, nullptr, koff, nullptr, E, 0, Rb, out,
-                                                none, eval, Ra, status, sms, s);
+                                                none, eval, nosync, Ra, status, sms, s);
 }
 
 }  // namespace moe

@@ -108,7 +108,6 @@ class ExpertParallelMOE(nn.Module):
         self.hidden_size = hidden_size
         self.d_ff = hidden_size * expansion_factor if d_ff is None else d_ff
         self.top_k = top_k
-        self.epoch = 0
         self._plan = _Plan()
         self._plan_ft = _Plan()
         self._lora = _MergedLora()
@@ -145,7 +144,6 @@ class ExpertParallelMOE(nn.Module):
         # the placement tables live in the workspace: uploaded here, once per workspace
         check(lib.moe_b200_ep_setup(owner, vmap, N_local, d, f, E, k, G, len(self.v_owner), ws_base,
                                     wbytes, _stream(dev)), "ep_setup")
-        self.epoch = 0
         self._state = {
             "key": key, "symm": symm, "hdl": hdl, "bases": (C.c_void_p * G)(*bases),
             "ws": ws, "ws_base": ws_base, "ws_bytes": wbytes,
@@ -195,10 +193,9 @@ class ExpertParallelMOE(nn.Module):
                 plan = self._plan_ft.get([merged[e] for e in self.local_ids], d, f, dtype, dev)
             else:
                 plan = self._plan.get(local, d, f, dtype, dev)
-            self.epoch += 1
             check(lib.moe_b200_ep_forward(
                 x.data_ptr(), self.gate.weight.data_ptr(), self.gate.bias.data_ptr(), plan, res_ptr,
-                N, d, f, E, k, dtype, 0, self.rank, self.world, self.epoch, len(self.v_owner),
+                N, d, f, E, k, dtype, 0, self.rank, self.world, len(self.v_owner),
                 len(self.local_virtual), st["bases"],
                 st["ws_base"], st["ws_bytes"], out.data_ptr(), self._stage_events, _stream(dev)),
                 "ep_forward")
@@ -298,8 +295,9 @@ class ExpertParallelMOE(nn.Module):
     def time_stages(self, tensor: torch.Tensor, reps: int = 10) -> dict:
         """CUDA-event time (ms, mean over ``reps`` calls) of each stage of the sharded forward on
         this rank: the library records an event at every stage boundary of the call. The waits
-        on peers belong to the stages they end ("arrived", "returned"), so a rank that is ahead
-        of its peers shows its lead there. All ranks must call this together."""
+        on peers sit at the head of the stage that needs the data ("experts" waits for the rows,
+        "combine" for the outputs), so a rank that is ahead of its peers shows its lead there.
+        All ranks must call this together."""
         n = len(_cabi.EP_STAGES) + 1
         sets = []
         for _ in range(reps):

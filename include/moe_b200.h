@@ -434,7 +434,8 @@ enum {
   MOE_B200_EP_SYMM_NUM
 };
 enum {
-  MOE_B200_EP_WS_STATUS = 0, MOE_B200_EP_WS_LOGITS, MOE_B200_EP_WS_IDX, MOE_B200_EP_WS_W,
+  MOE_B200_EP_WS_STATUS = 0, /* int32 [16] status words, then the call counter */
+  MOE_B200_EP_WS_LOGITS, MOE_B200_EP_WS_IDX, MOE_B200_EP_WS_W,
   MOE_B200_EP_WS_PSUM_PART, MOE_B200_EP_WS_PSUM, /* float [E], summed over all ranks */
   MOE_B200_EP_WS_AUX,          /* loss over all N_local*world tokens (model.py:213-216) */
   MOE_B200_EP_WS_SCRATCH, MOE_B200_EP_WS_CNT_SLOT0, /* int32 [E], all ranks */
@@ -455,7 +456,9 @@ int moe_b200_ep_workspace_layout(int64_t N_local, int d, int f, int E, int k, in
  * h_vmap[e * world + r] the virtual expert that rank r's rows for expert e go to.
  * Without replication EV = E and h_vmap[e * world + r] = e. Giving a popular
  * expert several virtual ids on different ranks (with the same weights in each
- * rank's plan) splits its rows between them. Also zeroes the status words. */
+ * rank's plan) splits its rows between them. Also zeroes the status words and
+ * the call counter: call it on all ranks together, with the symmetric buffers
+ * zero-filled. */
 int moe_b200_ep_setup(const int32_t* h_owner, const int32_t* h_vmap, int64_t N_local, int d, int f,
                       int E, int k, int world, int EV, void* workspace, size_t workspace_bytes,
                       void* stream);
@@ -469,12 +472,14 @@ int moe_b200_ep_setup(const int32_t* h_owner, const int32_t* h_vmap, int64_t N_l
  * h_stage_events: NULL, or MOE_B200_EP_EV_NUM cudaEvent_t handles that the call
  * records on `stream` at the stage boundaries (for per-stage timing; the waits
  * on peers are part of the stages they end).
- * `epoch` is 1 on the first call and one more on every later call, the same on
- * all ranks. All ranks must make the same sequence of calls. A peer that never
- * arrives makes the bounded waits run out: status word = MOE_B200_DEV_TIMEOUT. */
+ * All ranks must make the same sequence of calls on workspaces and symmetric
+ * buffers that were set up together: the hand-shakes are numbered by a call
+ * counter that lives in the workspace (so the launches of one call can be
+ * captured in a CUDA graph and replayed). A peer that never arrives makes the
+ * bounded waits run out: status word = MOE_B200_DEV_TIMEOUT. */
 int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const void* plan_local,
                         const void* residual, int64_t N_local, int d, int f, int E, int k,
-                        int dtype, int flags, int rank, int world, uint32_t epoch, int EV,
+                        int dtype, int flags, int rank, int world, int EV,
                         int E_local, void* const* h_symm_bases,
                         void* workspace, size_t workspace_bytes, void* out,
                         void* const* h_stage_events, void* stream);
@@ -482,10 +487,9 @@ enum {
   MOE_B200_EP_EV_START = 0, /* before the router */
   MOE_B200_EP_EV_ROUTER,    /* router done */
   MOE_B200_EP_EV_DISPATCH,  /* counts exchanged, own rows pushed to their owners */
-  MOE_B200_EP_EV_ARRIVED,   /* every source's rows have landed here */
-  MOE_B200_EP_EV_EXPERTS,   /* both grouped GEMMs done, outputs stored to the token owners */
-  MOE_B200_EP_EV_RETURNED,  /* every owner's outputs for the local tokens have landed */
-  MOE_B200_EP_EV_COMBINE,   /* combine done */
+  MOE_B200_EP_EV_EXPERTS,   /* every source's rows waited for, both grouped GEMMs done, outputs
+                             * stored to the token owners */
+  MOE_B200_EP_EV_COMBINE,   /* every owner's outputs waited for, combine done */
   MOE_B200_EP_EV_NUM
 };
 

@@ -89,7 +89,7 @@ def test_missing_peer_ends_in_timeout_status(cuda_device):
                                 helpers.stream(dev)), "ep_setup")
     torch.cuda.synchronize()
     check(lib.moe_b200_ep_forward(x.data_ptr(), dp["gate_w"].data_ptr(), dp["gate_b"].data_ptr(),
-                                  plan.ptr, None, N, d, f, E, k, _cabi.BF16, 0, 0, world, 1, E,
+                                  plan.ptr, None, N, d, f, E, k, _cabi.BF16, 0, 0, world, E,
                                   len(local), bases, ws_base, wbytes,
                                   out.data_ptr(), None, helpers.stream(dev)), "ep_forward")
     torch.cuda.synchronize()                      # returns: no wait is unbounded
