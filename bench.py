@@ -591,7 +591,7 @@ def run_ours(args, wl):
             gbs_step = nbytes_step / (ms_step * 1e-3) / 1e9
             gbs_experts = wbytes / (stage_ms["experts"] * 1e-3) / 1e9
             line["roofline"] = {
-                "kernel": ("decode_spec_kernel / decode_fused_kernel (GEGLU + split-K down tiles, one launch)"
+                "kernel": ("decode_spec_kernel (GEGLU + split-K down tiles, one launch) / geglu_gemv + down_gemv"
                            if small_n else "decode_spec_kernel<SORTED> (GEGLU + split-K down tiles on sorted rows)"),
                 "bound": "hbm", "achieved": gbs_experts, "peak": hbm, "unit": "GB/s",
                 "frac": gbs_experts / hbm, "traffic": traffic, "traffic_source": traffic_source,
@@ -904,6 +904,181 @@ def run_ep(args, wl):
         sys.exit(1)
 
 
+# ---------------------------------------------------------------------------
+# the whole decoder forward with the block swapped in (workload "c3")
+# ---------------------------------------------------------------------------
+
+C3 = {"layers": 12, "vocab": 32000, "context": 64, "d_model": 1024, "factor": 4, "head_dim": 64,
+      "q_heads": 16, "kv_heads": 1, "n_experts": 8, "batch": 512}
+
+
+def build_decoder(device, swap: bool, dtype):
+    """The reference's LLM (model.py:322-372, from oracle/_ref) with seeded N(0, 0.02^2) weights
+    and zero biases; with `swap` every layer.moe is replaced by the new block through the strict
+    state_dict."""
+    from gemmallm_b200 import MOE
+    from oracle import make_ref
+    ref = make_ref.load()
+    c = C3
+    reset = torch.nn.Linear.reset_parameters
+    torch.nn.Linear.reset_parameters = lambda self: None    # every Linear is overwritten below
+    try:
+        with torch.device(device):
+            llm = ref.LLM(c["layers"], c["vocab"], c["context"], c["d_model"], expansion_factor=c["factor"],
+                          head_dim=c["head_dim"], q_head=c["q_heads"], kv_head=c["kv_heads"], use_moe=True,
+                          num_experts=c["n_experts"], device=str(device)).eval()
+    finally:
+        torch.nn.Linear.reset_parameters = reset
+    g = torch.Generator(device=device).manual_seed(0)
+    with torch.no_grad():
+        for name, p in llm.named_parameters():
+            if "pos_emb" in name or "norm" in name:
+                continue
+            if name.endswith(".bias"):
+                p.zero_()
+            else:
+                p.copy_(torch.randn(p.shape, generator=g, device=device) * 0.02)
+    if swap:
+        for layer in llm.transformer:
+            new = MOE(c["d_model"], num_experts=c["n_experts"], expansion_factor=c["factor"], device="cuda").eval()
+            new.to(device)
+            new.load_state_dict(layer.moe.state_dict(), strict=True)
+            layer.moe = new
+    return llm.to(dtype=dtype)
+
+
+def decoder_config():
+    c = C3
+    return {"workload": "c3", "tokens": c["batch"] * c["context"], "d_model": c["d_model"],
+            "n_experts": c["n_experts"], "d_ff": c["d_model"] * c["factor"], "top_k": 2, "routing": "zero",
+            "layers": c["layers"], "vocab": c["vocab"], "context": c["context"],
+            "l2": "no flush: one layer's working set exceeds the 126 MB L2"}
+
+
+def run_decoder(args):
+    """tokens/s of the reference's whole 12-layer decoder forward in bf16 with the new block in
+    every layer; attention, norms and classifier are the reference's own torch code."""
+    c = C3
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    dt = torch.bfloat16
+    llm = build_decoder(dev, True, dt)
+    ids = torch.randint(0, c["vocab"], (c["batch"], c["context"]), generator=torch.Generator().manual_seed(3))
+    table = (torch.randn(c["vocab"], c["d_model"], generator=torch.Generator().manual_seed(2)) * 0.02)
+    x_host = table[ids].to(dt).pin_memory()
+    x = x_host.to(dev)
+    mask = torch.triu(torch.full((c["context"], c["context"]), float("-inf"), device=dev, dtype=dt), 1)
+    moe_events = []
+
+    def pre(mod, a):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        moe_events.append([e, None])
+
+    def post(mod, a, o):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        moe_events[-1][1] = e
+
+    tokens = c["batch"] * c["context"]
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            logits, aux = llm(x.clone(), mask, False)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(dev.index or 0) as clocks:
+            e0.record()
+            for _ in range(args.steps):
+                logits, aux = llm(x.clone(), mask, False)
+            e1.record()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        # the block's share: events around every layer.moe call of a few more forwards
+        handles = []
+        for layer in llm.transformer:
+            handles += [layer.moe.register_forward_pre_hook(pre), layer.moe.register_forward_hook(post)]
+        for _ in range(3):
+            llm(x.clone(), mask, False)
+        torch.cuda.synchronize()
+        for h in handles:
+            h.remove()
+        moe_ms = sum(a.elapsed_time(b) for a, b in moe_events) / 3
+        # end to end: embeddings from pinned host memory in, last-position logits and loss out
+        out_host = torch.empty(c["batch"], c["vocab"], dtype=dt).pin_memory()
+        aux_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            xin = x_host.to(dev, non_blocking=True)
+            logits, aux = llm(xin, mask, False)
+            out_host.copy_(logits[:, -1, :], non_blocking=True)
+            aux_host.copy_(aux.float().view(1), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        t1.record()
+        torch.cuda.synchronize()
+        e2e_ms = t0.elapsed_time(t1) / args.steps
+    status = max(layer.moe.device_status() for layer in llm.transformer)
+    if status != 0:
+        raise RuntimeError(f"device status {status}")
+    peaks, peak_kind = load_peaks()
+    flops = 6.0 * 2 * c["d_model"] * c["d_model"] * c["factor"] * tokens * c["layers"]
+    line = {
+        "metric": "moe_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": decoder_config(),
+        "run": {"what": "whole decoder forward (reference LLM, every layer.moe swapped for the new block)",
+                "moe_ms_per_forward": moe_ms, "moe_share": moe_ms / ms,
+                "moe_tflops_incl_router_dispatch_combine": flops / (moe_ms * 1e-3) / 1e12},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": tokens * c["d_model"] * 2,
+                "d2h_bytes_per_step": c["batch"] * c["vocab"] * 2 + 4, "ms_per_step": e2e_ms,
+                "mode": "embeddings from pinned host memory, last-position logits and loss back, host waits"},
+        "gpu_launches": 5 * c["layers"] * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": {"kernel": "grouped_gemm_tc2_kernel inside the 12 blocks (whole block timed)",
+                     "bound": "tensor", "achieved": flops / (moe_ms * 1e-3) / 1e12,
+                     "peak": float(peaks["bf16_tflops"]), "unit": "TFLOP/s",
+                     "frac": flops / (moe_ms * 1e-3) / 1e12 / float(peaks["bf16_tflops"]), "traffic": None,
+                     "peak_source": f"{peak_kind} bf16 burst"},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_decoder_reference(args):
+    """The unmodified reference LLM (its own MoE) on the host cores, fp32: a bounded sample of
+    16 sequences per step instead of 512."""
+    c = C3
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    llm = build_decoder(torch.device("cpu"), False, torch.float32)
+    batch = 16
+    ids = torch.randint(0, c["vocab"], (batch, c["context"]), generator=torch.Generator().manual_seed(3))
+    table = (torch.randn(c["vocab"], c["d_model"], generator=torch.Generator().manual_seed(2)) * 0.02)
+    x = table[ids]
+    mask = torch.triu(torch.full((c["context"], c["context"]), float("-inf")), 1)
+    with torch.no_grad():
+        for _ in range(max(1, min(args.warmup, 2))):
+            llm(x.clone(), mask, False)
+        times = []
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            llm(x.clone(), mask, False)
+            times.append(time.perf_counter() - t0)
+    value = batch * c["context"] * args.steps / sum(times)
+    line = {"impl": "reference", "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * sum(times) / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": decoder_config(),
+            "run": {"parallelism": "cpu", "threads": cores},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "reference",
+                             "sample": f"{batch} of {c['batch']} sequences per step, whole decoder forward, fp32"},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
 def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: bool = False):
     """CUDA-event time of each stage, called through its own C-ABI entry point
     on the buffers of the module's workspace, on the current stream."""
@@ -950,6 +1125,11 @@ def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: b
             calls["experts"] = lambda: lib.moe_b200_experts_decode_spec(
                 x2d.data_ptr(), p["idx"], p["offsets"], plan, N, k, d, f, E, p["h"], p["part"], ready,
                 p["status"], s)
+        calls["experts_gemv"] = lambda: lib.moe_b200_experts_gemv(
+            p["perm"], p["offsets"], plan, N * k, d, f, E, p["h"], p["part"], s)
+        if "experts_sorted" not in calls:
+            # a row or two per expert: the forward uses the matrix-vector kernels
+            calls["experts_fused"], calls["experts"] = calls["experts"], calls["experts_gemv"]
         calls["combine"] = lambda: lib.moe_b200_combine_decode(
             p["part"], splits, N * k, p["row_of"], p["idx"], p["w"], plan, E, None, N, d, k,
             out.data_ptr(), s)
@@ -995,7 +1175,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None,
-                    help="default: c1_uniform on one GPU, c4 (expert-parallel) on several")
+                    help="default: c1_uniform on one GPU, c4 (expert-parallel) on several; c3 = the whole "
+                         "12-layer decoder forward with the block swapped in (one GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="one GPU, default workload: skip the decode-shaped sweep and the "
@@ -1013,6 +1194,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.workload is None:
         args.workload = "c1_uniform" if world == 1 else "c4"
+    if args.workload == "c3":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_decoder_reference(args) if args.impl == "reference" else run_decoder(args)
+        return
     wl = synthetic.WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, wl)

@@ -51,6 +51,7 @@ SIGNATURES = {
     "moe_b200_experts_decode_spec": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "moe_b200_decode_spec_rows": (_i, [_i64]),
     "moe_b200_experts_decode_fused": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "moe_b200_experts_gemv": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp, _vp]),
     "moe_b200_decode_splits": (_i, [_i]),
     "moe_b200_decode_max_rows": (_i64, []),
     "moe_b200_combine_decode": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _vp, _i64, _i, _i, _vp,

@@ -330,6 +330,17 @@ int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, cons
                                         (cudaStream_t)stream);
 }
 
+int moe_b200_experts_gemv(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
+                          int f, int E, void* h, float* part, void* stream) {
+  int rc = check_shape(0, d, f, E, 1, MOE_B200_BF16);
+  if (rc) return rc;
+  if (M < 0 || M > kDecodeMaxRows) return set_error(MOE_B200_ERR_SHAPE, "M exceeds the small-N path's row limit");
+  if (M == 0) return 0;
+  if (!perm || !offsets || !plan || !h || !part) return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(perm) || !aligned16(h) || !aligned16(part)) return set_error(MOE_B200_ERR_ALIGN, "buffers must be 16-byte aligned");
+  return launch_experts_gemv(perm, offsets, plan, M, d, f, E, decode_splits(f), h, part, (cudaStream_t)stream);
+}
+
 int moe_b200_decode_spec_rows(int64_t N) { return decode_spec_rows(N); }
 
 int moe_b200_experts_decode_spec(const void* x, const int32_t* idx, const int32_t* offsets,
@@ -459,9 +470,8 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
     if (spec)
       rc = launch_experts_tc_decode_spec(x, idx, offsets, plan, N, k, d, f, E, h, part,
                                          status + MOE_B200_READY_OFFSET, status, s);
-    else
-      rc = launch_experts_tc_decode_fused(perm, offsets, plan, N * k, d, f, E, h, part,
-                                          status + MOE_B200_READY_OFFSET, status, s);
+    else   // a row or two per expert: matrix-vector streaming of the experts that were hit
+      rc = launch_experts_gemv(perm, offsets, plan, N * k, d, f, E, decode_splits(f), h, part, s);
     if (rc) return rc;
     return moe_b200_combine_decode(part, decode_splits(f), N * k, row_of, idx, w, plan, E, residual,
                                    N, d, k, out, stream);

@@ -321,6 +321,9 @@ int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_
                           const int32_t* idx, const float* w, const void* plan, int E,
                           const void* residual, int64_t N, int d, int k, void* out, cudaStream_t s);
 
+int launch_experts_gemv(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
+                        int f, int E, int ksplit, void* h, float* part, cudaStream_t s);
+
 // ---- backward.cu ----
 int launch_pair_of(const int32_t* row_of, int64_t M, int32_t* pair_of, cudaStream_t s);
 int launch_pad_offsets(const int32_t* offsets, int E, int32_t* koff, cudaStream_t s);

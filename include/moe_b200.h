@@ -274,6 +274,16 @@ int moe_b200_experts_decode_fused(const void* perm, const int32_t* offsets, cons
 int moe_b200_decode_splits(int f);
 int64_t moe_b200_decode_max_rows(void);
 
+/* Part 3 for a row or two per expert (decode with a few tokens), bf16, M <=
+ * moe_b200_decode_max_rows(): h [M,f] and part[s][M][d] as moe_b200_experts_decode_fused,
+ * from two weight-streaming launches (GEGLU, then the down product split over K into
+ * moe_b200_decode_splits(f) ranges) in which the weights are the 16-row operand of
+ * mma.sync and thousands of warps stream at once even when only two experts are hit
+ * (model.py:174-184; the reference skips experts without rows, model.py:256, so does this).
+ * Its blocks do not wait on one another: no residency requirement. */
+int moe_b200_experts_gemv(const void* perm, const int32_t* offsets, const void* plan,
+                          int64_t M, int d, int f, int E, void* h, float* part, void* stream);
+
 /* Part 3 for small N without waiting for the routing: the same partial sums
  * part[s][M][d] as moe_b200_experts_decode_fused (row order of moe_b200_dispatch), but
  * computed from the UNSORTED tokens x [N,d]: every expert's weights are streamed and

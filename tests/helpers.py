@@ -126,6 +126,17 @@ def experts_decode_fused(perm, offsets, plan: Plan):
     return h, part, status
 
 
+def experts_gemv(perm, offsets, plan: Plan):
+    M, d = perm.shape
+    dev = perm.device
+    splits = lib.moe_b200_decode_splits(plan.f)
+    h = torch.full((M, plan.f), float("nan"), dtype=perm.dtype, device=dev)
+    part = torch.full((splits, M, d), float("nan"), dtype=torch.float32, device=dev)
+    check(lib.moe_b200_experts_gemv(perm.data_ptr(), offsets.data_ptr(), plan.ptr, M, d, plan.f, plan.E,
+                                    h.data_ptr(), part.data_ptr(), stream(dev)), "experts_gemv")
+    return h, part
+
+
 def experts_decode_spec(x, idx, offsets, plan: Plan):
     """x [N,d] unsorted tokens; returns part [splits, N*k, d] in dispatch row order."""
     N, d = x.shape

@@ -1,89 +1,142 @@
-"""The block inside a 12-layer pre-norm decoder stack in bf16 (the shape of the
-reference's LLMLayer, model.py:305-321: norm1 -> attention -> += skip -> norm2 ->
-MoE -> += skip), with the skip connection fused into the block's combine kernel.
-The non-MoE parts are plain torch ops of this test harness (multi-query
-attention with 16 query heads, 1 KV head, head_dim 64, causal; LayerNorm);
-every layer's MoE call is checked teacher-forced against the CPU oracle on the
-input it actually saw."""
+"""The block inside the reference's own decoder: ``LLM`` of model.py:322-372 (12 pre-norm
+layers: LayerNorm -> multi-query attention with RoPE and a sigmoid head gate -> += skip ->
+LayerNorm -> MoE -> += skip; 16 query heads, 1 KV head, head_dim 64, context 64), built
+from the unmodified reference module under oracle/_ref, with every ``layer.moe`` replaced by
+the new block through ``load_state_dict(strict=True)``. The reference's attention, norms
+and classifier run as they are (torch ops, bf16); each layer's MoE call is checked
+teacher-forced against the CPU oracle on the input it actually saw, and the logits of the
+whole forward are compared with the fp32 reference model on the CPU."""
 import pytest
 import torch
-import torch.nn as nn
-import torch.nn.functional as F
 
-import helpers
 from gemmallm_b200 import MOE, synthetic
-from oracle import moe_oracle
+from oracle import make_ref, moe_oracle
 
 pytestmark = pytest.mark.gpu
 
-
-class Layer(nn.Module):
-    def __init__(self, d, heads, head_dim, E, f, k):
-        super().__init__()
-        self.heads, self.head_dim = heads, head_dim
-        self.norm1, self.norm2 = nn.LayerNorm(d), nn.LayerNorm(d)
-        self.q = nn.Linear(d, heads * head_dim)
-        self.kv = nn.Linear(d, 2 * head_dim)          # one KV head
-        self.o = nn.Linear(heads * head_dim, d)
-        self.moe = MOE(d, num_experts=E, d_ff=f, top_k=k, device="cuda")
-
-    def forward(self, x, trace):
-        B, S, d = x.shape
-        skip = x
-        h = self.norm1(x)
-        q = self.q(h).view(B, S, self.heads, self.head_dim).transpose(1, 2)
-        kk, vv = self.kv(h).view(B, S, 2, self.head_dim).unbind(2)
-        kk = kk.unsqueeze(1).expand(B, self.heads, S, self.head_dim)
-        vv = vv.unsqueeze(1).expand(B, self.heads, S, self.head_dim)
-        a = F.scaled_dot_product_attention(q, kk, vv, is_causal=True)
-        x = self.o(a.transpose(1, 2).reshape(B, S, -1)) + skip
-        skip = x
-        h = self.norm2(x)
-        y, aux = self.moe(h, residual=skip)           # `tensor += skip_connection` fused
-        trace.append((h.detach(), skip.detach(), y.detach(), self.moe.last["logits"].clone(), aux))
-        return y, aux
+D, HEADS, HEAD_DIM, E, FACTOR, K, S, VOCAB = 1024, 16, 64, 8, 4, 2, 64, 32000
 
 
-def check_layer(layer_params, h, skip, y, logits, k):
-    N, d = h.shape[0] * h.shape[1], h.shape[2]
-    x = h.reshape(N, d).float().cpu()
+def build_reference_llm(layers, device, seed=0):
+    """The reference LLM with the weight rule of the benchmarks (weights ~ N(0, 0.02^2), biases
+    0, LayerNorm at its identity), in fp32 on `device`."""
+    ref = make_ref.load()
+    torch.manual_seed(seed)
+    # every Linear is overwritten below: skip torch's own (slow, 1.3 G numbers) initialisation
+    reset = torch.nn.Linear.reset_parameters
+    torch.nn.Linear.reset_parameters = lambda self: None
+    try:
+        with torch.device(device):
+            llm = ref.LLM(layers, VOCAB, S, D, expansion_factor=FACTOR, head_dim=HEAD_DIM, q_head=HEADS,
+                          kv_head=1, use_moe=True, num_experts=E, device=str(device)).eval()
+    finally:
+        torch.nn.Linear.reset_parameters = reset
+    g = torch.Generator().manual_seed(seed)
     with torch.no_grad():
-        o = moe_oracle.moe_forward(x, layer_params, k, logits=logits.cpu())
-    ok = ~moe_oracle.tie_rows(o["probs"], k)
-    ref = o["out"] + skip.reshape(N, d).float().cpu()
-    got = y.reshape(N, d).float().cpu()
-    err = (got - ref)[ok].abs().max()
-    # bf16 tolerance of the block: relative 2e-2 (against the largest reference value)
-    assert err <= 2e-2 * ref.abs().max(), f"max-abs {err} vs scale {ref.abs().max()}"
-    return float(err / ref.abs().max())
+        for name, p in llm.named_parameters():
+            if "pos_emb" in name or "norm" in name:
+                continue
+            if name.endswith(".bias"):
+                p.zero_()
+            else:
+                p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.device))
+    return llm
 
 
-@pytest.mark.parametrize("layers,batch", [(12, 32), (1, 512)])
-def test_moe_inside_decoder_stack(cuda_device, layers, batch):
-    d, heads, head_dim, E, f, k, S = 1024, 16, 64, 8, 4096, 2, 64
+def swap_in_new_blocks(llm, device, dtype):
+    """layer.moe := the new block, parameters carried over by the strict state_dict."""
+    for layer in llm.transformer:
+        new = MOE(D, num_experts=E, expansion_factor=FACTOR, device="cuda").eval()
+        new.load_state_dict(layer.moe.state_dict(), strict=True)
+        layer.moe = new
+        layer.device = str(device)     # where the reference creates its scalar tensors
+    llm.device = str(device)
+    return llm.to(device=device, dtype=dtype)
+
+
+def causal_mask(device, dtype):
+    return torch.triu(torch.full((S, S), float("-inf"), device=device, dtype=dtype), diagonal=1)
+
+
+def layer_params(moe):
+    """CPU fp32 copies of one block's parameters in the oracle's layout."""
+    f32 = lambda t: t.detach().float().cpu()
+    return {"gate_w": f32(moe.gate.weight), "gate_b": f32(moe.gate.bias),
+            "w1": torch.stack([f32(ex.gate_and_up.weight) for ex in moe.experts]),
+            "b1": torch.stack([f32(ex.gate_and_up.bias) for ex in moe.experts]),
+            "w2": torch.stack([f32(ex.down.weight) for ex in moe.experts]),
+            "b2": torch.stack([f32(ex.down.bias) for ex in moe.experts])}
+
+
+@pytest.mark.skipif(not make_ref.available(), reason="oracle/_ref/model.py absent (run oracle/make_ref.py)")
+@pytest.mark.parametrize("layers,batch", [(12, 16), (2, 512)])
+def test_new_block_inside_the_reference_decoder(cuda_device, layers, batch):
     dt = torch.bfloat16
-    torch.manual_seed(0)
-    stack, cpu_params = [], []
-    for i in range(layers):
-        layer = Layer(d, heads, head_dim, E, f, k).eval()
-        p = helpers.rounded_params(synthetic.make_params(d, E, f, seed=100 + i), dt)
-        synthetic.load_into(layer.moe, p, dt, cuda_device)
-        layer.to(device=cuda_device, dtype=dt)
-        stack.append(layer)
-        cpu_params.append(p)
-    table = (torch.randn(32000, d, generator=torch.Generator().manual_seed(2)) * 0.02)
-    ids = torch.randint(0, 32000, (batch, S), generator=torch.Generator().manual_seed(3))
-    x = table[ids].to(dt).to(cuda_device)
-    trace, total_aux = [], 0.0
+    llm = build_reference_llm(layers, "cpu")
     with torch.no_grad():
-        for layer in stack:
-            x, aux = layer(x, trace)
-            total_aux = total_aux + aux
+        for p in llm.parameters():        # bf16-representable values, so that every run below sees the same numbers
+            p.copy_(p.to(dt).float())
+    ids = torch.randint(0, VOCAB, (batch, S), generator=torch.Generator().manual_seed(3))
+    table = torch.randn(VOCAB, D, generator=torch.Generator().manual_seed(2)) * 0.02
+    x = table[ids].to(dt).float()
+    # the unmodified reference (its own MoE) in fp32 on the CPU, small batches only
+    ref_logits = None
+    if batch <= 16:
+        with torch.no_grad():
+            ref_logits, ref_aux = llm(x.clone(), causal_mask("cpu", torch.float32), False)
+    swap_in_new_blocks(llm, cuda_device, torch.float32)
+    msg = f"{layers} layers x {batch * S} tokens"
+    if ref_logits is not None:
+        # (1) drop-in in fp32: the whole forward with the new block in every layer against the
+        # reference's own forward. Same arithmetic type, so the logits have to agree closely.
+        with torch.no_grad():
+            logits32, aux32 = llm(x.to(cuda_device), causal_mask(cuda_device, torch.float32), False)
+        torch.cuda.synchronize()
+        assert all(layer.moe.device_status() == 0 for layer in llm.transformer)
+        scale = float(ref_logits.abs().max())
+        per_token = (logits32.cpu() - ref_logits).abs().amax(-1).flatten() / scale
+        agree = float((logits32.cpu().argmax(-1) == ref_logits.argmax(-1)).float().mean())
+        msg += (f"; fp32 logits vs the reference's forward: per-token max-abs/max median "
+                f"{float(per_token.median()):.2e}, worst {float(per_token.max()):.2e}, arg-max agreement {agree:.4f}")
+        assert float(per_token.quantile(0.99)) < 1e-3      # a routing flip may move a token; the rest agree
+        assert agree > 0.99
+        assert abs(float(aux32) - float(ref_aux)) <= 1e-4 * abs(float(ref_aux)) + 1e-7
+    # (2) bf16 (the benchmarked type): every layer's MoE call teacher-forced against the oracle on
+    # the input it actually saw
+    llm.to(dtype=dt)
+    trace = []
+
+    def hook(moe, args, output):
+        trace.append((moe, args[0].detach(), output[0].detach().clone(), moe.last["logits"].clone()))
+
+    handles = [layer.moe.register_forward_hook(hook) for layer in llm.transformer]
+    with torch.no_grad():
+        logits, aux = llm(x.to(dt).to(cuda_device), causal_mask(cuda_device, dt), False)
     torch.cuda.synchronize()
-    assert torch.isfinite(x.float()).all()
-    assert all(layer.moe.device_status() == 0 for layer in stack)
+    for h in handles:
+        h.remove()
+    assert torch.isfinite(logits.float()).all()
+    assert all(layer.moe.device_status() == 0 for layer in llm.transformer)
+    assert len(trace) == layers
     worst = 0.0
-    for p, (h, skip, y, logits, aux) in zip(cpu_params, trace):
-        worst = max(worst, check_layer(p, h, skip, y, logits, k))
-    print(f"{layers} layers x {batch * S} tokens: worst relative error {worst:.3e}, "
-          f"mean load-balancing loss {float(total_aux) / layers:.4f}")
+    for moe, xin, out, lg in trace:
+        n = min(xin.shape[0] * xin.shape[1], 2048)        # tokens are independent (model.py:201)
+        xi = xin.reshape(-1, D)[:n].float().cpu()
+        with torch.no_grad():
+            o = moe_oracle.moe_forward(xi, layer_params(moe), K, logits=lg[:n].cpu())
+        ok = ~moe_oracle.tie_rows(o["probs"], K)
+        got = out.reshape(-1, D)[:n].float().cpu()
+        err = (got - o["out"])[ok].abs().max()
+        # bf16 tolerance of the block: relative 2e-2 (against the largest reference value)
+        assert err <= 2e-2 * o["out"].abs().max(), f"max-abs {err} vs scale {o['out'].abs().max()}"
+        worst = max(worst, float(err / o["out"].abs().max()))
+    msg += f"; bf16: worst per-layer relative error of the block {worst:.2e}"
+    if ref_logits is not None:
+        # informative: a whole bf16 forward (the reference's attention and classifier in bf16 too)
+        # against fp32; tokens whose routing flips in some layer end far from the reference
+        got = logits.float().cpu()
+        per_token = (got - ref_logits).abs().amax(-1).flatten() / float(ref_logits.abs().max())
+        agree = float((got.argmax(-1) == ref_logits.argmax(-1)).float().mean())
+        msg += (f", bf16 logits vs fp32 reference: per-token max-abs/max median {float(per_token.median()):.2e}, "
+                f"90th percentile {float(per_token.quantile(0.9)):.2e}, arg-max agreement {agree:.3f}")
+    print(msg)

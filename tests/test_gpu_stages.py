@@ -290,6 +290,29 @@ def test_experts_decode_fused_repeats_bit_for_bit(cuda_device, rows, d, f):
         assert torch.equal(partf, part)
 
 
+@pytest.mark.parametrize("rows,d,f", DECODE_CASES + [([3, 0, 1, 0, 0, 0, 2, 0], 1024, 4096), ([40, 9], 72, 264)])
+def test_experts_gemv_bf16(cuda_device, rows, d, f):
+    """The matrix-vector streaming kernels for a few rows per expert (any count works):
+    h and sum(part) + bias against the oracle and against the single-launch small-N kernel."""
+    params, x, offsets = expert_inputs(rows, d, f, torch.bfloat16, seed=len(rows) + f)
+    dp = helpers.device_params(params, torch.bfloat16, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    xd, od = x.to(torch.bfloat16).to(cuda_device), offsets.to(cuda_device)
+    hf, partf, _ = helpers.experts_decode_fused(xd, od, plan)
+    h_ref, y_ref = oracle_experts(params, x, offsets)
+    M = sum(rows)
+    e_of_row = torch.bucketize(torch.arange(M), offsets.long()[1:], right=True)
+    for _ in range(2):
+        h, part = helpers.experts_gemv(xd, od, plan)
+        torch.cuda.synchronize()
+        assert not torch.isnan(part).any() and not torch.isnan(h.float()).any()
+        assert (h.float().cpu() - h_ref).abs().max() <= 2e-2 * h_ref.abs().max()
+        assert (h.float() - hf.float()).abs().max() <= 1e-2 * hf.float().abs().max()
+        y = part.sum(0).cpu() + params["b2"][e_of_row]
+        assert (y - y_ref).abs().max() <= 2e-2 * y_ref.abs().max()
+        assert (part.sum(0) - partf.sum(0)).abs().max() <= 1e-2 * partf.sum(0).abs().max()
+
+
 SPEC_CASES = [(1, 64, 128, 2, 2), (8, 1024, 4096, 8, 2), (17, 72, 264, 5, 3), (32, 256, 1408, 32, 4),
               (64, 1024, 4096, 8, 2), (100, 128, 512, 3, 2), (128, 256, 384, 16, 2), (64, 128, 256, 8, 1)]
 

@@ -62,7 +62,7 @@ def test_training_forward_applies_the_reproducible_dropout_mask(cuda_device, N, 
         out, aux = m(x.to(DT).to(cuda_device).view(1, N, d))
     torch.cuda.synchronize()
     assert m.device_status() == 0
-    seed = m.last["seed"]
+    seed = m.last.get("seed", 0)      # p = 0 without gradients is the inference path: no seed
     mult = torch.from_numpy(philox_ref.dropout_multiplier(N * k, f, p, seed)).view(N, k, f)
     if p > 0:
         kept = float((mult > 0).float().mean())
@@ -112,7 +112,7 @@ def test_backward_matches_autograd_on_the_oracle(cuda_device, N, d, E, f, k, p):
     o, gx, gp = oracle_run(x, params, k, mult, grad_out, grad_aux)
     # the gradients only compare under the same routing: the seeds are chosen so that it is
     assert torch.equal(m.last["idx"].cpu().long(), o["idx"]), "routing differs from the oracle's own"
-    close(out.view(N, d) - res.view(N, d), o["out"].detach(), 2e-2, "forward")
+    close(out.view(N, d), o["out"].detach() + res.detach().view(N, d).float().cpu(), 2e-2, "forward")
     assert torch.equal(res.grad.view(N, d).float().cpu(), grad_out)          # the residual's gradient
     close(xd.grad.view(N, d), gx, 3e-2, "grad x")
     close(m.gate.weight.grad, gp["gate_w"], 3e-2, "grad gate.weight")
