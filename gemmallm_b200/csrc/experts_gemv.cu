@@ -25,6 +25,23 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The grid has one group of blocks per expert that can be hit (at most min(E, rows) of them):
+// group i works on the i-th expert with rows. -1: fewer experts were hit.
+__device__ __forceinline__ int nth_expert_with_rows(const int32_t* __restrict__ offsets, int E, int nth,
+                                                    int* row0, int* rows) {
+  int prev = __ldcg(&offsets[0]);
+  for (int e = 0; e < E; ++e) {
+    const int next = __ldcg(&offsets[e + 1]);
+    if (next > prev && nth-- == 0) {
+      *row0 = prev;
+      *rows = next - prev;
+      return e;
+    }
+    prev = next;
+  }
+  return -1;
+}
+
 constexpr int kWarps = 4;       // warps of a block split the contraction range of one tile
 constexpr int kUnroll = 4;      // 32-element chunks in flight per lane and weight row
 constexpr int kMaxPass = 2;     // n-tiles (of 8 rows) whose accumulators a warp keeps at once
@@ -70,18 +87,18 @@ __device__ __forceinline__ void stream_tile(const uint4* const (&wrow)[NW][2], c
 // expert; block = (expert, 16 features), its warps split d.
 __global__ void __launch_bounds__(kWarps * 32)
 geglu_gemv_kernel(const __nv_bfloat16* __restrict__ perm, const int32_t* __restrict__ offsets,
-                  const void* const* __restrict__ W1, const void* const* __restrict__ b1, int d, int f,
-                  int tiles_per_expert, __nv_bfloat16* __restrict__ h) {
+                  const void* const* __restrict__ W1, const void* const* __restrict__ b1, int E, int d,
+                  int f, int tiles_per_expert, __nv_bfloat16* __restrict__ h) {
   __shared__ float s_red[kWarps][2][kMaxPass][4][32];
-  const int e = blockIdx.x / tiles_per_expert;
-  const int j0 = (blockIdx.x - e * tiles_per_expert) * 16;
+  const int slot = blockIdx.x / tiles_per_expert;
+  const int j0 = (blockIdx.x - slot * tiles_per_expert) * 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   pdl_wait();                 // offsets and the sorted rows come from the routing kernel
   pdl_launch_dependents();
-  const int row0 = __ldcg(&offsets[e]);
-  const int rows = __ldcg(&offsets[e + 1]) - row0;
-  if (rows <= 0) return;
+  int row0 = 0, rows = 0;
+  const int e = nth_expert_with_rows(offsets, E, slot, &row0, &rows);
+  if (e < 0) return;
   const int pieces = d >> 3;
   const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(W1[e]);
   const int ja = min(j0 + g, f - 1), jb = min(j0 + g + 8, f - 1);   // clamped: masked at the store
@@ -141,19 +158,19 @@ geglu_gemv_kernel(const __nv_bfloat16* __restrict__ perm, const int32_t* __restr
 // (expert, 16 output columns, k range), its warps split the range.
 __global__ void __launch_bounds__(kWarps * 32)
 down_gemv_kernel(const __nv_bfloat16* __restrict__ h, const int32_t* __restrict__ offsets,
-                 const void* const* __restrict__ W2, int d, int f, int tiles_per_expert, int ksplit,
-                 int64_t part_stride, float* __restrict__ part) {
+                 const void* const* __restrict__ W2, int E, int d, int f, int tiles_per_expert,
+                 int ksplit, int64_t part_stride, float* __restrict__ part) {
   __shared__ float s_red[kWarps][kMaxPass][4][32];
   const int s = blockIdx.y;
-  const int e = blockIdx.x / tiles_per_expert;
-  const int c0 = (blockIdx.x - e * tiles_per_expert) * 16;
+  const int slot = blockIdx.x / tiles_per_expert;
+  const int c0 = (blockIdx.x - slot * tiles_per_expert) * 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   pdl_wait();                 // h comes from the kernel before this one
   pdl_launch_dependents();
-  const int row0 = __ldcg(&offsets[e]);
-  const int rows = __ldcg(&offsets[e + 1]) - row0;
-  if (rows <= 0) return;
+  int row0 = 0, rows = 0;
+  const int e = nth_expert_with_rows(offsets, E, slot, &row0, &rows);
+  if (e < 0) return;
   const int pieces = f >> 3;
   const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(W2[e]);
   const int ca = min(c0 + g, d - 1), cb = min(c0 + g + 8, d - 1);
@@ -206,12 +223,13 @@ int launch_experts_gemv(const void* perm, const int32_t* offsets, const void* pl
   if (M == 0) return 0;
   PlanView pv = plan_view(plan, E);
   const int t1 = (f + 15) / 16, t2 = (d + 15) / 16;
-  MOE_CUDA_CHECK(launch_pdl(geglu_gemv_kernel, dim3((unsigned)(E * t1)), dim3(kWarps * 32), 0, s,
-                            static_cast<const __nv_bfloat16*>(perm), offsets, pv.W1, pv.b1, d, f, t1,
+  const int slots = (int)(M < E ? M : E);    // no more experts than rows can be hit
+  MOE_CUDA_CHECK(launch_pdl(geglu_gemv_kernel, dim3((unsigned)(slots * t1)), dim3(kWarps * 32), 0, s,
+                            static_cast<const __nv_bfloat16*>(perm), offsets, pv.W1, pv.b1, E, d, f, t1,
                             static_cast<__nv_bfloat16*>(h)));
-  MOE_CUDA_CHECK(launch_pdl(down_gemv_kernel, dim3((unsigned)(E * t2), (unsigned)ksplit),
+  MOE_CUDA_CHECK(launch_pdl(down_gemv_kernel, dim3((unsigned)(slots * t2), (unsigned)ksplit),
                             dim3(kWarps * 32), 0, s, static_cast<const __nv_bfloat16*>(h), offsets,
-                            pv.W2, d, f, t2, ksplit, M * (int64_t)d, part));
+                            pv.W2, E, d, f, t2, ksplit, M * (int64_t)d, part));
   return 0;
 }
 

@@ -9,6 +9,9 @@
 //     fp32). Operands go from global memory straight into fragment registers
 //     with 16-byte loads: the contraction index inside each 32-element chunk is
 //     permuted the same way for x and Wg, which a dot product does not notice.
+//     Eight warps per block: two warps share each group of 16 tokens and split d
+//     between them (twice the loads in flight per SM; the op is latency-bound
+//     otherwise), the second one's partial sums pass through shared memory.
 //     Then one lane per token does softmax / top-k serially over the E logits.
 //   fp32: router_kernel. CUDA-core FMA (TF32 would perturb the logits), four
 //     tokens x eight experts per warp pass, warp-shuffle reductions, softmax and
@@ -250,7 +253,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 
 constexpr int kMmaTokPerWarp = 16;
-constexpr int kMmaUnroll = 4;  // 32-element chunks in flight per lane
+constexpr int kMmaWarps = 2 * kWarps;   // two warps per token group: each takes half of d
 
 // NT = n-tiles (of 8 experts) per pass over x; E > 8*NT makes more passes.
 __device__ __forceinline__ void shifted_sums(const uint4& v, float shift, float& s1, float& s2) {
@@ -264,24 +267,30 @@ __device__ __forceinline__ void shifted_sums(const uint4& v, float shift, float&
 }
 
 template <int NT, bool NORM>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kMmaWarps * 32)
 router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ Wg,
                   const __nv_bfloat16* __restrict__ bg, int64_t N, int d, int E, int k,
                   float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
                   float* __restrict__ out_w, float* __restrict__ psum_part,
                   const float* __restrict__ norm_c, float eps, float* __restrict__ stats) {
+  constexpr int kMmaUnroll = NT <= 2 ? 8 : 4;   // 32-element chunks in flight per lane
+  constexpr int kXch = NT * 4 + 4;              // floats a lane hands over: accumulators, row sums
   extern __shared__ float smem[];
   const int ld = E + 1;                                           // row pitch: no bank conflicts
   float* s_logits = smem;                                          // [64][E+1]
   float* s_psum = smem + (size_t)kRouterTokensPerBlock * ld;       // [kWarps][E]
+  float* s_xch = s_psum + (size_t)kWarps * E;                      // [kWarps][32][kXch]
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31;
+  const int warp = (threadIdx.x >> 5) & (kWarps - 1);   // token group
+  const int khalf = threadIdx.x >> 7;                   // which half of d this warp contracts
   const int g = lane >> 2, t = lane & 3;
   const int64_t tok0 = (int64_t)blockIdx.x * kRouterTokensPerBlock + warp * kMmaTokPerWarp;
   const int nvalid = (int)(N - tok0 < kMmaTokPerWarp ? (N - tok0 > 0 ? N - tok0 : 0) : kMmaTokPerWarp);
   float* my_logits = s_logits + (size_t)warp * kMmaTokPerWarp * ld;
+  float* my_xch = s_xch + ((size_t)warp * 32 + lane) * kXch;
 
-  if (nvalid > 0) {
+  {
     const int row_pieces = d >> 3;  // 16-byte pieces per row
     const int64_t ra = tok0 + g < N ? tok0 + g : N - 1;
     const int64_t rb = tok0 + g + 8 < N ? tok0 + g + 8 : N - 1;
@@ -289,6 +298,9 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     const uint4* xb = reinterpret_cast<const uint4*>(x + rb * d);
     const uint4* w4 = reinterpret_cast<const uint4*>(Wg);
     const int nchunk = (d + 31) >> 5;
+    const int half = ((nchunk + 1) / 2 + kMmaUnroll - 1) / kMmaUnroll * kMmaUnroll;
+    const int c_begin = khalf ? (half < nchunk ? half : nchunk) : 0;
+    const int c_end = khalf ? nchunk : (half < nchunk ? half : nchunk);
     const uint4 zero = make_uint4(0, 0, 0, 0);
     // LayerNorm statistics of rows g and g+8: this lane's pieces, then the quad's four lanes
     float sha = 0.f, shb = 0.f, s1a = 0.f, s2a = 0.f, s1b = 0.f, s2b = 0.f;
@@ -303,12 +315,12 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-      for (int c0 = 0; c0 < nchunk; c0 += kMmaUnroll) {
+      for (int c0 = c_begin; c0 < c_end; c0 += kMmaUnroll) {
         uint4 A[kMmaUnroll], B[kMmaUnroll];
 #pragma unroll
         for (int u = 0; u < kMmaUnroll; ++u) {
           const int piece = 4 * (c0 + u) + t;
-          const bool ok = piece < row_pieces;
+          const bool ok = piece < row_pieces && c0 + u < c_end;
           A[u] = ok ? xa[piece] : zero;
           B[u] = ok ? xb[piece] : zero;
           if (NORM && e_base == 0 && ok) {
@@ -322,14 +334,32 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 #pragma unroll
           for (int j = 0; j < NT; ++j) {
             const int row = e_base + 8 * j + g;
-            const uint4 w = (row < E && piece < row_pieces)
+            const uint4 w = (row < E && piece < row_pieces && c0 + u < c_end)
                                 ? __ldg(w4 + (size_t)row * row_pieces + piece) : zero;
             mma_bf16_16816(acc[j], A[u].x, B[u].x, A[u].y, B[u].y, w.x, w.y);
             mma_bf16_16816(acc[j], A[u].z, B[u].z, A[u].w, B[u].w, w.z, w.w);
           }
         }
       }
+      // the second half's partial sums join the first half's
+      __syncthreads();
+      if (khalf == 1) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) my_xch[j * 4 + i] = acc[j][i];
+        my_xch[NT * 4 + 0] = s1a; my_xch[NT * 4 + 1] = s2a;
+        my_xch[NT * 4 + 2] = s1b; my_xch[NT * 4 + 3] = s2b;
+      }
+      __syncthreads();
+      if (khalf == 1) continue;
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] += my_xch[j * 4 + i];
       if (NORM && e_base == 0) {
+        s1a += my_xch[NT * 4 + 0]; s2a += my_xch[NT * 4 + 1];
+        s1b += my_xch[NT * 4 + 2]; s2b += my_xch[NT * 4 + 3];
 #pragma unroll
         for (int o = 1; o <= 2; o <<= 1) {
           s1a += __shfl_xor_sync(0xffffffffu, s1a, o);
@@ -368,6 +398,7 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       }
     }
   }
+  if (khalf == 0) {
   __syncwarp();
   if (out_logits != nullptr) {
     for (int i = lane; i < nvalid * E; i += 32) {
@@ -420,6 +451,7 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     for (int tl = 0; tl < nvalid; ++tl) s += my_logits[tl * ld + e];
     s_psum[warp * E + e] = s;
   }
+  }   // khalf == 0
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     float s = 0.f;
@@ -434,13 +466,14 @@ int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, 
                float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
                const float* norm_c, float eps, float* stats, cudaStream_t s) {
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
-  const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E);
+  const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E +
+                                       (size_t)kWarps * 32 * (NT * 4 + 4));
   static PerDeviceOnce once;
   if (smem > 48 * 1024) {
-    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM>, 80 * 1024);
+    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM>, 100 * 1024);
     if (rc) return rc;
   }
-  router_mma_kernel<NT, NORM><<<(unsigned)blocks, kWarps * 32, smem, s>>>(
+  router_mma_kernel<NT, NORM><<<(unsigned)blocks, kMmaWarps * 32, smem, s>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
       static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part,
       norm_c, eps, stats);
