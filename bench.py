@@ -1003,6 +1003,24 @@ def run_decoder(args):
         for h in handles:
             h.remove()
         moe_ms = sum(a.elapsed_time(b) for a, b in moe_events) / 3
+        # beyond the named configuration: the layers' attention replaced as well (fused RoPE /
+        # scores / softmax / PV / head-gate kernel between the reference's Linears)
+        from gemmallm_b200 import Attention
+        for layer in llm.transformer:
+            old = layer.mqa
+            new = Attention(c["d_model"], c["head_dim"], c["q_heads"], c["kv_heads"], old.embedding).eval()
+            new.load_state_dict(old.state_dict(), strict=True)
+            layer.mqa = new.to(device=dev, dtype=dt)
+        for _ in range(3):
+            llm(x.clone(), mask, False)
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(args.steps):
+            llm(x.clone(), mask, False)
+        a1.record()
+        torch.cuda.synchronize()
+        ms_att = a0.elapsed_time(a1) / args.steps
         # end to end: embeddings from pinned host memory in, last-position logits and loss out
         out_host = torch.empty(c["batch"], c["vocab"], dtype=dt).pin_memory()
         aux_host = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -1030,8 +1048,10 @@ def run_decoder(args):
         "config": decoder_config(),
         "run": {"what": "whole decoder forward (reference LLM, every layer.moe swapped for the new block)",
                 "moe_ms_per_forward": moe_ms, "moe_share": moe_ms / ms,
+                "with_new_attention_too": {"ms_per_step": ms_att, "tokens_per_s": tokens / (ms_att * 1e-3)},
                 "moe_tflops_incl_router_dispatch_combine": flops / (moe_ms * 1e-3) / 1e12},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "configuration": "new block and new attention in every layer",
                 "h2d_bytes_per_step": tokens * c["d_model"] * 2,
                 "d2h_bytes_per_step": c["batch"] * c["vocab"] * 2 + 4, "ms_per_step": e2e_ms,
                 "mode": "embeddings from pinned host memory, last-position logits and loss back, host waits"},

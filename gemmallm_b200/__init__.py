@@ -1,18 +1,22 @@
 """gemmallm_b200: GemmaLLM's Mixture-of-Experts feed-forward block as
 hand-written CUDA kernels for NVIDIA B200 (sm_100a), behind the C ABI of
 include/moe_b200.h. ``MOE`` and ``FeedForward`` are drop-ins for the reference
-classes of model.py:154-276.
+classes of model.py:154-276, ``Attention`` for the decoder layer's attention
+(model.py:59-152) the block sits behind.
 
 Attributes are resolved on first use so that ``python -m gemmallm_b200.build``
 can (re)build libmoe_b200.so before anything tries to load it.
 """
-__all__ = ["MOE", "FeedForward", "MoeB200Error"]
+__all__ = ["MOE", "FeedForward", "Attention", "MoeB200Error"]
 
 
 def __getattr__(name):
     if name in ("MOE", "FeedForward"):
         from . import moe
         return getattr(moe, name)
+    if name == "Attention":
+        from .attention import Attention
+        return Attention
     if name == "MoeB200Error":
         from ._cabi import MoeB200Error
         return MoeB200Error

@@ -65,6 +65,7 @@ SIGNATURES = {
     "moe_b200_dispatch_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
                                     _vp, _vp, _vp, _vp, _vp, _vp]),
     "moe_b200_layernorm": (_i, [_vp, _vp, _vp, _f, _i64, _i, _i, _vp, _vp]),
+    "moe_b200_attention": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _f, _vp, _vp]),
     "moe_b200_train_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),
     "moe_b200_train_workspace_layout": (_i, [_i64, _i, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_train_setup": (_i, [_i64, _i, _i, _i, _i, _i, _vp, _sz, _vp]),

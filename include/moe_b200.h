@@ -367,6 +367,21 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg,
                      void* workspace, size_t workspace_bytes,
                      void* out, void* stream);
 
+/* ---- Attention core of the decoder layer ---------------------------------------
+ * What the reference's Attention.forward does between its Linears (model.py:104-142),
+ * for the decoder the block sits in: qkv [B,S,(q_heads + 2 kv_heads) * 64] bf16 is the
+ * output of the fused QKV Linear (queries, then keys, then values, model.py:104); every
+ * group of q_heads / kv_heads query heads shares one KV head (model.py:112-115); queries
+ * and keys are rotated with pos_emb float [>= S, 128] (row m = [cos | signed sin] of
+ * position m, model.py:14-36, 50-57); scores = q k^T * scaler + mask, softmax, times V
+ * (model.py:127-132); the result of head h at token s is multiplied by
+ * sigmoid(gate[b,s,h]) (gate bf16 [B,S,q_heads], the head-gate Linear's output,
+ * model.py:139-142). mask: NULL or float [S,S], added to every sequence's scores.
+ * out bf16 [B,S,q_heads * 64]. head_dim 64, S <= 128; else MOE_B200_ERR_UNSUPPORTED. */
+int moe_b200_attention(const void* qkv, const void* gate, const float* pos_emb, const float* mask,
+                       int64_t B, int S, int q_heads, int kv_heads, int head_dim, float scaler,
+                       void* out, void* stream);
+
 /* ---- Training mode ---------------------------------------------------------------
  * The reference trains through this block (loss.backward(), train.py:140-141): under
  * .train() FeedForward.forward applies nn.Dropout to h (model.py:164,183), and
