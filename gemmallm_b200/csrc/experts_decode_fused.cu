@@ -347,7 +347,9 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
   }
   // The last CTA to get here leaves the counters zero for the next call on this workspace:
   // by then every CTA has read its last completion count.
-  if (threadIdx.x == 0 && !*reinterpret_cast<volatile int*>(&ctl->abort)) {
+  // A CTA that gave up on a wait counts too: the status word keeps the failure, the counters
+  // are clean again for the next call.
+  if (threadIdx.x == 0) {
     int* exit_count = ready + (MOE_B200_READY_INTS - 2);
     __threadfence();
     if (atomicAdd(exit_count, 1) == (int)gridDim.x - 1) {

@@ -12,7 +12,7 @@
 //     Eight warps per block: two warps share each group of 16 tokens and split d
 //     between them (twice the loads in flight per SM; the op is latency-bound
 //     otherwise), the second one's partial sums pass through shared memory.
-//     Then one lane per token does softmax / top-k serially over the E logits.
+//     Then four lanes per token do softmax / top-k over a quarter of the E logits each.
 //   fp32: router_kernel. CUDA-core FMA (TF32 would perturb the logits), four
 //     tokens x eight experts per warp pass, warp-shuffle reductions, softmax and
 //     top-k with one expert slice per lane.
@@ -398,23 +398,28 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       }
     }
   }
-  if (khalf == 0) {
-  __syncwarp();
+  __syncthreads();   // the logits of the block's 64 tokens are in shared memory
+  const int64_t blk_tok0 = (int64_t)blockIdx.x * kRouterTokensPerBlock;
+  const int blk_valid = (int)(N - blk_tok0 < kRouterTokensPerBlock ? N - blk_tok0 : kRouterTokensPerBlock);
   if (out_logits != nullptr) {
-    for (int i = lane; i < nvalid * E; i += 32) {
+    for (int i = threadIdx.x; i < blk_valid * E; i += blockDim.x) {
       const int tl = i / E, e = i - tl * E;
-      out_logits[tok0 * E + i] = my_logits[tl * ld + e];
+      out_logits[blk_tok0 * E + i] = s_logits[tl * ld + e];
     }
   }
-  __syncwarp();
-
-  // ---- one lane per token: softmax, top-k by (logit desc, index asc), renormalise ----
-  if (lane < nvalid) {
-    float* lg = my_logits + lane * ld;
+  // ---- four lanes per token (experts sub, sub + 4, ...): softmax, top-k by (logit desc,
+  // index asc), renormalise; the quad's lanes are neighbours in a warp ----
+  {
+    const int tl = threadIdx.x >> 2, sub = threadIdx.x & 3;
+    float* lg = s_logits + tl * ld;
     float m = -INFINITY;
-    for (int e = 0; e < E; ++e) m = fmaxf(m, lg[e]);
+    for (int e = sub; e < E; e += 4) m = fmaxf(m, lg[e]);
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
     float sum = 0.f;
-    for (int e = 0; e < E; ++e) sum += expf(lg[e] - m);
+    for (int e = sub; e < E; e += 4) sum += expf(lg[e] - m);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     int sel[kMaxTopK];
     float sl[kMaxTopK], vals[kMaxTopK];
     float total = 0.f;
@@ -422,41 +427,41 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     for (int j = 0; j < kMaxTopK; ++j) {
       if (j < k) {
         float bl = -INFINITY;
-        int be = 0;
-        for (int e = 0; e < E; ++e) {
+        int be = 0x7fffffff;
+        for (int e = sub; e < E; e += 4) {
           const float v = lg[e];
           if (v > bl) { bl = v; be = e; }   // strict: the lowest index wins among equals
+        }
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+          const float ol = __shfl_xor_sync(0xffffffffu, bl, o);
+          const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+          if (ol > bl || (ol == bl && oe < be)) { bl = ol; be = oe; }
         }
         sel[j] = be;
         sl[j] = bl;
         vals[j] = expf(bl - m) / sum;
         total += vals[j];                    // left-to-right sum, as model.py:221
-        lg[be] = -INFINITY;                  // taken
+        if ((be & 3) == sub && be < E) lg[be] = -INFINITY;   // taken (only its owner reads it again)
       }
     }
-    const int64_t tok = tok0 + lane;
 #pragma unroll
     for (int j = 0; j < kMaxTopK; ++j) {
       if (j < k) {
-        lg[sel[j]] = sl[j];
-        out_idx[tok * k + j] = sel[j];
-        out_w[tok * k + j] = vals[j] / total;
+        if ((sel[j] & 3) == sub && sel[j] < E) lg[sel[j]] = sl[j];
+        if (sub == 0 && tl < blk_valid) {
+          out_idx[(blk_tok0 + tl) * k + j] = sel[j];
+          out_w[(blk_tok0 + tl) * k + j] = vals[j] / total;
+        }
       }
     }
-    for (int e = 0; e < E; ++e) lg[e] = expf(lg[e] - m) / sum;  // probabilities, in place
+    for (int e = sub; e < E; e += 4) lg[e] = expf(lg[e] - m) / sum;  // probabilities, in place
   }
-  __syncwarp();
-  for (int e = lane; e < E; e += 32) {
-    float s = 0.f;
-    for (int tl = 0; tl < nvalid; ++tl) s += my_logits[tl * ld + e];
-    s_psum[warp * E + e] = s;
-  }
-  }   // khalf == 0
   __syncthreads();
+  // per-block probability sums, tokens in order
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) s += s_psum[w * E + e];
+    for (int tl = 0; tl < blk_valid; ++tl) s += s_logits[tl * ld + e];
     psum_part[(size_t)blockIdx.x * E + e] = s;
   }
 }
