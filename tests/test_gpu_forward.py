@@ -402,3 +402,19 @@ def test_feedforward_alone(cuda_device, dtype, rows):
     assert torch.equal(y, y2)
     err = (y.view(rows, d).float().cpu() - ref).abs().max()
     assert err <= (1e-4 if dtype == torch.float32 else 2e-2 * ref.abs().max())
+
+
+def test_two_devices_in_one_process():
+    """One process driving two GPUs: kernel attributes, occupancy results and SM counts are
+    cached per device, so the second device gets its own (a per-process cache would leave its
+    kernels without their shared-memory limit)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    for dtype, N in ((torch.bfloat16, 6000), (torch.bfloat16, 40), (torch.bfloat16, 700), (torch.float32, 300)):
+        d, E, f, k = 256, 8, 512, 2
+        params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=N), dtype)
+        x = synthetic.round_to(synthetic.make_input(N, d, seed=N + 1), dtype)
+        for index in (0, 1, 0):
+            dev = torch.device("cuda", index)
+            m = build(params, d, E, f, k, dtype, dev)
+            check_against_oracle(m, params, x, k, dtype, dev)
