@@ -73,6 +73,10 @@ SIGNATURES = {
                                     _vp, _sz, _vp, _sz, _vp, _vp]),
     "moe_b200_backward": (_i, [_vp, _vp, _vp, _vp, _f, _i64, _i, _i, _i, _i, _i, _f, C.c_uint64,
                                _vp, _sz, _vp, _sz, _vp, _vp]),
+    "moe_b200_experts_train": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _f, C.c_uint64, _vp, _sz, _vp, _vp,
+                                    _vp, _vp]),
+    "moe_b200_experts_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _f, C.c_uint64, _vp, _sz,
+                                       _vp, _vp, _vp]),
     "moe_b200_ep_symm_bytes": (_sz, [_i64, _i, _i, _i, _i]),
     "moe_b200_ep_symm_layout": (_i, [_i64, _i, _i, _i, _i, C.POINTER(_sz)]),
     "moe_b200_ep_workspace_bytes": (_sz, [_i64, _i, _i, _i, _i, _i]),

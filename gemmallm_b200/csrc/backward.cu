@@ -197,6 +197,11 @@ router_bwd_wx_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
+__global__ void iota_kernel(int32_t* __restrict__ p, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = (int32_t)i;
+}
+
 __global__ void f32_to_bf16_kernel(const float* __restrict__ src, int64_t n, __nv_bfloat16* __restrict__ dst) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = __float2bfloat16_rn(src[i]);
@@ -380,6 +385,13 @@ int launch_router_bwd(const float* logits, const int32_t* idx, const float* w, c
   f32_to_bf16_kernel<<<blocks_for((int64_t)E * d, 256), 256, 0, s>>>(dWg_f32, (int64_t)E * d,
                                                                        static_cast<__nv_bfloat16*>(dWg));
   f32_to_bf16_kernel<<<blocks_for(E, 256), 256, 0, s>>>(dbg_f32, E, static_cast<__nv_bfloat16*>(dbg));
+  MOE_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int launch_iota(int32_t* p, int64_t n, cudaStream_t s) {
+  if (n == 0) return 0;
+  iota_kernel<<<blocks_for(n, 256), 256, 0, s>>>(p, n);
   MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

@@ -334,6 +334,7 @@ int launch_router_bwd(const float* logits, const int32_t* idx, const float* w, c
                       int d, int E, int k, float* dl, float* dWg_f32, float* dbg_f32, void* dWg,
                       void* dbg, void* dxr, cudaStream_t s);
 int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t s);
+int launch_iota(int32_t* p, int64_t n, cudaStream_t s);
 int launch_geglu_bwd(const void* dh, void* gu, const int32_t* pair_of, int64_t M, int f,
                      uint32_t thresh, float scale, uint32_t seed_lo, uint32_t seed_hi, cudaStream_t s);
 int launch_transpose_weights(const void* const* src_ptrs, int E, int R, int C, void* dst, cudaStream_t s);

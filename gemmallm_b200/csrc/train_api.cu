@@ -71,6 +71,57 @@ TrainArgs train_args(char* tws, const size_t* to, float p, uint64_t seed) {
   return tr;
 }
 
+// Backward of the grouped expert feed-forward (model.py:174-184) on sorted rows: given dy (gradient
+// of y, in the training workspace), h (the dropped h of the forward), the saved pre-activations and
+// the sorted inputs, writes dxs (gradient of the sorted inputs) and the four parameter gradients.
+int experts_backward(const void* perm, const void* h, const int32_t* offsets, const void* plan,
+                     int64_t M, int d, int f, int E, const TrainArgs& tr, char* tws, const size_t* to,
+                     int32_t* status, cudaStream_t s) {
+  const int64_t Kp = padded_rows(M, E);
+  const PlanView pv = plan_view(plan, E);
+  int32_t* koff = reinterpret_cast<int32_t*>(tws + to[MOE_B200_TWS_KOFF]);
+  void* gu = tws + to[MOE_B200_TWS_GU];
+  void* dy = tws + to[MOE_B200_TWS_DY];
+  void* dh = tws + to[MOE_B200_TWS_DH];
+  void* dxs = tws + to[MOE_B200_TWS_DXS];
+  const char* tmaps = tws + to[MOE_B200_TWS_TMAPS];
+  // experts without rows get no tile in the weight-gradient products
+  MOE_CUDA_CHECK(cudaMemsetAsync(tws + to[MOE_B200_TWS_G_W1], 0, (size_t)E * 2 * f * d * 2, s));
+  MOE_CUDA_CHECK(cudaMemsetAsync(tws + to[MOE_B200_TWS_G_W2], 0, (size_t)E * d * f * 2, s));
+  int rc = launch_pad_offsets(offsets, E, koff, s);
+  if (rc) return rc;
+  // down Linear (model.py:184): dh = dy W2, dW2 = dy^T h, db2 = column sums of dy
+  rc = launch_transpose_weights(pv.W2, E, d, f, tws + to[MOE_B200_TWS_W2T], s);
+  if (rc) return rc;
+  rc = launch_grouped_rows(dy, M, d, tmaps + (size_t)128 * E, offsets, nullptr, E, f, dh, status, s);
+  if (rc) return rc;
+  rc = launch_transpose_pad(dy, offsets, koff, E, d, Kp, tws + to[MOE_B200_TWS_DYT], s);
+  if (rc) return rc;
+  rc = launch_transpose_pad(h, offsets, koff, E, f, Kp, tws + to[MOE_B200_TWS_HT], s);
+  if (rc) return rc;
+  rc = launch_grouped_cols(tws + to[MOE_B200_TWS_DYT], tws + to[MOE_B200_TWS_HT], Kp, d, f, koff,
+                           tws + to[MOE_B200_TWS_G_W2], E, status, s);
+  if (rc) return rc;
+  rc = launch_colsum(dy, offsets, E, d, tws + to[MOE_B200_TWS_G_B2], s);
+  if (rc) return rc;
+  // dropout, product and GELU (model.py:180-183): (g, u) -> (dg, du) in place
+  rc = launch_geglu_bwd(dh, gu, tr.pair_of, M, f, tr.thresh, tr.scale, tr.seed_lo, tr.seed_hi, s);
+  if (rc) return rc;
+  // gate_and_up Linear (model.py:174): dx = dgu W1, dW1 = dgu^T x, db1 = column sums of dgu
+  rc = launch_transpose_weights(pv.W1, E, 2 * f, d, tws + to[MOE_B200_TWS_W1T], s);
+  if (rc) return rc;
+  rc = launch_grouped_rows(gu, M, 2 * f, tmaps, offsets, nullptr, E, d, dxs, status, s);
+  if (rc) return rc;
+  rc = launch_transpose_pad(gu, offsets, koff, E, 2 * f, Kp, tws + to[MOE_B200_TWS_DGUT], s);
+  if (rc) return rc;
+  rc = launch_transpose_pad(perm, offsets, koff, E, d, Kp, tws + to[MOE_B200_TWS_XT], s);
+  if (rc) return rc;
+  rc = launch_grouped_cols(tws + to[MOE_B200_TWS_DGUT], tws + to[MOE_B200_TWS_XT], Kp, 2 * f, d, koff,
+                           tws + to[MOE_B200_TWS_G_W1], E, status, s);
+  if (rc) return rc;
+  return launch_colsum(gu, offsets, E, 2 * f, tws + to[MOE_B200_TWS_G_B1], s);
+}
+
 }  // namespace
 }  // namespace moe
 
@@ -225,11 +276,6 @@ int moe_b200_backward(const void* x, const void* Wg, const void* plan, const voi
   const PlanView pv = plan_view(plan, E);
   const TrainArgs tr = train_args(tws, to, dropout_p, seed);
 
-  // experts without rows get no tile in the weight-gradient products
-  MOE_CUDA_CHECK(cudaMemsetAsync(tws + to[MOE_B200_TWS_G_W1], 0, (size_t)E * 2 * f * d * 2, s));
-  MOE_CUDA_CHECK(cudaMemsetAsync(tws + to[MOE_B200_TWS_G_W2], 0, (size_t)E * d * f * 2, s));
-  rc = launch_pad_offsets(offsets, E, koff, s);
-  if (rc) return rc;
   // combine (model.py:271) and router (model.py:206-223)
   rc = launch_combine_bwd(grad_out, y, pair_of, w, M, d, k, dy, dw, s);
   if (rc) return rc;
@@ -237,39 +283,57 @@ int moe_b200_backward(const void* x, const void* Wg, const void* plan, const voi
                          dwg32 + (size_t)E * d, tws + to[MOE_B200_TWS_G_WG], tws + to[MOE_B200_TWS_G_BG],
                          dxr, s);
   if (rc) return rc;
-  // down Linear (model.py:184): dh = dy W2, dW2 = dy^T h, db2 = column sums of dy
-  rc = launch_transpose_weights(pv.W2, E, d, f, w2t, s);
-  if (rc) return rc;
-  rc = launch_grouped_rows(dy, M, d, tmaps + (size_t)128 * E, offsets, nullptr, E, f, dh, status, s);
-  if (rc) return rc;
-  rc = launch_transpose_pad(dy, offsets, koff, E, d, Kp, tws + to[MOE_B200_TWS_DYT], s);
-  if (rc) return rc;
-  rc = launch_transpose_pad(h, offsets, koff, E, f, Kp, tws + to[MOE_B200_TWS_HT], s);
-  if (rc) return rc;
-  rc = launch_grouped_cols(tws + to[MOE_B200_TWS_DYT], tws + to[MOE_B200_TWS_HT], Kp, d, f, koff,
-                           tws + to[MOE_B200_TWS_G_W2], E, status, s);
-  if (rc) return rc;
-  rc = launch_colsum(dy, offsets, E, d, tws + to[MOE_B200_TWS_G_B2], s);
-  if (rc) return rc;
-  // dropout, product and GELU (model.py:180-183): (g, u) -> (dg, du) in place
-  rc = launch_geglu_bwd(dh, gu, pair_of, M, f, tr.thresh, tr.scale, tr.seed_lo, tr.seed_hi, s);
-  if (rc) return rc;
-  // gate_and_up Linear (model.py:174): dx = dgu W1, dW1 = dgu^T x, db1 = column sums of dgu
-  rc = launch_transpose_weights(pv.W1, E, 2 * f, d, w1t, s);
-  if (rc) return rc;
-  rc = launch_grouped_rows(gu, M, 2 * f, tmaps, offsets, nullptr, E, d, dxs, status, s);
-  if (rc) return rc;
-  rc = launch_transpose_pad(gu, offsets, koff, E, 2 * f, Kp, tws + to[MOE_B200_TWS_DGUT], s);
-  if (rc) return rc;
-  rc = launch_transpose_pad(perm, offsets, koff, E, d, Kp, tws + to[MOE_B200_TWS_XT], s);
-  if (rc) return rc;
-  rc = launch_grouped_cols(tws + to[MOE_B200_TWS_DGUT], tws + to[MOE_B200_TWS_XT], Kp, 2 * f, d, koff,
-                           tws + to[MOE_B200_TWS_G_W1], E, status, s);
-  if (rc) return rc;
-  rc = launch_colsum(gu, offsets, E, 2 * f, tws + to[MOE_B200_TWS_G_B1], s);
+  // the experts (model.py:174-184)
+  rc = experts_backward(perm, h, offsets, plan, M, d, f, E, tr, tws, to, status, s);
   if (rc) return rc;
   // gather (model.py:248-253) and the router's share: dx[t] = sum_j dxs[row_of[t,j]] + dxr[t]
   return launch_combine(dxs, row_of, ones, dxr, N, d, k, dtype, grad_x, s);
+}
+
+// ---- the expert feed-forward alone (the reference's dense FeedForward, model.py:154-190, is one
+// group; any grouping by offsets works) ----
+
+int moe_b200_experts_train(const void* x_sorted, const int32_t* offsets, const void* plan, int64_t M,
+                           int d, int f, int E, float dropout_p, uint64_t seed, void* train_ws,
+                           size_t train_ws_bytes, void* h, void* y, int32_t* status, void* stream) {
+  int rc = train_check(M, d, f, E, 1, MOE_B200_BF16, dropout_p);
+  if (rc) return rc;
+  if (M == 0) return 0;
+  if (!x_sorted || !offsets || !plan || !train_ws || !h || !y || !status)
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  size_t to[MOE_B200_TWS_NUM], ttotal;
+  tws_layout(M, d, f, E, 1, to, &ttotal);
+  if (train_ws_bytes < ttotal) return set_error(MOE_B200_ERR_WORKSPACE, "training workspace too small");
+  if ((uintptr_t)train_ws & 1023) return set_error(MOE_B200_ERR_ALIGN, "training workspace must be 1024-byte aligned");
+  char* tws = static_cast<char*>(train_ws);
+  cudaStream_t s = (cudaStream_t)stream;
+  // row r is pair r: the dropout mask of element (r, c) depends on the row's position only
+  rc = launch_iota(reinterpret_cast<int32_t*>(tws + to[MOE_B200_TWS_PAIR_OF]), M, s);
+  if (rc) return rc;
+  const TrainArgs tr = train_args(tws, to, dropout_p, seed);
+  return launch_experts_tc2(x_sorted, offsets, plan, M, d, f, E, h, y, nullptr, status, s, &tr);
+}
+
+int moe_b200_experts_backward(const void* x_sorted, const void* h, const int32_t* offsets,
+                              const void* plan, const void* grad_y, int64_t M, int d, int f, int E,
+                              float dropout_p, uint64_t seed, void* train_ws, size_t train_ws_bytes,
+                              void* grad_x, int32_t* status, void* stream) {
+  int rc = train_check(M, d, f, E, 1, MOE_B200_BF16, dropout_p);
+  if (rc) return rc;
+  if (M == 0) return 0;
+  if (!x_sorted || !h || !offsets || !plan || !grad_y || !train_ws || !grad_x || !status)
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  size_t to[MOE_B200_TWS_NUM], ttotal;
+  tws_layout(M, d, f, E, 1, to, &ttotal);
+  if (train_ws_bytes < ttotal) return set_error(MOE_B200_ERR_WORKSPACE, "training workspace too small");
+  char* tws = static_cast<char*>(train_ws);
+  cudaStream_t s = (cudaStream_t)stream;
+  const TrainArgs tr = train_args(tws, to, dropout_p, seed);
+  MOE_CUDA_CHECK(cudaMemcpyAsync(tws + to[MOE_B200_TWS_DY], grad_y, (size_t)M * d * 2, cudaMemcpyDeviceToDevice, s));
+  rc = experts_backward(x_sorted, h, offsets, plan, M, d, f, E, tr, tws, to, status, s);
+  if (rc) return rc;
+  MOE_CUDA_CHECK(cudaMemcpyAsync(grad_x, tws + to[MOE_B200_TWS_DXS], (size_t)M * d * 2, cudaMemcpyDeviceToDevice, s));
+  return 0;
 }
 
 }  // extern "C"

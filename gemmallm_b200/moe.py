@@ -147,6 +147,28 @@ class _TrainFn(torch.autograd.Function):
         return (None, grad_x, grad_res, None, *grads)
 
 
+class _FfnTrainFn(torch.autograd.Function):
+    """FeedForward.forward in training mode as one autograd node (moe_b200_experts_train /
+    moe_b200_experts_backward: dropout on h, model.py:183; gradients of model.py:173-184)."""
+
+    @staticmethod
+    def forward(ctx, module, x, seed, *params):
+        y, h = module._forward_train(x, seed)
+        ctx.module, ctx.seed, ctx.gen = module, seed, module._train_gen
+        ctx.save_for_backward(x, h)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        m = ctx.module
+        if ctx.gen != m._train_gen:
+            raise RuntimeError("this module ran another training forward before the backward of this "
+                               "one: its training workspace holds the later call's tensors")
+        x, h = ctx.saved_tensors
+        (grad_x,) = m._backward_train(x, h, grad_y.contiguous(), ctx.seed)
+        return (None, grad_x, None, *m._last_param_grads)
+
+
 class FeedForward(nn.Module):
     """GeGLU feed-forward expert; mirrors reference model.py:154-190.
 
@@ -174,16 +196,91 @@ class FeedForward(nn.Module):
         self._plan_ft = _Plan()
         self._lora = _MergedLora()
         self._offsets = None   # ((rows, device), int32 [0, rows]) of the last call
+        self._tws = None
+        self._tws_key = None
+        self._train_gen = 0
+        self._last_param_grads = None
+        self.last_seed = None
+
+    # -- training mode (bf16): dropout on h and a backward pass -----------------
+    def _train_ws(self, M: int, device: torch.device):
+        key = (M, str(device))
+        if key != self._tws_key:
+            d, f = self.hidden_size, self.d_ff
+            nbytes = lib.moe_b200_train_workspace_bytes(M, d, f, 1, 1, _cabi.BF16)
+            if nbytes == 0:
+                raise _cabi.MoeB200Error(lib.moe_b200_last_error_string().decode())
+            buf = torch.zeros(nbytes + 1024, dtype=torch.uint8, device=device)
+            base = (buf.data_ptr() + 1023) & ~1023
+            check(lib.moe_b200_train_setup(M, d, f, 1, 1, _cabi.BF16, base, nbytes, _stream(device)), "train_setup")
+            self._tws = (buf, base, nbytes, _cabi.train_workspace_layout(M, d, f, 1, 1, _cabi.BF16))
+            self._tws_key = key
+        return self._tws
+
+    def _tws_view(self, name: str, shape) -> torch.Tensor:
+        buf, base, _, layout = self._tws
+        start = base - buf.data_ptr() + layout[name]
+        n = 2
+        for s in shape:
+            n *= s
+        return buf[start:start + n].view(torch.bfloat16).view(*shape)
+
+    def _rows(self, tensor):
+        x = tensor.reshape(-1, tensor.shape[-1]).contiguous()
+        M, dev = x.shape[0], x.device
+        if self._offsets is None or self._offsets[0] != (M, str(dev)):
+            self._offsets = ((M, str(dev)), torch.tensor([0, M], dtype=torch.int32, device=dev))
+        return x, M, dev, self._offsets[1]
+
+    def _forward_train(self, tensor, seed: int):
+        x, M, dev, offsets = self._rows(tensor)
+        d, f = self.hidden_size, self.d_ff
+        h = torch.empty(M, f, dtype=x.dtype, device=dev)
+        y = torch.empty(M, d, dtype=x.dtype, device=dev)
+        with torch.cuda.device(dev):
+            plan = self._plan.get([self], d, f, _cabi.BF16, dev)
+            _, tbase, tbytes, _ = self._train_ws(M, dev)
+            status = torch.zeros(16, dtype=torch.int32, device=dev)
+            check(lib.moe_b200_experts_train(x.data_ptr(), offsets.data_ptr(), plan, M, d, f, 1,
+                                             float(self.dropout.p), seed, tbase, tbytes, h.data_ptr(),
+                                             y.data_ptr(), status.data_ptr(), _stream(dev)), "experts_train")
+        self._train_gen += 1
+        self.last_seed = seed
+        return y.reshape(tensor.shape), h
+
+    def _backward_train(self, tensor, h, grad_y, seed: int):
+        x, M, dev, offsets = self._rows(tensor)
+        d, f = self.hidden_size, self.d_ff
+        g = grad_y.reshape(-1, d).contiguous().to(x.dtype)
+        grad_x = torch.empty_like(x)
+        with torch.cuda.device(dev):
+            plan = self._plan.get([self], d, f, _cabi.BF16, dev)
+            _, tbase, tbytes, _ = self._train_ws(M, dev)
+            status = torch.zeros(16, dtype=torch.int32, device=dev)
+            check(lib.moe_b200_experts_backward(x.data_ptr(), h.data_ptr(), offsets.data_ptr(), plan, g.data_ptr(),
+                                                M, d, f, 1, float(self.dropout.p), seed, tbase, tbytes,
+                                                grad_x.data_ptr(), status.data_ptr(), _stream(dev)),
+                  "experts_backward")
+        self._last_param_grads = [self._tws_view("g_w1", (2 * f, d)).clone(), self._tws_view("g_b1", (2 * f,)).clone(),
+                                  self._tws_view("g_w2", (d, f)).clone(), self._tws_view("g_b2", (d,)).clone()]
+        return [grad_x.reshape(tensor.shape)]
 
     def forward(self, tensor: torch.Tensor, fine_tuning: bool = False) -> torch.Tensor:
         """y = down(gelu_tanh(gate) * up) for every row, through the grouped
         expert kernels with a single group. ``fine_tuning=True`` adds the LoRA
         branch (model.py:175-179,185-189) folded into merged copies of the two weight
         matrices (refreshed when a parameter changes); forward only."""
-        if self.training and self.dropout.p > 0:
-            raise NotImplementedError("dropout in training mode is not implemented; call .eval()")
         if not tensor.is_cuda:
             raise RuntimeError("libmoe_b200 runs on CUDA tensors only; there is no CPU path")
+        if self.training and (torch.is_grad_enabled() or self.dropout.p > 0):
+            if fine_tuning:
+                raise NotImplementedError("training mode runs the plain feed-forward: the LoRA branch "
+                                          "has no backward pass here")
+            if tensor.dtype != torch.bfloat16:
+                raise NotImplementedError("training mode computes in bfloat16")
+            seed = int(torch.randint(0, 2 ** 62, (1,), dtype=torch.int64).item())
+            return _FfnTrainFn.apply(self, tensor, seed, self.gate_and_up.weight, self.gate_and_up.bias,
+                                     self.down.weight, self.down.bias)
         dtype = _dtype_code(tensor)
         shape = tensor.shape
         x = tensor.reshape(-1, shape[-1]).contiguous()

@@ -441,6 +441,22 @@ int moe_b200_backward(const void* x, const void* Wg, const void* plan, const voi
                       float dropout_p, uint64_t seed, void* workspace, size_t workspace_bytes,
                       void* train_ws, size_t train_ws_bytes, void* grad_x, void* stream);
 
+/* The expert feed-forward alone in training mode: FeedForward.forward under .train()
+ * (model.py:173-190 with model.py:183 active) for the rows of every group of `offsets`; the
+ * reference's dense FeedForward (use_moe=False, model.py:302,316) is one group. The training
+ * workspace is laid out by moe_b200_train_workspace_layout(M, d, f, E, 1, dtype) and prepared
+ * by moe_b200_train_setup with the same arguments. Row r's dropout mask is that of pair r. */
+int moe_b200_experts_train(const void* x_sorted, const int32_t* offsets, const void* plan,
+                           int64_t M, int d, int f, int E, float dropout_p, uint64_t seed,
+                           void* train_ws, size_t train_ws_bytes, void* h, void* y,
+                           int32_t* status, void* stream);
+/* Its backward: grad_y [M,d] -> grad_x [M,d], parameter gradients in the MOE_B200_TWS_G_W1 /
+ * G_B1 / G_W2 / G_B2 regions; x_sorted and h are the forward's input and (dropped) h. */
+int moe_b200_experts_backward(const void* x_sorted, const void* h, const int32_t* offsets,
+                              const void* plan, const void* grad_y, int64_t M, int d, int f, int E,
+                              float dropout_p, uint64_t seed, void* train_ws, size_t train_ws_bytes,
+                              void* grad_x, int32_t* status, void* stream);
+
 /* ---- Expert-parallel configuration ------------------------------------------
  * Tokens are sharded over `world` ranks (one process per GPU, rank r owns
  * N_local tokens) and experts are owned by rank h_expert_owner[e]; the

@@ -138,3 +138,37 @@ def test_training_mode_limits(cuda_device):
         m(x, fine_tuning=True)
     with pytest.raises(NotImplementedError):
         m.float()(x.float())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,d,f,p", [(700, 128, 384, 0.1), (64, 64, 128, 0.0), (3000, 256, 520, 0.2)])
+def test_dense_feedforward_trains(cuda_device, rows, d, f, p):
+    """The reference's dense FeedForward (use_moe=False, model.py:302,316) under .train(): forward
+    with the reproducible dropout mask and every gradient against torch.autograd on the oracle's
+    expert_ffn (model.py:173-184)."""
+    from gemmallm_b200 import FeedForward
+    prm = helpers.rounded_params(synthetic.make_params(d, 1, f, seed=rows), DT)
+    g = torch.Generator().manual_seed(rows + 1)
+    prm["w1"] = synthetic.round_to(prm["w1"] * 2.0, DT)
+    prm["b1"] = synthetic.round_to(torch.randn(1, 2 * f, generator=g) * 0.05, DT)
+    prm["b2"] = synthetic.round_to(torch.randn(1, d, generator=g) * 0.05, DT)
+    ff = FeedForward(d, dropout_ratio=p, d_ff=f).to(device=cuda_device, dtype=DT).train()
+    with torch.no_grad():
+        ff.gate_and_up.weight.copy_(prm["w1"][0]); ff.gate_and_up.bias.copy_(prm["b1"][0])
+        ff.down.weight.copy_(prm["w2"][0]); ff.down.bias.copy_(prm["b2"][0])
+    x = synthetic.round_to(synthetic.make_input(rows, d, seed=rows + 2), DT)
+    grad_y = synthetic.round_to(torch.randn(rows, d, generator=g), DT)
+    xd = x.to(DT).to(cuda_device).view(1, rows, d).requires_grad_(True)
+    y = ff(xd)
+    (y.float() * grad_y.to(cuda_device).view(1, rows, d)).sum().backward()
+    torch.cuda.synchronize()
+    mult = torch.from_numpy(philox_ref.dropout_multiplier(rows, f, p, ff.last_seed))
+    leaves = [t.clone().requires_grad_(True) for t in (x, prm["w1"][0], prm["b1"][0], prm["w2"][0], prm["b2"][0])]
+    ref = moe_oracle.expert_ffn(*leaves, h_mask=mult)
+    (ref * grad_y).sum().backward()
+    close(y.view(rows, d), ref.detach(), 2e-2, "forward")
+    close(xd.grad.view(rows, d), leaves[0].grad, 3e-2, "grad x")
+    close(ff.gate_and_up.weight.grad, leaves[1].grad, 3e-2, "grad gate_and_up.weight")
+    close(ff.gate_and_up.bias.grad, leaves[2].grad, 3e-2, "grad gate_and_up.bias")
+    close(ff.down.weight.grad, leaves[3].grad, 3e-2, "grad down.weight")
+    close(ff.down.bias.grad, leaves[4].grad, 3e-2, "grad down.bias")
