@@ -70,7 +70,7 @@ def test_no_cpu_path_and_unimplemented_branches_raise():
     with pytest.raises(RuntimeError, match="no CPU path"):
         m(x, fine_tuning=True)
     m.train()
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError, match="no CPU path"):
         m(x)
     ff = FeedForward(32, 2).eval()
     with pytest.raises(RuntimeError, match="no CPU path"):
