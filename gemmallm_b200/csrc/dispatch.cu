@@ -5,12 +5,15 @@
 // (model.py:226-253), and finishes the load-balancing loss (model.py:213-216).
 //
 // HBM-bound: x [N,d] is read once and written k times with 16-byte accesses.
-// Tokens are cut into chunks of 64; chunk c belongs to block c mod gridDim in
-// both phases. Phase 1 counts experts per chunk into scratch. After a grid
-// barrier every block sums the chunk counts (all of them for the expert
-// offsets, those before its own chunk for its base), ranks its chunk's
-// (token, slot) pairs in token order, and copies the rows. Rows of one expert
-// therefore stay in token order whatever the grid size.
+// Tokens are cut into chunks of 64; every block owns one contiguous range of
+// chunks (the first nchunk mod gridDim blocks one chunk more than the rest) in
+// both phases. Phase 1 counts experts per chunk and per block into scratch.
+// After a grid barrier every block sums the per-block counts (gridDim * E
+// numbers: all of them for the expert offsets, those of earlier blocks for its
+// base), then for each of its chunks ranks the (token, slot) pairs in token
+// order and copies the rows, the loads of one batch of rows in flight while
+// the batch before it is stored. Rows of one expert therefore stay in token
+// order whatever the grid size.
 // With the caller's LayerNorm folded in (norm_stats != nullptr, see norm.cu) a row is
 // copied as (x - mean) * rstd * gamma + beta, with (mean, rstd) from the router
 // (reference model.py:311-312).
@@ -29,6 +32,13 @@ constexpr int kChunk = kDispatchChunk;
 constexpr int kScratchHeader = 32;  // ints: [0] = blocks finished
 
 __host__ __device__ inline int64_t num_chunks(int64_t N) { return (N + kChunk - 1) / kChunk; }
+
+// chunks [first, first + count) of block b out of G
+__device__ inline void chunk_range(int64_t nchunk, int G, int b, int64_t& first, int64_t& count) {
+  const int64_t lo = nchunk / G, extra = nchunk - lo * G;
+  count = lo + (b < extra ? 1 : 0);
+  first = lo * b + (b < extra ? b : extra);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -56,11 +66,15 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
   int32_t* done = scratch;
   int32_t* chunk_cnt = scratch + kScratchHeader;     // [nchunk][E]
   int32_t* blk_slot = chunk_cnt + nchunk * E;        // [G][k][E]
+  int32_t* blk_cnt = blk_slot + (size_t)kNumSMs * 2 * k * E;   // [G][E]
+  int64_t c_first, c_count;
+  chunk_range(nchunk, G, blockIdx.x, c_first, c_count);
 
   // ---- phase 1: histograms -----------------------------------------------
   for (int i = tid; i < k * E; i += kThreads) s_slot[i] = 0;
+  for (int e = tid; e < E; e += kThreads) s_base[e] = 0;   // this block's total per expert
   if (blockIdx.x == 0 && tid == 0) *done = 0;
-  for (int64_t c = blockIdx.x; c < nchunk; c += G) {
+  for (int64_t c = c_first; c < c_first + c_count; ++c) {
     for (int e = tid; e < E; e += kThreads) s_hist[e] = 0;
     __syncthreads();
     const int64_t t0 = c * kChunk;
@@ -75,37 +89,43 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
       atomicAdd(&s_slot[(p % k) * E + e], 1);
     }
     __syncthreads();
-    for (int e = tid; e < E; e += kThreads) chunk_cnt[c * E + e] = s_hist[e];
+    for (int e = tid; e < E; e += kThreads) {
+      chunk_cnt[c * E + e] = s_hist[e];
+      s_base[e] += s_hist[e];
+    }
     __syncthreads();
   }
   for (int i = tid; i < k * E; i += kThreads) blk_slot[(size_t)blockIdx.x * k * E + i] = s_slot[i];
+  for (int e = tid; e < E; e += kThreads) blk_cnt[(size_t)blockIdx.x * E + e] = s_base[e];
 
   grid.sync();
 
   // ---- phase 2: scan ------------------------------------------------------
   for (int e = tid; e < E; e += kThreads) { s_hist[e] = 0; s_base[e] = 0; }
   __syncthreads();
-  const int64_t c0 = blockIdx.x;
-  if (kThreads % E == 0) {
-    // every element this thread visits belongs to the same expert: sum in registers,
-    // one shared-memory atomic per thread at the end
-    const int e = tid % E;
-    int tot = 0, before = 0;
-    for (int64_t i = tid; i < nchunk * E; i += kThreads) {
-      const int v = __ldcg(&chunk_cnt[i]);
-      tot += v;
-      if (i / E < c0) before += v;
-    }
-    if (tot != 0) atomicAdd(&s_hist[e], tot);
-    if (before != 0) atomicAdd(&s_base[e], before);
-  } else {
-    for (int64_t i = tid; i < nchunk * E; i += kThreads) {
-      int v = __ldcg(&chunk_cnt[i]);
-      int64_t cc = i / E;
-      int e = (int)(i - cc * E);
-      if (v != 0) {
-        atomicAdd(&s_hist[e], v);
-        if (cc < c0) atomicAdd(&s_base[e], v);
+  {
+    const int bme = (int)blockIdx.x;
+    if (kThreads % E == 0) {
+      // every count this thread visits belongs to the same expert: sum in registers,
+      // one shared-memory atomic per thread at the end
+      const int e = tid % E, step = kThreads / E;
+      int tot = 0, before = 0;
+#pragma unroll 8
+      for (int bb = tid / E; bb < G; bb += step) {
+        const int v = __ldcg(&blk_cnt[(size_t)bb * E + e]);
+        tot += v;
+        before += bb < bme ? v : 0;
+      }
+      if (tot != 0) atomicAdd(&s_hist[e], tot);
+      if (before != 0) atomicAdd(&s_base[e], before);
+    } else {
+      for (int i = tid; i < G * E; i += kThreads) {
+        const int v = __ldcg(&blk_cnt[i]);
+        const int bb = i / E, e = i - bb * E;
+        if (v != 0) {
+          atomicAdd(&s_hist[e], v);
+          if (bb < bme) atomicAdd(&s_base[e], v);
+        }
       }
     }
   }
@@ -140,10 +160,54 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
 
   // ---- phase 2: rank and copy ---------------------------------------------
   const int warp = tid >> 5, lane = tid & 31;
-  for (int64_t c = c0; c < nchunk; c += G) {
+  constexpr int kVec = 16 / (int)sizeof(T);
+  constexpr int kInFlight = 8;
+  constexpr int kBatch = kThreads * kInFlight;
+  const int pieces = d / kVec;
+  for (int64_t c = c_first; c < c_first + c_count; ++c) {
     const int64_t t0 = c * kChunk;
     const int ntok = (int)((N - t0) < kChunk ? (N - t0) : kChunk);
     const int npair = ntok * k;
+    // rows: the chunk's 16-byte pieces are spread over the block, kInFlight loads per
+    // thread and batch; each piece is stored once per slot. The first batch is
+    // requested before the ranks are known, every later one before the batch in
+    // front of it is stored.
+    const int items = ntok * pieces;
+    const uint4* src = reinterpret_cast<const uint4*>(x + t0 * d);
+    auto load = [&](uint4 (&v)[kInFlight], int i0) {
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < items) v[u] = __ldg(src + i);
+      }
+    };
+    auto store = [&](uint4 (&v)[kInFlight], int i0) {
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < items) {
+          const int tl = i / pieces, pc = i - tl * pieces;
+          if (norm_stats != nullptr) {
+            // 16 bytes = 4 fp32 or 8 bf16 elements of row t0 + tl, columns from pc * kVec
+            const float mean = __ldg(&norm_stats[2 * (t0 + tl)]);
+            const float rstd = __ldg(&norm_stats[2 * (t0 + tl) + 1]);
+            T* e = reinterpret_cast<T*>(&v[u]);
+#pragma unroll
+            for (int q = 0; q < kVec; ++q) {
+              const float y = fmaf((to_f32(e[q]) - mean) * rstd, to_f32(__ldg(&gamma[pc * kVec + q])),
+                                   to_f32(__ldg(&beta[pc * kVec + q])));
+              from_f32(e[q], y);
+            }
+          }
+          for (int j = 0; j < k; ++j) {
+            const int row = s_row[tl * k + j];
+            if (row >= 0) __stcs(reinterpret_cast<uint4*>(perm + (int64_t)row * d) + pc, v[u]);
+          }
+        }
+      }
+    };
+    uint4 va[kInFlight], vb[kInFlight];
+    load(va, tid);
     if (warp == 0) {
       for (int e = lane; e < E; e += 32) s_run[e] = 0;
       __syncwarp();
@@ -168,55 +232,19 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
       }
     }
     __syncthreads();
-    // copy rows: the chunk's 16-byte pieces are spread over the block, 8 loads
-    // in flight per thread; each piece is stored once per slot
-    constexpr int kVec = 16 / (int)sizeof(T);
-    constexpr int kInFlight = 8;
-    const int pieces = d / kVec;
-    const int items = ntok * pieces;
-    const uint4* src = reinterpret_cast<const uint4*>(x + t0 * d);
-    for (int i0 = tid; i0 < items; i0 += kThreads * kInFlight) {
-      uint4 v[kInFlight];
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i < items) v[u] = __ldg(src + i);
-      }
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i < items) {
-          const int tl = i / pieces, pc = i - tl * pieces;
-          if (norm_stats != nullptr) {
-            // 16 bytes = 4 fp32 or 8 bf16 elements of row t0 + tl, columns from pc * kVec
-            const float mean = __ldg(&norm_stats[2 * (t0 + tl)]);
-            const float rstd = __ldg(&norm_stats[2 * (t0 + tl) + 1]);
-            T* e = reinterpret_cast<T*>(&v[u]);
-#pragma unroll
-            for (int q = 0; q < kVec; ++q) {
-              const float y = fmaf((to_f32(e[q]) - mean) * rstd, to_f32(__ldg(&gamma[pc * kVec + q])),
-                                   to_f32(__ldg(&beta[pc * kVec + q])));
-              from_f32(e[q], y);
-            }
-          }
-          for (int j = 0; j < k; ++j) {
-            const int row = s_row[tl * k + j];
-            if (row >= 0) __stcs(reinterpret_cast<uint4*>(perm + (int64_t)row * d) + pc, v[u]);
-          }
-        }
-      }
+    for (int i0 = tid;;) {
+      const int i1 = i0 + kBatch;
+      if (i1 < items) load(vb, i1);
+      store(va, i0);
+      if (i1 >= items) break;
+      i0 = i1 + kBatch;
+      if (i0 < items) load(va, i0);
+      store(vb, i1);
+      if (i0 >= items) break;
     }
     __syncthreads();
-    if (c + G >= nchunk) break;
-    // rows of chunks [c, c+G) precede this block's next chunk
-    for (int64_t i = tid; i < (int64_t)G * E; i += kThreads) {
-      int64_t cc = c + i / E;
-      int e = (int)(i % E);
-      if (cc < nchunk) {
-        int v = __ldcg(&chunk_cnt[cc * E + e]);
-        if (v != 0) atomicAdd(&s_base[e], v);
-      }
-    }
+    // this chunk's rows precede the next chunk's
+    for (int e = tid; e < E; e += kThreads) s_base[e] += chunk_cnt[c * E + e];
     __syncthreads();
   }
 
@@ -268,7 +296,7 @@ dispatch_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx, int64_
 }  // namespace
 
 int64_t dispatch_scratch_ints(int64_t N, int E, int k) {
-  return kScratchHeader + num_chunks(N) * E + (int64_t)kNumSMs * 2 * k * E;
+  return kScratchHeader + num_chunks(N) * E + (int64_t)kNumSMs * 2 * k * E + (int64_t)kNumSMs * 2 * E;
 }
 
 int launch_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int k, int dtype,

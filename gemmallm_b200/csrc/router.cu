@@ -266,8 +266,11 @@ __device__ __forceinline__ void shifted_sums(const uint4& v, float shift, float&
   }
 }
 
-template <int NT, bool NORM>
-__global__ void __launch_bounds__(kMmaWarps * 32)
+// STAGE: the block's slice of Wg goes through shared memory (two cp.async stages), so the four
+// token groups of a block share one read of it. Without it every warp reads its fragments of Wg
+// straight from L1/L2, which is the faster way while Wg fits L1 (E <= 16).
+template <int NT, bool NORM, bool STAGE>
+__global__ void __launch_bounds__(kMmaWarps * 32, (NT >= 4 || NORM) ? 2 : 0)
 router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ Wg,
                   const __nv_bfloat16* __restrict__ bg, int64_t N, int d, int E, int k,
                   float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
@@ -280,6 +283,10 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   float* s_logits = smem;                                          // [64][E+1]
   float* s_psum = smem + (size_t)kRouterTokensPerBlock * ld;       // [kWarps][E]
   float* s_xch = s_psum + (size_t)kWarps * E;                      // [kWarps][32][kXch]
+  // [2 stages][2 halves of d][kMmaUnroll chunks][8*NT rows][4 pieces] of 16 bytes
+  constexpr int kStagePieces = 2 * kMmaUnroll * 8 * NT * 4;
+  uint4* s_stage = reinterpret_cast<uint4*>(
+      (reinterpret_cast<uintptr_t>(s_xch + (size_t)kWarps * 32 * kXch) + 15) & ~(uintptr_t)15);
 
   const int lane = threadIdx.x & 31;
   const int warp = (threadIdx.x >> 5) & (kWarps - 1);   // token group
@@ -302,6 +309,32 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     const int c_begin = khalf ? (half < nchunk ? half : nchunk) : 0;
     const int c_end = khalf ? nchunk : (half < nchunk ? half : nchunk);
     const uint4 zero = make_uint4(0, 0, 0, 0);
+    // staged mode: step = pass over experts * iters + iteration; both halves of d make `iters`
+    // iterations (the shorter half pads with zeros) so that the block's barriers line up
+    const int iters = half / kMmaUnroll;
+    const int passes = (E + 8 * NT - 1) / (8 * NT);
+    auto prefetch = [&](int step) {
+      const int pass = step / iters, it = step - pass * iters;
+      uint4* dst = s_stage + (size_t)(step & 1) * kStagePieces;
+      for (int i = threadIdx.x; i < kStagePieces; i += kMmaWarps * 32) {
+        const int tt = i & 3, u = (i >> 2) % kMmaUnroll, rest = (i >> 2) / kMmaUnroll;
+        const int r = rest % (8 * NT), h = rest / (8 * NT);
+        const int chunk = (h ? (half < nchunk ? half : nchunk) : 0) + it * kMmaUnroll + u;
+        const int ce = h ? nchunk : (half < nchunk ? half : nchunk);
+        const int piece = 4 * chunk + tt;
+        const int row = pass * 8 * NT + r;
+        uint4* d4 = dst + ((size_t)(h * kMmaUnroll + u) * 8 * NT + r) * 4 + tt;
+        if (row < E && chunk < ce && piece < row_pieces) {
+          const uint32_t sa = (uint32_t)__cvta_generic_to_shared(d4);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                       :: "r"(sa), "l"(w4 + (size_t)row * row_pieces + piece) : "memory");
+        } else {
+          *d4 = zero;
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (STAGE) prefetch(0);
     // LayerNorm statistics of rows g and g+8: this lane's pieces, then the quad's four lanes
     float sha = 0.f, shb = 0.f, s1a = 0.f, s2a = 0.f, s1b = 0.f, s2b = 0.f;
     float mean_a = 0.f, rstd_a = 1.f, mean_b = 0.f, rstd_b = 1.f;
@@ -315,7 +348,7 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-      for (int c0 = c_begin; c0 < c_end; c0 += kMmaUnroll) {
+      for (int c0 = c_begin, it = 0; STAGE ? it < iters : c0 < c_end; c0 += kMmaUnroll, ++it) {
         uint4 A[kMmaUnroll], B[kMmaUnroll];
 #pragma unroll
         for (int u = 0; u < kMmaUnroll; ++u) {
@@ -328,14 +361,27 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
             shifted_sums(B[u], shb, s1b, s2b);
           }
         }
+        const uint4* st = nullptr;
+        if (STAGE) {
+          const int step = (e_base / (8 * NT)) * iters + it;
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          __syncthreads();   // this step's slice is complete; the other stage is free again
+          if (step + 1 < passes * iters) prefetch(step + 1);
+          st = s_stage + (size_t)(step & 1) * kStagePieces + (size_t)khalf * kMmaUnroll * 8 * NT * 4;
+        }
 #pragma unroll
         for (int u = 0; u < kMmaUnroll; ++u) {
           const int piece = 4 * (c0 + u) + t;
 #pragma unroll
           for (int j = 0; j < NT; ++j) {
-            const int row = e_base + 8 * j + g;
-            const uint4 w = (row < E && piece < row_pieces && c0 + u < c_end)
-                                ? __ldg(w4 + (size_t)row * row_pieces + piece) : zero;
+            uint4 w;
+            if (STAGE) {
+              w = st[((size_t)u * 8 * NT + 8 * j + g) * 4 + t];
+            } else {
+              const int row = e_base + 8 * j + g;
+              w = (row < E && piece < row_pieces && c0 + u < c_end)
+                      ? __ldg(w4 + (size_t)row * row_pieces + piece) : zero;
+            }
             mma_bf16_16816(acc[j], A[u].x, B[u].x, A[u].y, B[u].y, w.x, w.y);
             mma_bf16_16816(acc[j], A[u].z, B[u].z, A[u].w, B[u].w, w.z, w.w);
           }
@@ -471,14 +517,17 @@ int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, 
                float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
                const float* norm_c, float eps, float* stats, cudaStream_t s) {
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
+  constexpr bool kStage = NT >= 4;
+  constexpr int kUnroll = NT <= 2 ? 8 : 4;
   const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E +
-                                       (size_t)kWarps * 32 * (NT * 4 + 4));
+                                       (size_t)kWarps * 32 * (NT * 4 + 4)) +
+                      (kStage ? 16 + (size_t)2 * 2 * kUnroll * 8 * NT * 4 * 16 : 0);
   static PerDeviceOnce once;
   if (smem > 48 * 1024) {
-    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM>, 100 * 1024);
+    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM, kStage>, 160 * 1024);
     if (rc) return rc;
   }
-  router_mma_kernel<NT, NORM><<<(unsigned)blocks, kMmaWarps * 32, smem, s>>>(
+  router_mma_kernel<NT, NORM, kStage><<<(unsigned)blocks, kMmaWarps * 32, smem, s>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
       static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part,
       norm_c, eps, stats);
