@@ -598,6 +598,13 @@ def run_ours(args, wl):
                 "peak_source": f"{peak_kind} copy",
                 "bytes_per_step": wbytes, "experts_hit": hit, "ms": stage_ms["experts"],
                 "whole_step_gbs": gbs_step, "whole_step_frac": gbs_step / hbm}
+            if small_n and N <= 8 and N * k < 2 * E:
+                # one to eight tokens: the whole call is one kernel, timed by the step itself
+                line["roofline"].update({
+                    "kernel": "decode_tiny_kernel (routing, GEGLU, down product, weighted sum: one cooperative launch)",
+                    "achieved": gbs_step, "frac": gbs_step / hbm, "bytes_per_step": nbytes_step,
+                    "ms": ms_step})
+                line["gpu_launches"] = args.steps
         if world == 1 and wl.name == "c1_uniform" and not args.no_extras:
             # the other single-GPU records of the default run: the decode-shaped calls of this
             # block, and the expert-parallel workload on this one GPU (the same-workload

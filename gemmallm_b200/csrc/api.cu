@@ -419,6 +419,9 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   // most experts hit: stream all of them without waiting for the routing
   const bool spec = small_n && front_small_supported(N, E, k, dtype) && decode_spec_supported(N, E, k) &&
                     N * k >= 2 * (int64_t)E;
+  // a handful of tokens, a row or two per expert: routing, both products and the weighted sum
+  // in one cooperative launch
+  const bool tiny = small_n && !spec && decode_tiny_supported(N, d, f, E, k, dtype);
   // between the decode and the prefill sizes: the streaming kernel on the sorted rows
   const bool rows_path = dtype == MOE_B200_BF16 && !small_n && N * k <= kRowsPathMaxRows &&
                          rows_supported(N * k, E);
@@ -438,6 +441,9 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
     x = xn;
   }
   const bool fold = norm && N > 0 && x != ws + off[MOE_B200_WS_XN];
+  if (tiny)
+    return launch_decode_tiny(x, Wg, bg, N, d, f, E, k, plan, residual, logits, idx, w, cnt_slot,
+                              offsets, row_of, perm, psum, aux, h, out, status, s);
   if (front) {
     // router and dispatch of up to a few hundred tokens in one launch
     // (beyond 128 tokens its blocks share the work and meet at a counter behind the status words)

@@ -321,6 +321,13 @@ int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_
                           const int32_t* idx, const float* w, const void* plan, int E,
                           const void* residual, int64_t N, int d, int k, void* out, cudaStream_t s);
 
+// The whole block for one to eight tokens in one cooperative launch (experts_tiny.cu):
+// routing results as launch_front_small, h [N*k, f] scratch, out [N, d].
+bool decode_tiny_supported(int64_t N, int d, int f, int E, int k, int dtype);
+int launch_decode_tiny(const void* x, const void* Wg, const void* bg, int64_t N, int d, int f, int E,
+                       int k, const void* plan, const void* residual, float* logits, int32_t* idx,
+                       float* w, int32_t* cnt_slot, int32_t* offsets, int32_t* row_of, void* perm,
+                       float* psum, float* aux, void* h, void* out, int32_t* status, cudaStream_t s);
 int launch_experts_gemv(const void* perm, const int32_t* offsets, const void* plan, int64_t M, int d,
                         int f, int E, int ksplit, void* h, float* part, cudaStream_t s);
 

@@ -149,6 +149,24 @@ def test_c2_decode_shapes_bf16(cuda_device, name):
     check_against_oracle(m, params, x, wl.top_k, torch.bfloat16, cuda_device, residual=res)
 
 
+@pytest.mark.parametrize("d,E,f,k", [(1024, 8, 4096, 2), (256, 16, 200, 4), (2048, 8, 1408, 2),
+                                     (128, 5, 264, 3), (64, 32, 136, 8), (72, 8, 24, 1)])
+def test_one_to_eight_tokens_single_launch(cuda_device, d, E, f, k):
+    """bf16 calls of one to eight tokens with fewer than 2E rows run routing, both products and
+    the weighted sum in one cooperative launch: every token count, shapes whose output columns
+    per block need one and two column groups, feature counts that are no multiple of 16, all
+    tokens equal (every row on the same k experts), with and without a residual, call after call."""
+    params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=d + f), torch.bfloat16)
+    m = build(params, d, E, f, k, torch.bfloat16, cuda_device)
+    for N in range(1, 9):
+        x = synthetic.round_to(synthetic.make_input(N, d, seed=31 * N + k), torch.bfloat16)
+        res = synthetic.round_to(synthetic.make_input(N, d, seed=31 * N + 7), torch.bfloat16)
+        check_against_oracle(m, params, x, k, torch.bfloat16, cuda_device)
+        check_against_oracle(m, params, x, k, torch.bfloat16, cuda_device, residual=res)
+        same = x[:1].repeat(N, 1).contiguous()
+        check_against_oracle(m, params, same, k, torch.bfloat16, cuda_device, residual=res)
+
+
 @pytest.mark.parametrize("N,d,E,f,k", [(129, 64, 8, 128, 2), (300, 256, 8, 1024, 2), (512, 512, 8, 2048, 2),
                                        (400, 1024, 8, 4096, 2), (250, 128, 16, 200, 4), (1500, 256, 8, 1024, 2),
                                        (2048, 128, 8, 256, 2)])
