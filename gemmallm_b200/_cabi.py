@@ -44,6 +44,7 @@ SIGNATURES = {
     "moe_b200_experts": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "moe_b200_front_small": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _vp, _vp]),
+    "moe_b200_decode_tiny": (_i, [_vp] * 5 + [_i64, _i, _i, _i, _i] + [_vp] * 13),
     "moe_b200_front_small_split": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i] + [_vp] * 12 + [_vp]),
     "moe_b200_front_exchange_ints": (_i64, [_i64, _i, _i]),
     "moe_b200_experts_rows": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -312,6 +312,27 @@ int moe_b200_front_small_split(const void* x, const void* Wg, const void* bg, in
                             row_of, perm, psum, aux, (cudaStream_t)stream, exchange, counter, status);
 }
 
+int moe_b200_decode_tiny(const void* x, const void* Wg, const void* bg, const void* plan,
+                         const void* residual, int64_t N, int d, int f, int E, int k,
+                         float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot,
+                         int32_t* offsets, int32_t* row_of, void* perm, float* psum, float* aux,
+                         void* h, void* out, int32_t* status, void* stream) {
+  int rc = check_shape(N, d, f, E, k, MOE_B200_BF16);
+  if (rc) return rc;
+  if (!decode_tiny_supported(N, d, f, E, k, MOE_B200_BF16))
+    return set_error(MOE_B200_ERR_UNSUPPORTED,
+                     "moe_b200_decode_tiny needs 1 <= N <= 8, E <= 32, d and f multiples of 8");
+  if (!x || !Wg || !bg || !plan || !out_idx || !out_w || !cnt_slot || !offsets || !row_of || !perm ||
+      !psum || !aux || !h || !out || !status)
+    return set_error(MOE_B200_ERR_NULL, "NULL argument");
+  if (!aligned16(x) || !aligned16(Wg) || !aligned16(perm) || !aligned16(h) || !aligned16(out) ||
+      (residual && !aligned16(residual)))
+    return set_error(MOE_B200_ERR_ALIGN, "x, Wg, perm, h, out and residual must be 16-byte aligned");
+  return launch_decode_tiny(x, Wg, bg, N, d, f, E, k, plan, residual, out_logits, out_idx, out_w,
+                            cnt_slot, offsets, row_of, perm, psum, aux, h, out, status,
+                            (cudaStream_t)stream);
+}
+
 int moe_b200_decode_splits(int f) { return f >= 8 ? decode_splits(f) : 0; }
 
 int64_t moe_b200_decode_max_rows(void) { return kDecodeMaxRows; }

@@ -284,6 +284,23 @@ int64_t moe_b200_decode_max_rows(void);
 int moe_b200_experts_gemv(const void* perm, const int32_t* offsets, const void* plan,
                           int64_t M, int d, int f, int E, void* h, float* part, void* stream);
 
+/* The whole block for one to eight tokens in ONE cooperative launch (model.py:206-276 and
+ * the caller's model.py:319): routing as moe_b200_front_small (same results: logits may be
+ * NULL, idx, w, cnt_slot, offsets, row_of, perm, psum, aux), then the hit experts' GEGLU
+ * product into h [N*k,f] (scratch), a grid barrier, the down product from weight rows that
+ * were requested into shared memory before the GEGLU product, and
+ * out[t] = sum_j w[t,j] * bf16(y[t,j]) (+ residual[t]) in slot order, as
+ * moe_b200_combine_decode. bf16, 1 <= N <= 8, E <= 32, d and f multiples of 8.
+ * moe_b200_forward takes this path when, in addition, N*k < 2E (few experts hit). One block
+ * per SM; the launch itself guarantees that they are resident together. status: the 16
+ * status words (a time-out of the weight rows' arrival is reported there and the rows are
+ * then read from global memory). */
+int moe_b200_decode_tiny(const void* x, const void* Wg, const void* bg, const void* plan,
+                         const void* residual, int64_t N, int d, int f, int E, int k,
+                         float* out_logits, int32_t* out_idx, float* out_w, int32_t* cnt_slot,
+                         int32_t* offsets, int32_t* row_of, void* perm, float* psum, float* aux,
+                         void* h, void* out, int32_t* status, void* stream);
+
 /* Part 3 for small N without waiting for the routing: the same partial sums
  * part[s][M][d] as moe_b200_experts_decode_fused (row order of moe_b200_dispatch), but
  * computed from the UNSORTED tokens x [N,d]: every expert's weights are streamed and

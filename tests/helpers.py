@@ -137,6 +137,29 @@ def experts_gemv(perm, offsets, plan: Plan):
     return h, part
 
 
+def decode_tiny(x, gate_w, gate_b, plan: Plan, k: int, f: int, residual=None):
+    """moe_b200_decode_tiny: the whole block for one to eight bf16 tokens in one launch."""
+    N, d = x.shape
+    E = gate_w.shape[0]
+    dev = x.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    f32 = dict(dtype=torch.float32, device=dev)
+    r = {"logits": torch.empty(N, E, **f32), "idx": torch.empty(N, k, **i32), "w": torch.empty(N, k, **f32),
+         "cnt_slot": torch.empty(k, E, **i32), "offsets": torch.empty(E + 1, **i32),
+         "row_of": torch.empty(N, k, **i32), "perm": torch.empty(N * k, d, dtype=x.dtype, device=dev),
+         "psum": torch.empty(E, **f32), "aux": torch.empty(1, **f32),
+         "h": torch.empty(N * k, f, dtype=x.dtype, device=dev), "out": torch.empty_like(x),
+         "status": torch.zeros(16, **i32)}
+    check(lib.moe_b200_decode_tiny(
+        x.data_ptr(), gate_w.data_ptr(), gate_b.data_ptr(), plan.ptr,
+        residual.data_ptr() if residual is not None else None, N, d, f, E, k,
+        r["logits"].data_ptr(), r["idx"].data_ptr(), r["w"].data_ptr(), r["cnt_slot"].data_ptr(),
+        r["offsets"].data_ptr(), r["row_of"].data_ptr(), r["perm"].data_ptr(), r["psum"].data_ptr(),
+        r["aux"].data_ptr(), r["h"].data_ptr(), r["out"].data_ptr(), r["status"].data_ptr(), stream(dev)),
+        "decode_tiny")
+    return r
+
+
 def experts_decode_spec(x, idx, offsets, plan: Plan):
     """x [N,d] unsorted tokens; returns part [splits, N*k, d] in dispatch row order."""
     N, d = x.shape

@@ -313,6 +313,34 @@ def test_experts_gemv_bf16(cuda_device, rows, d, f):
         assert (part.sum(0) - partf.sum(0)).abs().max() <= 1e-2 * partf.sum(0).abs().max()
 
 
+@pytest.mark.parametrize("N,d,f,E,k", [(8, 1024, 4096, 8, 2), (8, 256, 200, 8, 4), (5, 2048, 1408, 16, 4),
+                                       (1, 64, 24, 4, 4), (8, 128, 264, 32, 8)])
+def test_decode_tiny_entry_point(cuda_device, N, d, f, E, k):
+    """The one-launch block for one to eight tokens, called directly at sizes where most or all
+    experts are hit (more weight rows than its shared memory holds, several column groups per
+    block): routing results and output against the oracle, twice in a row."""
+    dt = torch.bfloat16
+    params = helpers.rounded_params(synthetic.make_params(d, E, f, seed=N + d), dt)
+    dp = helpers.device_params(params, dt, cuda_device)
+    plan = helpers.Plan(dp["w1"], dp["b1"], dp["w2"], dp["b2"])
+    x = synthetic.round_to(synthetic.make_input(N, d, seed=N + f), dt)
+    res = synthetic.round_to(synthetic.make_input(N, d, seed=N + f + 1), dt)
+    xd, rd = x.to(dt).to(cuda_device), res.to(dt).to(cuda_device)
+    for residual in (None, rd):
+        r = helpers.decode_tiny(xd, dp["gate_w"], dp["gate_b"], plan, k, f, residual)
+        torch.cuda.synchronize()
+        assert int(r["status"][0]) == 0
+        o = moe_oracle.moe_forward(x, params, k, logits=r["logits"].cpu())
+        ok = ~moe_oracle.tie_rows(o["probs"], k)
+        assert torch.equal(r["idx"].cpu()[ok].long(), o["idx"][ok])
+        assert int(r["offsets"][-1]) == N * k
+        assert torch.allclose(r["w"].cpu()[ok], o["w"][ok], atol=2e-6, rtol=0)
+        ref = o["out"] if residual is None else o["out"] + res
+        got = r["out"].float().cpu()
+        assert (got - ref)[ok].abs().max() <= 2e-2 * ref.abs().max()
+        assert (got - ref)[ok].norm() <= 2e-2 * ref[ok].norm()
+
+
 SPEC_CASES = [(1, 64, 128, 2, 2), (8, 1024, 4096, 8, 2), (17, 72, 264, 5, 3), (32, 256, 1408, 32, 4),
               (64, 1024, 4096, 8, 2), (100, 128, 512, 3, 2), (128, 256, 384, 16, 2), (64, 128, 256, 8, 1)]
 
