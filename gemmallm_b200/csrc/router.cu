@@ -266,9 +266,11 @@ __device__ __forceinline__ void shifted_sums(const uint4& v, float shift, float&
   }
 }
 
-// STAGE: the block's slice of Wg goes through shared memory (two cp.async stages), so the four
-// token groups of a block share one read of it. Without it every warp reads its fragments of Wg
-// straight from L1/L2, which is the faster way while Wg fits L1 (E <= 16).
+// STAGE: x and the block's slice of Wg go through shared memory in four cp.async stages of one
+// 32-element chunk per half of d: the four token groups of a block share one read of Wg, and the
+// loads of x run three steps ahead of the products without costing registers. Without it every
+// warp reads its fragments straight from global memory, which is the faster way while Wg fits
+// L1 (E <= 16) and few accumulators leave room for many loads in flight.
 template <int NT, bool NORM, bool STAGE>
 __global__ void __launch_bounds__(kMmaWarps * 32, (NT >= 4 || NORM) ? 2 : 0)
 router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ Wg,
@@ -276,15 +278,17 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
                   float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
                   float* __restrict__ out_w, float* __restrict__ psum_part,
                   const float* __restrict__ norm_c, float eps, float* __restrict__ stats) {
-  constexpr int kMmaUnroll = NT <= 2 ? 8 : 4;   // 32-element chunks in flight per lane
+  constexpr int kMmaUnroll = STAGE ? 1 : (NT <= 2 ? 8 : 4);   // 32-element chunks per lane and step
+  constexpr int kStages = 4;
   constexpr int kXch = NT * 4 + 4;              // floats a lane hands over: accumulators, row sums
   extern __shared__ float smem[];
   const int ld = E + 1;                                           // row pitch: no bank conflicts
   float* s_logits = smem;                                          // [64][E+1]
   float* s_psum = smem + (size_t)kRouterTokensPerBlock * ld;       // [kWarps][E]
   float* s_xch = s_psum + (size_t)kWarps * E;                      // [kWarps][32][kXch]
-  // [2 stages][2 halves of d][kMmaUnroll chunks][8*NT rows][4 pieces] of 16 bytes
-  constexpr int kStagePieces = 2 * kMmaUnroll * 8 * NT * 4;
+  // one stage, in 16-byte pieces: Wg [2 halves of d][8*NT rows][4], then x [2 halves][64 tokens][4]
+  constexpr int kStageW = 2 * 8 * NT * 4;
+  constexpr int kStagePieces = kStageW + 2 * kRouterTokensPerBlock * 4;
   uint4* s_stage = reinterpret_cast<uint4*>(
       (reinterpret_cast<uintptr_t>(s_xch + (size_t)kWarps * 32 * kXch) + 15) & ~(uintptr_t)15);
 
@@ -313,28 +317,53 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     // iterations (the shorter half pads with zeros) so that the block's barriers line up
     const int iters = half / kMmaUnroll;
     const int passes = (E + 8 * NT - 1) / (8 * NT);
+    const int total_steps = passes * iters;
+    const int64_t blk_tok0 = (int64_t)blockIdx.x * kRouterTokensPerBlock;
+    // this thread's pieces of a stage: x piece (token, tt) of both halves of d, and one or two
+    // pieces of Wg; only the chunk index changes from step to step
+    const int p_tt = threadIdx.x & 3;
+    const int p_tok = (threadIdx.x >> 2) & (kRouterTokensPerBlock - 1);
+    const int64_t p_row = blk_tok0 + p_tok < N ? blk_tok0 + p_tok : N - 1;   // clamped: masked later
+    const uint4* p_x = reinterpret_cast<const uint4*>(x) + (size_t)p_row * row_pieces + p_tt;
+    constexpr int kWPer = kStageW / (kMmaWarps * 32);       // 1 (NT = 4) or 2 (NT = 8)
+    static_assert(!STAGE || (kStageW % (kMmaWarps * 32) == 0 && kWPer >= 1), "stage shape");
+    const int cb1 = half < nchunk ? half : nchunk;          // first chunk of the second half
     auto prefetch = [&](int step) {
-      const int pass = step / iters, it = step - pass * iters;
-      uint4* dst = s_stage + (size_t)(step & 1) * kStagePieces;
-      for (int i = threadIdx.x; i < kStagePieces; i += kMmaWarps * 32) {
-        const int tt = i & 3, u = (i >> 2) % kMmaUnroll, rest = (i >> 2) / kMmaUnroll;
-        const int r = rest % (8 * NT), h = rest / (8 * NT);
-        const int chunk = (h ? (half < nchunk ? half : nchunk) : 0) + it * kMmaUnroll + u;
-        const int ce = h ? nchunk : (half < nchunk ? half : nchunk);
-        const int piece = 4 * chunk + tt;
-        const int row = pass * 8 * NT + r;
-        uint4* d4 = dst + ((size_t)(h * kMmaUnroll + u) * 8 * NT + r) * 4 + tt;
-        if (row < E && chunk < ce && piece < row_pieces) {
-          const uint32_t sa = (uint32_t)__cvta_generic_to_shared(d4);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
-                       :: "r"(sa), "l"(w4 + (size_t)row * row_pieces + piece) : "memory");
-        } else {
-          *d4 = zero;
+      if (step < total_steps) {
+        const int pass = step / iters, it = step - pass * iters;
+        uint4* dst = s_stage + (size_t)(step % kStages) * kStagePieces;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int chunk = (h ? cb1 : 0) + it;
+          const int piece = 4 * chunk + p_tt;
+          uint4* d4 = dst + kStageW + (size_t)threadIdx.x + h * (kMmaWarps * 32);
+          if (chunk < (h ? nchunk : cb1) && piece < row_pieces) {
+            const uint32_t sa = (uint32_t)__cvta_generic_to_shared(d4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(sa), "l"(p_x + 4 * chunk) : "memory");
+          } else {
+            *d4 = zero;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < kWPer; ++q) {
+          const int i = threadIdx.x + q * (kMmaWarps * 32);
+          const int r = (i >> 2) & (8 * NT - 1), h = i / (8 * NT * 4);
+          const int chunk = (h ? cb1 : 0) + it;
+          const int piece = 4 * chunk + p_tt;
+          const int row = pass * 8 * NT + r;
+          if (row < E && chunk < (h ? nchunk : cb1) && piece < row_pieces) {
+            const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + i);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                         :: "r"(sa), "l"(w4 + (size_t)row * row_pieces + piece) : "memory");
+          } else {
+            dst[i] = zero;
+          }
         }
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.commit_group;" ::: "memory");   // one group per step, empty or not
     };
-    if (STAGE) prefetch(0);
+    if (STAGE)
+      for (int s0 = 0; s0 < kStages - 1; ++s0) prefetch(s0);
     // LayerNorm statistics of rows g and g+8: this lane's pieces, then the quad's four lanes
     float sha = 0.f, shb = 0.f, s1a = 0.f, s2a = 0.f, s1b = 0.f, s2b = 0.f;
     float mean_a = 0.f, rstd_a = 1.f, mean_b = 0.f, rstd_b = 1.f;
@@ -350,24 +379,30 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
       for (int c0 = c_begin, it = 0; STAGE ? it < iters : c0 < c_end; c0 += kMmaUnroll, ++it) {
         uint4 A[kMmaUnroll], B[kMmaUnroll];
+        const uint4* st = nullptr;
+        if (STAGE) {
+          const int step = (e_base / (8 * NT)) * iters + it;
+          asm volatile("cp.async.wait_group %0;" :: "n"(kStages - 2) : "memory");
+          __syncthreads();   // this step's stage is complete; the stage of the step before is free
+          prefetch(step + kStages - 1);
+          st = s_stage + (size_t)(step % kStages) * kStagePieces;
+        }
 #pragma unroll
         for (int u = 0; u < kMmaUnroll; ++u) {
           const int piece = 4 * (c0 + u) + t;
           const bool ok = piece < row_pieces && c0 + u < c_end;
-          A[u] = ok ? xa[piece] : zero;
-          B[u] = ok ? xb[piece] : zero;
+          if (STAGE) {
+            const uint4* sx = st + kStageW + ((size_t)khalf * kRouterTokensPerBlock + warp * kMmaTokPerWarp) * 4;
+            A[u] = sx[g * 4 + t];
+            B[u] = sx[(g + 8) * 4 + t];
+          } else {
+            A[u] = ok ? xa[piece] : zero;
+            B[u] = ok ? xb[piece] : zero;
+          }
           if (NORM && e_base == 0 && ok) {
             shifted_sums(A[u], sha, s1a, s2a);
             shifted_sums(B[u], shb, s1b, s2b);
           }
-        }
-        const uint4* st = nullptr;
-        if (STAGE) {
-          const int step = (e_base / (8 * NT)) * iters + it;
-          asm volatile("cp.async.wait_group 0;" ::: "memory");
-          __syncthreads();   // this step's slice is complete; the other stage is free again
-          if (step + 1 < passes * iters) prefetch(step + 1);
-          st = s_stage + (size_t)(step & 1) * kStagePieces + (size_t)khalf * kMmaUnroll * 8 * NT * 4;
         }
 #pragma unroll
         for (int u = 0; u < kMmaUnroll; ++u) {
@@ -376,7 +411,7 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
           for (int j = 0; j < NT; ++j) {
             uint4 w;
             if (STAGE) {
-              w = st[((size_t)u * 8 * NT + 8 * j + g) * 4 + t];
+              w = st[((size_t)khalf * 8 * NT + 8 * j + g) * 4 + t];
             } else {
               const int row = e_base + 8 * j + g;
               w = (row < E && piece < row_pieces && c0 + u < c_end)
@@ -518,10 +553,9 @@ int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, 
                const float* norm_c, float eps, float* stats, cudaStream_t s) {
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
   constexpr bool kStage = NT >= 4;
-  constexpr int kUnroll = NT <= 2 ? 8 : 4;
   const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E +
                                        (size_t)kWarps * 32 * (NT * 4 + 4)) +
-                      (kStage ? 16 + (size_t)2 * 2 * kUnroll * 8 * NT * 4 * 16 : 0);
+                      (kStage ? 16 + (size_t)4 * (2 * 8 * NT * 4 + 2 * kRouterTokensPerBlock * 4) * 16 : 0);
   static PerDeviceOnce once;
   if (smem > 48 * 1024) {
     int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM, kStage>, 160 * 1024);
