@@ -1106,6 +1106,178 @@ def run_decoder_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------
+# training step of the block (reference train.py:136-142 around model.py:200-276):
+# forward in training mode, loss = sum(out * g) + 0.01 * load_balancing_loss, backward
+# ---------------------------------------------------------------------------
+
+TRAIN_DROPOUT = 0.1     # the reference's default dropout_ratio (model.py:155,193)
+
+
+def train_config(wl):
+    c = workload_config(wl)
+    c["workload"] = wl.name + "_train"
+    c["dropout"] = TRAIN_DROPOUT
+    c["step"] = "forward in training mode + backward for the input and every parameter; no optimizer"
+    return c
+
+
+def run_train(args, wl):
+    """One step = training-mode forward (dropout on h) plus the whole backward pass of the block at
+    the workload's shape, device-resident; e2e adds the host copies of the input and of the
+    input gradient. flops: 6kdfN forward, 12kdfN backward."""
+    from gemmallm_b200 import synthetic
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dt = synthetic.torch_dtype(wl.dtype)
+    N, d, f, E, k = wl.tokens, wl.d_model, wl.d_ff, wl.n_experts, wl.top_k
+    m = build_block(wl, dev, dt)
+    for ex in m.experts:
+        ex.dropout.p = TRAIN_DROPOUT
+    m.train()
+    x = synthetic.make_input(N, d, seed=1).to(dt).to(dev).view(1, N, d).requires_grad_(True)
+    g = (torch.randn(N, d, generator=torch.Generator().manual_seed(5)) * 0.01).to(dt).to(dev).view(1, N, d)
+    params = [p for p in m.parameters() if p.requires_grad]
+
+    def step():
+        out, aux = m(x)
+        loss = (out.float() * g.float()).sum() + 0.01 * aux
+        loss.backward()
+        for p in params:
+            p.grad = None
+        gx, x.grad = x.grad, None
+        return gx, loss
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if m.device_status() != 0:
+        raise RuntimeError("device status non-zero after the warm-up")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms_step = e0.elapsed_time(e1) / args.steps
+    # end to end: input from pinned host memory, input gradient and loss back to the host
+    x_host = synthetic.make_input(N, d, seed=1).to(dt).pin_memory()
+    gx_host = torch.empty(N, d, dtype=dt).pin_memory()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        with torch.no_grad():
+            x.view(N, d).copy_(x_host, non_blocking=True)
+        gx, loss = step()
+        gx_host.copy_(gx.view(N, d), non_blocking=True)
+        _ = float(loss)
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / args.steps
+    peaks, peak_kind = load_peaks()
+    flops = 18.0 * k * d * f * N
+    peak = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+    es = 2
+    line = {
+        "metric": "moe_train_tokens_per_s", "value": N / (ms_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+        "data": "synthetic", "config": train_config(wl),
+        "run": {"parallelism": "single", "cuda_graph": False},
+        "e2e": {"value": N / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": N * d * es,
+                "d2h_bytes_per_step": N * d * es + 4, "ms_per_step": e2e_ms,
+                "mode": "input copied in, input gradient and loss copied out, every step, one stream"},
+        "gpu_launches": 32 * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": {"kernel": "whole step: six grouped_gemm_tc2_kernel launches (two forward, four backward) "
+                               "plus router, dispatch, combine, their backward kernels and the transposes",
+                     "bound": "tensor", "achieved": flops / (ms_step * 1e-3) / 1e12, "peak": peak,
+                     "unit": "TFLOP/s", "frac": flops / (ms_step * 1e-3) / 1e12 / peak, "traffic": None,
+                     "peak_source": f"{peak_kind} bf16 sustained (the step is a seconds-long loop of GEMMs)",
+                     "flops_per_step": flops},
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = train_reference_record(wl, 3)
+    print(json.dumps(line), flush=True)
+
+
+def cpu_train_step(wl, tokens):
+    """The reference class (oracle/_ref) in training mode on the host cores: forward, the same
+    loss, backward. Returns (kind, step function)."""
+    from gemmallm_b200 import synthetic
+    from oracle import make_ref
+    dt = synthetic.torch_dtype(wl.dtype)
+    d, E, f, k = wl.d_model, wl.n_experts, wl.d_ff, wl.top_k
+    ref = make_ref.load()
+    m = ref.MOE(d, num_experts=E, expansion_factor=f // d, dropout_ratio=TRAIN_DROPOUT, device="cpu")
+    params = {n: synthetic.round_to(t, dt) for n, t in synthetic.make_params(
+        d, E, f, seed=0, gate_bias_kind=wl.gate_bias).items()}
+    synthetic.load_into(m, params, torch.float32, "cpu")
+    m.train()
+    x = synthetic.round_to(synthetic.make_input(wl.tokens, d, seed=1), dt)[:tokens].clone().requires_grad_(True)
+    g = torch.randn(tokens, d, generator=torch.Generator().manual_seed(5)) * 0.01
+
+    def step():
+        out, aux = m(x.view(1, tokens, d))
+        loss = (out.view(tokens, d) * g).sum() + 0.01 * aux
+        loss.backward()
+        m.zero_grad(set_to_none=True)
+        x.grad = None
+    return step
+
+
+def train_reference_times(wl, steps, warmup, budget_s):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    tokens = wl.tokens
+    step = cpu_train_step(wl, tokens)
+    t0 = time.perf_counter()
+    step()
+    first = time.perf_counter() - t0
+    calls = steps + max(warmup - 1, 0)
+    if first * calls > budget_s and tokens > 1024:
+        tokens = max(1024, int(tokens * budget_s / (first * calls)) // 1024 * 1024)
+        step = cpu_train_step(wl, tokens)
+        step()
+    for _ in range(max(warmup - 1, 0)):
+        step()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    sample = (f"all {tokens} tokens per step" if tokens == wl.tokens else
+              f"first {tokens} of {wl.tokens} tokens per step (the whole batch would pass the time limit)")
+    return times, cores, sample + ", fp32 on bf16-rounded values, forward + backward", tokens
+
+
+def train_reference_record(wl, reps):
+    times, cores, sample, tokens = train_reference_times(wl, reps, 1, 30.0)
+    times.sort()
+    return {"value": tokens / times[len(times) // 2], "unit": "tokens/s", "cores": cores,
+            "kind": "reference", "sample": f"{sample}, median of {reps}"}
+
+
+def run_train_reference(args, wl):
+    times, cores, sample, tokens = train_reference_times(wl, args.steps, args.warmup, CPU_ARM_BUDGET_S)
+    total = sum(times)
+    value = tokens * args.steps / total
+    line = {
+        "impl": "reference", "metric": "moe_train_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": train_config(wl),
+        "run": {"parallelism": "cpu", "threads": cores},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "reference",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: bool = False):
     """CUDA-event time of each stage, called through its own C-ABI entry point
     on the buffers of the module's workspace, on the current stream."""
@@ -1203,7 +1375,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None,
                     help="default: c1_uniform on one GPU, c4 (expert-parallel) on several; c3 = the whole "
-                         "12-layer decoder forward with the block swapped in (one GPU)")
+                         "12-layer decoder forward with the block swapped in (one GPU); c1_uniform_train = "
+                         "training-mode forward + backward of the block (one GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="one GPU, default workload: skip the decode-shaped sweep and the "
@@ -1224,6 +1397,11 @@ def main():
     if args.workload == "c3":
         if int(os.environ.get("RANK", "0")) == 0:
             run_decoder_reference(args) if args.impl == "reference" else run_decoder(args)
+        return
+    if args.workload.endswith("_train"):
+        if int(os.environ.get("RANK", "0")) == 0:
+            wl = synthetic.WORKLOADS[args.workload[:-len("_train")]]
+            run_train_reference(args, wl) if args.impl == "reference" else run_train(args, wl)
         return
     wl = synthetic.WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -252,25 +252,54 @@ geglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, __nv_bfloat16* __restrict
   store8(gu + r * 2 * f + f + c, du);
 }
 
-// dst[e] [C, R] = src_e [R, C]^T, 64 x 64 tiles through shared memory.
+// 64 x 64 tile transpose with 16-byte global accesses on both sides: rows r < rows_valid of
+// `src` (row pitch C elements, columns [c0, c0 + 64)) become columns of `dst`:
+// dst[(c0 + c) * ldd + i] = src[i][c0 + c], zero where i >= rows_valid. Positions i >= k_valid of
+// dst do not exist and are not written. Shared memory holds the tile as 32-bit words (two
+// neighbouring columns), 33 words per row; a thread then reads one word of eight consecutive
+// rows and splits them into the two columns' 16-byte pieces.
+__device__ __forceinline__ void transpose_tile64(const __nv_bfloat16* __restrict__ src, int rows_valid,
+                                                 int C, int c0, __nv_bfloat16* __restrict__ dst,
+                                                 int64_t ldd, int k_valid, uint32_t (&tile)[64 * 33]) {
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const int p = tid + s * 256;
+    const int i = p >> 3, pc = p & 7;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (i < rows_valid && c0 + pc * 8 < C)
+      v = __ldg(reinterpret_cast<const uint4*>(src + (size_t)i * C + c0 + pc * 8));
+    uint32_t* t4 = &tile[i * 33 + pc * 4];
+    t4[0] = v.x; t4[1] = v.y; t4[2] = v.z; t4[3] = v.w;
+  }
+  __syncthreads();
+  const int kp = tid & 7, cp = tid >> 3;     // eight rows kp*8.., columns 2cp and 2cp + 1
+  uint32_t w[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) w[q] = tile[(kp * 8 + q) * 33 + cp];
+  uint4 lo, hi;
+  lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+  lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+  lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+  lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+  if (kp * 8 < k_valid) {
+    const int c = c0 + 2 * cp;
+    if (c < C) *reinterpret_cast<uint4*>(dst + (size_t)(2 * cp) * ldd + kp * 8) = lo;
+    if (c + 1 < C) *reinterpret_cast<uint4*>(dst + (size_t)(2 * cp + 1) * ldd + kp * 8) = hi;
+  }
+}
+
+// dst[e] [C, R] = src[e] [R, C] transposed (R, C multiples of 8); one block per 64 x 64 tile.
 __global__ void __launch_bounds__(256)
 transpose_weight_kernel(const void* const* __restrict__ src_ptrs, int R, int C,
                         __nv_bfloat16* __restrict__ dst) {
-  __shared__ __nv_bfloat16 tile[64][66];
+  __shared__ uint32_t tile[64 * 33];
   const int e = blockIdx.z;
   const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(src_ptrs[e]);
-  __nv_bfloat16* out = dst + (size_t)e * R * C;
   const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-  for (int i = ty; i < 64; i += 4) {
-    const int r = r0 + i, c = c0 + tx;
-    tile[i][tx] = (r < R && c < C) ? src[(size_t)r * C + c] : __float2bfloat16_rn(0.f);
-  }
-  __syncthreads();
-  for (int i = ty; i < 64; i += 4) {
-    const int c = c0 + i, r = r0 + tx;
-    if (c < C && r < R) out[(size_t)c * R + r] = tile[tx][i];
-  }
+  const int rows = R - r0 < 64 ? R - r0 : 64;
+  transpose_tile64(src + (size_t)r0 * C, rows, C, c0,
+                   dst + (size_t)e * R * C + (size_t)c0 * R + r0, R, rows, tile);
 }
 
 // dst [C, Kpad]: column koff[e] + j holds row offsets[e] + j of src [M, C] for j < rows of e,
@@ -279,7 +308,7 @@ __global__ void __launch_bounds__(256)
 transpose_pad_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ offsets,
                      const int32_t* __restrict__ koff, int E, int C, int64_t Kpad,
                      __nv_bfloat16* __restrict__ dst) {
-  __shared__ __nv_bfloat16 tile[64][66];
+  __shared__ uint32_t tile[64 * 33];
   __shared__ int s_row0, s_rows;
   const int k0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
   if (threadIdx.x == 0) {
@@ -299,38 +328,62 @@ transpose_pad_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __res
     s_rows = rows;
   }
   __syncthreads();
-  const int row0 = s_row0, rows = s_rows;
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-  for (int i = ty; i < 64; i += 4) {
-    const int c = c0 + tx;
-    tile[i][tx] = (i < rows && c < C) ? src[(size_t)(row0 + i) * C + c] : __float2bfloat16_rn(0.f);
-  }
-  __syncthreads();
-  for (int i = ty; i < 64; i += 4) {
-    const int c = c0 + i;
-    if (c < C && k0 + tx < Kpad) dst[(size_t)c * Kpad + k0 + tx] = tile[tx][i];
-  }
+  transpose_tile64(src + (size_t)s_row0 * C, s_rows, C, c0, dst + (size_t)c0 * Kpad + k0, Kpad, 64, tile);
 }
 
-// db[e][c] = sum over the expert's rows of src[r][c]; one block per (expert, 256 columns).
+// db[e][c] = sum over the expert's rows of src[r][c] (C a multiple of 8). One block per (expert,
+// 64 columns): eight threads cover a row's 128 bytes, 32 such groups take rows r, r + 32, ...
+// with four 16-byte loads in flight each; the 32 partial sums of a column are added in order.
 __global__ void __launch_bounds__(256)
 colsum_kernel(const __nv_bfloat16* __restrict__ src, const int32_t* __restrict__ offsets, int C,
               __nv_bfloat16* __restrict__ db) {
+  __shared__ float part[32][65];
   const int e = blockIdx.y;
-  const int c = blockIdx.x * 256 + threadIdx.x;
-  if (c >= C) return;
-  float acc = 0.f;
-  const int r1 = offsets[e + 1];
-  int r = offsets[e];
-  for (; r + 4 <= r1; r += 4) {      // four independent loads in flight
-    const float a0 = __bfloat162float(src[(size_t)r * C + c]);
-    const float a1 = __bfloat162float(src[(size_t)(r + 1) * C + c]);
-    const float a2 = __bfloat162float(src[(size_t)(r + 2) * C + c]);
-    const float a3 = __bfloat162float(src[(size_t)(r + 3) * C + c]);
-    acc += (a0 + a1) + (a2 + a3);
+  const int pc = threadIdx.x & 7, lane_r = threadIdx.x >> 3;
+  const int c = blockIdx.x * 64 + pc * 8;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (c < C) {
+    const int r1 = offsets[e + 1];
+    int r = offsets[e] + lane_r;
+    const uint4* base = reinterpret_cast<const uint4*>(src + c);
+    const size_t pitch = (size_t)C >> 3;     // 16-byte pieces per row
+    for (; r + 96 < r1; r += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldg(base + (size_t)(r + 32 * u) * pitch);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] += bf16_lo(w[i]);
+          acc[2 * i + 1] += bf16_hi(w[i]);
+        }
+      }
+    }
+    for (; r < r1; r += 32) {
+      const uint4 v = __ldg(base + (size_t)r * pitch);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] += bf16_lo(w[i]);
+        acc[2 * i + 1] += bf16_hi(w[i]);
+      }
+    }
   }
-  for (; r < r1; ++r) acc += __bfloat162float(src[(size_t)r * C + c]);
-  db[(size_t)e * C + c] = __float2bfloat16_rn(acc);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) part[lane_r][pc * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    const int col = blockIdx.x * 64 + threadIdx.x;
+    if (col < C) {
+      float sum = 0.f;
+      for (int q = 0; q < 32; ++q) sum += part[q][threadIdx.x];
+      db[(size_t)e * C + col] = __float2bfloat16_rn(sum);
+    }
+  }
 }
 
 unsigned blocks_for(int64_t n, int per) { return (unsigned)((n + per - 1) / per); }
@@ -430,7 +483,7 @@ int launch_transpose_pad(const void* src, const int32_t* offsets, const int32_t*
 }
 
 int launch_colsum(const void* src, const int32_t* offsets, int E, int C, void* db, cudaStream_t s) {
-  colsum_kernel<<<dim3((C + 255) / 256, E), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src),
+  colsum_kernel<<<dim3((C + 63) / 64, E), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src),
                                                         offsets, C, static_cast<__nv_bfloat16*>(db));
   MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
