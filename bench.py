@@ -610,6 +610,7 @@ def run_ours(args, wl):
             # block, and the expert-parallel workload on this one GPU (the same-workload
             # denominator of the multi-GPU speed-ups)
             line["c2"] = decode_sweep(m, wl, dev, dt, hbm)
+            line["around_the_block"] = around_the_block(m, x, dev)
             del m, x
             torch.cuda.empty_cache()
             line["c4_one_gpu"] = one_gpu_record(synthetic.WORKLOADS["c4"], dev, peak)
@@ -619,6 +620,47 @@ def run_ours(args, wl):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def around_the_block(m, x, dev, reps=20):
+    """The block's callers on this workload, device-resident, ms per call: the LoRA branch
+    (model.py:175-179,185-189: merged weights cached / re-merged after every parameter update) and
+    the caller's LayerNorm (model.py:311-312,319) folded into the block or applied in front of it."""
+    def timed(fn):
+        with torch.no_grad():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(reps):
+                fn()
+            t1.record()
+            torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / reps
+
+    d = x.shape[-1]
+    ln = torch.nn.LayerNorm(d).to(device=dev, dtype=x.dtype)
+    with torch.no_grad():
+        ln.weight.uniform_(0.5, 1.5)
+        ln.bias.uniform_(-0.1, 0.1)
+
+    def bump():
+        # what an optimizer step does to the LoRA tensors: the cached merged weights are stale
+        for ex in m.experts:
+            ex.lora_down_b.weight.add_(0.0)
+            ex.lora_gate_and_up_b.weight.add_(0.0)
+
+    rec = {
+        "plain_ms": timed(lambda: m(x, residual=x)),
+        "lora_merged_cached_ms": timed(lambda: m(x, fine_tuning=True, residual=x)),
+        "lora_remerged_every_call_ms": timed(lambda: (bump(), m(x, fine_tuning=True, residual=x))),
+        "layernorm_folded_ms": timed(lambda: m(x, residual=x, norm=ln)),
+        "layernorm_in_front_ms": timed(lambda: m(ln(x), residual=x)),
+    }
+    if m.device_status() != 0:
+        raise RuntimeError("device status non-zero in the LoRA / LayerNorm timings")
+    return rec
 
 
 def one_gpu_record(wl, dev, peak, steps=10):
