@@ -88,6 +88,25 @@ class _MergedLora:
         return self.merged
 
 
+def _lora_grads(ex, g_w1, g_b1, g_w2, g_b2):
+    """Gradients of an expert's four LoRA Linears (weight, bias each, in the order
+    gate_and_up a, b, down a, b) from the gradients G = dL/dW', g = dL/db' of its two merged
+    Linears W' = W + s B A, b' = b + s (B a + b_lora) (model.py:175-179,185-189):
+    dL/dA = s B^T G, dL/da = s B^T g, dL/dB = s (G A^T + g a^T), dL/db_lora = s g."""
+    out = []
+    s = float(ex.lora_scale)
+    with torch.no_grad():
+        for G, g, a, b in ((g_w1, g_b1, ex.lora_gate_and_up_a, ex.lora_gate_and_up_b),
+                           (g_w2, g_b2, ex.lora_down_a, ex.lora_down_b)):
+            Gf, gf = G.float(), g.float()
+            Af, af, Bf = a.weight.float(), a.bias.float(), b.weight.float()
+            dA = (Bf.t() @ Gf).mul_(s)
+            da = (Bf.t() @ gf).mul_(s)
+            dB = (Gf @ Af.t()).addr_(gf, af).mul_(s)
+            out += [dA.to(G.dtype), da.to(G.dtype), dB.to(G.dtype), (gf * s).to(G.dtype)]
+    return out
+
+
 class _Plan:
     """Device copy of the experts' parameter pointers and TMA tensor maps.
 
@@ -127,9 +146,10 @@ class _TrainFn(torch.autograd.Function):
     moe_b200_backward (dropout on h, model.py:183; gradients of model.py:200-276)."""
 
     @staticmethod
-    def forward(ctx, module, x, residual, seed, *params):
-        out, aux = module._forward_train(x, residual, seed)
+    def forward(ctx, module, x, residual, seed, fine_tuning, *params):
+        out, aux = module._forward_train(x, residual, seed, fine_tuning)
         ctx.module, ctx.seed, ctx.gen = module, seed, module._train_gen
+        ctx.fine_tuning = fine_tuning
         ctx.has_residual = residual is not None
         ctx.save_for_backward(x)
         return out, aux
@@ -141,10 +161,10 @@ class _TrainFn(torch.autograd.Function):
             raise RuntimeError("this block ran another training forward before the backward of this "
                                "one: its workspace holds the later call's tensors")
         (x,) = ctx.saved_tensors
-        grads = m._backward_train(x, grad_out.contiguous(), float(grad_aux), ctx.seed)
+        grads = m._backward_train(x, grad_out.contiguous(), float(grad_aux), ctx.seed, ctx.fine_tuning)
         grad_x = grads.pop(0)
         grad_res = grad_out if ctx.has_residual else None
-        return (None, grad_x, grad_res, None, *grads)
+        return (None, grad_x, grad_res, None, None, *grads)
 
 
 class _FfnTrainFn(torch.autograd.Function):
@@ -152,9 +172,10 @@ class _FfnTrainFn(torch.autograd.Function):
     moe_b200_experts_backward: dropout on h, model.py:183; gradients of model.py:173-184)."""
 
     @staticmethod
-    def forward(ctx, module, x, seed, *params):
-        y, h = module._forward_train(x, seed)
+    def forward(ctx, module, x, seed, fine_tuning, *params):
+        y, h = module._forward_train(x, seed, fine_tuning)
         ctx.module, ctx.seed, ctx.gen = module, seed, module._train_gen
+        ctx.fine_tuning = fine_tuning
         ctx.save_for_backward(x, h)
         return y
 
@@ -165,8 +186,8 @@ class _FfnTrainFn(torch.autograd.Function):
             raise RuntimeError("this module ran another training forward before the backward of this "
                                "one: its training workspace holds the later call's tensors")
         x, h = ctx.saved_tensors
-        (grad_x,) = m._backward_train(x, h, grad_y.contiguous(), ctx.seed)
-        return (None, grad_x, None, *m._last_param_grads)
+        (grad_x,) = m._backward_train(x, h, grad_y.contiguous(), ctx.seed, ctx.fine_tuning)
+        return (None, grad_x, None, None, *m._last_param_grads)
 
 
 class FeedForward(nn.Module):
@@ -232,13 +253,18 @@ class FeedForward(nn.Module):
             self._offsets = ((M, str(dev)), torch.tensor([0, M], dtype=torch.int32, device=dev))
         return x, M, dev, self._offsets[1]
 
-    def _forward_train(self, tensor, seed: int):
+    def _train_plan(self, fine_tuning: bool, d, f, dev):
+        if fine_tuning:
+            return self._plan_ft.get(self._lora.get([self], _cabi.BF16, dev), d, f, _cabi.BF16, dev)
+        return self._plan.get([self], d, f, _cabi.BF16, dev)
+
+    def _forward_train(self, tensor, seed: int, fine_tuning: bool = False):
         x, M, dev, offsets = self._rows(tensor)
         d, f = self.hidden_size, self.d_ff
         h = torch.empty(M, f, dtype=x.dtype, device=dev)
         y = torch.empty(M, d, dtype=x.dtype, device=dev)
         with torch.cuda.device(dev):
-            plan = self._plan.get([self], d, f, _cabi.BF16, dev)
+            plan = self._train_plan(fine_tuning, d, f, dev)
             _, tbase, tbytes, _ = self._train_ws(M, dev)
             status = torch.zeros(16, dtype=torch.int32, device=dev)
             check(lib.moe_b200_experts_train(x.data_ptr(), offsets.data_ptr(), plan, M, d, f, 1,
@@ -248,13 +274,13 @@ class FeedForward(nn.Module):
         self.last_seed = seed
         return y.reshape(tensor.shape), h
 
-    def _backward_train(self, tensor, h, grad_y, seed: int):
+    def _backward_train(self, tensor, h, grad_y, seed: int, fine_tuning: bool = False):
         x, M, dev, offsets = self._rows(tensor)
         d, f = self.hidden_size, self.d_ff
         g = grad_y.reshape(-1, d).contiguous().to(x.dtype)
         grad_x = torch.empty_like(x)
         with torch.cuda.device(dev):
-            plan = self._plan.get([self], d, f, _cabi.BF16, dev)
+            plan = self._train_plan(fine_tuning, d, f, dev)
             _, tbase, tbytes, _ = self._train_ws(M, dev)
             status = torch.zeros(16, dtype=torch.int32, device=dev)
             check(lib.moe_b200_experts_backward(x.data_ptr(), h.data_ptr(), offsets.data_ptr(), plan, g.data_ptr(),
@@ -263,24 +289,27 @@ class FeedForward(nn.Module):
                   "experts_backward")
         self._last_param_grads = [self._tws_view("g_w1", (2 * f, d)).clone(), self._tws_view("g_b1", (2 * f,)).clone(),
                                   self._tws_view("g_w2", (d, f)).clone(), self._tws_view("g_b2", (d,)).clone()]
+        if fine_tuning:
+            self._last_param_grads += _lora_grads(self, *self._last_param_grads[:4])
         return [grad_x.reshape(tensor.shape)]
 
     def forward(self, tensor: torch.Tensor, fine_tuning: bool = False) -> torch.Tensor:
         """y = down(gelu_tanh(gate) * up) for every row, through the grouped
         expert kernels with a single group. ``fine_tuning=True`` adds the LoRA
         branch (model.py:175-179,185-189) folded into merged copies of the two weight
-        matrices (refreshed when a parameter changes); forward only."""
+        matrices (refreshed when a parameter changes); under ``.train()`` the LoRA tensors
+        receive gradients too."""
         if not tensor.is_cuda:
             raise RuntimeError("libmoe_b200 runs on CUDA tensors only; there is no CPU path")
         if self.training and (torch.is_grad_enabled() or self.dropout.p > 0):
-            if fine_tuning:
-                raise NotImplementedError("training mode runs the plain feed-forward: the LoRA branch "
-                                          "has no backward pass here")
             if tensor.dtype != torch.bfloat16:
                 raise NotImplementedError("training mode computes in bfloat16")
             seed = int(torch.randint(0, 2 ** 62, (1,), dtype=torch.int64).item())
-            return _FfnTrainFn.apply(self, tensor, seed, self.gate_and_up.weight, self.gate_and_up.bias,
-                                     self.down.weight, self.down.bias)
+            params = [self.gate_and_up.weight, self.gate_and_up.bias, self.down.weight, self.down.bias]
+            if fine_tuning:
+                for lin in (self.lora_gate_and_up_a, self.lora_gate_and_up_b, self.lora_down_a, self.lora_down_b):
+                    params += [lin.weight, lin.bias]
+            return _FfnTrainFn.apply(self, tensor, seed, bool(fine_tuning), *params)
         dtype = _dtype_code(tensor)
         shape = tensor.shape
         x = tensor.reshape(-1, shape[-1]).contiguous()
@@ -368,21 +397,25 @@ class MOE(nn.Module):
         ``moe(x, residual=x, norm=layer.norm2)`` replaces model.py:311-319. ``fine_tuning=True``
         runs the experts with their LoRA branches (model.py:175-179,185-189)
         folded into merged copies of their weights (refreshed when a parameter
-        changes); forward only."""
+        changes); under ``.train()`` the LoRA tensors receive gradients too."""
         if not tensor.is_cuda:
             raise RuntimeError("libmoe_b200 runs on CUDA tensors only; there is no CPU path")
         if self.training and (torch.is_grad_enabled() or self.experts[0].dropout.p > 0):
             # training mode: dropout on h (model.py:183) and a backward pass
-            if fine_tuning or norm is not None:
-                raise NotImplementedError("training mode runs the plain block: LoRA branches and the "
-                                          "folded LayerNorm have no backward pass here")
+            if norm is not None:
+                raise NotImplementedError("training mode has no backward pass for the folded LayerNorm: "
+                                          "apply the LayerNorm in front of the block")
             if tensor.dtype != torch.bfloat16:
                 raise NotImplementedError("training mode computes in bfloat16")
             seed = int(torch.randint(0, 2 ** 62, (1,), dtype=torch.int64).item())   # torch's CPU generator
             params = [self.gate.weight, self.gate.bias]
             for ex in self.experts:
                 params += [ex.gate_and_up.weight, ex.gate_and_up.bias, ex.down.weight, ex.down.bias]
-            return _TrainFn.apply(self, tensor, residual, seed, *params)
+            if fine_tuning:
+                for ex in self.experts:
+                    for lin in (ex.lora_gate_and_up_a, ex.lora_gate_and_up_b, ex.lora_down_a, ex.lora_down_b):
+                        params += [lin.weight, lin.bias]
+            return _TrainFn.apply(self, tensor, residual, seed, bool(fine_tuning), *params)
         dtype = _dtype_code(tensor)
         shape = tensor.shape
         d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
@@ -454,7 +487,12 @@ class MOE(nn.Module):
             n *= s
         return buf[start:start + n].view(torch.bfloat16).view(*shape)
 
-    def _forward_train(self, tensor, residual, seed: int):
+    def _train_plan(self, fine_tuning: bool, d, f, dtype, dev):
+        if fine_tuning:
+            return self._plan_ft.get(self._lora.get(list(self.experts), dtype, dev), d, f, dtype, dev)
+        return self._plan.get(self.experts, d, f, dtype, dev)
+
+    def _forward_train(self, tensor, residual, seed: int, fine_tuning: bool = False):
         dtype = _dtype_code(tensor)
         shape = tensor.shape
         d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
@@ -470,7 +508,7 @@ class MOE(nn.Module):
             res_ptr = residual.reshape(-1, d).contiguous().data_ptr()
         out = torch.empty_like(x)
         with torch.cuda.device(dev):
-            plan = self._plan.get(self.experts, d, f, dtype, dev)
+            plan = self._train_plan(fine_tuning, d, f, dtype, dev)
             _, base, nbytes, _ = self._workspace(N, dtype, dev)
             _, tbase, tbytes, _ = self._train_workspace(N, dtype, dev)
             check(lib.moe_b200_forward_train(
@@ -492,9 +530,16 @@ class MOE(nn.Module):
         aux = self._view("aux", torch.float32, (1,))[0].clone()
         return out.reshape(shape), aux
 
-    def _backward_train(self, tensor, grad_out, grad_aux: float, seed: int):
+    def _backward_train(self, tensor, grad_out, grad_aux: float, seed: int, fine_tuning: bool = False):
         """[grad_x, grad gate.weight, grad gate.bias, then per expert the gradients of
-        gate_and_up.weight, gate_and_up.bias, down.weight, down.bias]."""
+        gate_and_up.weight, gate_and_up.bias, down.weight, down.bias; with ``fine_tuning`` then
+        per expert those of the four LoRA Linears (weight, bias each)].
+
+        With ``fine_tuning`` the kernels run on the merged weights W' = W + s B A,
+        b' = b + s (B a + b_lora) (model.py:175-179,185-189), so what they return for a Linear
+        is G = dL/dW' = dL/dW and g = dL/db' = dL/db; _lora_grads forms the LoRA tensors'
+        gradients from them: four small products per Linear on the gradient the grouped
+        kernel already produced."""
         dtype = _dtype_code(tensor)
         shape = tensor.shape
         d, f, E, k = self.hidden_size, self.d_ff, self.num_experts, self.top_k
@@ -506,7 +551,7 @@ class MOE(nn.Module):
             g = g.to(tensor.dtype)
         grad_x = torch.empty_like(x)
         with torch.cuda.device(dev):
-            plan = self._plan.get(self.experts, d, f, dtype, dev)
+            plan = self._train_plan(fine_tuning, d, f, dtype, dev)
             _, base, nbytes, _ = self._workspace(N, dtype, dev)
             _, tbase, tbytes, _ = self._train_workspace(N, dtype, dev)
             check(lib.moe_b200_backward(
@@ -521,6 +566,9 @@ class MOE(nn.Module):
         g_b2 = self._tws_view("g_b2", (E, d)).clone()
         for e in range(E):
             grads += [g_w1[e], g_b1[e], g_w2[e], g_b2[e]]
+        if fine_tuning:
+            for e, ex in enumerate(self.experts):
+                grads += _lora_grads(ex, g_w1[e], g_b1[e], g_w2[e], g_b2[e])
         return grads
 
     def device_status(self) -> int:

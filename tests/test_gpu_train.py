@@ -129,13 +129,67 @@ def test_backward_matches_autograd_on_the_oracle(cuda_device, N, d, E, f, k, p):
     assert torch.isfinite(m.experts[0].down.weight.grad.float()).all()
 
 
+LORA_NAMES = (("lora_gate_and_up_a", "gu_a"), ("lora_gate_and_up_b", "gu_b"),
+              ("lora_down_a", "dn_a"), ("lora_down_b", "dn_b"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,d,E,f,k,p", [(600, 128, 8, 256, 2, 0.1), (900, 256, 4, 264, 2, 0.0)])
+def test_fine_tuning_trains_the_lora_tensors(cuda_device, N, d, E, f, k, p):
+    """fine_tuning=True under .train() (what the reference's fine-tuning loop runs,
+    model.py:175-179,185-189 with train.py's backward): the gradients of the four LoRA Linears
+    of every expert, of the base Linears, the gate and the input against torch.autograd on the
+    fp32 oracle with the same dropout mask."""
+    m, params = make_block(d, E, f, k, p, cuda_device, seed=N + 11)
+    g = torch.Generator().manual_seed(N + 12)
+    with torch.no_grad():
+        for ex in m.experts:
+            for name, _ in LORA_NAMES:
+                lin = getattr(ex, name)
+                lin.weight.copy_(synthetic.round_to(torch.randn(lin.weight.shape, generator=g) * 0.05, DT))
+                lin.bias.copy_(synthetic.round_to(torch.randn(lin.bias.shape, generator=g) * 0.05, DT))
+    m.train()
+    x = synthetic.round_to(synthetic.make_input(N, d, seed=N + 13), DT)
+    grad_out = synthetic.round_to(torch.randn(N, d, generator=g), DT)
+    grad_aux = 0.25
+    xd = x.to(DT).to(cuda_device).view(1, N, d).requires_grad_(True)
+    out, aux = m(xd, fine_tuning=True)
+    ((out.float() * grad_out.to(cuda_device).view(1, N, d)).sum() + grad_aux * aux).backward()
+    torch.cuda.synchronize()
+    assert m.device_status() == 0
+    mult = torch.from_numpy(philox_ref.dropout_multiplier(N * k, f, p, m.last["seed"])).view(N, k, f)
+    leaves = {n: t.clone().requires_grad_(True) for n, t in params.items()}
+    lora = []
+    for ex in m.experts:
+        dct = {"scale": ex.lora_scale}
+        for name, short in LORA_NAMES:
+            lin = getattr(ex, name)
+            dct[short + "_w"] = lin.weight.detach().float().cpu().requires_grad_(True)
+            dct[short + "_b"] = lin.bias.detach().float().cpu().requires_grad_(True)
+        lora.append(dct)
+    xl = x.clone().requires_grad_(True)
+    o = moe_oracle.moe_forward(xl, leaves, k, lora=lora, h_mask=mult)
+    ((o["out"] * grad_out).sum() + grad_aux * o["aux"]).backward()
+    assert torch.equal(m.last["idx"].cpu().long(), o["idx"]), "routing differs from the oracle's own"
+    close(out.view(N, d), o["out"].detach(), 2e-2, "forward")
+    close(xd.grad.view(N, d), xl.grad, 3e-2, "grad x")
+    close(m.gate.weight.grad, leaves["gate_w"].grad, 3e-2, "grad gate.weight")
+    for e, ex in enumerate(m.experts):
+        close(ex.gate_and_up.weight.grad, leaves["w1"].grad[e], 3e-2, f"grad experts.{e}.gate_and_up.weight")
+        close(ex.down.bias.grad, leaves["b2"].grad[e], 3e-2, f"grad experts.{e}.down.bias")
+        for name, short in LORA_NAMES:
+            lin = getattr(ex, name)
+            close(lin.weight.grad, lora[e][short + "_w"].grad, 4e-2, f"grad experts.{e}.{name}.weight")
+            close(lin.bias.grad, lora[e][short + "_b"].grad, 4e-2, f"grad experts.{e}.{name}.bias")
+
+
 @pytest.mark.gpu
 def test_training_mode_limits(cuda_device):
     m, _ = make_block(64, 8, 128, 2, 0.1, cuda_device, seed=3)
     m.train()
     x = torch.zeros(1, 16, 64, dtype=DT, device=cuda_device)
     with pytest.raises(NotImplementedError):
-        m(x, fine_tuning=True)
+        m(x, norm=torch.nn.LayerNorm(64).to(device=cuda_device, dtype=DT))
     with pytest.raises(NotImplementedError):
         m.float()(x.float())
 
@@ -172,3 +226,37 @@ def test_dense_feedforward_trains(cuda_device, rows, d, f, p):
     close(ff.gate_and_up.bias.grad, leaves[2].grad, 3e-2, "grad gate_and_up.bias")
     close(ff.down.weight.grad, leaves[3].grad, 3e-2, "grad down.weight")
     close(ff.down.bias.grad, leaves[4].grad, 3e-2, "grad down.bias")
+
+
+@pytest.mark.gpu
+def test_dense_feedforward_fine_tuning_trains_the_lora_tensors(cuda_device):
+    """The dense FeedForward with fine_tuning=True under .train(): LoRA gradients against
+    torch.autograd on the oracle's expert_ffn with the same dropout mask."""
+    from gemmallm_b200 import FeedForward
+    rows, d, f, p = 900, 128, 264, 0.1
+    g = torch.Generator().manual_seed(77)
+    ff = FeedForward(d, dropout_ratio=p, d_ff=f).to(device=cuda_device, dtype=DT).train()
+    with torch.no_grad():
+        for prm in ff.parameters():
+            prm.copy_(synthetic.round_to(torch.randn(prm.shape, generator=g) * 0.05, DT))
+    x = synthetic.round_to(synthetic.make_input(rows, d, seed=78), DT)
+    grad_y = synthetic.round_to(torch.randn(rows, d, generator=g), DT)
+    xd = x.to(DT).to(cuda_device).view(1, rows, d).requires_grad_(True)
+    y = ff(xd, fine_tuning=True)
+    (y.float() * grad_y.to(cuda_device).view(1, rows, d)).sum().backward()
+    torch.cuda.synchronize()
+    mult = torch.from_numpy(philox_ref.dropout_multiplier(rows, f, p, ff.last_seed))
+    cpu = lambda t: t.detach().float().cpu().requires_grad_(True)
+    lora = {"scale": ff.lora_scale}
+    for name, short in LORA_NAMES:
+        lora[short + "_w"], lora[short + "_b"] = cpu(getattr(ff, name).weight), cpu(getattr(ff, name).bias)
+    xl = x.clone().requires_grad_(True)
+    base = [cpu(ff.gate_and_up.weight), cpu(ff.gate_and_up.bias), cpu(ff.down.weight), cpu(ff.down.bias)]
+    ref = moe_oracle.expert_ffn(xl, *base, lora, mult)
+    (ref * grad_y).sum().backward()
+    close(y.view(rows, d), ref.detach(), 2e-2, "forward")
+    close(xd.grad.view(rows, d), xl.grad, 3e-2, "grad x")
+    close(ff.down.weight.grad, base[2].grad, 3e-2, "grad down.weight")
+    for name, short in LORA_NAMES:
+        close(getattr(ff, name).weight.grad, lora[short + "_w"].grad, 4e-2, f"grad {name}.weight")
+        close(getattr(ff, name).bias.grad, lora[short + "_b"].grad, 4e-2, f"grad {name}.bias")
