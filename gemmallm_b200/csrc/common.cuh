@@ -286,7 +286,8 @@ int launch_grouped_rows(const void* A, int64_t M, int K, const void* tmaps_b, co
 int launch_grouped_cols(const void* At, const void* Bt, int64_t Kpad, int Ra, int Rb,
                         const int32_t* koff, void* out, int E, int32_t* status, cudaStream_t s);
 int64_t ep_scratch_ints(int64_t N, int EV, int E);
-int launch_ep_begin(uint32_t* epoch, uint32_t* done_counter, int32_t* status, cudaStream_t s);
+int launch_ep_begin(uint32_t* epoch, uint32_t* done_counter, int32_t* status, int32_t* scratch, int EV,
+                    int E, cudaStream_t s);
 int launch_ep_dispatch(const void* x, const int32_t* idx, int64_t N, int d, int E, int EV, int k,
                        int dtype, const EpPeers& peers, int rank, int world, const uint32_t* epoch,
                        const int32_t* owner, const int32_t* vmap, int32_t* scratch,

@@ -193,7 +193,7 @@ int moe_b200_ep_forward(const void* x, const void* Wg, const void* bg, const voi
   uint32_t* epoch = reinterpret_cast<uint32_t*>(status + 16);
   uint32_t* done_counter = reinterpret_cast<uint32_t*>(status + 17);
   // the call's epoch lives on the device, so the same launches can be replayed from a CUDA graph
-  rc = launch_ep_begin(epoch, done_counter, status, s);
+  rc = launch_ep_begin(epoch, done_counter, status, scratch, EV, E, s);
   if (rc) return rc;
   if ((rc = stamp(MOE_B200_EP_EV_START))) return rc;
   if (N_local > 0) {

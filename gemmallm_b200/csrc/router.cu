@@ -547,26 +547,35 @@ router_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   }
 }
 
-template <int NT, bool NORM>
-int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
-               float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
-               const float* norm_c, float eps, float* stats, cudaStream_t s) {
+template <int NT, bool NORM, bool STAGE>
+int launch_mma_variant(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+                       float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+                       const float* norm_c, float eps, float* stats, cudaStream_t s) {
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
-  constexpr bool kStage = NT >= 4;
   const size_t smem = sizeof(float) * ((size_t)kRouterTokensPerBlock * (E + 1) + (size_t)kWarps * E +
                                        (size_t)kWarps * 32 * (NT * 4 + 4)) +
-                      (kStage ? 16 + (size_t)4 * (2 * 8 * NT * 4 + 2 * kRouterTokensPerBlock * 4) * 16 : 0);
+                      (STAGE ? 16 + (size_t)4 * (2 * 8 * NT * 4 + 2 * kRouterTokensPerBlock * 4) * 16 : 0);
   static PerDeviceOnce once;
   if (smem > 48 * 1024) {
-    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM, kStage>, 160 * 1024);
+    int rc = ensure_dynamic_smem(once, router_mma_kernel<NT, NORM, STAGE>, 160 * 1024);
     if (rc) return rc;
   }
-  router_mma_kernel<NT, NORM, kStage><<<(unsigned)blocks, kMmaWarps * 32, smem, s>>>(
+  router_mma_kernel<NT, NORM, STAGE><<<(unsigned)blocks, kMmaWarps * 32, smem, s>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(Wg),
       static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part,
       norm_c, eps, stats);
   MOE_CUDA_CHECK(cudaGetLastError());
   return 0;
+}
+
+template <int NT, bool NORM>
+int launch_mma(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+               float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+               const float* norm_c, float eps, float* stats, cudaStream_t s) {
+  // more than 16 experts: x and Wg staged through shared memory (also the faster of the two for
+  // grids of less than one wave: 34 us against 43 us for 8192 tokens and 64 experts)
+  return launch_mma_variant<NT, NORM, (NT >= 4)>(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w,
+                                                  psum_part, norm_c, eps, stats, s);
 }
 
 template <bool NORM>
