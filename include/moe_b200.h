@@ -160,9 +160,9 @@ int64_t moe_b200_router_blocks(int64_t N);
  * token rows into one expert-contiguous buffer; replaces the per-slot argsort,
  * count loop, gather and split of model.py:226-253. Rows of one expert keep
  * token order (stable).
- *   scratch    moe_b200_dispatch_scratch_bytes(N,E,k) bytes: per-chunk expert
- *              counts and per-block per-slot counts; contents need no
- *              initialisation and are overwritten by every call
+ *   scratch    moe_b200_dispatch_scratch_bytes(N,E,k) bytes: per-chunk and
+ *              per-block expert counts, per-block per-slot counts; contents
+ *              need no initialisation and are overwritten by every call
  *   cnt_slot   int32 [k,E]   (top_expert_counts, second_expert_counts, ...)
  *   offsets    int32 [E+1]
  *   row_of     int32 [N,k]
@@ -376,7 +376,12 @@ int moe_b200_layernorm(const void* x, const void* norm_weight, const void* norm_
  * (model.py:195). norm_weight/norm_bias: NULL, or the LayerNorm in front of the
  * block (see above; x is then the un-normalised tensor, which is usually also
  * the residual). After it the workspace holds logits, idx, w, counts,
- * offsets, psum and the loss (see moe_b200_workspace_layout). */
+ * offsets, psum and the loss (see moe_b200_workspace_layout). The size of the
+ * call selects the kernels (bf16): one to eight tokens with fewer than 2E rows
+ * moe_b200_decode_tiny; up to moe_b200_decode_max_rows() rows the single-launch
+ * front and a weight-streaming expert kernel; up to 4096 rows the front and the
+ * streaming kernel on sorted rows; beyond that router, dispatch, the two grouped
+ * GEMM passes and combine. */
 int moe_b200_forward(const void* x, const void* Wg, const void* bg,
                      const void* plan, const void* residual,
                      const void* norm_weight, const void* norm_bias, float norm_eps,
