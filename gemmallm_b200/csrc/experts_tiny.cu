@@ -8,9 +8,10 @@
 // block per SM does it all:
 //   0. every block derives the routing by itself (front_small_body: same instructions on the
 //      same data in every block, so no exchange is needed); block 0 writes the routing results;
-//   1. every block requests its share of the down weights into shared memory (cp.async): the
-//      block owns d/gridDim output columns of EVERY hit expert, and these bytes do not depend
-//      on the hidden activations, so they stream while step 2 runs;
+//   1. every block requests its share of the down weights into shared memory (one bulk copy
+//      per weight row, completing on an mbarrier): the block owns d/gridDim output columns of
+//      EVERY hit expert, and these bytes do not depend on the hidden activations, so they
+//      stream while step 2 runs;
 //   2. GEGLU product: tiles of 8 features (8 gate rows and 8 up rows of W1 form the 16-row A
 //      operand of mma.sync m16n8k16, so a lane's accumulators hold a feature's gate and up sums
 //      side by side), the expert's rows (at most 8) are the B operand, four warps split d;
