@@ -322,6 +322,11 @@ int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_
                           const int32_t* idx, const float* w, const void* plan, int E,
                           const void* residual, int64_t N, int d, int k, void* out, cudaStream_t s);
 
+// Router for 17 to 64 experts on the tcgen05 path (router_tc.cu); same results as launch_router.
+bool router_tc_supported(int64_t N, int d, int E, int k);
+int launch_router_tc(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
+                     float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+                     int32_t* status, cudaStream_t s);
 // The whole block for one to eight tokens in one cooperative launch (experts_tiny.cu):
 // routing results as launch_front_small, h [N*k, f] scratch, out [N, d].
 bool decode_tiny_supported(int64_t N, int d, int f, int E, int k, int dtype);

@@ -595,8 +595,11 @@ int launch_mma_nt(const void* x, const void* Wg, const void* bg, int64_t N, int 
 int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
                   int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
                   int32_t* status, cudaStream_t s, const float* norm_c, float eps, float* stats) {
-  (void)status;
   if (N == 0) return 0;
+  // 17 to 64 experts without a folded LayerNorm: the tcgen05 kernel (the legacy tensor path's
+  // issue rate, not HBM, bounds router_mma_kernel at that width)
+  if (dtype == MOE_B200_BF16 && norm_c == nullptr && status != nullptr && router_tc_supported(N, d, E, k))
+    return launch_router_tc(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, status, s);
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;
   const size_t smem = sizeof(float) * (size_t)(kRouterTokensPerBlock + kWarps) * E;
   if (dtype == MOE_B200_BF16) {

@@ -18,7 +18,7 @@ ROUTER_CASES = [
     (127, 64, 8, 2, torch.bfloat16), (128, 64, 8, 2, torch.bfloat16), (129, 64, 8, 2, torch.bfloat16),
     (512, 512, 8, 2, torch.float32), (1000, 256, 64, 4, torch.bfloat16),
     (300, 128, 256, 8, torch.bfloat16), (77, 72, 5, 3, torch.float32), (50, 40, 1, 1, torch.float32),
-    (4096, 2048, 64, 4, torch.bfloat16),
+    (4096, 2048, 64, 4, torch.bfloat16), (20000, 264, 32, 4, torch.bfloat16), (9000, 1024, 24, 2, torch.bfloat16),
 ]
 
 
