@@ -24,8 +24,8 @@ using namespace tc;
 
 constexpr int kTokens = 128;          // per CTA: the accumulator's 128 lanes
 constexpr int BK = 64;                // bf16 elements per stage: one 128-byte swizzle row
-constexpr int kStages = 3;           // three stages of 24 KB: two CTAs per SM, so that one CTA's
-                                      // epilogue runs under the other's loads
+constexpr int kMaxStages = 6;        // three stages of 24 KB: two CTAs per SM; six when the call has no
+                                      // more tiles than SMs (one tile per CTA: the loads' latency counts)
 constexpr int kThreads = 192;         // warp 0: TMA, warp 1: MMA and TMEM, warps 2-5: epilogue
 
 template <int EP>
@@ -38,8 +38,8 @@ struct Layout {
 };
 
 struct Control {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -48,8 +48,8 @@ struct Control {
   float inv_sum[kTokens];     // 1 / softmax denominator of every token of the CTA
 };
 
-template <int EP>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int EP, int kStages>
+__global__ void __launch_bounds__(kThreads, kStages > 3 ? 1 : 2)
 router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const __nv_bfloat16* __restrict__ bg, int64_t N, int d, int E, int k,
                  float* __restrict__ out_logits, int32_t* __restrict__ out_idx,
@@ -280,30 +280,41 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   }
 }
 
+template <int EP, int kStages>
+int launch_stages(const CUtensorMap& tx, const CUtensorMap& tw, const void* bg, int64_t N, int d, int E,
+                  int k, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
+                  int32_t* status, int64_t blocks, cudaStream_t s) {
+  using L = Layout<EP>;
+  const size_t smem = 1024 + (size_t)kStages * L::kStageBytes + L::kBufBytes + sizeof(Control);
+  static PerDeviceOnce once;
+  int rc = ensure_dynamic_smem(once, router_tc_kernel<EP, kStages>, 224 * 1024);
+  if (rc) return rc;
+  router_tc_kernel<EP, kStages><<<(unsigned)blocks, kThreads, smem, s>>>(
+      tx, tw, static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part,
+      status);
+  MOE_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
 template <int EP>
 int launch(const void* x, const void* Wg, const void* bg, int64_t N, int d, int E, int k,
            float* out_logits, int32_t* out_idx, float* out_w, float* psum_part, int32_t* status,
            cudaStream_t s) {
-  using L = Layout<EP>;
   alignas(64) CUtensorMap tx, tw;
   int rc = encode_tmap_2d(&tx, x, (uint64_t)N, (uint64_t)d, kTokens);
   if (rc) return rc;
   rc = encode_tmap_2d(&tw, Wg, (uint64_t)E, (uint64_t)d, EP);
   if (rc) return rc;
-  const size_t smem = 1024 + (size_t)kStages * L::kStageBytes + L::kBufBytes + sizeof(Control);
-  static PerDeviceOnce once;
-  rc = ensure_dynamic_smem(once, router_tc_kernel<EP>, 224 * 1024);
-  if (rc) return rc;
   const int64_t tiles = (N + kTokens - 1) / kTokens;
   int sms = 0;
   rc = sm_count(&sms);
   if (rc) return rc;
-  const int64_t blocks = tiles < 2 * (int64_t)sms ? tiles : 2 * (int64_t)sms;   // two persistent CTAs per SM
-  router_tc_kernel<EP><<<(unsigned)blocks, kThreads, smem, s>>>(
-      tx, tw, static_cast<const __nv_bfloat16*>(bg), N, d, E, k, out_logits, out_idx, out_w, psum_part,
-      status);
-  MOE_CUDA_CHECK(cudaGetLastError());
-  return 0;
+  if (tiles <= sms)
+    return launch_stages<EP, 6>(tx, tw, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, status,
+                                tiles, s);
+  // two persistent CTAs per SM
+  return launch_stages<EP, 3>(tx, tw, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, status,
+                              tiles < 2 * (int64_t)sms ? tiles : 2 * (int64_t)sms, s);
 }
 
 }  // namespace
