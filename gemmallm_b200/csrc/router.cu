@@ -596,8 +596,9 @@ int launch_router(const void* x, const void* Wg, const void* bg, int64_t N, int 
                   int dtype, float* out_logits, int32_t* out_idx, float* out_w, float* psum_part,
                   int32_t* status, cudaStream_t s, const float* norm_c, float eps, float* stats) {
   if (N == 0) return 0;
-  // 17 to 64 experts without a folded LayerNorm: the tcgen05 kernel (the legacy tensor path's
-  // issue rate, not HBM, bounds router_mma_kernel at that width)
+  // 17 to 64 experts without a folded LayerNorm: the tcgen05 kernel, whose epilogue has a token's
+  // logits in one thread's registers (at that width router_mma_kernel spends its time in the
+  // softmax/top-k of its four lanes per token, not in the product)
   if (dtype == MOE_B200_BF16 && norm_c == nullptr && status != nullptr && router_tc_supported(N, d, E, k))
     return launch_router_tc(x, Wg, bg, N, d, E, k, out_logits, out_idx, out_w, psum_part, status, s);
   const int64_t blocks = (N + kRouterTokensPerBlock - 1) / kRouterTokensPerBlock;

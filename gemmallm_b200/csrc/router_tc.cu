@@ -1,9 +1,9 @@
 // Router for 17 to 64 experts on the tcgen05 path (reference model.py:206-223): logits =
 // x Wg^T + bg, softmax, top-k, renormalised scores, per-block probability sums.
 //
-// With E = 64 the projection is 2 * 64 flops per input element: on the legacy mma.sync path the
-// kernel is bound by that path's issue rate, not by HBM (router.cu reaches 0.3 of the copy rate
-// there). Here a persistent CTA (two per SM) walks tiles of 128 tokens: x [128 x 64] and
+// With E = 64 the softmax and top-k over 64 logits per token, not the projection, decide the
+// kernel's time (router.cu reaches 0.3 of the HBM copy rate there: four lanes share a token and
+// divide, exponentiate and scan 16 experts each). Here a persistent CTA (two per SM) walks tiles of 128 tokens: x [128 x 64] and
 // Wg [E x 64] tiles arrive by TMA (128-byte swizzle, three stages), one thread issues
 // tcgen05.mma (M = 128, N = E padded to 32 or 64, K = 16) into one of two TMEM accumulators
 // whose lane is the token, and four epilogue warps read their token's logits straight into
