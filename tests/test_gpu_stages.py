@@ -19,6 +19,7 @@ ROUTER_CASES = [
     (512, 512, 8, 2, torch.float32), (1000, 256, 64, 4, torch.bfloat16),
     (300, 128, 256, 8, torch.bfloat16), (77, 72, 5, 3, torch.float32), (50, 40, 1, 1, torch.float32),
     (4096, 2048, 64, 4, torch.bfloat16), (20000, 264, 32, 4, torch.bfloat16), (9000, 1024, 24, 2, torch.bfloat16),
+    (5, 72, 40, 3, torch.bfloat16), (129, 64, 17, 1, torch.bfloat16), (40000, 512, 64, 8, torch.bfloat16),
 ]
 
 
