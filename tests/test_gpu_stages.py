@@ -315,7 +315,8 @@ def test_experts_gemv_bf16(cuda_device, rows, d, f):
 
 
 @pytest.mark.parametrize("N,d,f,E,k", [(8, 1024, 4096, 8, 2), (8, 256, 200, 8, 4), (5, 2048, 1408, 16, 4),
-                                       (1, 64, 24, 4, 4), (8, 128, 264, 32, 8)])
+                                       (1, 64, 24, 4, 4), (8, 128, 264, 32, 8), (8, 64, 64, 8, 8),
+                                       (7, 1024, 4096, 8, 2)])
 def test_decode_tiny_entry_point(cuda_device, N, d, f, E, k):
     """The one-launch block for one to eight tokens, called directly at sizes where most or all
     experts are hit (more weight rows than its shared memory holds, several column groups per
