@@ -347,7 +347,7 @@ def time_streaming(replicas, make_replica, wl, x, steps, graphs=True):
         for _ in range(3):
             m(x)
     torch.cuda.synchronize()
-    spec_all = N * k >= 2 * E and is_small_n(wl)
+    spec_all = N * k >= E and is_small_n(wl)
     _, _, _, touched = streamed_bytes(m, wl, spec_all)
     n_rep = max(1, -(-int(2 * L2_BYTES) // touched))
     while len(replicas) < n_rep:
@@ -598,7 +598,7 @@ def run_ours(args, wl):
                 "peak_source": f"{peak_kind} copy",
                 "bytes_per_step": wbytes, "experts_hit": hit, "ms": stage_ms["experts"],
                 "whole_step_gbs": gbs_step, "whole_step_frac": gbs_step / hbm}
-            if small_n and N <= 8 and N * k < 2 * E:
+            if small_n and N <= 8 and N * k < E:
                 # one to eight tokens: the whole call is one kernel, timed by the step itself
                 line["roofline"].update({
                     "kernel": "decode_tiny_kernel (routing, GEGLU, down product, weighted sum: one cooperative launch)",
@@ -1359,7 +1359,7 @@ def time_stages(m, x2d, wl, dev, small_n: bool = False, reps: int = 20, mid_n: b
         ready = p["status"] + 4 * _cabi.READY_OFFSET
         calls["experts"] = lambda: lib.moe_b200_experts_decode_fused(
             p["perm"], p["offsets"], plan, N * k, d, f, E, p["h"], p["part"], ready, p["status"], s)
-        if N * k >= 2 * E and N <= 128 and E <= 32:
+        if N * k >= E and N <= 128 and E <= 32:
             # the kernel the forward uses when most experts are hit (timed here without its overlap
             # with the routing kernel); "experts_sorted" is the kernel for a few hit experts
             calls["experts_sorted"] = calls["experts"]

@@ -437,9 +437,12 @@ int moe_b200_forward(const void* x, const void* Wg, const void* bg, const void* 
   // a size switch, not a backend switch: up to 256 rows the weight-streaming kernels
   const bool small_n = dtype == MOE_B200_BF16 && N * k <= kDecodeMaxRows;
 
-  // most experts hit: stream all of them without waiting for the routing
+  // as many rows as experts: most experts are hit, stream all of them without waiting for the
+  // routing (measured at d=1024, f=4096, E=8, k=2: 43-45 us from 4 to 64 tokens, against 23 / 34 /
+  // 40 / 50 / 66 us for the one-launch kernel below at 1 / 2 / 3 / 4 / 6 tokens, whose time grows
+  // with every expert that is hit)
   const bool spec = small_n && front_small_supported(N, E, k, dtype) && decode_spec_supported(N, E, k) &&
-                    N * k >= 2 * (int64_t)E;
+                    N * k >= (int64_t)E;
   // a handful of tokens, a row or two per expert: routing, both products and the weighted sum
   // in one cooperative launch
   const bool tiny = small_n && !spec && decode_tiny_supported(N, d, f, E, k, dtype);

@@ -291,7 +291,7 @@ int moe_b200_experts_gemv(const void* perm, const int32_t* offsets, const void* 
  * were requested into shared memory before the GEGLU product, and
  * out[t] = sum_j w[t,j] * bf16(y[t,j]) (+ residual[t]) in slot order, as
  * moe_b200_combine_decode. bf16, 1 <= N <= 8, E <= 32, d and f multiples of 8.
- * moe_b200_forward takes this path when, in addition, N*k < 2E (few experts hit). One block
+ * moe_b200_forward takes this path when, in addition, N*k < E (few experts hit). One block
  * per SM; the launch itself guarantees that they are resident together. status: the 16
  * status words (a time-out of the weight rows' arrival is reported there and the rows are
  * then read from global memory). */
@@ -309,7 +309,7 @@ int moe_b200_decode_tiny(const void* x, const void* Wg, const void* bg, const vo
  * dependent launch it overlaps the routing kernel before it in the stream
  * (model.py:174-184 per expert; the reference skips experts without tokens,
  * model.py:256, this kernel reads their GEGLU weights anyway: worth it when most
- * experts are hit, roughly N*k >= 2E). bf16, N <= 128, E <= 32, N*k <=
+ * experts are hit; moe_b200_forward uses it from N*k >= E on). bf16, N <= 128, E <= 32, N*k <=
  * moe_b200_decode_max_rows(). h_all: bf16 [E][moe_b200_decode_spec_rows(N)][f]
  * scratch; ready: int32[MOE_B200_READY_INTS], zeroed by this call. Residency rule
  * and timeout behaviour as for moe_b200_experts_decode_fused. */
@@ -377,7 +377,7 @@ int moe_b200_layernorm(const void* x, const void* norm_weight, const void* norm_
  * block (see above; x is then the un-normalised tensor, which is usually also
  * the residual). After it the workspace holds logits, idx, w, counts,
  * offsets, psum and the loss (see moe_b200_workspace_layout). The size of the
- * call selects the kernels (bf16): one to eight tokens with fewer than 2E rows
+ * call selects the kernels (bf16): one to eight tokens with fewer than E rows
  * moe_b200_decode_tiny; up to moe_b200_decode_max_rows() rows the single-launch
  * front and a weight-streaming expert kernel; up to 4096 rows the front and the
  * streaming kernel on sorted rows; beyond that router, dispatch, the two grouped

@@ -152,7 +152,7 @@ def test_c2_decode_shapes_bf16(cuda_device, name):
 @pytest.mark.parametrize("d,E,f,k", [(1024, 8, 4096, 2), (256, 16, 200, 4), (2048, 8, 1408, 2),
                                      (128, 5, 264, 3), (64, 32, 136, 8), (72, 8, 24, 1)])
 def test_one_to_eight_tokens_single_launch(cuda_device, d, E, f, k):
-    """bf16 calls of one to eight tokens with fewer than 2E rows run routing, both products and
+    """bf16 calls of one to eight tokens with fewer rows than experts run routing, both products and
     the weighted sum in one cooperative launch: every token count, shapes whose output columns
     per block need one and two column groups, feature counts that are no multiple of 16, all
     tokens equal (every row on the same k experts), with and without a residual, call after call."""
