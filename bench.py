@@ -42,7 +42,7 @@ NCU_TRAFFIC = {
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_BYTES = 126e6
-CPU_ARM_BUDGET_S = 240.0      # the whole --impl reference run should end within a few minutes
+CPU_ARM_LIMIT_S = 240.0      # the whole --impl reference run should end within a few minutes
 
 
 def load_peaks():
@@ -214,10 +214,10 @@ def cpu_block(wl):
     return "port", (lambda x: moe_oracle.moe_forward(x, params, k)), why
 
 
-def cpu_arm(wl, steps, warmup, budget_s):
+def cpu_arm(wl, steps, warmup, limit_s):
     """Times the CPU block: fp32 on bf16-rounded values (the reference cannot run in bf16),
     all host threads. The sample is the whole token batch unless one step is so slow that
-    steps + warmup of them would pass `budget_s`; then the first tokens of the batch, as many
+    steps + warmup of them would pass `limit_s`; then the first tokens of the batch, as many
     as fit. Returns (per-step seconds, cores, kind, sample text, tokens per step, note)."""
     from gemmallm_b200 import synthetic
     cores = os.cpu_count() or 1
@@ -231,8 +231,8 @@ def cpu_arm(wl, steps, warmup, budget_s):
         fwd(x_all)
         first = time.perf_counter() - t0
         total_calls = steps + max(warmup - 1, 0)
-        if first * total_calls > budget_s and tokens > 1024:
-            tokens = max(1024, int(tokens * budget_s / (first * total_calls)) // 1024 * 1024)
+        if first * total_calls > limit_s and tokens > 1024:
+            tokens = max(1024, int(tokens * limit_s / (first * total_calls)) // 1024 * 1024)
         x = x_all[:tokens]
         for _ in range(max(warmup - 1, 0)):
             fwd(x)
@@ -251,7 +251,7 @@ def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    times, cores, kind, sample, tokens, why = cpu_arm(wl, args.steps, args.warmup, CPU_ARM_BUDGET_S)
+    times, cores, kind, sample, tokens, why = cpu_arm(wl, args.steps, args.warmup, CPU_ARM_LIMIT_S)
     total = sum(times)
     value = tokens * args.steps / total
     line = {
@@ -1270,7 +1270,7 @@ def cpu_train_step(wl, tokens):
     return step
 
 
-def train_reference_times(wl, steps, warmup, budget_s):
+def train_reference_times(wl, steps, warmup, limit_s):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     tokens = wl.tokens
@@ -1279,8 +1279,8 @@ def train_reference_times(wl, steps, warmup, budget_s):
     step()
     first = time.perf_counter() - t0
     calls = steps + max(warmup - 1, 0)
-    if first * calls > budget_s and tokens > 1024:
-        tokens = max(1024, int(tokens * budget_s / (first * calls)) // 1024 * 1024)
+    if first * calls > limit_s and tokens > 1024:
+        tokens = max(1024, int(tokens * limit_s / (first * calls)) // 1024 * 1024)
         step = cpu_train_step(wl, tokens)
         step()
     for _ in range(max(warmup - 1, 0)):
@@ -1303,7 +1303,7 @@ def train_reference_record(wl, reps):
 
 
 def run_train_reference(args, wl):
-    times, cores, sample, tokens = train_reference_times(wl, args.steps, args.warmup, CPU_ARM_BUDGET_S)
+    times, cores, sample, tokens = train_reference_times(wl, args.steps, args.warmup, CPU_ARM_LIMIT_S)
     total = sum(times)
     value = tokens * args.steps / total
     line = {
