@@ -1070,6 +1070,25 @@ def run_decoder(args):
         a1.record()
         torch.cuda.synchronize()
         ms_att = a0.elapsed_time(a1) / args.steps
+        # the whole layer replaced (model.py:278-321): the second LayerNorm folded into the block's
+        # router and dispatch, the second skip connection into its combine
+        from gemmallm_b200 import LLMLayer
+        for i, layer in enumerate(llm.transformer):
+            new = LLMLayer(c["d_model"], c["head_dim"], c["q_heads"], c["kv_heads"], layer.mqa.embedding,
+                           expansion_factor=c["factor"], use_moe=True, num_experts=c["n_experts"],
+                           device="cuda").eval()
+            new.load_state_dict(layer.state_dict(), strict=True)
+            llm.transformer[i] = new.to(device=dev, dtype=dt)
+        for _ in range(3):
+            llm(x.clone(), mask, False)
+        torch.cuda.synchronize()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(args.steps):
+            llm(x.clone(), mask, False)
+        b1.record()
+        torch.cuda.synchronize()
+        ms_layer = b0.elapsed_time(b1) / args.steps
         # end to end: embeddings from pinned host memory in, last-position logits and loss out
         out_host = torch.empty(c["batch"], c["vocab"], dtype=dt).pin_memory()
         aux_host = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -1098,9 +1117,11 @@ def run_decoder(args):
         "run": {"what": "whole decoder forward (reference LLM, every layer.moe swapped for the new block)",
                 "moe_ms_per_forward": moe_ms, "moe_share": moe_ms / ms,
                 "with_new_attention_too": {"ms_per_step": ms_att, "tokens_per_s": tokens / (ms_att * 1e-3)},
+                "with_the_whole_layer_replaced": {"ms_per_step": ms_layer,
+                                                  "tokens_per_s": tokens / (ms_layer * 1e-3)},
                 "moe_tflops_incl_router_dispatch_combine": flops / (moe_ms * 1e-3) / 1e12},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
-                "configuration": "new block and new attention in every layer",
+                "configuration": "every layer replaced by the new layer (block, attention, folded LayerNorm)",
                 "h2d_bytes_per_step": tokens * c["d_model"] * 2,
                 "d2h_bytes_per_step": c["batch"] * c["vocab"] * 2 + 4, "ms_per_step": e2e_ms,
                 "mode": "embeddings from pinned host memory, last-position logits and loss back, host waits"},

@@ -140,3 +140,39 @@ def test_new_block_inside_the_reference_decoder(cuda_device, layers, batch):
         msg += (f", bf16 logits vs fp32 reference: per-token max-abs/max median {float(per_token.median()):.2e}, "
                 f"90th percentile {float(per_token.quantile(0.9)):.2e}, arg-max agreement {agree:.3f}")
     print(msg)
+
+
+@pytest.mark.skipif(not make_ref.available(), reason="oracle/_ref/model.py absent (run oracle/make_ref.py)")
+def test_decoder_layer_drop_in(cuda_device):
+    """gemmallm_b200.LLMLayer against the reference's own LLMLayer (model.py:278-321): the strict
+    state_dict loads, and the bf16 layer (attention kernel, second LayerNorm folded into the
+    block, skip connection in the combine kernel) reproduces the fp32 reference layer on
+    bf16-representable parameters and inputs. A routing flip may move a token; the rest agree."""
+    from gemmallm_b200 import LLMLayer
+    dt = torch.bfloat16
+    llm = build_reference_llm(1, "cpu", seed=5)
+    ref_layer = llm.transformer[0]
+    g = torch.Generator().manual_seed(6)
+    with torch.no_grad():
+        for norm in (ref_layer.norm1, ref_layer.norm2):
+            norm.weight.copy_(1.0 + 0.2 * torch.randn(D, generator=g))
+            norm.bias.copy_(0.1 * torch.randn(D, generator=g))
+        for p in ref_layer.parameters():
+            p.copy_(p.to(dt).float())
+    batch = 8
+    x = (torch.randn(batch, S, D, generator=g) * 0.5).to(dt).float()
+    with torch.no_grad():
+        ref_out, ref_aux = ref_layer(x.clone(), causal_mask("cpu", torch.float32), False)
+    new = LLMLayer(D, HEAD_DIM, HEADS, 1, ref_layer.mqa.embedding, expansion_factor=FACTOR, use_moe=True,
+                   num_experts=E, device="cuda").eval()
+    new.load_state_dict(ref_layer.state_dict(), strict=True)
+    new.to(device=cuda_device, dtype=dt)
+    with torch.no_grad():
+        out, aux = new(x.to(dt).to(cuda_device), causal_mask(cuda_device, dt), False)
+    torch.cuda.synchronize()
+    assert new.moe.device_status() == 0
+    scale = float(ref_out.abs().max())
+    per_token = (out.float().cpu() - ref_out).abs().amax(-1).flatten() / scale
+    assert float(per_token.median()) < 1e-2, float(per_token.median())
+    assert float(per_token.quantile(0.97)) < 3e-2, float(per_token.quantile(0.97))
+    assert abs(float(aux) - float(ref_aux)) <= 2e-2 * abs(float(ref_aux)) + 1e-6
