@@ -89,24 +89,51 @@ attention_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __r
   __syncthreads();
 
   __nv_bfloat16* myQ = sQ + warp * 16 * KP;
-  for (int hh = warp; hh < heads_per_kv; hh += kWarpsAtt) {
-    const int h = kvh * heads_per_kv + hh;
-    for (int mt = 0; mt < S_TILES; ++mt) {
+  // A warp's work: (query head, 16-row tile) items. The rows of the next item and its gate
+  // values are requested before the products of the current one, so that a warp always has
+  // loads in flight.
+  const int my_heads = warp < heads_per_kv ? (heads_per_kv - warp + kWarpsAtt - 1) / kWarpsAtt : 0;
+  const int items = my_heads * S_TILES;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  auto fetch = [&](int item, uint4 (&raw)[4], float& ga, float& gb) {
+    const int h = kvh * heads_per_kv + warp + (item / S_TILES) * kWarpsAtt, mt = item % S_TILES;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int i = lane + 32 * q;
+      const int s = mt * 16 + (i >> 3), c = (i & 7) * 8;
+      raw[q] = s < S ? __ldg(reinterpret_cast<const uint4*>(base + (size_t)s * row_elems + h * HD + c)) : zero4;
+    }
+    const int r0 = mt * 16 + g;
+    ga = r0 < S ? __bfloat162float(gate[((size_t)b * S + r0) * H + h]) : 0.f;
+    gb = r0 + 8 < S ? __bfloat162float(gate[((size_t)b * S + r0 + 8) * H + h]) : 0.f;
+  };
+  uint4 raw[4];
+  float gate_a = 0.f, gate_b = 0.f;
+  if (items > 0) fetch(0, raw, gate_a, gate_b);
+  for (int item = 0; item < items; ++item) {
+    {
+      const int h = kvh * heads_per_kv + warp + (item / S_TILES) * kWarpsAtt, mt = item % S_TILES;
       // ---- 16 query rows of this head, rotated, into the warp's staging area ----
       __syncwarp();
-      for (int i = lane; i < 16 * (HD / 8); i += 32) {
-        const int sl = i / (HD / 8), c = (i - sl * (HD / 8)) * 8;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int i = lane + 32 * q;
+        const int sl = i >> 3, c = (i & 7) * 8;
         const int s = mt * 16 + sl;
+        const uint32_t w[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
         float qx[8], qo[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { qx[2 * e] = bf16_lo(w[e]); qx[2 * e + 1] = bf16_hi(w[e]); }
         if (s < S) {
-          load8(base + (size_t)s * row_elems + h * HD + c, qx);
           rope8(qx, sPE + s * 2 * HD, c, qo);
         } else {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) qo[q] = 0.f;
+          for (int e = 0; e < 8; ++e) qo[e] = 0.f;
         }
         store8(myQ + sl * KP + c, qo);
       }
+      const float cur_ga = gate_a, cur_gb = gate_b;
+      if (item + 1 < items) fetch(item + 1, raw, gate_a, gate_b);
       __syncwarp();
       // ---- scores of 16 query rows against all keys ----
       float sc[2 * S_TILES][4];
@@ -183,19 +210,24 @@ attention_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __r
                    *reinterpret_cast<const uint32_t*>(vb + 8));
         }
       }
-      // ---- sigmoid head gate (model.py:139-142) and store ----
-      float g0 = 0.f, g1 = 0.f;
-      if (r0 < S) g0 = 1.f / (1.f + __expf(-__bfloat162float(gate[((size_t)b * S + r0) * H + h])));
-      if (r1 < S) g1 = 1.f / (1.f + __expf(-__bfloat162float(gate[((size_t)b * S + r1) * H + h])));
+      // ---- sigmoid head gate (model.py:139-142); the tile leaves through the warp's staging
+      // area (free since the score products) as 128-byte runs per row ----
+      const float g0 = 1.f / (1.f + __expf(-cur_ga)), g1 = 1.f / (1.f + __expf(-cur_gb));
+      __syncwarp();
 #pragma unroll
       for (int n = 0; n < HD / 8; ++n) {
-        const int col = h * HD + n * 8 + 2 * t;
-        if (r0 < S)
-          *reinterpret_cast<uint32_t*>(out + ((size_t)b * S + r0) * H * HD + col) =
-              pack_bf16x2(o_acc[n][0] * g0, o_acc[n][1] * g0);
-        if (r1 < S)
-          *reinterpret_cast<uint32_t*>(out + ((size_t)b * S + r1) * H * HD + col) =
-              pack_bf16x2(o_acc[n][2] * g1, o_acc[n][3] * g1);
+        *reinterpret_cast<uint32_t*>(myQ + g * KP + n * 8 + 2 * t) = pack_bf16x2(o_acc[n][0] * g0, o_acc[n][1] * g0);
+        *reinterpret_cast<uint32_t*>(myQ + (g + 8) * KP + n * 8 + 2 * t) = pack_bf16x2(o_acc[n][2] * g1, o_acc[n][3] * g1);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int i = lane + 32 * q;
+        const int sl = i >> 3, c = (i & 7) * 8;
+        const int srow = mt * 16 + sl;
+        if (srow < S)
+          *reinterpret_cast<uint4*>(out + ((size_t)b * S + srow) * H * HD + h * HD + c) =
+              *reinterpret_cast<const uint4*>(myQ + sl * KP + c);
       }
     }
   }

@@ -52,8 +52,9 @@ norm_fold_kernel(const T* __restrict__ Wg, const T* __restrict__ bg, const T* __
   }
 }
 
-// One warp per row: mean, biased variance around the mean (two passes over the row, the
-// second from L1), y = (x - mean) * rstd * gamma + beta, as torch.nn.LayerNorm.
+// One warp per row: mean, biased variance around the mean, y = (x - mean) * rstd * gamma + beta,
+// as torch.nn.LayerNorm. Rows of up to 2048 elements stay in the lanes' registers between the
+// three steps (one pass over memory); longer rows are re-read (from L1).
 template <typename T>
 __global__ void __launch_bounds__(256)
 layernorm_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
@@ -64,34 +65,73 @@ layernorm_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
   const int lane = threadIdx.x & 31;
   if (row >= N) return;
   const T* xr = x + row * d;
+  constexpr int kKeep = 8;                 // 8 x 8 elements per lane = rows of up to 2048
+  const bool keep = d <= kKeep * 256;
+  float r[kKeep][8];
   float sum = 0.f;
-  for (int c = lane * 8; c < d; c += 256) {
-    float v[8];
-    load8(xr + c, v);
+  if (keep) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sum += v[i];
+    for (int i = 0; i < kKeep; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < d) {
+        load8(xr + c, r[i]);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) sum += r[i][q];
+      }
+    }
+  } else {
+    for (int c = lane * 8; c < d; c += 256) {
+      float v[8];
+      load8(xr + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += v[i];
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   const float mean = sum / (float)d;
   float sq = 0.f;
-  for (int c = lane * 8; c < d; c += 256) {
-    float v[8];
-    load8(xr + c, v);
+  if (keep) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sq = fmaf(v[i] - mean, v[i] - mean, sq);
+    for (int i = 0; i < kKeep; ++i)
+      if (lane * 8 + i * 256 < d) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) sq = fmaf(r[i][q] - mean, r[i][q] - mean, sq);
+      }
+  } else {
+    for (int c = lane * 8; c < d; c += 256) {
+      float v[8];
+      load8(xr + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sq = fmaf(v[i] - mean, v[i] - mean, sq);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
   const float rstd = rsqrtf(sq / (float)d + eps);
-  for (int c = lane * 8; c < d; c += 256) {
-    float v[8], g[8], b[8], o[8];
-    load8(xr + c, v);
-    load8_ldg(gamma + c, g);
-    load8_ldg(beta + c, b);
+  if (keep) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = fmaf((v[i] - mean) * rstd, g[i], b[i]);
-    store8(out + row * d + c, o);
+    for (int i = 0; i < kKeep; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < d) {
+        float g[8], b[8], o[8];
+        load8_ldg(gamma + c, g);
+        load8_ldg(beta + c, b);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o[q] = fmaf((r[i][q] - mean) * rstd, g[q], b[q]);
+        store8(out + row * d + c, o);
+      }
+    }
+  } else {
+    for (int c = lane * 8; c < d; c += 256) {
+      float v[8], g[8], b[8], o[8];
+      load8(xr + c, v);
+      load8_ldg(gamma + c, g);
+      load8_ldg(beta + c, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = fmaf((v[i] - mean) * rstd, g[i], b[i]);
+      store8(out + row * d + c, o);
+    }
   }
   if (stats != nullptr && lane == 0) {
     stats[2 * row] = mean;
