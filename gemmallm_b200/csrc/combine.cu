@@ -54,6 +54,10 @@ combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ row_of,
 // Small-N variant: the down product arrives as `ksplit` fp32 partial buffers
 // part[s][M][d] without bias; sum them in order s = 0..ksplit-1, add the
 // expert's down.bias, then weight and add as above.
+// TWO: the call has two slots per token (the reference's k): the routing of both and all the
+// partial sums of both are requested before anything is added, so that the kernel is two
+// round trips to L2 long instead of one per slot and kind of load.
+template <bool TWO>
 __global__ void __launch_bounds__(64)
 combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_stride,
                       const int32_t* __restrict__ row_of, const int32_t* __restrict__ idx,
@@ -70,6 +74,52 @@ combine_decode_kernel(const float* __restrict__ part, int ksplit, int64_t part_s
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if constexpr (TWO) {
+    // (routing through L2 after the wait, as below)
+    int row[2], e[2];
+    float wj[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      row[j] = __ldcg(&row_of[t * 2 + j]);
+      e[j] = __ldcg(&idx[t * 2 + j]);
+      wj[j] = __ldcg(&w[t * 2 + j]);
+    }
+    float r[8];
+    if (residual != nullptr) load8(residual + t * d + c, r);
+    float v[2][8], pv[2][8][8];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      if (row[j] >= 0) {
+        load8_ldg(static_cast<const __nv_bfloat16*>(b2[e[j]]) + c, v[j]);
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < ksplit) load8(part + (int64_t)sp * part_stride + (int64_t)row[j] * d + c, pv[j][sp]);
+      }
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      if (row[j] >= 0) {
+        float s2[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s2[i] = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          if (sp < ksplit) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s2[i] += pv[j][sp][i];
+          }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float yv = __bfloat162float(__float2bfloat16_rn(s2[i] + v[j][i]));
+          acc[i] = __fadd_rn(acc[i], __fmul_rn(wj[j], yv));
+        }
+      }
+    if (residual != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
+    }
+    store8(out + t * d + c, acc);
+    return;
+  }
   for (int j = 0; j < k; ++j) {
     // row_of, idx and w come from the routing kernel, which may still be running when this
     // kernel becomes resident: read them through L2 after the wait, never through the read-only
@@ -119,10 +169,16 @@ int launch_combine_decode(const float* part, int ksplit, int64_t M, const int32_
   PlanView pv = plan_view(plan, E);
   const int64_t items = N * (d >> 3);
   const int64_t blocks = (items + 63) / 64;   // small blocks: spread few items over many SMs
-  MOE_CUDA_CHECK(launch_pdl(combine_decode_kernel, dim3((unsigned)blocks), dim3(64), 0, s, part, ksplit,
-                            M * (int64_t)d, row_of, idx, w, pv.b2,
-                            static_cast<const __nv_bfloat16*>(residual), N, d, k,
-                            static_cast<__nv_bfloat16*>(out)));
+  if (k == 2)
+    MOE_CUDA_CHECK(launch_pdl(combine_decode_kernel<true>, dim3((unsigned)blocks), dim3(64), 0, s, part, ksplit,
+                              M * (int64_t)d, row_of, idx, w, pv.b2,
+                              static_cast<const __nv_bfloat16*>(residual), N, d, k,
+                              static_cast<__nv_bfloat16*>(out)));
+  else
+    MOE_CUDA_CHECK(launch_pdl(combine_decode_kernel<false>, dim3((unsigned)blocks), dim3(64), 0, s, part, ksplit,
+                              M * (int64_t)d, row_of, idx, w, pv.b2,
+                              static_cast<const __nv_bfloat16*>(residual), N, d, k,
+                              static_cast<__nv_bfloat16*>(out)));
   return 0;
 }
 
