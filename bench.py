@@ -1252,7 +1252,7 @@ def run_train(args, wl):
         "e2e": {"value": N / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": N * d * es,
                 "d2h_bytes_per_step": N * d * es + 4, "ms_per_step": e2e_ms,
                 "mode": "input copied in, input gradient and loss copied out, every step, one stream"},
-        "gpu_launches": 32 * args.steps,
+        "gpu_launches": 26 * args.steps,   # the library's kernels per step (launch list in profiles/)
         "clocks": clocks.summary(),
         "roofline": {"kernel": "whole step: six grouped_gemm_tc2_kernel launches (two forward, four backward) "
                                "plus router, dispatch, combine, their backward kernels and the transposes",
