@@ -84,3 +84,10 @@ def test_small_and_mid_size_entry_points_check_their_arguments():
     assert lib.moe_b200_front_exchange_ints(512, 8, 2) == 32 * 2 * 8 + 32 * 8
     # the single-launch kernels' fused entry point: row limit
     assert lib.moe_b200_experts_decode_fused(a, a, a, 257, 1024, 4096, 8, a, a, a, a, None) == -2
+    # the one-launch block: one to eight tokens, at most 32 experts, no NULL output, aligned rows
+    tiny = lambda N, d, f, E, k, x=a, out=a: lib.moe_b200_decode_tiny(
+        x, a, a, a, None, N, d, f, E, k, a, a, a, a, a, a, a, a, a, a, out, a, None)
+    assert tiny(9, 1024, 4096, 8, 2) == -7 and b"N <= 8" in lib.moe_b200_last_error_string()
+    assert tiny(4, 1024, 4096, 33, 2) == -7
+    assert tiny(4, 1024, 4096, 8, 2, out=None) == -1
+    assert tiny(4, 1024, 4096, 8, 2, x=a + 8) == -3
